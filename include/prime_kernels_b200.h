@@ -1,0 +1,116 @@
+/*
+ * C ABI of libprime_kernels_b200.so -- the drop-in boundary of the B200-native decode hot path.
+ *
+ * Plain pointers and sizes only; every pointer is a CUDA device pointer unless stated otherwise,
+ * `stream` is a cudaStream_t passed as void*.  Every function that can fail returns an int:
+ * 0 = ok, 9101..9111 = contract violations (see pk_status_string), any other value is a
+ * cudaError_t.  Nothing here allocates device memory; nothing here falls back to the CPU.
+ *
+ * Each entry cites the reference interface it replaces (paths inside the reference project).
+ */
+#ifndef PRIME_KERNELS_B200_H
+#define PRIME_KERNELS_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------- fused RMSNorm + residual + MXFP8 */
+
+/* Replaces fused_rmsnorm_residual_forward (prime_kernels/rmsnorm/rmsnorm.cuh:15-18,85):
+ * vals e4m3 [N,C]; scales e8m0, blocked 128x4 layout, pk_rmsnorm_scale_bytes(N,C) bytes;
+ * rrms fp32 [N]; branch/residual bf16 [N,C]; weight bf16 [C].
+ * out = rmsnorm(branch) * weight + residual, quantised per 32 elements.
+ * Differences: returns a status instead of assert/exit; N may be any size >= 0 and C any positive
+ * multiple of 32 (bytes of partially covered scale tiles are written as 0). */
+int pk_fused_rmsnorm_residual_forward(void* vals, void* scales, float* rrms, const void* branch,
+                                      const void* residual, const void* weight, float epsilon, int N, int C,
+                                      void* stream);
+
+/* Extension of the above.  mode 0: as above; mode 1: residual added before the norm (forward
+ * semantics of triton_residual_rmsnorm, prime_kernels/triton_rmsnorm/rmsnorm.py:711-722) followed by
+ * the same quantiser.  res_out (nullable, bf16 [N,C]) receives the updated residual stream
+ * (mode 0: the bf16 value that was quantised; mode 1: bf16(branch + residual)). */
+int pk_fused_rmsnorm_residual_forward_ex(void* vals, void* scales, float* rrms, void* res_out, const void* branch,
+                                         const void* residual, const void* weight, float epsilon, int N, int C,
+                                         int mode, void* stream);
+
+/* Size in bytes of the blocked scale buffer: ceil(N/128) * ceil(C/128) * 512
+ * (scale_numel in prime_kernels/rmsnorm/csrc/torch_interface.cpp:18-20, extended to ragged shapes). */
+long long pk_rmsnorm_scale_bytes(int N, int C);
+
+/* ---------------------------------------------------------------- decode megakernel, generic geometry */
+
+typedef struct PkDecodeModel {
+    int hidden, intermediate, layers, q_heads, kv_heads, vocab; /* head_dim is 64 */
+    int weight_format; /* 0 = bf16 row-major; 1 = MXFP8 packed rows: [K e4m3][K/32 e8m0][pad to 16 B] */
+    float eps;
+} PkDecodeModel;
+
+/* Argument block of one decode step.  Field meaning follows the reference's Params
+ * (prime_kernels/decode_megakernel/csrc/megakernel.cu:125-154) and mk_decode (:844-851):
+ * layers = device table int64 [L][6] (norm1, qkv, o, norm2, gate_up, down); kv_layers = device table
+ * int64 [L]; KV strides in elements of a [blocks, kv_heads, block_size, 128] bf16 cache; seq_lens
+ * include the token being decoded; slot_mapping -1 skips the cache write.
+ * Extensions: logits (nullable, bf16 [B, vocab]) and next_ids (nullable, int64 [B]) enable the fused
+ * tied lm_head + argmax when lm_head != 0; advance != 0 additionally rewrites input_ids, positions,
+ * seq_lens and slot_mapping in place for the next step (device-driven greedy generation);
+ * embed_lookup (nullable) is the bf16 embedding used for the input lookup when `embed` is MXFP8. */
+typedef struct PkDecodeArgs {
+    void* stream;
+    int batch;
+    const void* input_ids; int ids_i64;
+    const void* positions; const void* seq_lens; const void* block_table; int bt_stride; const void* slot_mapping;
+    const void* layers; const void* embed; const void* embed_lookup; const void* final_norm; const void* kv_layers;
+    long long k_off, v_off, block_stride, token_stride, head_stride; int block_size;
+    const void* cos_sin; int cs_fp32;
+    void* out_hidden; void* logits; void* next_ids; void* layer_outputs;
+    void* workspace; size_t workspace_bytes; int max_seq_len; int lm_head; int advance;
+} PkDecodeArgs;
+
+/* Generic form of mk_workspace_bytes / decode360_workspace_bytes. */
+size_t pk_decode_workspace_bytes(const PkDecodeModel* model, int max_batch);
+/* Generic form of mk_decode / decode360 (one cooperative launch on args->stream). */
+int pk_decode_step(const PkDecodeModel* model, const PkDecodeArgs* args);
+/* Zero a workspace in stream order (also done implicitly the first time a pointer is seen). */
+int pk_decode_workspace_init(void* workspace, size_t bytes, void* stream);
+void pk_decode_workspace_forget(void* workspace);
+/* Synchronise `stream` and return the device-side status word (9110 = a bounded wait gave up). */
+int pk_decode_status(void* workspace, void* stream);
+/* Generic form of mk_query (prime_kernels/decode_megakernel/csrc/megakernel.cu:833-836). */
+int pk_decode_query(int* sm_count, int* coop, int* major, int* minor, int* smem_optin, int* threads,
+                    int* consumer_warps);
+/* Replaces mk_status_string / decode360_status_string for every code above. */
+const char* pk_status_string(int status);
+
+/* ---------------------------------------------------------------- drop-in signatures of the reference */
+
+/* SmolLM2-135M: prime_kernels/decode_megakernel/csrc/megakernel.cu:833-927 (same arguments, same
+ * status numbers; 9106 now means "requires sm_100"; 9110/9111 are new). */
+int mk_query(int* sm_count, int* coop, int* active_per_sm, int* major, int* minor, int* regs, int* static_smem);
+size_t mk_workspace_bytes(int B, int max_seq_len);
+int mk_decode(void* stream, int B, const void* input_ids, int ids_i64, const void* positions, const void* seq_lens,
+              const void* block_table, int bt_stride, const void* slot_mapping, const void* layers, const void* embed,
+              const void* final_norm, void* const* kv_layers, long long k_off, long long v_off, long long block_stride,
+              long long token_stride, long long head_stride, int block_size, const void* cos_sin, int cs_fp32,
+              void* out_hidden, void* scratch, size_t scratch_bytes, int max_seq_len);
+const char* mk_status_string(int status);
+
+/* SmolLM2-360M: prime_kernels/decode_megakernel_360m/csrc/block360_kernel.inc:849-938.  The debug
+ * stage dump is accepted and ignored (nothing is written to it). */
+size_t decode360_workspace_bytes(void);
+size_t decode360_debug_bytes(void);
+int decode360(void* stream, int B, const void* input_ids, const void* embed, const void* final_norm,
+              const void* positions, const void* seq_lens, const void* block_table, int bt_stride,
+              const void* slot_mapping, const void* layers, void* const* kv, long long k_off, long long v_off,
+              long long block_stride, long long token_stride, long long head_stride, int block_size,
+              const void* cos_sin, int cs_fp32, void* out_hidden, void* layer_outputs, void* scratch,
+              size_t scratch_bytes, void* debug, size_t debug_bytes, int max_seq_len, int debug_layer_index);
+const char* decode360_status_string(int status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PRIME_KERNELS_B200_H */

@@ -1,0 +1,1495 @@
+// Single-launch decode step for Llama-style small LMs (SmolLM2 135M / 360M / 1.7B) on sm_100a.
+//
+// One persistent cooperative kernel, one CTA per SM, runs every layer of one decode step:
+//   RMSNorm -> QKV GEMV -> RoPE + paged-KV append + split-KV attention -> merge -> O GEMV + residual
+//   -> RMSNorm -> gate/up GEMV + SwiGLU -> down GEMV + residual -> ... -> final norm
+//   -> tied lm_head GEMV + argmax (optional extension; the reference op stops at the final norm,
+//      prime_kernels/decode_megakernel/csrc/megakernel.cu:786-798).
+//
+// B200 design (not a translation of the reference's 24-CTA grid.sync design):
+//  * Weight streaming is decoupled from the dependency chain.  Weights do not depend on
+//    activations, so a producer warp runs ahead of the math through the whole step and keeps
+//    ~190 KB of weights per SM in flight / staged in shared memory with bulk async copies
+//    (cp.async.bulk + mbarrier complete_tx, L2 evict-first).  Each of the 16 consumer warps owns a
+//    private single-producer/single-consumer byte ring; one producer lane serves each ring, and
+//    the 16 lanes advance in lock step so copy issue is 16-way parallel.  The row -> CTA -> warp
+//    schedule is a pure function of the geometry, evaluated identically on both sides.
+//  * There is no grid barrier.  Activations cross CTAs through "flagged word" buffers in L2:
+//    every 64-bit word carries 32 bits of payload and a 32-bit tag (launch epoch, layer), written
+//    and polled with single 8-byte relaxed accesses, so a consumer needs one L2 round trip per
+//    hand-off instead of barrier + fence + reload.  Buffers are double-buffered by layer parity;
+//    every wait is bounded and reports kErrBarrierTimeout instead of hanging.
+//  * GEMVs are warp-per-row-group SIMT fp32 FMA on bf16 (or MXFP8: E4M3 + E8M0 per 32 along K,
+//    de-quantised in registers) with 128-bit shared-memory reads; results are rounded to bf16 at
+//    the points HuggingFace eager rounds (see the rounding notes at each epilogue).
+//
+// Reference behaviour followed (file:line inside the reference project):
+//   prime_kernels/decode_megakernel/csrc/megakernel.cu:294-799      phase structure, paged KV contract
+//   prime_kernels/decode_megakernel_360m_lossless/csrc/block360.cu:121-166,239-255  norm / RoPE rounding
+//   prime_kernels/decode_megakernel_360m_lossless/csrc/block360_kernel.inc:114-234,360-436  split-KV + merge
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+#include "pk_common.cuh"
+
+namespace pk {
+
+constexpr int kNW = 16;                    // consumer warps per CTA
+constexpr int kCT = kNW * 32;              // consumer threads
+constexpr int kThreads = kCT + 32;         // + one producer warp
+constexpr int kD = 64;                     // head dim (fixed)
+constexpr int kE = 8;                      // ring entries in flight per consumer warp
+constexpr int kRMax = 4;                   // max weight rows staged per ring entry
+constexpr int kMaxB = 8;
+constexpr int kNCMax = 64;                 // max split-KV chunks per (request, kv head)
+constexpr int kMaxSeq = 8192;
+constexpr int kMaxLayers = 120;
+constexpr unsigned kSpinLimit = 1u << 22;  // bounded waits: ~1-2 s of L2 polling
+
+enum PhaseType { kQKV = 0, kO = 1, kGU = 2, kDown = 3, kLM = 4, kNumPhaseTypes = 5 };
+
+struct PhaseDesc {
+    int nrows;          // output rows of the phase (row pairs for gate/up)
+    int kchunks;        // 16-byte chunks per stored row
+    int rowbytes;       // bytes per stored row (multiple of 16)
+    int rows_per_entry; // rows (pairs) per ring entry when nseg == 1
+    int nseg;           // K segments per row; > 1 only when a row does not fit an entry
+    int segchunks;      // chunks per segment (multiple of 32 when nseg > 1)
+    int pair;           // 1: every entry stages a gate part and an up part
+    int widx;           // index in the per-layer pointer table, -1 = embedding matrix (lm_head)
+    long long pair_off; // byte offset from a gate row to its up row
+    int kact;           // activation length K (elements)
+    int pad;
+};
+
+struct DecodeParams {
+    // model
+    const unsigned long long* layers;   // device table [L][6]: norm1, qkv, o, norm2, gate_up, down
+    const unsigned long long* kv;       // device table [L]
+    const uint16_t* embed;              // [V, H] bf16 (or packed MXFP8 rows when wfmt == 1)
+    const uint16_t* embed_bf16;         // [V, H] bf16 embedding rows for the input lookup
+    const uint16_t* final_norm;         // [H]
+    // step inputs
+    const void* input_ids;
+    const long long* positions;
+    const int* seq_lens;
+    const int* block_table;
+    const long long* slot_mapping;
+    const void* cos_sin;
+    // outputs
+    uint16_t* out_hidden;               // [B, H] bf16, final-normed
+    uint16_t* logits;                   // optional [B, V] bf16
+    long long* next_ids;                // optional [B]
+    uint16_t* layer_outputs;            // optional [L, B, H]
+    // workspace
+    unsigned int* ctrl;                 // control words (see Ctrl* below)
+    unsigned long long* argkey;         // [2][kMaxB]
+    unsigned long long* ll_x;           // [2][B*H]
+    unsigned long long* ll_qkv;         // [2][B*NQKV]
+    unsigned long long* ll_attn;        // [2][B*QH*32]      (two bf16 per word)
+    unsigned long long* ll_h1;          // [2][B*H]
+    unsigned long long* ll_act;         // [2][B*I]
+    unsigned long long* ll_part;        // [2][B*KVH*kNCMax*G*66]
+    long long k_off, v_off, block_stride, token_stride, head_stride;
+    int block_size, bt_stride, ids_i64, cs_fp32;
+    int H, I, L, QH, KVH, V, B, G;
+    int wfmt;                           // 0 = bf16 weights, 1 = MXFP8 packed rows
+    int lm_head, advance;
+    int max_seq_len;
+    int ring_bytes;                     // per consumer warp
+    int act_elems;                      // max(H, I)
+    float eps;
+    PhaseDesc ph[kNumPhaseTypes];
+};
+
+enum CtrlWord { kCtrlEpoch = 0, kCtrlStatus = 1, kCtrlDone = 2, kCtrlWords = 16 };
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+// global -> this CTA's shared memory, completion counted in bytes on an mbarrier; never multicast
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+        : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_flagged(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_flagged(unsigned long long* p, uint32_t payload, uint32_t tag) {
+    const unsigned long long v = ((unsigned long long)tag << 32) | payload;
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kCT) : "memory"); }
+
+// ------------------------------------------------------------------ shared state
+struct Shared {
+    uint64_t full[kNW][kE];
+    uint64_t empty[kNW][kE];
+    uint32_t ent_off[kNW][kE];
+    uint32_t ent_foot[kNW][kE];
+    int row_a[kNumPhaseTypes][kNW];
+    int row_b[kNumPhaseTypes][kNW];
+    float red[kMaxB][kNW];
+    int seq[kMaxB], pos[kMaxB], nc[kMaxB], lc[kMaxB];
+    long long slot[kMaxB];
+    long long tok[kMaxB];
+    volatile int abort_flag;
+    uint32_t epoch;
+};
+
+struct Ctx {
+    const DecodeParams& p;
+    Shared& sh;
+    uint4* act;        // [B][act_elems/8] bf16 activations of the current phase
+    float* res;        // [B][H] residual stream copy (x or h1) for the epilogues
+    unsigned char* ring;  // this warp's ring (consumer) / ring of warp `lane` (producer)
+    uint32_t tag_base;
+    int warp, lane, cta, ncta;
+};
+
+__device__ __forceinline__ void raise_abort(Ctx& c, int code) {
+    c.sh.abort_flag = 1;
+    atomicCAS(c.p.ctrl + kCtrlStatus, 0u, (unsigned)code);
+}
+__device__ __forceinline__ bool aborted(const Ctx& c) { return c.sh.abort_flag != 0; }
+
+// Bounded poll of one flagged word.  Returns the payload; on timeout raises the abort flag.
+__device__ __forceinline__ uint32_t wait_flagged(Ctx& c, const unsigned long long* p, uint32_t tag) {
+    if (aborted(c)) return 0;
+    unsigned spins = 0;
+    for (;;) {
+        const unsigned long long v = ld_flagged(p);
+        if ((uint32_t)(v >> 32) == tag) return (uint32_t)v;
+        if ((++spins & 1023u) == 0) {
+            if (aborted(c)) return 0;
+            if (*((volatile unsigned int*)(c.p.ctrl + kCtrlStatus)) != 0) {
+                c.sh.abort_flag = 1;
+                return 0;
+            }
+            if (spins >= kSpinLimit) {
+                raise_abort(c, kErrBarrierTimeout);
+                return 0;
+            }
+        }
+    }
+}
+
+// N consecutive flagged words: all loads are issued before any is checked, so the common case
+// (data already there) costs one L2 round trip instead of N.
+template <int N>
+__device__ __forceinline__ void wait_flagged_vec(Ctx& c, const unsigned long long* p, uint32_t tag, uint32_t (&out)[N]) {
+    unsigned long long v[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] = ld_flagged(p + i);
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = ((uint32_t)(v[i] >> 32) == tag) ? (uint32_t)v[i] : wait_flagged(c, p + i, tag);
+}
+
+// Up to 4 words at indices first, first+stride, ... (< n), loads issued together.
+__device__ __forceinline__ void wait_flagged_strided4(Ctx& c, const unsigned long long* base, int first, int stride,
+                                                      int n, uint32_t tag, uint32_t (&out)[4]) {
+    unsigned long long v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int idx = first + u * stride;
+        v[u] = idx < n ? ld_flagged(base + idx) : 0ull;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int idx = first + u * stride;
+        out[u] = 0;
+        if (idx < n) out[u] = ((uint32_t)(v[u] >> 32) == tag) ? (uint32_t)v[u] : wait_flagged(c, base + idx, tag);
+    }
+}
+
+__device__ __forceinline__ bool wait_mbar(Ctx& c, uint64_t* bar, uint32_t parity) {
+    if (aborted(c)) return false;
+    unsigned spins = 0;
+    while (!mbar_test(bar, parity)) {
+        if ((++spins & 255u) == 0) {
+            if (aborted(c)) return false;
+            if (spins >= kSpinLimit) {
+                raise_abort(c, kErrBarrierTimeout);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// ------------------------------------------------------------------ schedule (shared by both sides)
+// Rows of phase type t owned by (cta, warp): the CTA takes an even contiguous share of the rows,
+// and its warps take even contiguous shares of that.
+__device__ __forceinline__ void warp_rows(int nrows, int cta, int ncta, int warp, int& a, int& b) {
+    const int r0 = (int)((long long)nrows * cta / ncta);
+    const int r1 = (int)((long long)nrows * (cta + 1) / ncta);
+    const int n = r1 - r0;
+    a = r0 + n * warp / kNW;
+    b = r0 + n * (warp + 1) / kNW;
+}
+
+// One ring entry of the schedule.
+struct Entry {
+    const unsigned char* src;   // first (or only) part
+    const unsigned char* src2;  // second part for gate/up pairs, else nullptr
+    uint32_t part_bytes;        // bytes per part
+};
+
+// Cursor over the ring entries of one consumer warp, in schedule order.
+struct Cursor {
+    int gp;       // global phase: layer * 4 + type, or L * 4 for the lm_head
+    int row;      // current row (pair) index
+    int seg;
+    int end_gp;
+    __device__ __forceinline__ int type(const DecodeParams& p) const { return gp < p.L * 4 ? (gp & 3) : (int)kLM; }
+    __device__ __forceinline__ bool valid() const { return gp < end_gp; }
+    __device__ void seek(const DecodeParams& p, const Shared& sh, int w) {
+        // skip phases in which this warp owns no rows
+        while (gp < end_gp) {
+            const int t = type(p);
+            if (sh.row_a[t][w] < sh.row_b[t][w]) {
+                row = sh.row_a[t][w];
+                seg = 0;
+                return;
+            }
+            ++gp;
+        }
+    }
+    __device__ void init(const DecodeParams& p, const Shared& sh, int w) {
+        gp = 0;
+        end_gp = p.L * 4 + (p.lm_head ? 1 : 0);
+        seek(p, sh, w);
+    }
+    __device__ void advance(const DecodeParams& p, const Shared& sh, int w) {
+        const int t = type(p);
+        const PhaseDesc& d = p.ph[t];
+        if (++seg < d.nseg) return;
+        seg = 0;
+        row += d.rows_per_entry;
+        if (row < sh.row_b[t][w]) return;
+        ++gp;
+        seek(p, sh, w);
+    }
+    __device__ Entry entry(const DecodeParams& p, const Shared& sh, int w) const {
+        const int t = type(p);
+        const PhaseDesc& d = p.ph[t];
+        const unsigned char* base =
+            d.widx < 0 ? reinterpret_cast<const unsigned char*>(p.embed)
+                       : reinterpret_cast<const unsigned char*>(p.layers[(gp >> 2) * 6 + d.widx]);
+        Entry e;
+        if (d.nseg == 1) {
+            const int nre = min(d.rows_per_entry, sh.row_b[t][w] - row);
+            e.part_bytes = (uint32_t)nre * (uint32_t)d.rowbytes;
+            e.src = base + (size_t)row * d.rowbytes;
+        } else {
+            const int sc = min(d.segchunks, d.kchunks - seg * d.segchunks);
+            e.part_bytes = (uint32_t)sc * 16u;
+            e.src = base + (size_t)row * d.rowbytes + (size_t)seg * d.segchunks * 16;
+        }
+        e.src2 = d.pair ? e.src + d.pair_off : nullptr;
+        return e;
+    }
+};
+
+// ------------------------------------------------------------------ producer warp
+// Lane w (< kNW) feeds the ring of consumer warp w.  All lanes run the same loop in lock step;
+// every iteration a lane either issues its next entry (if the ring has room) or polls the oldest
+// outstanding entry for release.  Nothing here blocks, so one slow ring never stalls the others.
+__device__ void producer_loop(Ctx& c, unsigned char* ring_base) {
+    const DecodeParams& p = c.p;
+    Shared& sh = c.sh;
+    const int w = c.lane;
+    const bool active = w < kNW;
+    const uint32_t RW = (uint32_t)p.ring_bytes;
+    unsigned char* ring = ring_base + (size_t)(active ? w : 0) * RW;
+    const uint64_t pol = evict_first_policy();
+    Cursor cur;
+    cur.gp = cur.end_gp = 0;
+    cur.row = cur.seg = 0;
+    if (active) cur.init(p, sh, w);
+    uint32_t issued = 0, tail = 0, head = 0, used = 0;
+    unsigned idle = 0;
+    for (;;) {
+        const bool done = !active || !cur.valid();
+        bool progressed = false;
+        if (!done) {
+            const Entry e = cur.entry(p, sh, w);
+            const uint32_t bytes = e.src2 ? 2 * e.part_bytes : e.part_bytes;
+            const uint32_t gap = (head + bytes > RW) ? RW - head : 0;
+            const uint32_t foot = bytes + gap;
+            if (issued - tail < (uint32_t)kE && used + foot <= RW) {
+                const uint32_t off = gap ? 0 : head;
+                const uint32_t slot = issued % kE;
+                sh.ent_off[w][slot] = off;
+                sh.ent_foot[w][slot] = foot;
+                mbar_expect_tx(&sh.full[w][slot], bytes);
+                bulk_g2s(ring + off, e.src, e.part_bytes, &sh.full[w][slot], pol);
+                if (e.src2) bulk_g2s(ring + off + e.part_bytes, e.src2, e.part_bytes, &sh.full[w][slot], pol);
+                head = off + bytes;
+                if (head >= RW) head = 0;
+                used += foot;
+                ++issued;
+                cur.advance(p, sh, w);
+                progressed = true;
+            } else {
+                const uint32_t slot = tail % kE;
+                if (mbar_test(&sh.empty[w][slot], (tail / kE) & 1)) {
+                    used -= sh.ent_foot[w][slot];
+                    ++tail;
+                    progressed = true;
+                }
+            }
+        }
+        if (__all_sync(kFullMask, done)) break;
+        idle = (progressed || done) ? 0 : idle + 1;
+        if ((idle & 255u) == 255u) {
+            if (idle >= kSpinLimit) raise_abort(c, kErrBarrierTimeout);
+        }
+        if (__any_sync(kFullMask, aborted(c))) break;
+    }
+    // Drain: never leave the CTA while bulk copies into its shared memory are still in flight.
+    if (active) {
+        for (uint32_t n = tail; n < issued; ++n) {
+            const uint32_t slot = n % kE;
+            unsigned spins = 0;
+            while (!mbar_test(&sh.full[w][slot], (n / kE) & 1)) {
+                if (++spins >= kSpinLimit) break;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ math helpers
+__device__ __forceinline__ float dot8_bf16(const uint4 w, const uint4 a, float acc) {
+    acc = fmaf(bf16_lo(w.x), bf16_lo(a.x), acc);
+    acc = fmaf(bf16_hi(w.x), bf16_hi(a.x), acc);
+    acc = fmaf(bf16_lo(w.y), bf16_lo(a.y), acc);
+    acc = fmaf(bf16_hi(w.y), bf16_hi(a.y), acc);
+    acc = fmaf(bf16_lo(w.z), bf16_lo(a.z), acc);
+    acc = fmaf(bf16_hi(w.z), bf16_hi(a.z), acc);
+    acc = fmaf(bf16_lo(w.w), bf16_lo(a.w), acc);
+    acc = fmaf(bf16_hi(w.w), bf16_hi(a.w), acc);
+    return acc;
+}
+
+// four E4M3 bytes (one 32-bit word) -> four fp32 (exact)
+__device__ __forceinline__ void e4m3x4_to_f32(uint32_t v, float (&f)[4]) {
+    uint32_t h0, h1;
+    asm("{\n.reg .b16 lo, hi;\nmov.b32 {lo, hi}, %2;\ncvt.rn.f16x2.e4m3x2 %0, lo;\ncvt.rn.f16x2.e4m3x2 %1, hi;\n}"
+        : "=r"(h0), "=r"(h1)
+        : "r"(v));
+    const __half2 a = *reinterpret_cast<__half2*>(&h0);
+    const __half2 b = *reinterpret_cast<__half2*>(&h1);
+    const float2 fa = __half22float2(a), fb = __half22float2(b);
+    f[0] = fa.x;
+    f[1] = fa.y;
+    f[2] = fb.x;
+    f[3] = fb.y;
+}
+
+__device__ __forceinline__ float dot16_e4m3(const uint4 w, const uint4 a0, const uint4 a1, float acc) {
+    float f[4];
+    e4m3x4_to_f32(w.x, f);
+    acc = fmaf(f[0], bf16_lo(a0.x), acc);
+    acc = fmaf(f[1], bf16_hi(a0.x), acc);
+    acc = fmaf(f[2], bf16_lo(a0.y), acc);
+    acc = fmaf(f[3], bf16_hi(a0.y), acc);
+    e4m3x4_to_f32(w.y, f);
+    acc = fmaf(f[0], bf16_lo(a0.z), acc);
+    acc = fmaf(f[1], bf16_hi(a0.z), acc);
+    acc = fmaf(f[2], bf16_lo(a0.w), acc);
+    acc = fmaf(f[3], bf16_hi(a0.w), acc);
+    e4m3x4_to_f32(w.z, f);
+    acc = fmaf(f[0], bf16_lo(a1.x), acc);
+    acc = fmaf(f[1], bf16_hi(a1.x), acc);
+    acc = fmaf(f[2], bf16_lo(a1.y), acc);
+    acc = fmaf(f[3], bf16_hi(a1.y), acc);
+    e4m3x4_to_f32(w.w, f);
+    acc = fmaf(f[0], bf16_lo(a1.z), acc);
+    acc = fmaf(f[1], bf16_hi(a1.z), acc);
+    acc = fmaf(f[2], bf16_lo(a1.w), acc);
+    acc = fmaf(f[3], bf16_hi(a1.w), acc);
+    return acc;
+}
+
+__device__ __forceinline__ uint32_t layer_tag(const Ctx& c, int layer) { return c.tag_base + (uint32_t)layer + 1u; }
+
+// ------------------------------------------------------------------ GEMV phase (consumer warps)
+// Consumes this warp's ring entries of phase type T at `layer`, multiplying the staged rows with
+// the bf16 activations in c.act, and hands each finished row to the phase epilogue.
+template <int B, int T>
+__device__ void gemv_phase(Ctx& c, int layer, uint32_t& consumed) {
+    const DecodeParams& p = c.p;
+    Shared& sh = c.sh;
+    const PhaseDesc& d = p.ph[T];
+    const int w = c.warp, lane = c.lane;
+    const int ra = sh.row_a[T][w], rb = sh.row_b[T][w];
+    const int actc = p.act_elems >> 3;                 // uint4 per request in c.act
+    const uint32_t tag = layer_tag(c, layer);
+    const int par = layer & 1;
+    for (int row = ra; row < rb; row += d.rows_per_entry) {
+        const int nre = min(d.rows_per_entry, rb - row);
+        const int nmem = d.pair ? 2 * nre : nre;       // rows staged in the entry
+        float acc[kRMax][B];
+#pragma unroll
+        for (int i = 0; i < kRMax; ++i)
+#pragma unroll
+            for (int b = 0; b < B; ++b) acc[i][b] = 0.f;
+        for (int seg = 0; seg < d.nseg; ++seg) {
+            const uint32_t slot = consumed % kE;
+            if (!wait_mbar(c, &sh.full[w][slot], (consumed / kE) & 1)) return;
+            const uint4* ep = reinterpret_cast<const uint4*>(c.ring + sh.ent_off[w][slot]);
+            if (p.wfmt == 0) {
+                const int sc = d.nseg == 1 ? d.kchunks : min(d.segchunks, d.kchunks - seg * d.segchunks);
+                const int kc0 = seg * d.segchunks;
+                for (int it = lane; it < sc; it += 32) {
+                    uint4 a[B];
+#pragma unroll
+                    for (int b = 0; b < B; ++b) a[b] = c.act[b * actc + kc0 + it];
+#pragma unroll
+                    for (int i = 0; i < kRMax; ++i) {
+                        if (i < nmem) {
+                            const uint4 wv = ep[i * sc + it];
+#pragma unroll
+                            for (int b = 0; b < B; ++b) acc[i][b] = dot8_bf16(wv, a[b], acc[i][b]);
+                        }
+                    }
+                }
+            } else {
+                // MXFP8 packed row: [K e4m3][K/32 e8m0][pad to 16]; one lane-chunk = 16 values
+                const int vc = d.kact >> 4;              // value chunks per row
+                const int rc = d.kchunks;                // stored chunks per row
+                for (int it = lane; it < vc; it += 32) {
+                    uint4 a0[B], a1[B];
+#pragma unroll
+                    for (int b = 0; b < B; ++b) {
+                        a0[b] = c.act[b * actc + 2 * it];
+                        a1[b] = c.act[b * actc + 2 * it + 1];
+                    }
+#pragma unroll
+                    for (int i = 0; i < kRMax; ++i) {
+                        if (i < nmem) {
+                            const uint4 wv = ep[i * rc + it];
+                            const unsigned char sb =
+                                reinterpret_cast<const unsigned char*>(ep + i * rc)[d.kact + (it >> 1)];
+                            const float scale = __uint_as_float(sb ? ((uint32_t)sb << 23) : 0x00400000u);
+#pragma unroll
+                            for (int b = 0; b < B; ++b) acc[i][b] = fmaf(scale, dot16_e4m3(wv, a0[b], a1[b], 0.f), acc[i][b]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.empty[w][slot]);
+            ++consumed;
+        }
+        // warp-reduce every accumulator, then lane i finishes row i
+#pragma unroll
+        for (int i = 0; i < kRMax; ++i)
+#pragma unroll
+            for (int b = 0; b < B; ++b) acc[i][b] = warp_sum(acc[i][b]);
+#pragma unroll
+        for (int i = 0; i < kRMax; ++i) {
+            if (i < nre && lane == i) {
+                const int r = row + i;
+#pragma unroll
+                for (int b = 0; b < B; ++b) {
+                    if (T == kQKV) {
+                        // projection output rounded to bf16 (HF linear output dtype)
+                        st_flagged(p.ll_qkv + (size_t)par * B * d.nrows + b * d.nrows + r,
+                                   f32_to_bf16_bits(acc[i][b]), tag);
+                    } else if (T == kO) {
+                        // h1 = bf16( x + bf16(o_proj) )
+                        const float o = round_bf16(acc[i][b]);
+                        const float h = round_bf16(__fadd_rn(c.res[b * p.H + r], o));
+                        st_flagged(p.ll_h1 + (size_t)par * B * p.H + b * p.H + r, f32_to_bf16_bits(h), tag);
+                    } else if (T == kGU) {
+                        // act = bf16( bf16(silu(bf16 gate)) * bf16 up )   (HF LlamaMLP rounding)
+                        const float g = round_bf16(acc[i][b]);
+                        const float u = round_bf16(acc[i + nre][b]);
+                        const float silu = round_bf16(g / (1.f + expf(-g)));
+                        const float a = round_bf16(__fmul_rn(silu, u));
+                        st_flagged(p.ll_act + (size_t)par * B * p.I + b * p.I + r, f32_to_bf16_bits(a), tag);
+                    } else if (T == kDown) {
+                        // x' = bf16( h1 + bf16(down_proj) ), handed to the next layer's parity slot
+                        const float dn = round_bf16(acc[i][b]);
+                        const uint32_t xb = f32_to_bf16_bits(__fadd_rn(c.res[b * p.H + r], dn));
+                        st_flagged(p.ll_x + (size_t)((layer + 1) & 1) * B * p.H + b * p.H + r, xb,
+                                   layer_tag(c, layer + 1));
+                        if (p.layer_outputs) p.layer_outputs[((size_t)layer * B + b) * p.H + r] = (uint16_t)xb;
+                    } else {
+                        // logits rounded to bf16; argmax breaks ties toward the lowest index
+                        const uint32_t lb = f32_to_bf16_bits(acc[i][b]);
+                        if (p.logits) p.logits[(size_t)b * p.V + r] = (uint16_t)lb;
+                        if (p.next_ids) {
+                            const uint32_t ord = (lb & 0x8000u) ? (~lb & 0xffffu) : (lb | 0x8000u);
+                            const unsigned long long key =
+                                ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - (uint32_t)r);
+                            atomicMax(p.argkey + (size_t)(sh.epoch & 1u) * kMaxB + b, key);
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ activation staging
+// Load the residual stream (embedding row for layer 0, flagged X words otherwise), keep an fp32
+// copy for the residual add, and write bf16( bf16(x * rsqrt(mean x^2 + eps)) * w ) to c.act.
+// HF LlamaRMSNorm: fp32 statistics, cast to bf16, then multiply by the bf16 weight.
+template <int B>
+__device__ void stage_norm(Ctx& c, const unsigned long long* src_words, uint32_t tag, const uint16_t* weight,
+                           bool from_embed) {
+    const DecodeParams& p = c.p;
+    Shared& sh = c.sh;
+    const int ct = threadIdx.x;
+    const int H = p.H;
+    consumer_bar();   // everyone is done with the previous phase's act/res
+    float ss[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+        ss[b] = 0.f;
+        for (int i0 = ct; i0 < H; i0 += 4 * kCT) {
+            uint32_t xv[4];
+            if (from_embed) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + u * kCT;
+                    xv[u] = i < H ? (uint32_t)p.embed_bf16[(size_t)sh.tok[b] * H + i] : 0u;
+                }
+            } else {
+                wait_flagged_strided4(c, src_words + b * H, i0, kCT, H, tag, xv);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * kCT;
+                if (i < H) {
+                    const float x = __uint_as_float(xv[u] << 16);
+                    c.res[b * H + i] = x;
+                    ss[b] = fmaf(x, x, ss[b]);
+                }
+            }
+        }
+        ss[b] = warp_sum(ss[b]);
+        if (c.lane == 0) sh.red[b][c.warp] = ss[b];
+    }
+    consumer_bar();
+    uint16_t* act16 = reinterpret_cast<uint16_t*>(c.act);
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kNW; ++w) tot += sh.red[b][w];
+        const float s = rsqrtf(tot * (1.f / (float)H) + p.eps);
+        for (int i = ct; i < H; i += kCT) {
+            const float wv = __uint_as_float((uint32_t)weight[i] << 16);
+            const float n = round_bf16(__fmul_rn(c.res[b * H + i], s));
+            act16[(size_t)b * p.act_elems + i] = (uint16_t)f32_to_bf16_bits(__fmul_rn(n, wv));
+        }
+    }
+    consumer_bar();
+}
+
+// Copy flagged bf16 words into c.act.  `packed` words carry two bf16 values each.
+template <int B>
+__device__ void stage_copy(Ctx& c, const unsigned long long* src_words, uint32_t tag, int n, bool packed) {
+    const DecodeParams& p = c.p;
+    const int ct = threadIdx.x;
+    consumer_bar();
+    if (packed) {
+        uint32_t* act32 = reinterpret_cast<uint32_t*>(c.act);
+        const int nw = n >> 1;
+        for (int b = 0; b < B; ++b)
+            for (int i0 = ct; i0 < nw; i0 += 4 * kCT) {
+                uint32_t v[4];
+                wait_flagged_strided4(c, src_words + b * nw, i0, kCT, nw, tag, v);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (i0 + u * kCT < nw) act32[(size_t)b * (p.act_elems >> 1) + i0 + u * kCT] = v[u];
+            }
+    } else {
+        uint16_t* act16 = reinterpret_cast<uint16_t*>(c.act);
+        for (int b = 0; b < B; ++b)
+            for (int i0 = ct; i0 < n; i0 += 4 * kCT) {
+                uint32_t v[4];
+                wait_flagged_strided4(c, src_words + b * n, i0, kCT, n, tag, v);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (i0 + u * kCT < n) act16[(size_t)b * p.act_elems + i0 + u * kCT] = (uint16_t)v[u];
+            }
+    }
+    consumer_bar();
+}
+
+// ------------------------------------------------------------------ attention
+// HF apply_rotary_pos_emb rounding: bf16( bf16(x*cos) + bf16(rotate_half(x)*sin) ).
+__device__ __forceinline__ float rope_elem(float x, float partner, float cs, float sn, bool first_half) {
+    const float xc = round_bf16(__fmul_rn(x, cs));
+    const float ys = round_bf16(__fmul_rn(partner, sn));
+    return round_bf16(__fadd_rn(xc, first_half ? -ys : ys));
+}
+
+// One warp = one (request b, kv head, chunk) item over cache positions [start, end).
+// Lane j = lane & 7 owns dims 8j..8j+7; lane group g = lane >> 3 takes positions start+g, +4, ...
+// so one 128-byte K (or V) row is one coalesced 8-lane 16-byte load.  fp32 online softmax per
+// lane group, groups combined at the end; partial (m, l, acc[64]) per query head of the GQA group
+// goes out as flagged words.
+template <int G>
+__device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
+    const DecodeParams& p = c.p;
+    Shared& sh = c.sh;
+    const int lane = c.lane, j = lane & 7, g = lane >> 3;
+    const uint32_t tag = layer_tag(c, layer);
+    const int par = layer & 1;
+    const int nqkv = (p.QH + 2 * p.KVH) * kD;
+    const unsigned long long* qkv = p.ll_qkv + (size_t)par * p.B * nqkv + (size_t)b * nqkv;
+    const int seq = sh.seq[b], pos = sh.pos[b];
+    const int start = chunk * sh.lc[b];
+    const int end = min(start + sh.lc[b], seq);
+    const bool has_new = (seq - 1 >= start) && (seq - 1 < end);
+
+    // cos/sin of this position for dims (8j+i) & 31
+    float cs[8], sn[8];
+    {
+        const int base = pos * kD + 8 * (j & 3);
+        if (p.cs_fp32) {
+            const float* t = reinterpret_cast<const float*>(p.cos_sin);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                cs[i] = t[base + i];
+                sn[i] = t[base + 32 + i];
+            }
+        } else {
+            const uint16_t* t = reinterpret_cast<const uint16_t*>(p.cos_sin);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                cs[i] = __uint_as_float((uint32_t)t[base + i] << 16);
+                sn[i] = __uint_as_float((uint32_t)t[base + 32 + i] << 16);
+            }
+        }
+    }
+    // rotated queries of the G heads sharing this kv head
+    float q[G][8];
+#pragma unroll
+    for (int hh = 0; hh < G; ++hh) {
+        const int hq = kvh * G + hh;
+        uint32_t rawb[8];
+        wait_flagged_vec<8>(c, qkv + hq * kD + 8 * j, tag, rawb);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float x = __uint_as_float(rawb[i] << 16);
+            const float partner = __shfl_xor_sync(kFullMask, x, 4);
+            q[hh][i] = rope_elem(x, partner, cs[i], sn[i], j < 4);
+        }
+    }
+    // the new token's K (rotated) and V; appended to the paged cache by the item that owns seq-1
+    float kn[8], vn[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) kn[i] = vn[i] = 0.f;
+    if (has_new) {
+        uint32_t rawk[8], rawv[8];
+        wait_flagged_vec<8>(c, qkv + (p.QH + kvh) * kD + 8 * j, tag, rawk);
+        wait_flagged_vec<8>(c, qkv + (p.QH + p.KVH + kvh) * kD + 8 * j, tag, rawv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float x = __uint_as_float(rawk[i] << 16);
+            const float partner = __shfl_xor_sync(kFullMask, x, 4);
+            kn[i] = rope_elem(x, partner, cs[i], sn[i], j < 4);
+            vn[i] = __uint_as_float(rawv[i] << 16);
+        }
+        const long long slot = sh.slot[b];
+        if (slot >= 0 && g == 0) {
+            uint16_t* kvw = reinterpret_cast<uint16_t*>(p.kv[layer]);
+            const long long blk = slot / p.block_size, off = slot % p.block_size;
+            const long long e = blk * p.block_stride + off * p.token_stride + (long long)kvh * p.head_stride + 8 * j;
+            uint4 kw, vw;
+            kw.x = pack_bf16x2(kn[0], kn[1]);
+            kw.y = pack_bf16x2(kn[2], kn[3]);
+            kw.z = pack_bf16x2(kn[4], kn[5]);
+            kw.w = pack_bf16x2(kn[6], kn[7]);
+            vw.x = pack_bf16x2(vn[0], vn[1]);
+            vw.y = pack_bf16x2(vn[2], vn[3]);
+            vw.z = pack_bf16x2(vn[4], vn[5]);
+            vw.w = pack_bf16x2(vn[6], vn[7]);
+            *reinterpret_cast<uint4*>(kvw + p.k_off + e) = kw;
+            *reinterpret_cast<uint4*>(kvw + p.v_off + e) = vw;
+        }
+    }
+
+    const uint16_t* kvr = reinterpret_cast<const uint16_t*>(p.kv[layer]);
+    float m[G], l[G], acc[G][8];
+#pragma unroll
+    for (int hh = 0; hh < G; ++hh) {
+        m[hh] = -INFINITY;
+        l[hh] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[hh][i] = 0.f;
+    }
+    const int niter = (end - start + 3) >> 2;   // positions per lane group, uniform over the warp
+    for (int it0 = 0; it0 < niter; it0 += 4) {
+        uint4 kk[4], vv[4];
+        int st[4];   // 0 = out of range, 1 = from cache, 2 = the new token (registers)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int pp = start + g + 4 * (it0 + u);
+            st[u] = 0;
+            kk[u] = vv[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (it0 + u < niter && pp < end) {
+                if (pp == seq - 1) {
+                    st[u] = 2;
+                } else {
+                    st[u] = 1;
+                    const int blk = p.block_table[b * p.bt_stride + pp / p.block_size];
+                    const long long e = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride +
+                                        (long long)kvh * p.head_stride + 8 * j;
+                    kk[u] = __ldcg(reinterpret_cast<const uint4*>(kvr + p.k_off + e));
+                    vv[u] = __ldcg(reinterpret_cast<const uint4*>(kvr + p.v_off + e));
+                }
+            }
+        }
+        float sc[4][G];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float kf[8];
+            if (st[u] == 2) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) kf[i] = kn[i];
+            } else {
+                kf[0] = bf16_lo(kk[u].x); kf[1] = bf16_hi(kk[u].x);
+                kf[2] = bf16_lo(kk[u].y); kf[3] = bf16_hi(kk[u].y);
+                kf[4] = bf16_lo(kk[u].z); kf[5] = bf16_hi(kk[u].z);
+                kf[6] = bf16_lo(kk[u].w); kf[7] = bf16_hi(kk[u].w);
+            }
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) {
+                float dsum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dsum = fmaf(q[hh][i], kf[i], dsum);
+                dsum += __shfl_xor_sync(kFullMask, dsum, 4);
+                dsum += __shfl_xor_sync(kFullMask, dsum, 2);
+                dsum += __shfl_xor_sync(kFullMask, dsum, 1);
+                // bf16 matmul output, then the exact 1/8 scale (HF eager_attention_forward)
+                sc[u][hh] = st[u] ? round_bf16(dsum) * 0.125f : -INFINITY;
+            }
+        }
+        float ev[4][G];
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) {
+            float mx = m[hh];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) mx = fmaxf(mx, sc[u][hh]);
+            const float alpha = (mx == -INFINITY) ? 1.f : expf(m[hh] - mx);
+            float es = 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                ev[u][hh] = (sc[u][hh] == -INFINITY) ? 0.f : expf(sc[u][hh] - mx);
+                es += ev[u][hh];
+            }
+            l[hh] = l[hh] * alpha + es;
+            m[hh] = mx;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[hh][i] *= alpha;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float vf[8];
+            if (st[u] == 2) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) vf[i] = vn[i];
+            } else {
+                vf[0] = bf16_lo(vv[u].x); vf[1] = bf16_hi(vv[u].x);
+                vf[2] = bf16_lo(vv[u].y); vf[3] = bf16_hi(vv[u].y);
+                vf[4] = bf16_lo(vv[u].z); vf[5] = bf16_hi(vv[u].z);
+                vf[6] = bf16_lo(vv[u].w); vf[7] = bf16_hi(vv[u].w);
+            }
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[hh][i] = fmaf(ev[u][hh], vf[i], acc[hh][i]);
+        }
+    }
+    // combine the 4 lane groups, publish the partial of every head of the group
+    const size_t item = ((size_t)(b * p.KVH + kvh) * kNCMax + chunk) * G;
+    unsigned long long* part = p.ll_part + ((size_t)par * p.B * p.KVH * kNCMax * G + item) * 66;
+#pragma unroll
+    for (int hh = 0; hh < G; ++hh) {
+        float mm = fmaxf(m[hh], __shfl_xor_sync(kFullMask, m[hh], 8));
+        mm = fmaxf(mm, __shfl_xor_sync(kFullMask, mm, 16));
+        const float f = (m[hh] == -INFINITY) ? 0.f : expf(m[hh] - mm);
+        float lt = l[hh] * f;
+        lt += __shfl_xor_sync(kFullMask, lt, 8);
+        lt += __shfl_xor_sync(kFullMask, lt, 16);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float a = acc[hh][i] * f;
+            a += __shfl_xor_sync(kFullMask, a, 8);
+            a += __shfl_xor_sync(kFullMask, a, 16);
+            acc[hh][i] = a;
+        }
+        if (g == 0) {
+            unsigned long long* dst = part + hh * 66;
+            if (j == 0) {
+                st_flagged(dst + 0, __float_as_uint(mm), tag);
+                st_flagged(dst + 1, __float_as_uint(lt), tag);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) st_flagged(dst + 2 + 8 * j + i, __float_as_uint(acc[hh][i]), tag);
+        }
+    }
+}
+
+// Log-sum-exp merge of the chunk partials of one (request, query head); output rounded to bf16
+// (the attention output dtype) and published two values per flagged word.
+__device__ void merge_task(Ctx& c, int layer, int b, int hq) {
+    const DecodeParams& p = c.p;
+    Shared& sh = c.sh;
+    const int lane = c.lane;
+    const uint32_t tag = layer_tag(c, layer);
+    const int par = layer & 1;
+    const int G = p.G;
+    const int kvh = hq / G, hh = hq - kvh * G;
+    const int nc = sh.nc[b];
+    const unsigned long long* part =
+        p.ll_part + ((size_t)par * p.B * p.KVH * kNCMax * G + ((size_t)(b * p.KVH + kvh) * kNCMax) * G + hh) * 66;
+    const size_t cstride = (size_t)G * 66;
+    float mc[2], lc[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int ch = lane + 32 * u;
+        mc[u] = -INFINITY;
+        lc[u] = 0.f;
+        if (ch < nc) {
+            mc[u] = __uint_as_float(wait_flagged(c, part + ch * cstride + 0, tag));
+            lc[u] = __uint_as_float(wait_flagged(c, part + ch * cstride + 1, tag));
+        }
+    }
+    const float M = warp_max(fmaxf(mc[0], mc[1]));
+    float wc[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) wc[u] = (mc[u] == -INFINITY) ? 0.f : expf(mc[u] - M);
+    const float den = warp_sum(lc[0] * wc[0] + lc[1] * wc[1]);
+    float a0 = 0.f, a1 = 0.f;
+    for (int ch0 = 0; ch0 < nc; ch0 += 8) {
+        unsigned long long v[8][2];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (ch0 + u < nc) {
+                v[u][0] = ld_flagged(part + (ch0 + u) * cstride + 2 + 2 * lane);
+                v[u][1] = ld_flagged(part + (ch0 + u) * cstride + 3 + 2 * lane);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int ch = ch0 + u;
+            if (ch < nc) {   // warp-uniform
+                const float wgt = __shfl_sync(kFullMask, ch < 32 ? wc[0] : wc[1], ch & 31);
+                const uint32_t b0 = ((uint32_t)(v[u][0] >> 32) == tag) ? (uint32_t)v[u][0]
+                                                                        : wait_flagged(c, part + ch * cstride + 2 + 2 * lane, tag);
+                const uint32_t b1 = ((uint32_t)(v[u][1] >> 32) == tag) ? (uint32_t)v[u][1]
+                                                                        : wait_flagged(c, part + ch * cstride + 3 + 2 * lane, tag);
+                a0 = fmaf(wgt, __uint_as_float(b0), a0);
+                a1 = fmaf(wgt, __uint_as_float(b1), a1);
+            }
+        }
+    }
+    const float inv = 1.f / den;
+    const uint32_t packed = pack_bf16x2(a0 * inv, a1 * inv);
+    const int nattn = p.QH * kD / 2;
+    st_flagged(p.ll_attn + (size_t)par * p.B * nattn + (size_t)b * nattn + hq * (kD / 2) + lane, packed, tag);
+}
+
+template <int G>
+__device__ void attention_phase(Ctx& c, int layer) {
+    const DecodeParams& p = c.p;
+    Shared& sh = c.sh;
+    const int total_warps = c.ncta * kNW;
+    const int gw = c.warp * c.ncta + c.cta;
+    const int nslots = kNCMax * p.B * p.KVH;
+    for (int s = gw; s < nslots; s += total_warps) {
+        const int kvh = s % p.KVH;
+        const int rest = s / p.KVH;
+        const int b = rest % p.B;
+        const int chunk = rest / p.B;
+        if (chunk < sh.nc[b]) attention_item<G>(c, layer, b, kvh, chunk);
+    }
+    // merge tasks go to the highest warps first so they rarely queue behind an attention item
+    const int gm = (kNW - 1 - c.warp) * c.ncta + c.cta;
+    for (int t = gm; t < p.B * p.QH; t += total_warps) merge_task(c, layer, t / p.QH, t % p.QH);
+}
+
+// ------------------------------------------------------------------ the kernel
+template <int B, int G>
+__global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Shared& sh = *reinterpret_cast<Shared*>(smem_raw);
+    size_t off = (sizeof(Shared) + 127) & ~size_t(127);
+    uint4* act = reinterpret_cast<uint4*>(smem_raw + off);
+    off += ((size_t)B * p.act_elems * 2 + 127) & ~size_t(127);
+    float* res = reinterpret_cast<float*>(smem_raw + off);
+    off += ((size_t)B * p.H * 4 + 127) & ~size_t(127);
+    unsigned char* ring_base = smem_raw + off;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cta = blockIdx.x, ncta = gridDim.x;
+
+    if (tid == 0) {
+        sh.abort_flag = 0;
+        sh.epoch = p.ctrl[kCtrlEpoch];
+    }
+    if (tid < kNW * kE) {
+        mbar_init(&sh.full[tid / kE][tid % kE], 1);
+        mbar_init(&sh.empty[tid / kE][tid % kE], 1);
+    }
+    if (tid < kNumPhaseTypes * kNW) {
+        const int t = tid / kNW, w = tid % kNW;
+        int a = 0, b = 0;
+        if (t != kLM || p.lm_head) warp_rows(p.ph[t].nrows, cta, ncta, w, a, b);
+        sh.row_a[t][w] = a;
+        sh.row_b[t][w] = b;
+    }
+    if (tid < B) {
+        const int seq = max(p.seq_lens[tid], 1);
+        sh.seq[tid] = seq;
+        sh.pos[tid] = (int)max(p.positions[tid], 0LL);
+        sh.slot[tid] = p.slot_mapping[tid];
+        sh.tok[tid] = p.ids_i64 ? reinterpret_cast<const long long*>(p.input_ids)[tid]
+                                : (long long)reinterpret_cast<const int*>(p.input_ids)[tid];
+        // chunk length: whole 16-position blocks, at most kNCMax chunks per (request, kv head)
+        int lc = ((seq + kNCMax - 1) / kNCMax + 15) & ~15;
+        if (lc < 16) lc = 16;
+        sh.lc[tid] = lc;
+        sh.nc[tid] = (seq + lc - 1) / lc;
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+
+    Ctx c{p, sh, act, res, ring_base + (size_t)(warp < kNW ? warp : 0) * p.ring_bytes, 0u, warp, lane, cta, ncta};
+    c.tag_base = (sh.epoch + 1u) << 7;
+
+    if (warp == kNW) {
+        producer_loop(c, ring_base);
+    } else {
+        // reset the argmax cells the *next* launch will use
+        if (cta == 0 && tid < kMaxB && p.next_ids) p.argkey[(size_t)((sh.epoch + 1u) & 1u) * kMaxB + tid] = 0ull;
+        uint32_t consumed = 0;
+        const int nqkv = (p.QH + 2 * p.KVH) * kD;
+        (void)nqkv;
+        for (int layer = 0; layer < p.L; ++layer) {
+            const uint32_t tag = layer_tag(c, layer);
+            const int par = layer & 1;
+            const uint16_t* norm1 = reinterpret_cast<const uint16_t*>(p.layers[layer * 6 + 0]);
+            const uint16_t* norm2 = reinterpret_cast<const uint16_t*>(p.layers[layer * 6 + 3]);
+            stage_norm<B>(c, p.ll_x + (size_t)par * B * p.H, tag, norm1, layer == 0);
+            gemv_phase<B, kQKV>(c, layer, consumed);
+            attention_phase<G>(c, layer);
+            stage_copy<B>(c, p.ll_attn + (size_t)par * B * (p.QH * kD / 2), tag, p.QH * kD, true);
+            gemv_phase<B, kO>(c, layer, consumed);
+            stage_norm<B>(c, p.ll_h1 + (size_t)par * B * p.H, tag, norm2, false);
+            gemv_phase<B, kGU>(c, layer, consumed);
+            stage_copy<B>(c, p.ll_act + (size_t)par * B * p.I, tag, p.I, false);
+            gemv_phase<B, kDown>(c, layer, consumed);
+        }
+        if (p.lm_head || cta == 0) {
+            stage_norm<B>(c, p.ll_x + (size_t)(p.L & 1) * B * p.H, layer_tag(c, p.L), p.final_norm, false);
+            if (cta == 0) {
+                const uint16_t* act16 = reinterpret_cast<const uint16_t*>(c.act);
+                for (int b = 0; b < B; ++b)
+                    for (int i = tid; i < p.H; i += kCT) p.out_hidden[b * p.H + i] = act16[(size_t)b * p.act_elems + i];
+            }
+            if (p.lm_head) gemv_phase<B, kLM>(c, p.L, consumed);
+        }
+    }
+    __syncthreads();
+    // The last CTA to finish publishes the greedy ids, optionally advances the step inputs in
+    // place (device-driven generation), and opens the next launch's epoch.
+    if (tid == 0) {
+        __threadfence();
+        const unsigned prev = atomicAdd(p.ctrl + kCtrlDone, 1u);
+        if (prev == (unsigned)ncta - 1u) {
+            __threadfence();
+            const bool ok = *((volatile unsigned int*)(p.ctrl + kCtrlStatus)) == 0;
+            if (p.next_ids && p.lm_head && ok) {
+                for (int b = 0; b < B; ++b) {
+                    const unsigned long long key =
+                        *((volatile unsigned long long*)(p.argkey + (size_t)(sh.epoch & 1u) * kMaxB + b));
+                    const long long id = (long long)(0xffffffffu - (uint32_t)key);
+                    p.next_ids[b] = id;
+                    if (p.advance) {
+                        if (p.ids_i64) reinterpret_cast<long long*>(const_cast<void*>(p.input_ids))[b] = id;
+                        else reinterpret_cast<int*>(const_cast<void*>(p.input_ids))[b] = (int)id;
+                        const long long np = p.positions[b] + 1;
+                        const_cast<long long*>(p.positions)[b] = np;
+                        const_cast<int*>(p.seq_lens)[b] = p.seq_lens[b] + 1;
+                        if (p.slot_mapping[b] >= 0 && np < (long long)p.max_seq_len) {
+                            const long long blk = p.block_table[b * p.bt_stride + (int)(np / p.block_size)];
+                            const_cast<long long*>(p.slot_mapping)[b] = blk * p.block_size + np % p.block_size;
+                        }
+                    }
+                }
+            }
+            p.ctrl[kCtrlDone] = 0u;
+            p.ctrl[kCtrlEpoch] = sh.epoch + 1u;
+            __threadfence();
+        }
+    }
+}
+
+
+// ------------------------------------------------------------------ host side
+struct ModelGeom {
+    int H, I, L, QH, KVH, V, wfmt;
+    float eps;
+};
+
+struct WsLayout {
+    size_t ctrl, argkey, x, qkv, attn, h1, act, part, total;
+};
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static WsLayout ws_layout(const ModelGeom& g, int B) {
+    WsLayout l{};
+    size_t off = 0;
+    l.ctrl = off;
+    off += 256;
+    l.argkey = off;
+    off += align_up(sizeof(unsigned long long) * 2 * kMaxB, 256);
+    const int G = g.QH / g.KVH;
+    const size_t nqkv = (size_t)(g.QH + 2 * g.KVH) * kD;
+    auto take = [&](size_t words) {
+        const size_t at = off;
+        off += align_up(words * 2 * sizeof(unsigned long long), 256);   // x2: layer parity
+        return at;
+    };
+    l.x = take((size_t)B * g.H);
+    l.qkv = take((size_t)B * nqkv);
+    l.attn = take((size_t)B * g.QH * kD / 2);
+    l.h1 = take((size_t)B * g.H);
+    l.act = take((size_t)B * g.I);
+    l.part = take((size_t)B * g.KVH * kNCMax * G * 66);
+    l.total = off;
+    return l;
+}
+
+struct DeviceInfo {
+    bool valid = false;
+    int sm_count = 0, coop = 0, major = 0, minor = 0, smem_optin = 0;
+};
+static std::mutex g_mu;
+static std::unordered_map<int, DeviceInfo> g_devinfo;
+static std::unordered_map<const void*, size_t> g_ws_ready;      // workspace pointers already zeroed
+static std::unordered_map<const void*, int> g_kernel_smem;      // largest dynamic smem opted in per kernel
+
+static int device_info(DeviceInfo& out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceInfo& d = g_devinfo[dev];
+    if (!d.valid) {
+        if ((e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&d.coop, cudaDevAttrCooperativeLaunch, dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&d.minor, cudaDevAttrComputeCapabilityMinor, dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess)
+            return (int)e;
+        d.valid = true;
+    }
+    out = d;
+    return 0;
+}
+
+typedef void (*KernelFn)(const DecodeParams);
+static KernelFn pick_kernel(int B, int G) {
+#define PK_CASE(b, g) \
+    if (B == b && G == g) return decode_step_kernel<b, g>;
+    PK_CASE(1, 1) PK_CASE(2, 1) PK_CASE(3, 1) PK_CASE(4, 1)
+    PK_CASE(1, 3) PK_CASE(2, 3) PK_CASE(3, 3) PK_CASE(4, 3)
+#undef PK_CASE
+    return nullptr;
+}
+
+// Fill the per-phase staging descriptors for a ring of `rw` bytes per consumer warp.
+static int make_phases(const ModelGeom& g, int rw, PhaseDesc (&ph)[kNumPhaseTypes]) {
+    const int entry_max = rw / 2;
+    auto rowbytes = [&](int K) { return g.wfmt ? (int)align_up((size_t)K + K / 32, 16) : K * 2; };
+    struct Spec { int nrows, K, pair, widx; long long pair_rows; };
+    const int nqkv = (g.QH + 2 * g.KVH) * kD;
+    const Spec spec[kNumPhaseTypes] = {
+        {nqkv, g.H, 0, 1, 0}, {g.H, g.QH * kD, 0, 2, 0}, {g.I, g.H, 1, 4, g.I}, {g.H, g.I, 0, 5, 0}, {g.V, g.H, 0, -1, 0}};
+    for (int t = 0; t < kNumPhaseTypes; ++t) {
+        PhaseDesc& d = ph[t];
+        d = PhaseDesc{};
+        d.nrows = spec[t].nrows;
+        d.kact = spec[t].K;
+        if (spec[t].K % 32) return kErrShape;
+        d.rowbytes = rowbytes(spec[t].K);
+        d.kchunks = d.rowbytes / 16;
+        d.pair = spec[t].pair;
+        d.widx = spec[t].widx;
+        d.pair_off = spec[t].pair_rows * (long long)d.rowbytes;
+        const int unit = d.rowbytes * (d.pair ? 2 : 1);
+        int R = entry_max / unit;
+        const int rcap = d.pair ? kRMax / 2 : kRMax;
+        if (R > rcap) R = rcap;
+        if (R >= 1) {
+            d.rows_per_entry = R;
+            d.nseg = 1;
+            d.segchunks = d.kchunks;
+        } else {
+            if (g.wfmt) return kErrShape;   // packed MXFP8 rows are not split along K
+            const int part_max_chunks = entry_max / (d.pair ? 2 : 1) / 16 / 32 * 32;
+            if (part_max_chunks < 32) return kErrResidency;
+            int nseg = (d.kchunks + part_max_chunks - 1) / part_max_chunks;
+            int segc = ((d.kchunks + nseg - 1) / nseg + 31) / 32 * 32;
+            nseg = (d.kchunks + segc - 1) / segc;
+            d.rows_per_entry = 1;
+            d.nseg = nseg;
+            d.segchunks = segc;
+        }
+    }
+    return 0;
+}
+
+struct StepArgs {
+    cudaStream_t stream;
+    int B;
+    const void* input_ids; int ids_i64;
+    const void* positions; const void* seq_lens; const void* block_table; int bt_stride; const void* slot_mapping;
+    const void* layers; const void* embed; const void* embed_lookup; const void* final_norm; const void* kv;
+    long long k_off, v_off, block_stride, token_stride, head_stride; int block_size;
+    const void* cos_sin; int cs_fp32;
+    void* out_hidden; void* logits; void* next_ids; void* layer_outputs;
+    void* ws; size_t ws_bytes; int max_seq_len; int lm_head; int advance;
+};
+
+static int decode_launch(const ModelGeom& g, const StepArgs& a) {
+    if (a.B < 1 || a.B > 4) return kErrBatch;
+    if (a.max_seq_len < 1 || a.max_seq_len > kMaxSeq) return kErrMaxSeq;
+    if (!a.input_ids || !a.positions || !a.seq_lens || !a.block_table || !a.slot_mapping || !a.layers || !a.embed ||
+        !a.final_norm || !a.kv || !a.cos_sin || !a.out_hidden || !a.ws)
+        return kErrNull;
+    if (g.H <= 0 || g.I <= 0 || g.L < 1 || g.L > kMaxLayers || g.QH <= 0 || g.KVH <= 0 || g.QH % g.KVH || g.V <= 0 ||
+        g.H % 32 || g.I % 32 || (g.QH * kD) % 32)
+        return kErrShape;
+    const int G = g.QH / g.KVH;
+    KernelFn fn = pick_kernel(a.B, G);
+    if (!fn) return kErrShape;
+    if (a.block_size <= 0 || a.bt_stride < 1 || (long long)a.bt_stride * a.block_size < a.max_seq_len) return kErrBlock;
+    if (a.k_off % 8 || a.v_off % 8 || a.block_stride % 8 || a.token_stride % 8 || a.head_stride % 8 || a.k_off < 0 ||
+        a.v_off < 0 || a.block_stride < 0 || a.token_stride < 0 || a.head_stride < 0)
+        return kErrAlign;
+    auto mis16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) % 16) != 0; };
+    if (mis16(a.layers) || mis16(a.embed) || mis16(a.final_norm) || mis16(a.ws) || mis16(a.out_hidden) || mis16(a.kv) ||
+        (a.embed_lookup && mis16(a.embed_lookup)) || (a.layer_outputs && mis16(a.layer_outputs)) ||
+        (a.logits && mis16(a.logits)))
+        return kErrAlign;
+    const WsLayout lay = ws_layout(g, a.B);
+    if (a.ws_bytes < lay.total) return kErrScratch;
+
+    DeviceInfo di;
+    int rc = device_info(di);
+    if (rc) return rc;
+    if (di.major != 10) return kErrArch;
+    if (!di.coop) return kErrCoop;
+
+    // shared memory: fixed part + per-warp rings
+    const int act_elems = g.H > g.I ? g.H : g.I;
+    const size_t fixed = align_up(sizeof(Shared), 128) + align_up((size_t)a.B * act_elems * 2, 128) +
+                         align_up((size_t)a.B * g.H * 4, 128);
+    if ((size_t)di.smem_optin < fixed + (size_t)kNW * 2048) return kErrResidency;
+    int rw = (int)(((size_t)di.smem_optin - fixed) / kNW / 512 * 512);
+    DecodeParams p{};
+    rc = make_phases(g, rw, p.ph);
+    if (rc) return rc;
+    const size_t smem = fixed + (size_t)kNW * rw;
+
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        int& cur = g_kernel_smem[reinterpret_cast<const void*>(fn)];
+        if ((int)smem > cur) {
+            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            cur = (int)smem;
+        }
+        auto it = g_ws_ready.find(a.ws);
+        if (it == g_ws_ready.end() || it->second < lay.total) {
+            // first use of this workspace: zero it in stream order (tags, counters, epoch start at 0)
+            cudaError_t e = cudaMemsetAsync(a.ws, 0, a.ws_bytes, a.stream);
+            if (e != cudaSuccess) return (int)e;
+            g_ws_ready[a.ws] = a.ws_bytes;
+        }
+    }
+
+    // grid: one CTA per SM, but never more CTAs than rows in the smallest projection, so every
+    // CTA takes part in every hand-off (which bounds how far any CTA can run ahead of another)
+    int ncta = di.sm_count;
+    for (int t = 0; t < 4; ++t) ncta = p.ph[t].nrows < ncta ? p.ph[t].nrows : ncta;
+    if (ncta < 1) return kErrShape;
+
+    unsigned char* ws = static_cast<unsigned char*>(a.ws);
+    p.layers = static_cast<const unsigned long long*>(a.layers);
+    p.kv = static_cast<const unsigned long long*>(a.kv);
+    p.embed = static_cast<const uint16_t*>(a.embed);
+    p.embed_bf16 = static_cast<const uint16_t*>(a.embed_lookup ? a.embed_lookup : a.embed);
+    p.final_norm = static_cast<const uint16_t*>(a.final_norm);
+    p.input_ids = a.input_ids;
+    p.positions = static_cast<const long long*>(a.positions);
+    p.seq_lens = static_cast<const int*>(a.seq_lens);
+    p.block_table = static_cast<const int*>(a.block_table);
+    p.slot_mapping = static_cast<const long long*>(a.slot_mapping);
+    p.cos_sin = a.cos_sin;
+    p.out_hidden = static_cast<uint16_t*>(a.out_hidden);
+    p.logits = static_cast<uint16_t*>(a.logits);
+    p.next_ids = static_cast<long long*>(a.next_ids);
+    p.layer_outputs = static_cast<uint16_t*>(a.layer_outputs);
+    p.ctrl = reinterpret_cast<unsigned int*>(ws + lay.ctrl);
+    p.argkey = reinterpret_cast<unsigned long long*>(ws + lay.argkey);
+    p.ll_x = reinterpret_cast<unsigned long long*>(ws + lay.x);
+    p.ll_qkv = reinterpret_cast<unsigned long long*>(ws + lay.qkv);
+    p.ll_attn = reinterpret_cast<unsigned long long*>(ws + lay.attn);
+    p.ll_h1 = reinterpret_cast<unsigned long long*>(ws + lay.h1);
+    p.ll_act = reinterpret_cast<unsigned long long*>(ws + lay.act);
+    p.ll_part = reinterpret_cast<unsigned long long*>(ws + lay.part);
+    p.k_off = a.k_off;
+    p.v_off = a.v_off;
+    p.block_stride = a.block_stride;
+    p.token_stride = a.token_stride;
+    p.head_stride = a.head_stride;
+    p.block_size = a.block_size;
+    p.bt_stride = a.bt_stride;
+    p.ids_i64 = a.ids_i64 ? 1 : 0;
+    p.cs_fp32 = a.cs_fp32 ? 1 : 0;
+    p.H = g.H; p.I = g.I; p.L = g.L; p.QH = g.QH; p.KVH = g.KVH; p.V = g.V; p.B = a.B; p.G = G;
+    p.wfmt = g.wfmt;
+    p.lm_head = (a.lm_head && (a.logits || a.next_ids)) ? 1 : 0;
+    p.advance = (a.advance && p.lm_head && a.next_ids) ? 1 : 0;
+    p.max_seq_len = a.max_seq_len;
+    p.ring_bytes = rw;
+    p.act_elems = act_elems;
+    p.eps = g.eps;
+
+    void* args[] = {&p};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fn), dim3(ncta), dim3(kThreads), args,
+                                                smem, a.stream);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return e == cudaErrorCooperativeLaunchTooLarge ? (int)kErrResidency : (int)e;
+    }
+    return (int)cudaPeekAtLastError();
+}
+
+static const char* status_string(int status) {
+    switch (status) {
+        case kOk: return "ok";
+        case kErrBatch: return "batch_must_be_1_to_4";
+        case kErrMaxSeq: return "max_seq_len_must_be_1_to_8192";
+        case kErrNull: return "null_device_pointer";
+        case kErrCoop: return "cooperative_launch_unsupported";
+        case kErrResidency: return "grid_exceeds_resident_capacity_or_shared_memory";
+        case kErrArch: return "kernel_requires_sm100";
+        case kErrAlign: return "kv_offsets_or_pointers_not_16_byte_aligned";
+        case kErrScratch: return "scratch_smaller_than_workspace_bytes";
+        case kErrBlock: return "block_size_or_stride_invalid";
+        case kErrBarrierTimeout: return "device_wait_timed_out";
+        case kErrShape: return "unsupported_model_geometry";
+        default: return cudaGetErrorString(static_cast<cudaError_t>(status));
+    }
+}
+
+static const ModelGeom kGeom135{576, 1536, 30, 9, 3, 49152, 0, 1e-5f};
+static const ModelGeom kGeom360{960, 2560, 32, 15, 5, 49152, 0, 1e-5f};
+
+}  // namespace pk
+
+// ================================================================== C ABI
+using namespace pk;
+
+struct PkDecodeModel {
+    int hidden, intermediate, layers, q_heads, kv_heads, vocab;
+    int weight_format;   // 0 = bf16, 1 = MXFP8 packed rows
+    float eps;
+};
+
+struct PkDecodeArgs {
+    void* stream;
+    int batch;
+    const void* input_ids; int ids_i64;
+    const void* positions; const void* seq_lens; const void* block_table; int bt_stride; const void* slot_mapping;
+    const void* layers; const void* embed; const void* embed_lookup; const void* final_norm; const void* kv_layers;
+    long long k_off, v_off, block_stride, token_stride, head_stride; int block_size;
+    const void* cos_sin; int cs_fp32;
+    void* out_hidden; void* logits; void* next_ids; void* layer_outputs;
+    void* workspace; size_t workspace_bytes; int max_seq_len; int lm_head; int advance;
+};
+
+static ModelGeom to_geom(const PkDecodeModel* m) {
+    return ModelGeom{m->hidden, m->intermediate, m->layers, m->q_heads, m->kv_heads, m->vocab, m->weight_format, m->eps};
+}
+
+extern "C" size_t pk_decode_workspace_bytes(const PkDecodeModel* m, int max_batch) {
+    if (!m || max_batch < 1 || m->kv_heads <= 0) return 0;
+    return ws_layout(to_geom(m), max_batch).total;
+}
+
+extern "C" int pk_decode_step(const PkDecodeModel* m, const PkDecodeArgs* a) {
+    if (!m || !a) return kErrNull;
+    StepArgs s{static_cast<cudaStream_t>(a->stream), a->batch, a->input_ids, a->ids_i64, a->positions, a->seq_lens,
+               a->block_table, a->bt_stride, a->slot_mapping, a->layers, a->embed, a->embed_lookup, a->final_norm,
+               a->kv_layers, a->k_off, a->v_off, a->block_stride, a->token_stride, a->head_stride, a->block_size,
+               a->cos_sin, a->cs_fp32, a->out_hidden, a->logits, a->next_ids, a->layer_outputs, a->workspace,
+               a->workspace_bytes, a->max_seq_len, a->lm_head, a->advance};
+    return decode_launch(to_geom(m), s);
+}
+
+// Zero a workspace in stream order and mark it ready (also done implicitly on first use).
+extern "C" int pk_decode_workspace_init(void* workspace, size_t bytes, void* stream) {
+    if (!workspace) return kErrNull;
+    cudaError_t e = cudaMemsetAsync(workspace, 0, bytes, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return (int)e;
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_ws_ready[workspace] = bytes;
+    return 0;
+}
+
+// Forget a workspace pointer (call before freeing it, so a later allocation at the same address is re-zeroed).
+extern "C" void pk_decode_workspace_forget(void* workspace) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_ws_ready.erase(workspace);
+}
+
+// Synchronise the stream and return the device-side status word of the workspace (0 = ok,
+// 9110 = a bounded device wait gave up).  The word is cleared so the workspace can be reused.
+extern "C" int pk_decode_status(void* workspace, void* stream) {
+    if (!workspace) return kErrNull;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned int word = 0;
+    cudaError_t e = cudaMemcpyAsync(&word, static_cast<unsigned int*>(workspace) + kCtrlStatus, sizeof(word),
+                                    cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return (int)e;
+    if (word) {
+        e = cudaMemsetAsync(workspace, 0, 256, s);   // control words only; tags stay monotonic via the epoch reset to 0
+        if (e != cudaSuccess) return (int)e;
+        std::lock_guard<std::mutex> lk(g_mu);
+        g_ws_ready.erase(workspace);                 // force a full re-zero before the next launch
+    }
+    return (int)word;
+}
+
+extern "C" const char* pk_status_string(int status) { return status_string(status); }
+
+extern "C" int pk_decode_query(int* sm_count, int* coop, int* major, int* minor, int* smem_optin, int* threads,
+                               int* consumer_warps) {
+    DeviceInfo di;
+    const int rc = device_info(di);
+    if (rc) return rc;
+    if (sm_count) *sm_count = di.sm_count;
+    if (coop) *coop = di.coop;
+    if (major) *major = di.major;
+    if (minor) *minor = di.minor;
+    if (smem_optin) *smem_optin = di.smem_optin;
+    if (threads) *threads = kThreads;
+    if (consumer_warps) *consumer_warps = kNW;
+    return 0;
+}
+
+// ---- drop-in entry points with the reference's signatures -------------------------------------
+// SmolLM2-135M: prime_kernels/decode_megakernel/csrc/megakernel.cu:833-927
+extern "C" int mk_query(int* sm_count, int* coop, int* active_per_sm, int* major, int* minor, int* regs,
+                        int* static_smem) {
+    DeviceInfo di;
+    const int rc = device_info(di);
+    if (rc) return rc;
+    cudaFuncAttributes fa{};
+    cudaError_t e = cudaFuncGetAttributes(&fa, decode_step_kernel<4, 3>);
+    if (e != cudaSuccess) return (int)e;
+    *sm_count = di.sm_count;
+    *coop = di.coop;
+    *active_per_sm = 1;
+    *major = di.major;
+    *minor = di.minor;
+    *regs = fa.numRegs;
+    *static_smem = (int)fa.sharedSizeBytes;
+    return 0;
+}
+
+extern "C" size_t mk_workspace_bytes(int B, int max_seq_len) {
+    (void)B;
+    (void)max_seq_len;
+    return ws_layout(kGeom135, 4).total;
+}
+
+extern "C" int mk_decode(void* stream, int B, const void* input_ids, int ids_i64, const void* positions,
+                         const void* seq_lens, const void* block_table, int bt_stride, const void* slot_mapping,
+                         const void* layers, const void* embed, const void* final_norm, void* const* kv_layers,
+                         long long k_off, long long v_off, long long block_stride, long long token_stride,
+                         long long head_stride, int block_size, const void* cos_sin, int cs_fp32, void* out_hidden,
+                         void* scratch, size_t scratch_bytes, int max_seq_len) {
+    StepArgs s{static_cast<cudaStream_t>(stream), B, input_ids, ids_i64, positions, seq_lens, block_table, bt_stride,
+               slot_mapping, layers, embed, nullptr, final_norm, kv_layers, k_off, v_off, block_stride, token_stride,
+               head_stride, block_size, cos_sin, cs_fp32, out_hidden, nullptr, nullptr, nullptr, scratch, scratch_bytes,
+               max_seq_len, 0, 0};
+    return decode_launch(kGeom135, s);
+}
+
+extern "C" const char* mk_status_string(int status) { return status_string(status); }
+
+// SmolLM2-360M: prime_kernels/decode_megakernel_360m/csrc/block360_kernel.inc:849-938
+extern "C" size_t decode360_workspace_bytes() { return ws_layout(kGeom360, 4).total; }
+extern "C" size_t decode360_debug_bytes() { return 16; }   // stage dumps are not produced; accepted and ignored
+
+extern "C" int decode360(void* stream, int B, const void* input_ids, const void* embed, const void* final_norm,
+                         const void* positions, const void* seq_lens, const void* block_table, int bt_stride,
+                         const void* slot_mapping, const void* layers, void* const* kv, long long k_off, long long v_off,
+                         long long block_stride, long long token_stride, long long head_stride, int block_size,
+                         const void* cos_sin, int cs_fp32, void* out_hidden, void* layer_outputs, void* scratch,
+                         size_t scratch_bytes, void* debug, size_t debug_bytes, int max_seq_len,
+                         int debug_layer_index) {
+    (void)debug;
+    (void)debug_bytes;
+    if (debug_layer_index < -1 || debug_layer_index >= kGeom360.L) return kErrBlock;
+    StepArgs s{static_cast<cudaStream_t>(stream), B, input_ids, 0, positions, seq_lens, block_table, bt_stride,
+               slot_mapping, layers, embed, nullptr, final_norm, kv, k_off, v_off, block_stride, token_stride,
+               head_stride, block_size, cos_sin, cs_fp32, out_hidden, nullptr, nullptr, layer_outputs, scratch,
+               scratch_bytes, max_seq_len, 0, 0};
+    return decode_launch(kGeom360, s);
+}
+
+extern "C" const char* decode360_status_string(int status) { return status_string(status); }

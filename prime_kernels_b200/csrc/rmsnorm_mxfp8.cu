@@ -1,0 +1,282 @@
+// Fused RMSNorm + residual + MXFP8 quantisation for sm_100a.
+//
+// One row is handled by a team of W warps.  Every thread owns U 16-byte chunks (8 bf16) of the
+// row at chunk indices t, t+T, t+2T, ... (T = 32*W), so every load and store instruction of a
+// warp touches one contiguous 512-byte (loads) / 256-byte (fp8 stores) span: fully coalesced
+// 128-bit accesses with no 32-byte-sector over-fetch.  A 32-element MXFP8 group is 4 adjacent
+// lanes; the group amax takes two shuffles.  The whole row stays in registers between the
+// sum-of-squares reduction and the quantisation, so each input byte is read from HBM exactly once.
+// Scale bytes are written four at a time (one 32-bit store per 16 lanes) straight into the
+// blocked [mTile, kTile, 32, 4, 4] layout a block-scaled tensor-core GEMM reads.
+//
+// Arithmetic contract (bit-exact with the reference quantiser,
+// prime_kernels/rmsnorm/src/kernels/rmsnorm_03_fixed_32pt.cu:67-98 and test.cu:108-146):
+//   s   = rsqrtf(sum(x^2) * (1/C) + eps)
+//   res = bf16( s * (branch * w) + residual )      product exact in fp32, no FMA contraction
+//   sf  = e8m0_roundup( amax32(|res|) / 448 ),  q = e4m3_rn_sat( res * 2^(127 - sf) )
+// Extensions: C only needs to be a multiple of 32 and N is arbitrary (padded scale bytes are
+// written as 0); mode 1 adds the residual before the norm and can return the bf16 sum.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "pk_common.cuh"
+
+namespace pk {
+
+struct RmsParams {
+    uint8_t* vals;            // [N, C] e4m3
+    uint8_t* scales;          // ceil(N/128) * ceil(C/128) * 512 e8m0, blocked
+    float* rrms;              // [N]
+    uint16_t* res_out;        // optional [N, C] bf16 (mode 0: pre-quant value; mode 1: branch+residual)
+    const uint4* branch;      // [N, C] bf16
+    const uint4* residual;    // [N, C] bf16
+    const uint4* weight;      // [C] bf16
+    float eps;
+    float inv_c;
+    int n;
+    int c;
+    int n_pad;                // N rounded up to 128
+    int nkt;                  // ceil(C/128)
+    int warps_per_row;        // W
+    int rows_per_block;
+    int mode;                 // 0: residual added after the norm; 1: before
+};
+
+__device__ __forceinline__ uint32_t e8m0_roundup(float x) {
+    // cvt.rp.satfinite.ue8m0x2.f32 packs two results; the low byte is the conversion of the 2nd operand
+    uint16_t r;
+    asm("cvt.rp.satfinite.ue8m0x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.0f), "f"(x));
+    return r & 0xffu;
+}
+
+__device__ __forceinline__ uint32_t e4m3x2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+template <int U>
+__global__ void __launch_bounds__(512) rmsnorm_mxfp8_kernel(const RmsParams p) {
+    extern __shared__ float red_s[];   // [rows_per_block][W]
+    const int W = p.warps_per_row;
+    const int T = W * 32;
+    const int team = threadIdx.x / T;
+    const int tt = threadIdx.x - team * T;       // thread index inside the team
+    const int lane = threadIdx.x & 31;
+    const int warp_in_team = tt >> 5;
+    const int row = blockIdx.x * p.rows_per_block + team;
+    const int nch = p.c >> 3;                    // 16-byte chunks per row
+    const bool live = row < p.n;
+
+    uint4 br[U], rs[U], wt[U];
+    float ss = 0.f;
+    if (live) {
+        const uint4* bp = p.branch + (size_t)row * nch;
+        const uint4* rp = p.residual + (size_t)row * nch;
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            const int c = tt + i * T;
+            if (c < nch) {
+                br[i] = ld_stream_16(bp + c);
+                rs[i] = ld_stream_16(rp + c);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            const int c = tt + i * T;
+            if (c < nch) wt[i] = __ldg(p.weight + c);
+        }
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            const int c = tt + i * T;
+            if (c < nch) {
+                uint32_t a[4] = {br[i].x, br[i].y, br[i].z, br[i].w};
+                if (p.mode) {
+                    const uint32_t r4[4] = {rs[i].x, rs[i].y, rs[i].z, rs[i].w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        a[k] = pack_bf16x2(__fadd_rn(bf16_lo(a[k]), bf16_lo(r4[k])),
+                                           __fadd_rn(bf16_hi(a[k]), bf16_hi(r4[k])));
+                    br[i] = make_uint4(a[0], a[1], a[2], a[3]);
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float lo = bf16_lo(a[k]), hi = bf16_hi(a[k]);
+                    ss = fmaf(lo, lo, ss);
+                    ss = fmaf(hi, hi, ss);
+                }
+            }
+        }
+    }
+    ss = warp_sum(ss);
+    if (W > 1) {
+        if (lane == 0) red_s[team * W + warp_in_team] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < W; ++w) tot += red_s[team * W + w];
+        ss = tot;
+    }
+    const float s = rsqrtf(ss * p.inv_c + p.eps);
+
+    if (row >= p.n_pad) return;
+    uint32_t* sc32 = reinterpret_cast<uint32_t*>(p.scales);
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+        const int c = tt + i * T;
+        const bool has = live && c < nch;       // uniform over each aligned group of 4 lanes
+        float v[8];
+        float amax = 0.f;
+        if (has) {
+            const uint32_t a[4] = {br[i].x, br[i].y, br[i].z, br[i].w};
+            const uint32_t r4[4] = {rs[i].x, rs[i].y, rs[i].z, rs[i].w};
+            const uint32_t w4[4] = {wt[i].x, wt[i].y, wt[i].z, wt[i].w};
+            uint32_t packed[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float pl = __fmul_rn(bf16_lo(a[k]), bf16_lo(w4[k]));   // exact
+                const float ph = __fmul_rn(bf16_hi(a[k]), bf16_hi(w4[k]));
+                float ol = __fmul_rn(s, pl), oh = __fmul_rn(s, ph);
+                if (!p.mode) {
+                    ol = __fadd_rn(ol, bf16_lo(r4[k]));
+                    oh = __fadd_rn(oh, bf16_hi(r4[k]));
+                }
+                packed[k] = pack_bf16x2(ol, oh);
+                v[2 * k] = bf16_lo(packed[k]);
+                v[2 * k + 1] = bf16_hi(packed[k]);
+            }
+            if (p.res_out) {
+                const uint4 o = p.mode ? br[i] : make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                st_stream_16(p.res_out + ((size_t)row * nch + c) * 8, o);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
+        }
+        // group amax over the 4 lanes of a 32-element group (executed by the whole warp)
+        amax = fmaxf(amax, __shfl_xor_sync(kFullMask, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(kFullMask, amax, 2));
+        uint32_t sf = 0;
+        if (has) {
+            sf = e8m0_roundup(__fmul_rn(amax, 1.f / 448.f));
+            const uint32_t e = 254u - sf;
+            const float inv = __uint_as_float(e ? (e << 23) : 0x00400000u);   // 2^(127 - sf)
+            uint2 q;
+            q.x = e4m3x2(v[0] * inv, v[1] * inv) | (e4m3x2(v[2] * inv, v[3] * inv) << 16);
+            q.y = e4m3x2(v[4] * inv, v[5] * inv) | (e4m3x2(v[6] * inv, v[7] * inv) << 16);
+            st_stream_8(p.vals + ((size_t)row * nch + c) * 8, q);
+        }
+        // four consecutive groups (16 lanes) -> one 32-bit store of scale bytes; groups past the
+        // end of the row and rows past N get 0 so that padded tiles are fully defined
+        const int base = lane & 16;
+        const uint32_t b0 = __shfl_sync(kFullMask, sf, base + 0);
+        const uint32_t b1 = __shfl_sync(kFullMask, sf, base + 4);
+        const uint32_t b2 = __shfl_sync(kFullMask, sf, base + 8);
+        const uint32_t b3 = __shfl_sync(kFullMask, sf, base + 12);
+        if ((lane & 15) == 0 && c < p.nkt * 16) {
+            const int k = c >> 2;                 // group index, multiple of 4
+            const size_t off = ((size_t)(row >> 7) * p.nkt + (k >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
+            sc32[off >> 2] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+        }
+    }
+    if (live && tt == 0) p.rrms[row] = s;
+}
+
+static int launch_rmsnorm(const RmsParams& p0, cudaStream_t stream) {
+    RmsParams p = p0;
+    const int nch = p.c / 8;
+    int U = 4;
+    int W = (nch + 32 * U - 1) / (32 * U);
+    if (W > 16) {
+        U = 8;
+        W = (nch + 32 * U - 1) / (32 * U);
+    }
+    if (W > 16) return kErrShape;
+    // teams must tile the block exactly: W in {1,2,4,8,16} after rounding up to a power of two
+    int Wp = 1;
+    while (Wp < W) Wp <<= 1;
+    p.warps_per_row = Wp;
+    p.rows_per_block = (Wp * 32 >= 256) ? 1 : 256 / (Wp * 32);
+    const int threads = p.rows_per_block * Wp * 32;
+    const int grid = (p.n_pad + p.rows_per_block - 1) / p.rows_per_block;
+    if (grid == 0) return kOk;
+    const size_t smem = (size_t)p.rows_per_block * Wp * sizeof(float);
+    if (U == 4)
+        rmsnorm_mxfp8_kernel<4><<<grid, threads, smem, stream>>>(p);
+    else
+        rmsnorm_mxfp8_kernel<8><<<grid, threads, smem, stream>>>(p);
+    return (int)cudaPeekAtLastError();
+}
+
+}  // namespace pk
+
+// ---------------------------------------------------------------- C ABI
+// Replaces prime_kernels/rmsnorm/rmsnorm.cuh:15-18,85 (fused_rmsnorm_residual_forward): same
+// argument order and meaning, but plain pointers, a status return instead of assert/exit, and
+// relaxed shapes (any N >= 0, C a positive multiple of 32).
+extern "C" int pk_fused_rmsnorm_residual_forward(void* vals, void* scales, float* rrms, const void* branch,
+                                                 const void* residual, const void* weight, float epsilon,
+                                                 int N, int C, void* stream) {
+    using namespace pk;
+    if (N < 0 || C <= 0 || (C % 32) != 0) return kErrShape;
+    if (N == 0) return kOk;
+    if (!vals || !scales || !rrms || !branch || !residual || !weight) return kErrNull;
+    if ((reinterpret_cast<uintptr_t>(vals) % 8) || (reinterpret_cast<uintptr_t>(scales) % 4) ||
+        (reinterpret_cast<uintptr_t>(branch) % 16) || (reinterpret_cast<uintptr_t>(residual) % 16) ||
+        (reinterpret_cast<uintptr_t>(weight) % 16))
+        return kErrAlign;
+    RmsParams p{};
+    p.vals = static_cast<uint8_t*>(vals);
+    p.scales = static_cast<uint8_t*>(scales);
+    p.rrms = rrms;
+    p.res_out = nullptr;
+    p.branch = static_cast<const uint4*>(branch);
+    p.residual = static_cast<const uint4*>(residual);
+    p.weight = static_cast<const uint4*>(weight);
+    p.eps = epsilon;
+    p.inv_c = 1.f / (float)C;
+    p.n = N;
+    p.c = C;
+    p.n_pad = (N + 127) / 128 * 128;
+    p.nkt = (C + 127) / 128;
+    p.mode = 0;
+    return launch_rmsnorm(p, static_cast<cudaStream_t>(stream));
+}
+
+// Extended entry: mode 0 = residual added after the norm (reference semantics), mode 1 = residual
+// added before the norm (the semantics of the reference's Triton residual-RMSNorm op,
+// prime_kernels/triton_rmsnorm/rmsnorm.py:711-722, followed by the same quantiser).
+// res_out (optional, bf16 [N, C]) receives the updated residual stream.
+extern "C" int pk_fused_rmsnorm_residual_forward_ex(void* vals, void* scales, float* rrms, void* res_out,
+                                                    const void* branch, const void* residual,
+                                                    const void* weight, float epsilon, int N, int C, int mode,
+                                                    void* stream) {
+    using namespace pk;
+    if (N < 0 || C <= 0 || (C % 32) != 0 || mode < 0 || mode > 1) return kErrShape;
+    if (N == 0) return kOk;
+    if (!vals || !scales || !rrms || !branch || !residual || !weight) return kErrNull;
+    if ((reinterpret_cast<uintptr_t>(vals) % 8) || (reinterpret_cast<uintptr_t>(scales) % 4) ||
+        (reinterpret_cast<uintptr_t>(branch) % 16) || (reinterpret_cast<uintptr_t>(residual) % 16) ||
+        (reinterpret_cast<uintptr_t>(weight) % 16) || (res_out && reinterpret_cast<uintptr_t>(res_out) % 16))
+        return kErrAlign;
+    RmsParams p{};
+    p.vals = static_cast<uint8_t*>(vals);
+    p.scales = static_cast<uint8_t*>(scales);
+    p.rrms = rrms;
+    p.res_out = static_cast<uint16_t*>(res_out);
+    p.branch = static_cast<const uint4*>(branch);
+    p.residual = static_cast<const uint4*>(residual);
+    p.weight = static_cast<const uint4*>(weight);
+    p.eps = epsilon;
+    p.inv_c = 1.f / (float)C;
+    p.n = N;
+    p.c = C;
+    p.n_pad = (N + 127) / 128 * 128;
+    p.nkt = (C + 127) / 128;
+    p.mode = mode;
+    return launch_rmsnorm(p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" long long pk_rmsnorm_scale_bytes(int N, int C) {
+    return (long long)((N + 127) / 128) * ((C + 127) / 128) * 512;
+}

@@ -1,0 +1,149 @@
+// torch.ops bindings over the C ABI of libprime_kernels_b200.so.
+//
+// prime_rmsnorm::fused_rmsnorm_residual keeps the reference schema
+// (prime_kernels/rmsnorm/csrc/torch_interface.cpp:65-74): CUDA dispatch key, outputs allocated by
+// the op, current stream, errors as TORCH_CHECK.  Shapes are relaxed to any N and C % 32 == 0.
+// prime_decode::decode_step exposes the megakernel to the dispatcher (the reference reaches its
+// decode kernels through ctypes only; decode_megakernel/__init__.py:72-91).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/all.h>
+#include <torch/library.h>
+
+#include <tuple>
+
+#include "../../include/prime_kernels_b200.h"
+
+namespace {
+
+int64_t scale_numel(int64_t N, int64_t C) { return ((N + 127) / 128) * ((C + 127) / 128) * 512; }
+
+void check_rms_inputs(const torch::Tensor& branch, const torch::Tensor& residual, const torch::Tensor& weight) {
+    TORCH_CHECK(branch.dim() == 2, "branch must be a 2D (N, C) tensor");
+    const int64_t C = branch.size(1);
+    TORCH_CHECK(C > 0 && (C % 32) == 0, "C (", C, ") must be a positive multiple of 32");
+    TORCH_CHECK(residual.sizes() == branch.sizes(), "residual must have the same shape as branch");
+    TORCH_CHECK(weight.dim() == 1 && weight.size(0) == C, "weight must be a 1D (C,) tensor");
+    TORCH_CHECK(branch.is_contiguous() && residual.is_contiguous() && weight.is_contiguous(),
+                "branch, residual and weight must be contiguous");
+    TORCH_CHECK(branch.dtype() == torch::kBFloat16 && residual.dtype() == torch::kBFloat16 &&
+                    weight.dtype() == torch::kBFloat16,
+                "branch, residual and weight must be bfloat16");
+    TORCH_CHECK(branch.is_cuda(), "branch must be a CUDA tensor");
+    TORCH_CHECK(residual.device() == branch.device() && weight.device() == branch.device(),
+                "all inputs must be on the same device");
+}
+
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> fused_rmsnorm_residual(const torch::Tensor& branch,
+                                                                               const torch::Tensor& residual,
+                                                                               const torch::Tensor& weight,
+                                                                               double epsilon) {
+    check_rms_inputs(branch, residual, weight);
+    at::cuda::OptionalCUDAGuard guard{device_of(branch)};
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    const int64_t N = branch.size(0), C = branch.size(1);
+    auto opts = torch::TensorOptions().device(branch.device());
+    torch::Tensor vals = torch::empty({N, C}, opts.dtype(torch::kFloat8_e4m3fn));
+    torch::Tensor scales = torch::empty({scale_numel(N, C)}, opts.dtype(torch::kFloat8_e8m0fnu));
+    torch::Tensor rrms = torch::empty({N}, opts.dtype(torch::kFloat32));
+    const int rc = pk_fused_rmsnorm_residual_forward(vals.data_ptr(), scales.data_ptr(),
+                                                     static_cast<float*>(rrms.data_ptr()), branch.const_data_ptr(),
+                                                     residual.const_data_ptr(), weight.const_data_ptr(),
+                                                     static_cast<float>(epsilon), (int)N, (int)C, stream);
+    TORCH_CHECK(rc == 0, "fused_rmsnorm_residual failed: ", pk_status_string(rc));
+    return {vals, scales, rrms};
+}
+
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> fused_rmsnorm_residual_ex(
+    const torch::Tensor& branch, const torch::Tensor& residual, const torch::Tensor& weight, double epsilon,
+    bool residual_out, bool prenorm_add) {
+    check_rms_inputs(branch, residual, weight);
+    at::cuda::OptionalCUDAGuard guard{device_of(branch)};
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    const int64_t N = branch.size(0), C = branch.size(1);
+    auto opts = torch::TensorOptions().device(branch.device());
+    torch::Tensor vals = torch::empty({N, C}, opts.dtype(torch::kFloat8_e4m3fn));
+    torch::Tensor scales = torch::empty({scale_numel(N, C)}, opts.dtype(torch::kFloat8_e8m0fnu));
+    torch::Tensor rrms = torch::empty({N}, opts.dtype(torch::kFloat32));
+    torch::Tensor res = residual_out ? torch::empty({N, C}, opts.dtype(torch::kBFloat16))
+                                     : torch::empty({0}, opts.dtype(torch::kBFloat16));
+    const int rc = pk_fused_rmsnorm_residual_forward_ex(
+        vals.data_ptr(), scales.data_ptr(), static_cast<float*>(rrms.data_ptr()),
+        residual_out ? res.data_ptr() : nullptr, branch.const_data_ptr(), residual.const_data_ptr(),
+        weight.const_data_ptr(), static_cast<float>(epsilon), (int)N, (int)C, prenorm_add ? 1 : 0, stream);
+    TORCH_CHECK(rc == 0, "fused_rmsnorm_residual_ex failed: ", pk_status_string(rc));
+    return {vals, scales, rrms, res};
+}
+
+const void* opt_ptr(const std::optional<torch::Tensor>& t) { return t.has_value() ? t->const_data_ptr() : nullptr; }
+void* opt_mptr(const std::optional<torch::Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+
+// Returns the status code of the launch (0 = ok); the Python surface turns it into an exception.
+int64_t decode_step(const torch::Tensor& input_ids, const torch::Tensor& positions, const torch::Tensor& seq_lens,
+                    const torch::Tensor& block_table, const torch::Tensor& slot_mapping, const torch::Tensor& embed,
+                    const std::optional<torch::Tensor>& embed_lookup, const torch::Tensor& layers_table,
+                    const torch::Tensor& final_norm, const torch::Tensor& kv_table, int64_t k_off, int64_t v_off,
+                    int64_t block_stride, int64_t token_stride, int64_t head_stride, int64_t block_size,
+                    const torch::Tensor& cos_sin_cache, torch::Tensor out_hidden,
+                    std::optional<torch::Tensor> logits, std::optional<torch::Tensor> next_ids,
+                    std::optional<torch::Tensor> layer_outputs, torch::Tensor workspace, int64_t hidden,
+                    int64_t intermediate, int64_t layers, int64_t q_heads, int64_t kv_heads, int64_t vocab,
+                    int64_t weight_format, double eps, int64_t max_seq_len, bool lm_head, bool advance) {
+    at::cuda::OptionalCUDAGuard guard{device_of(input_ids)};
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    PkDecodeModel m{(int)hidden, (int)intermediate, (int)layers, (int)q_heads, (int)kv_heads, (int)vocab,
+                    (int)weight_format, (float)eps};
+    PkDecodeArgs a{};
+    a.stream = stream;
+    a.batch = (int)input_ids.size(0);
+    a.input_ids = input_ids.const_data_ptr();
+    a.ids_i64 = input_ids.dtype() == torch::kInt64;
+    a.positions = positions.const_data_ptr();
+    a.seq_lens = seq_lens.const_data_ptr();
+    a.block_table = block_table.const_data_ptr();
+    a.bt_stride = (int)block_table.stride(0);
+    a.slot_mapping = slot_mapping.const_data_ptr();
+    a.layers = layers_table.const_data_ptr();
+    a.embed = embed.const_data_ptr();
+    a.embed_lookup = opt_ptr(embed_lookup);
+    a.final_norm = final_norm.const_data_ptr();
+    a.kv_layers = kv_table.const_data_ptr();
+    a.k_off = k_off;
+    a.v_off = v_off;
+    a.block_stride = block_stride;
+    a.token_stride = token_stride;
+    a.head_stride = head_stride;
+    a.block_size = (int)block_size;
+    a.cos_sin = cos_sin_cache.const_data_ptr();
+    a.cs_fp32 = cos_sin_cache.dtype() == torch::kFloat32;
+    a.out_hidden = out_hidden.data_ptr();
+    a.logits = opt_mptr(logits);
+    a.next_ids = opt_mptr(next_ids);
+    a.layer_outputs = opt_mptr(layer_outputs);
+    a.workspace = workspace.data_ptr();
+    a.workspace_bytes = (size_t)workspace.numel() * workspace.element_size();
+    a.max_seq_len = (int)max_seq_len;
+    a.lm_head = lm_head;
+    a.advance = advance;
+    return pk_decode_step(&m, &a);
+}
+
+}  // namespace
+
+TORCH_LIBRARY_FRAGMENT(prime_rmsnorm, m) {
+    m.def("fused_rmsnorm_residual(Tensor branch, Tensor residual, Tensor weight, float epsilon) -> (Tensor, Tensor, Tensor)");
+    m.impl("fused_rmsnorm_residual", torch::kCUDA, &fused_rmsnorm_residual);
+    m.def("fused_rmsnorm_residual_ex(Tensor branch, Tensor residual, Tensor weight, float epsilon, bool residual_out, "
+          "bool prenorm_add) -> (Tensor, Tensor, Tensor, Tensor)");
+    m.impl("fused_rmsnorm_residual_ex", torch::kCUDA, &fused_rmsnorm_residual_ex);
+}
+
+TORCH_LIBRARY_FRAGMENT(prime_decode, m) {
+    m.def("decode_step(Tensor input_ids, Tensor positions, Tensor seq_lens, Tensor block_table, Tensor slot_mapping, "
+          "Tensor embed, Tensor? embed_lookup, Tensor layers_table, Tensor final_norm, Tensor kv_table, int k_off, "
+          "int v_off, int block_stride, int token_stride, int head_stride, int block_size, Tensor cos_sin_cache, "
+          "Tensor(a!) out_hidden, Tensor(b!)? logits, Tensor(c!)? next_ids, Tensor(d!)? layer_outputs, "
+          "Tensor(e!) workspace, int hidden, int intermediate, int layers, int q_heads, int kv_heads, int vocab, "
+          "int weight_format, float eps, int max_seq_len, bool lm_head, bool advance) -> int");
+    m.impl("decode_step", torch::kCUDA, &decode_step);
+}

@@ -1,0 +1,240 @@
+"""Geometry-generic single-launch decode step (sm_100a) with optional fused tied lm_head + argmax.
+
+The keyword contract of ``decode_step`` is the reference's (prime_kernels/decode_megakernel/__init__.py:134-205
+and prime_kernels/decode_megakernel_360m/__init__.py:122-214 in the reference project): vLLM
+FLASH_ATTN-style decode metadata, fused ``qkv`` / ``gate_up`` weights, a paged bf16 KV cache
+``[blocks, kv_heads, block_size, 128]`` (K in 0..63, V in 64..127) and a ``cos_sin_cache [max_pos, 64]``.
+The returned hidden state is a view of a per-device buffer that the next call overwrites.
+
+Extensions over the reference: any Llama geometry with head_dim 64 (SmolLM2 135M / 360M / 1.7B are
+predefined), batch up to 4, MXFP8-packed weights, and ``lm_head=True`` which also returns bf16
+logits and greedy next ids computed inside the same launch.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .._cabi import library, load_ops
+
+load_ops()
+
+__all__ = ["Geometry", "SMOLLM2_135M", "SMOLLM2_360M", "SMOLLM2_1P7B", "GEOMETRIES", "MAX_BATCH", "MAX_SEQ",
+           "HEAD_DIM", "decode_step", "check_status", "DecodeSession", "workspace_bytes"]
+
+MAX_BATCH = 4
+MAX_SEQ = 8192
+HEAD_DIM = 64
+
+
+@dataclass(frozen=True)
+class Geometry:
+    name: str
+    hidden: int
+    intermediate: int
+    layers: int
+    q_heads: int
+    kv_heads: int
+    vocab: int = 49152
+    rope_theta: float = 100000.0
+    eps: float = 1e-5
+    weight_format: int = 0   # 0 = bf16, 1 = MXFP8 packed rows
+
+    @property
+    def qkv_rows(self) -> int:
+        return (self.q_heads + 2 * self.kv_heads) * HEAD_DIM
+
+    def with_format(self, weight_format: int) -> "Geometry":
+        return Geometry(self.name, self.hidden, self.intermediate, self.layers, self.q_heads, self.kv_heads,
+                        self.vocab, self.rope_theta, self.eps, weight_format)
+
+
+SMOLLM2_135M = Geometry("smollm2-135m", 576, 1536, 30, 9, 3)
+SMOLLM2_360M = Geometry("smollm2-360m", 960, 2560, 32, 15, 5)
+SMOLLM2_1P7B = Geometry("smollm2-1.7b", 2048, 8192, 24, 32, 32, rope_theta=130000.0)
+GEOMETRIES = {g.name: g for g in (SMOLLM2_135M, SMOLLM2_360M, SMOLLM2_1P7B)}
+
+
+@torch.library.register_fake("prime_decode::decode_step")
+def _decode_step_fake(input_ids, positions, seq_lens, block_table, slot_mapping, embed, embed_lookup, layers_table,
+                      final_norm, kv_table, k_off, v_off, block_stride, token_stride, head_stride, block_size,
+                      cos_sin_cache, out_hidden, logits, next_ids, layer_outputs, workspace, hidden, intermediate,
+                      layers, q_heads, kv_heads, vocab, weight_format, eps, max_seq_len, lm_head, advance):
+    return 0
+
+
+def workspace_bytes(geometry: Geometry, max_batch: int = MAX_BATCH) -> int:
+    from .._cabi import PkDecodeModel
+    import ctypes
+
+    m = PkDecodeModel(geometry.hidden, geometry.intermediate, geometry.layers, geometry.q_heads, geometry.kv_heads,
+                      geometry.vocab, geometry.weight_format, geometry.eps)
+    return int(library().pk_decode_workspace_bytes(ctypes.byref(m), max_batch))
+
+
+class _Runtime:
+    """Per-(device, geometry) workspace, output buffers and cached pointer tables."""
+
+    def __init__(self, geometry: Geometry, device: torch.device):
+        self.geometry = geometry
+        self.device = device
+        self.scratch = torch.zeros(workspace_bytes(geometry, MAX_BATCH), dtype=torch.uint8, device=device)
+        self.out = torch.empty((MAX_BATCH, geometry.hidden), dtype=torch.bfloat16, device=device)
+        self.logits = None
+        self.next_ids = None
+        self.table_key = None
+        self.layers_t = None
+        self.kv_t = None
+
+    def lm_buffers(self):
+        if self.logits is None:
+            self.logits = torch.empty((MAX_BATCH, self.geometry.vocab), dtype=torch.bfloat16, device=self.device)
+            self.next_ids = torch.zeros((MAX_BATCH,), dtype=torch.int64, device=self.device)
+        return self.logits, self.next_ids
+
+    def tables(self, layers, kv_caches):
+        key = (tuple(t.data_ptr() for layer in layers for t in layer), tuple(kv.data_ptr() for kv in kv_caches))
+        if key != self.table_key:
+            layer_table = torch.tensor([[t.data_ptr() for t in layer] for layer in layers], dtype=torch.int64)
+            kv_table = torch.tensor([kv.data_ptr() for kv in kv_caches], dtype=torch.int64)
+            if self.layers_t is None:
+                self.layers_t = layer_table.to(self.device)
+                self.kv_t = kv_table.to(self.device)
+            else:
+                # in place, so CUDA graphs captured with these tables see the new pointers
+                self.layers_t.copy_(layer_table)
+                self.kv_t.copy_(kv_table)
+            self.table_key = key
+        return self.layers_t, self.kv_t
+
+
+_runtimes: dict = {}
+
+
+def _runtime(geometry: Geometry, device: torch.device) -> _Runtime:
+    key = (geometry, device)
+    if key not in _runtimes:
+        _runtimes[key] = _Runtime(geometry, device)
+    return _runtimes[key]
+
+
+def status_string(rc: int) -> str:
+    return library().pk_status_string(int(rc)).decode()
+
+
+def _check_kv(geometry: Geometry, kv_caches):
+    first = kv_caches[0]
+    if first.dtype != torch.bfloat16 or first.dim() != 4:
+        raise ValueError("kv_caches must be 4-D BF16 tensors")
+    if first.shape[1] != geometry.kv_heads or first.shape[3] != 2 * HEAD_DIM or first.stride(3) != 1:
+        raise ValueError(
+            f"kv_caches must be [blocks, {geometry.kv_heads}, block_size, {2 * HEAD_DIM}] with unit last stride")
+    for kv in kv_caches:
+        if kv.shape != first.shape or kv.stride() != first.stride() or kv.dtype != first.dtype:
+            raise ValueError("all layers must share one KV cache shape, dtype and strides")
+        if not kv.is_cuda:
+            raise ValueError("kv_caches must be CUDA tensors")
+
+
+def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_table, slot_mapping, embed, layers,
+                final_norm, kv_caches, cos_sin_cache, eps, layer_outputs=None, lm_head=False, advance=False,
+                embed_lookup=None, name="decode"):
+    """One decode step for ``geometry``.  Returns the final-normed hidden ``[B, hidden]`` (a view of a
+    shared buffer), or ``(hidden, logits, next_ids)`` when ``lm_head`` is true."""
+    batch = input_ids.shape[0]
+    if not 1 <= batch <= MAX_BATCH:
+        raise ValueError(f"batch must be 1..{MAX_BATCH}, got {batch}")
+    if eps != geometry.eps:
+        raise ValueError(f"the kernel is built for rms eps {geometry.eps}, got {eps}")
+    if len(layers) != geometry.layers or len(kv_caches) != geometry.layers:
+        raise ValueError(f"expected {geometry.layers} layers and KV caches")
+    if input_ids.dtype not in (torch.int32, torch.int64) or positions.dtype != torch.int64:
+        raise ValueError("input_ids must be int32 or int64 and positions int64")
+    if seq_lens.dtype != torch.int32 or block_table.dtype != torch.int32 or slot_mapping.dtype != torch.int64:
+        raise ValueError("seq_lens and block_table must be int32, slot_mapping int64")
+    if block_table.stride(1) != 1 or block_table.shape[0] < batch:
+        raise ValueError("block_table rows must be contiguous and cover the batch")
+    if cos_sin_cache.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("cos_sin_cache must be BF16 or FP32")
+    _check_kv(geometry, kv_caches)
+    device = input_ids.device
+    kv0 = kv_caches[0]
+    block_size = kv0.shape[2]
+    max_seq = block_table.shape[1] * block_size
+    if max_seq > MAX_SEQ:
+        raise ValueError(f"context limit {max_seq} exceeds the kernel's {MAX_SEQ}")
+
+    rt = _runtime(geometry, device)
+    layers_t, kv_t = rt.tables(layers, kv_caches)
+    logits = next_ids = None
+    if lm_head:
+        logits, next_ids = rt.lm_buffers()
+    rc = torch.ops.prime_decode.decode_step(
+        input_ids, positions, seq_lens, block_table, slot_mapping, embed, embed_lookup, layers_t, final_norm, kv_t,
+        0, kv0.shape[3] // 2, kv0.stride(0), kv0.stride(2), kv0.stride(1), block_size, cos_sin_cache, rt.out,
+        logits, next_ids, layer_outputs, rt.scratch, geometry.hidden, geometry.intermediate, geometry.layers,
+        geometry.q_heads, geometry.kv_heads, geometry.vocab, geometry.weight_format, float(eps), max_seq,
+        bool(lm_head), bool(advance))
+    if rc != 0:
+        raise RuntimeError(f"{name} failed: {status_string(rc)}")
+    if lm_head:
+        return rt.out[:batch], logits[:batch], next_ids[:batch]
+    return rt.out[:batch]
+
+
+def check_status(geometry: Geometry, device) -> None:
+    """Synchronise and raise if a bounded device-side wait of an earlier step gave up."""
+    device = torch.device(device)
+    rt = _runtimes.get((geometry, device))
+    if rt is None:
+        return
+    with torch.cuda.device(device):
+        rc = library().pk_decode_status(rt.scratch.data_ptr(), torch.cuda.current_stream(device).cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"decode failed on the device: {status_string(rc)}")
+
+
+class DecodeSession:
+    """Greedy generation driver: all step inputs live on the device and the kernel advances them in
+    place (``advance=True``), so ``steps`` launches run back to back with no host round trip."""
+
+    def __init__(self, geometry: Geometry, *, embed, layers, final_norm, kv_caches, cos_sin_cache, block_table,
+                 embed_lookup=None):
+        self.geometry = geometry
+        self.embed, self.layers, self.final_norm = embed, layers, final_norm
+        self.kv_caches, self.cos_sin_cache, self.block_table = kv_caches, cos_sin_cache, block_table
+        self.embed_lookup = embed_lookup
+        self.device = embed.device
+        self.block_size = kv_caches[0].shape[2]
+
+    def start(self, last_ids: torch.Tensor, context_lens: torch.Tensor):
+        """``last_ids [B]``: the token to feed first; ``context_lens [B]``: tokens already in the cache."""
+        dev = self.device
+        self.input_ids = last_ids.to(dev, torch.int64).clone()
+        self.positions = context_lens.to(dev, torch.int64).clone()
+        self.seq_lens = (context_lens.to(dev, torch.int32) + 1).clone()
+        bt = self.block_table
+        rows = torch.arange(bt.shape[0], device=dev)[: self.input_ids.shape[0]]
+        blk = bt[rows, (self.positions // self.block_size).long()].to(torch.int64)
+        self.slot_mapping = blk * self.block_size + self.positions % self.block_size
+
+    def step(self):
+        return decode_step(self.geometry, input_ids=self.input_ids, positions=self.positions,
+                           seq_lens=self.seq_lens, block_table=self.block_table, slot_mapping=self.slot_mapping,
+                           embed=self.embed, layers=self.layers, final_norm=self.final_norm,
+                           kv_caches=self.kv_caches, cos_sin_cache=self.cos_sin_cache, eps=self.geometry.eps,
+                           lm_head=True, advance=True, embed_lookup=self.embed_lookup)
+
+    def generate(self, steps: int, collect_logits: bool = False):
+        """Run ``steps`` greedy steps; returns ids ``[steps, B]`` (and logits ``[steps, B, V]``)."""
+        b = self.input_ids.shape[0]
+        ids = torch.empty((steps, b), dtype=torch.int64, device=self.device)
+        logs = torch.empty((steps, b, self.geometry.vocab), dtype=torch.bfloat16, device=self.device) if collect_logits else None
+        for t in range(steps):
+            _, logits, next_ids = self.step()
+            ids[t].copy_(next_ids)
+            if collect_logits:
+                logs[t].copy_(logits)
+        check_status(self.geometry, self.device)
+        return (ids, logs) if collect_logits else ids
