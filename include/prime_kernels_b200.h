@@ -82,6 +82,11 @@ int pk_decode_status(void* workspace, void* stream);
 /* Generic form of mk_query (prime_kernels/decode_megakernel/csrc/megakernel.cu:833-836). */
 int pk_decode_query(int* sm_count, int* coop, int* major, int* minor, int* smem_optin, int* threads,
                     int* consumer_warps);
+/* Debug aid modelled on the reference's private stage profiler
+ * (research/smollm2_360m_decode/experiments/r28-fast-stage-profile-r1/README.md:7-9): when a device
+ * buffer of at least ctas * layers * 24 * 8 bytes is set, thread 0 of every CTA stamps %globaltimer at
+ * each phase boundary of each layer ([cta][layer][24] uint64 ns).  Pass NULL to disable. */
+void pk_decode_set_profile(void* buffer, size_t bytes);
 /* Replaces mk_status_string / decode360_status_string for every code above. */
 const char* pk_status_string(int status);
 

@@ -46,6 +46,7 @@ SYMBOLS = {
     "pk_decode_workspace_forget": (None, [vp]),
     "pk_decode_status": (ci, [vp, vp]),
     "pk_decode_query": (ci, [ip] * 7),
+    "pk_decode_set_profile": (None, [vp, sz]),
     "pk_status_string": (ctypes.c_char_p, [ci]),
     "mk_query": (ci, [ip] * 7),
     "mk_workspace_bytes": (sz, [ci, ci]),

@@ -40,7 +40,7 @@
 
 namespace pk {
 
-constexpr int kNW = 16;                    // consumer warps per CTA
+constexpr int kNW = 7;                     // consumer warps per CTA (+1 producer = 256 threads: 255 registers each)
 constexpr int kCT = kNW * 32;              // consumer threads
 constexpr int kThreads = kCT + 32;         // + one producer warp
 constexpr int kD = 64;                     // head dim (fixed)
@@ -49,6 +49,11 @@ constexpr int kRMax = 4;                   // max weight rows staged per ring en
 constexpr int kMaxB = 8;
 constexpr int kNCMax = 64;                 // max split-KV chunks per (request, kv head)
 constexpr int kMaxSeq = 8192;
+constexpr int kMaxLayerEntries = 40;       // ring entries per consumer warp and layer
+constexpr int kMaxLmEntries = 56;          // ring entries per consumer warp for the lm_head
+constexpr int kNormRegs = 10;              // norm weights held per thread: hidden <= kNormRegs * kCT
+constexpr int kDirectWords = 8192;         // direct-merge limit: partial words every CTA stages per layer
+constexpr int kAttnScratchWords = 8192 + 512;   // staged partials + merge weights; also >= kNW * 4 * 66 + staging
 constexpr int kMaxLayers = 120;
 constexpr unsigned kSpinLimit = 1u << 22;  // bounded waits: ~1-2 s of L2 polling
 
@@ -87,6 +92,7 @@ struct DecodeParams {
     uint16_t* logits;                   // optional [B, V] bf16
     long long* next_ids;                // optional [B]
     uint16_t* layer_outputs;            // optional [L, B, H]
+    unsigned long long* profile;        // optional [ncta][L][kProfSlots] globaltimer stamps (ns)
     // workspace
     unsigned int* ctrl;                 // control words (see Ctrl* below)
     unsigned long long* argkey;         // [2][kMaxB]
@@ -108,6 +114,7 @@ struct DecodeParams {
     PhaseDesc ph[kNumPhaseTypes];
 };
 
+constexpr int kProfSlots = 24;
 enum CtrlWord { kCtrlEpoch = 0, kCtrlStatus = 1, kCtrlDone = 2, kCtrlWords = 16 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -127,6 +134,16 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// non-blocking probe (try_wait may suspend the warp for a while; the producer must never sleep)
+__device__ __forceinline__ bool mbar_probe(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
@@ -153,6 +170,11 @@ __device__ __forceinline__ void st_flagged(unsigned long long* p, uint32_t paylo
     const unsigned long long v = ((unsigned long long)tag << 32) | payload;
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kCT) : "memory"); }
 
 // ------------------------------------------------------------------ shared state
@@ -161,10 +183,13 @@ struct Shared {
     uint64_t empty[kNW][kE];
     uint32_t ent_off[kNW][kE];
     uint32_t ent_foot[kNW][kE];
+    uint2 ent_table[kNW][kMaxLayerEntries + kMaxLmEntries];   // per-warp ring schedule: one layer, then lm_head
+    int ent_count[kNW][2];
     int row_a[kNumPhaseTypes][kNW];
     int row_b[kNumPhaseTypes][kNW];
     float red[kMaxB][kNW];
     int seq[kMaxB], pos[kMaxB], nc[kMaxB], lc[kMaxB];
+    int ncmax, two_level;
     long long slot[kMaxB];
     long long tok[kMaxB];
     volatile int abort_flag;
@@ -176,9 +201,11 @@ struct Ctx {
     Shared& sh;
     uint4* act;        // [B][act_elems/8] bf16 activations of the current phase
     float* res;        // [B][H] residual stream copy (x or h1) for the epilogues
+    float* attn;       // attention scratch: per-warp partials / staged chunk partials (kAttnScratchWords)
     unsigned char* ring;  // this warp's ring (consumer) / ring of warp `lane` (producer)
     uint32_t tag_base;
     int warp, lane, cta, ncta;
+    unsigned long long* prof;   // non-null only in thread 0 while profiling: stamps of the current layer
 };
 
 __device__ __forceinline__ void raise_abort(Ctx& c, int code) {
@@ -208,32 +235,50 @@ __device__ __forceinline__ uint32_t wait_flagged(Ctx& c, const unsigned long lon
     }
 }
 
-// N consecutive flagged words: all loads are issued before any is checked, so the common case
-// (data already there) costs one L2 round trip instead of N.
-template <int N>
-__device__ __forceinline__ void wait_flagged_vec(Ctx& c, const unsigned long long* p, uint32_t tag, uint32_t (&out)[N]) {
-    unsigned long long v[N];
+// Wait for up to N flagged words at once.  Every round re-issues the loads of all words that are still
+// missing before checking any of them, so a round costs one L2 round trip no matter how many words
+// are outstanding (re-polling them one after the other would cost one round trip each).
+// ptr(u) returns the address of word u, or nullptr when slot u is unused.
+template <int N, typename PtrFn>
+__device__ __forceinline__ void wait_flagged_multi(Ctx& c, PtrFn ptr, uint32_t tag, uint32_t (&out)[N]) {
+    unsigned need = 0;
 #pragma unroll
-    for (int i = 0; i < N; ++i) v[i] = ld_flagged(p + i);
+    for (int u = 0; u < N; ++u) {
+        out[u] = 0;
+        if (ptr(u) != nullptr) need |= 1u << u;
+    }
+    if (aborted(c)) return;
+    unsigned spins = 0;
+    while (need) {
+        unsigned long long v[N];
 #pragma unroll
-    for (int i = 0; i < N; ++i) out[i] = ((uint32_t)(v[i] >> 32) == tag) ? (uint32_t)v[i] : wait_flagged(c, p + i, tag);
+        for (int u = 0; u < N; ++u)
+            if (need & (1u << u)) v[u] = ld_flagged(ptr(u));
+#pragma unroll
+        for (int u = 0; u < N; ++u)
+            if ((need & (1u << u)) && (uint32_t)(v[u] >> 32) == tag) {
+                out[u] = (uint32_t)v[u];
+                need &= ~(1u << u);
+            }
+        if (need && (++spins & 255u) == 0) {
+            if (aborted(c)) return;
+            if (*((volatile unsigned int*)(c.p.ctrl + kCtrlStatus)) != 0) {
+                c.sh.abort_flag = 1;
+                return;
+            }
+            if (spins >= kSpinLimit) {
+                raise_abort(c, kErrBarrierTimeout);
+                return;
+            }
+        }
+    }
 }
 
-// Up to 4 words at indices first, first+stride, ... (< n), loads issued together.
+// Up to 4 words at indices first, first+stride, ... (< n).
 __device__ __forceinline__ void wait_flagged_strided4(Ctx& c, const unsigned long long* base, int first, int stride,
                                                       int n, uint32_t tag, uint32_t (&out)[4]) {
-    unsigned long long v[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-        const int idx = first + u * stride;
-        v[u] = idx < n ? ld_flagged(base + idx) : 0ull;
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-        const int idx = first + u * stride;
-        out[u] = 0;
-        if (idx < n) out[u] = ((uint32_t)(v[u] >> 32) == tag) ? (uint32_t)v[u] : wait_flagged(c, base + idx, tag);
-    }
+    wait_flagged_multi<4>(
+        c, [&](int u) { const int idx = first + u * stride; return idx < n ? base + idx : nullptr; }, tag, out);
 }
 
 __device__ __forceinline__ bool wait_mbar(Ctx& c, uint64_t* bar, uint32_t parity) {
@@ -262,73 +307,35 @@ __device__ __forceinline__ void warp_rows(int nrows, int cta, int ncta, int warp
     b = r0 + n * (warp + 1) / kNW;
 }
 
-// One ring entry of the schedule.
-struct Entry {
-    const unsigned char* src;   // first (or only) part
-    const unsigned char* src2;  // second part for gate/up pairs, else nullptr
-    uint32_t part_bytes;        // bytes per part
-};
-
-// Cursor over the ring entries of one consumer warp, in schedule order.
-struct Cursor {
-    int gp;       // global phase: layer * 4 + type, or L * 4 for the lm_head
-    int row;      // current row (pair) index
-    int seg;
-    int end_gp;
-    __device__ __forceinline__ int type(const DecodeParams& p) const { return gp < p.L * 4 ? (gp & 3) : (int)kLM; }
-    __device__ __forceinline__ bool valid() const { return gp < end_gp; }
-    __device__ void seek(const DecodeParams& p, const Shared& sh, int w) {
-        // skip phases in which this warp owns no rows
-        while (gp < end_gp) {
-            const int t = type(p);
-            if (sh.row_a[t][w] < sh.row_b[t][w]) {
-                row = sh.row_a[t][w];
-                seg = 0;
-                return;
-            }
-            ++gp;
-        }
+// Ring entries of phase type t for a warp that owns rows [a, b): count, and the e-th entry in closed
+// form (no sequential state), so the per-warp entry tables can be filled by all lanes in parallel.
+// Descriptor: x = byte offset inside the weight matrix; y = part bytes | (widx + 1) << 16 | pair << 20.
+__device__ __forceinline__ int phase_entries(const PhaseDesc& d, int a, int b) {
+    const int n = b - a;
+    if (n <= 0) return 0;
+    return d.nseg == 1 ? (n + d.rows_per_entry - 1) / d.rows_per_entry : n * d.nseg;
+}
+__device__ __forceinline__ uint2 phase_entry(const PhaseDesc& d, int a, int b, int e) {
+    uint32_t off, bytes;
+    if (d.nseg == 1) {
+        const int row = a + e * d.rows_per_entry;
+        const int nre = min(d.rows_per_entry, b - row);
+        bytes = (uint32_t)nre * (uint32_t)d.rowbytes;
+        off = (uint32_t)row * (uint32_t)d.rowbytes;
+    } else {
+        const int row = a + e / d.nseg, seg = e % d.nseg;
+        const int sc = min(d.segchunks, d.kchunks - seg * d.segchunks);
+        bytes = (uint32_t)sc * 16u;
+        off = (uint32_t)row * (uint32_t)d.rowbytes + (uint32_t)seg * (uint32_t)d.segchunks * 16u;
     }
-    __device__ void init(const DecodeParams& p, const Shared& sh, int w) {
-        gp = 0;
-        end_gp = p.L * 4 + (p.lm_head ? 1 : 0);
-        seek(p, sh, w);
-    }
-    __device__ void advance(const DecodeParams& p, const Shared& sh, int w) {
-        const int t = type(p);
-        const PhaseDesc& d = p.ph[t];
-        if (++seg < d.nseg) return;
-        seg = 0;
-        row += d.rows_per_entry;
-        if (row < sh.row_b[t][w]) return;
-        ++gp;
-        seek(p, sh, w);
-    }
-    __device__ Entry entry(const DecodeParams& p, const Shared& sh, int w) const {
-        const int t = type(p);
-        const PhaseDesc& d = p.ph[t];
-        const unsigned char* base =
-            d.widx < 0 ? reinterpret_cast<const unsigned char*>(p.embed)
-                       : reinterpret_cast<const unsigned char*>(p.layers[(gp >> 2) * 6 + d.widx]);
-        Entry e;
-        if (d.nseg == 1) {
-            const int nre = min(d.rows_per_entry, sh.row_b[t][w] - row);
-            e.part_bytes = (uint32_t)nre * (uint32_t)d.rowbytes;
-            e.src = base + (size_t)row * d.rowbytes;
-        } else {
-            const int sc = min(d.segchunks, d.kchunks - seg * d.segchunks);
-            e.part_bytes = (uint32_t)sc * 16u;
-            e.src = base + (size_t)row * d.rowbytes + (size_t)seg * d.segchunks * 16;
-        }
-        e.src2 = d.pair ? e.src + d.pair_off : nullptr;
-        return e;
-    }
-};
+    return make_uint2(off, bytes | ((uint32_t)(d.widx + 1) << 16) | ((uint32_t)d.pair << 20));
+}
 
 // ------------------------------------------------------------------ producer warp
-// Lane w (< kNW) feeds the ring of consumer warp w.  All lanes run the same loop in lock step;
-// every iteration a lane either issues its next entry (if the ring has room) or polls the oldest
-// outstanding entry for release.  Nothing here blocks, so one slow ring never stalls the others.
+// Lane w (< kNW) feeds the ring of consumer warp w from that warp's entry table (one list per layer,
+// reused for every layer, plus the lm_head list).  All lanes run the same loop in lock step; every
+// iteration a lane retires up to two consumed entries (non-blocking probes) and issues up to two new
+// ones if the ring has room.  Nothing here blocks, so one slow ring never stalls the others.
 __device__ void producer_loop(Ctx& c, unsigned char* ring_base) {
     const DecodeParams& p = c.p;
     Shared& sh = c.sh;
@@ -337,43 +344,63 @@ __device__ void producer_loop(Ctx& c, unsigned char* ring_base) {
     const uint32_t RW = (uint32_t)p.ring_bytes;
     unsigned char* ring = ring_base + (size_t)(active ? w : 0) * RW;
     const uint64_t pol = evict_first_policy();
-    Cursor cur;
-    cur.gp = cur.end_gp = 0;
-    cur.row = cur.seg = 0;
-    if (active) cur.init(p, sh, w);
+    const int n_layer = active ? sh.ent_count[w][0] : 0;
+    const int n_lm = (active && p.lm_head) ? sh.ent_count[w][1] : 0;
+    const uint32_t total = (uint32_t)n_layer * (uint32_t)p.L + (uint32_t)n_lm;
+    const uint2* table = sh.ent_table[active ? w : 0];
+    const long long pair_off = p.ph[kGU].pair_off;
+    int li = 0, layer = 0;             // position in the schedule: entry li of `layer` (layer == L: lm_head list)
+    if (n_layer == 0) layer = p.L;
     uint32_t issued = 0, tail = 0, head = 0, used = 0;
     unsigned idle = 0;
     for (;;) {
-        const bool done = !active || !cur.valid();
         bool progressed = false;
-        if (!done) {
-            const Entry e = cur.entry(p, sh, w);
-            const uint32_t bytes = e.src2 ? 2 * e.part_bytes : e.part_bytes;
-            const uint32_t gap = (head + bytes > RW) ? RW - head : 0;
-            const uint32_t foot = bytes + gap;
-            if (issued - tail < (uint32_t)kE && used + foot <= RW) {
-                const uint32_t off = gap ? 0 : head;
-                const uint32_t slot = issued % kE;
-                sh.ent_off[w][slot] = off;
-                sh.ent_foot[w][slot] = foot;
-                mbar_expect_tx(&sh.full[w][slot], bytes);
-                bulk_g2s(ring + off, e.src, e.part_bytes, &sh.full[w][slot], pol);
-                if (e.src2) bulk_g2s(ring + off + e.part_bytes, e.src2, e.part_bytes, &sh.full[w][slot], pol);
-                head = off + bytes;
-                if (head >= RW) head = 0;
-                used += foot;
-                ++issued;
-                cur.advance(p, sh, w);
-                progressed = true;
-            } else {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            if (tail < issued) {
                 const uint32_t slot = tail % kE;
-                if (mbar_test(&sh.empty[w][slot], (tail / kE) & 1)) {
+                if (mbar_probe(&sh.empty[w][slot], (tail / kE) & 1)) {
                     used -= sh.ent_foot[w][slot];
                     ++tail;
                     progressed = true;
                 }
             }
         }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            if (issued < total) {
+                const uint2 dsc = table[layer < p.L ? li : kMaxLayerEntries + li];
+                const uint32_t part = dsc.y & 0xffffu;
+                const int widx = (int)((dsc.y >> 16) & 0xfu) - 1;
+                const bool pair = (dsc.y >> 20) & 1u;
+                const uint32_t bytes = pair ? 2 * part : part;
+                const uint32_t gap = (head + bytes > RW) ? RW - head : 0;
+                const uint32_t foot = bytes + gap;
+                if (issued - tail < (uint32_t)kE && used + foot <= RW) {
+                    const unsigned char* base =
+                        widx < 0 ? reinterpret_cast<const unsigned char*>(p.embed)
+                                 : reinterpret_cast<const unsigned char*>(__ldg(p.layers + layer * 6 + widx));
+                    const unsigned char* src = base + dsc.x;
+                    const uint32_t off = gap ? 0 : head;
+                    const uint32_t slot = issued % kE;
+                    sh.ent_off[w][slot] = off;
+                    sh.ent_foot[w][slot] = foot;
+                    mbar_expect_tx(&sh.full[w][slot], bytes);
+                    bulk_g2s(ring + off, src, part, &sh.full[w][slot], pol);
+                    if (pair) bulk_g2s(ring + off + part, src + pair_off, part, &sh.full[w][slot], pol);
+                    head = off + bytes;
+                    if (head >= RW) head = 0;
+                    used += foot;
+                    ++issued;
+                    if (++li == (layer < p.L ? n_layer : n_lm)) {
+                        li = 0;
+                        ++layer;
+                    }
+                    progressed = true;
+                }
+            }
+        }
+        const bool done = issued >= total;      // everything issued; outstanding copies are drained below
         if (__all_sync(kFullMask, done)) break;
         idle = (progressed || done) ? 0 : idle + 1;
         if ((idle & 255u) == 255u) {
@@ -386,7 +413,7 @@ __device__ void producer_loop(Ctx& c, unsigned char* ring_base) {
         for (uint32_t n = tail; n < issued; ++n) {
             const uint32_t slot = n % kE;
             unsigned spins = 0;
-            while (!mbar_test(&sh.full[w][slot], (n / kE) & 1)) {
+            while (!mbar_probe(&sh.full[w][slot], (n / kE) & 1)) {
                 if (++spins >= kSpinLimit) break;
             }
         }
@@ -448,6 +475,71 @@ __device__ __forceinline__ float dot16_e4m3(const uint4 w, const uint4 a0, const
 
 __device__ __forceinline__ uint32_t layer_tag(const Ctx& c, int layer) { return c.tag_base + (uint32_t)layer + 1u; }
 
+// ------------------------------------------------------------------ GEMV row kernels
+// NR staged rows (row r at ep + r * stride chunks) times B activation vectors, K-split over the lanes.
+// A lone warp cannot hide instruction latency behind other warps, so the loops are unrolled four
+// lane-chunks deep: every shared-memory load of a 128-chunk span is issued first, then the FMAs run
+// as independent chains (two accumulators per row and request).
+template <int B, int NR>
+__device__ __forceinline__ void gemv_rows_bf16(const uint4* ep, int sc, const uint4* act, int actc, int kc0, int lane,
+                                               float (&acc)[kRMax][B], float (&acc2)[kRMax][B]) {
+    constexpr int U = (NR * B <= 2) ? 4 : 2;     // lane-chunks in flight; bounded by the register budget
+    for (int it0 = 0; it0 < sc; it0 += 32 * U) {
+        uint4 av[U][B], wv[NR][U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int ch = it0 + 32 * u + lane;
+            const bool ok = ch < sc;
+#pragma unroll
+            for (int b = 0; b < B; ++b) av[u][b] = ok ? act[b * actc + kc0 + ch] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int r = 0; r < NR; ++r) wv[r][u] = ok ? ep[r * sc + ch] : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+#pragma unroll
+                for (int b = 0; b < B; ++b) {
+                    if (u & 1) acc2[r][b] = dot8_bf16(wv[r][u], av[u][b], acc2[r][b]);
+                    else acc[r][b] = dot8_bf16(wv[r][u], av[u][b], acc[r][b]);
+                }
+    }
+}
+
+// MXFP8 packed rows: [K e4m3][K/32 e8m0][pad to 16 B]; one lane-chunk = 16 values, scale per 32.
+template <int B, int NR>
+__device__ __forceinline__ void gemv_rows_mxfp8(const uint4* ep, int rc, int kact, const uint4* act, int actc, int lane,
+                                                float (&acc)[kRMax][B], float (&acc2)[kRMax][B]) {
+    const int vc = kact >> 4;
+    for (int it0 = 0; it0 < vc; it0 += 64) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int ch = it0 + 32 * u + lane;
+            if (ch < vc) {
+                uint4 a0[B], a1[B];
+#pragma unroll
+                for (int b = 0; b < B; ++b) {
+                    a0[b] = act[b * actc + 2 * ch];
+                    a1[b] = act[b * actc + 2 * ch + 1];
+                }
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    const uint4 wq = ep[r * rc + ch];
+                    const unsigned char sb = reinterpret_cast<const unsigned char*>(ep + r * rc)[kact + (ch >> 1)];
+                    const float scale = __uint_as_float(sb ? ((uint32_t)sb << 23) : 0x00400000u);
+#pragma unroll
+                    for (int b = 0; b < B; ++b) {
+                        const float part = dot16_e4m3(wq, a0[b], a1[b], 0.f);
+                        if (u & 1) acc2[r][b] = fmaf(scale, part, acc2[r][b]);
+                        else acc[r][b] = fmaf(scale, part, acc[r][b]);
+                    }
+                }
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ GEMV phase (consumer warps)
 // Consumes this warp's ring entries of phase type T at `layer`, multiplying the staged rows with
 // the bf16 activations in c.act, and hands each finished row to the phase epilogue.
@@ -461,67 +553,49 @@ __device__ void gemv_phase(Ctx& c, int layer, uint32_t& consumed) {
     const int actc = p.act_elems >> 3;                 // uint4 per request in c.act
     const uint32_t tag = layer_tag(c, layer);
     const int par = layer & 1;
+    constexpr bool kPair = (T == kGU);
     for (int row = ra; row < rb; row += d.rows_per_entry) {
         const int nre = min(d.rows_per_entry, rb - row);
-        const int nmem = d.pair ? 2 * nre : nre;       // rows staged in the entry
-        float acc[kRMax][B];
+        float acc[kRMax][B], acc2[kRMax][B];
 #pragma unroll
         for (int i = 0; i < kRMax; ++i)
 #pragma unroll
-            for (int b = 0; b < B; ++b) acc[i][b] = 0.f;
+            for (int b = 0; b < B; ++b) acc[i][b] = acc2[i][b] = 0.f;
         for (int seg = 0; seg < d.nseg; ++seg) {
             const uint32_t slot = consumed % kE;
             if (!wait_mbar(c, &sh.full[w][slot], (consumed / kE) & 1)) return;
+            if (T == kGU && c.prof) c.prof[16] = global_ns();
             const uint4* ep = reinterpret_cast<const uint4*>(c.ring + sh.ent_off[w][slot]);
+            // accumulator r <- staged row r; a gate/up entry stages nre gate rows, then nre up rows
+            const int nmem = kPair ? 2 * nre : nre;
             if (p.wfmt == 0) {
                 const int sc = d.nseg == 1 ? d.kchunks : min(d.segchunks, d.kchunks - seg * d.segchunks);
                 const int kc0 = seg * d.segchunks;
-                for (int it = lane; it < sc; it += 32) {
-                    uint4 a[B];
-#pragma unroll
-                    for (int b = 0; b < B; ++b) a[b] = c.act[b * actc + kc0 + it];
-#pragma unroll
-                    for (int i = 0; i < kRMax; ++i) {
-                        if (i < nmem) {
-                            const uint4 wv = ep[i * sc + it];
-#pragma unroll
-                            for (int b = 0; b < B; ++b) acc[i][b] = dot8_bf16(wv, a[b], acc[i][b]);
-                        }
-                    }
+                switch (nmem) {
+                    case 1: gemv_rows_bf16<B, 1>(ep, sc, c.act, actc, kc0, lane, acc, acc2); break;
+                    case 2: gemv_rows_bf16<B, 2>(ep, sc, c.act, actc, kc0, lane, acc, acc2); break;
+                    case 3: gemv_rows_bf16<B, 3>(ep, sc, c.act, actc, kc0, lane, acc, acc2); break;
+                    default: gemv_rows_bf16<B, 4>(ep, sc, c.act, actc, kc0, lane, acc, acc2); break;
                 }
             } else {
-                // MXFP8 packed row: [K e4m3][K/32 e8m0][pad to 16]; one lane-chunk = 16 values
-                const int vc = d.kact >> 4;              // value chunks per row
-                const int rc = d.kchunks;                // stored chunks per row
-                for (int it = lane; it < vc; it += 32) {
-                    uint4 a0[B], a1[B];
-#pragma unroll
-                    for (int b = 0; b < B; ++b) {
-                        a0[b] = c.act[b * actc + 2 * it];
-                        a1[b] = c.act[b * actc + 2 * it + 1];
-                    }
-#pragma unroll
-                    for (int i = 0; i < kRMax; ++i) {
-                        if (i < nmem) {
-                            const uint4 wv = ep[i * rc + it];
-                            const unsigned char sb =
-                                reinterpret_cast<const unsigned char*>(ep + i * rc)[d.kact + (it >> 1)];
-                            const float scale = __uint_as_float(sb ? ((uint32_t)sb << 23) : 0x00400000u);
-#pragma unroll
-                            for (int b = 0; b < B; ++b) acc[i][b] = fmaf(scale, dot16_e4m3(wv, a0[b], a1[b], 0.f), acc[i][b]);
-                        }
-                    }
+                switch (nmem) {
+                    case 1: gemv_rows_mxfp8<B, 1>(ep, d.kchunks, d.kact, c.act, actc, lane, acc, acc2); break;
+                    case 2: gemv_rows_mxfp8<B, 2>(ep, d.kchunks, d.kact, c.act, actc, lane, acc, acc2); break;
+                    case 3: gemv_rows_mxfp8<B, 3>(ep, d.kchunks, d.kact, c.act, actc, lane, acc, acc2); break;
+                    default: gemv_rows_mxfp8<B, 4>(ep, d.kchunks, d.kact, c.act, actc, lane, acc, acc2); break;
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh.empty[w][slot]);
             ++consumed;
+            if (T == kGU && c.prof) c.prof[17] = global_ns();
         }
         // warp-reduce every accumulator, then lane i finishes row i
 #pragma unroll
         for (int i = 0; i < kRMax; ++i)
 #pragma unroll
-            for (int b = 0; b < B; ++b) acc[i][b] = warp_sum(acc[i][b]);
+            for (int b = 0; b < B; ++b) acc[i][b] = warp_sum(acc[i][b] + acc2[i][b]);
+        if (T == kGU && c.prof) c.prof[18] = global_ns();
 #pragma unroll
         for (int i = 0; i < kRMax; ++i) {
             if (i < nre && lane == i) {
@@ -540,7 +614,9 @@ __device__ void gemv_phase(Ctx& c, int layer, uint32_t& consumed) {
                     } else if (T == kGU) {
                         // act = bf16( bf16(silu(bf16 gate)) * bf16 up )   (HF LlamaMLP rounding)
                         const float g = round_bf16(acc[i][b]);
-                        const float u = round_bf16(acc[i + nre][b]);
+                        // up row of pair i sits right after the nre gate rows: static selects, no dynamic register index
+                        const float upv = nre == 1 ? acc[1][b] : acc[(i + 2) & (kRMax - 1)][b];
+                        const float u = round_bf16(upv);
                         const float silu = round_bf16(g / (1.f + expf(-g)));
                         const float a = round_bf16(__fmul_rn(silu, u));
                         st_flagged(p.ll_act + (size_t)par * B * p.I + b * p.I + r, f32_to_bf16_bits(a), tag);
@@ -579,6 +655,13 @@ __device__ void stage_norm(Ctx& c, const unsigned long long* src_words, uint32_t
     Shared& sh = c.sh;
     const int ct = threadIdx.x;
     const int H = p.H;
+    // the norm weight does not depend on the activations: fetch it before waiting for them
+    float wreg[kNormRegs];
+#pragma unroll
+    for (int u = 0; u < kNormRegs; ++u) {
+        const int i = ct + u * kCT;
+        wreg[u] = i < H ? __uint_as_float((uint32_t)__ldg(weight + i) << 16) : 0.f;
+    }
     consumer_bar();   // everyone is done with the previous phase's act/res
     float ss[B];
 #pragma unroll
@@ -616,10 +699,13 @@ __device__ void stage_norm(Ctx& c, const unsigned long long* src_words, uint32_t
 #pragma unroll
         for (int w = 0; w < kNW; ++w) tot += sh.red[b][w];
         const float s = rsqrtf(tot * (1.f / (float)H) + p.eps);
-        for (int i = ct; i < H; i += kCT) {
-            const float wv = __uint_as_float((uint32_t)weight[i] << 16);
-            const float n = round_bf16(__fmul_rn(c.res[b * H + i], s));
-            act16[(size_t)b * p.act_elems + i] = (uint16_t)f32_to_bf16_bits(__fmul_rn(n, wv));
+#pragma unroll
+        for (int u = 0; u < kNormRegs; ++u) {
+            const int i = ct + u * kCT;
+            if (i < H) {
+                const float n = round_bf16(__fmul_rn(c.res[b * H + i], s));
+                act16[(size_t)b * p.act_elems + i] = (uint16_t)f32_to_bf16_bits(__fmul_rn(n, wreg[u]));
+            }
         }
     }
     consumer_bar();
@@ -664,11 +750,21 @@ __device__ __forceinline__ float rope_elem(float x, float partner, float cs, flo
     return round_bf16(__fadd_rn(xc, first_half ? -ys : ys));
 }
 
-// One warp = one (request b, kv head, chunk) item over cache positions [start, end).
-// Lane j = lane & 7 owns dims 8j..8j+7; lane group g = lane >> 3 takes positions start+g, +4, ...
-// so one 128-byte K (or V) row is one coalesced 8-lane 16-byte load.  fp32 online softmax per
-// lane group, groups combined at the end; partial (m, l, acc[64]) per query head of the GQA group
-// goes out as flagged words.
+__device__ __forceinline__ void unpack8(const uint4 v, float (&f)[8]) {
+    f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x);
+    f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+    f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z);
+    f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+
+// One CTA = one (request b, kv head, chunk) item over cache positions [start, end).  The 16 consumer
+// warps split the chunk; inside a warp lane j = lane & 7 owns dims 8j..8j+7 and lane group
+// g = lane >> 3 takes positions ws+g, ws+g+4, ... so one 128-byte K (or V) row is one coalesced
+// 8-lane 16-byte load.  fp32 online softmax per lane group; lane groups, then warps (through shared
+// memory), are combined with log-sum-exp, and one partial (m, l, acc[64]) per query head of the GQA
+// group leaves the CTA as flagged words.  Every global load this needs is issued before the first
+// dependent use: K/V of the first positions and cos/sin do not depend on q, and the q/k/v words of
+// the new token are fetched in one batch.
 template <int G>
 __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
     const DecodeParams& p = c.p;
@@ -681,77 +777,107 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
     const int seq = sh.seq[b], pos = sh.pos[b];
     const int start = chunk * sh.lc[b];
     const int end = min(start + sh.lc[b], seq);
-    const bool has_new = (seq - 1 >= start) && (seq - 1 < end);
+    // this warp's share of the chunk, a multiple of 4 positions
+    const int ppw = (((end - start + kNW - 1) / kNW) + 3) & ~3;
+    const int ws = min(start + c.warp * ppw, end);
+    const int we = min(ws + ppw, end);
+    const bool has_new = (seq - 1 >= ws) && (seq - 1 < we);
+    const uint16_t* kvr = reinterpret_cast<const uint16_t*>(p.kv[layer]);
+    const int niter = (we - ws + 3) >> 2;   // positions per lane group, uniform over the warp
 
-    // cos/sin of this position for dims (8j+i) & 31
-    float cs[8], sn[8];
-    {
-        const int base = pos * kD + 8 * (j & 3);
-        if (p.cs_fp32) {
-            const float* t = reinterpret_cast<const float*>(p.cos_sin);
+    // K/V fetch of kPB positions per lane group; st: 0 = out of range, 1 = from the cache,
+    // 2 = the new token (taken from registers).
+    constexpr int kPB = 4;
+    auto fetch = [&](int it, uint4* kk, uint4* vv, int* st) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                cs[i] = t[base + i];
-                sn[i] = t[base + 32 + i];
-            }
-        } else {
-            const uint16_t* t = reinterpret_cast<const uint16_t*>(p.cos_sin);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                cs[i] = __uint_as_float((uint32_t)t[base + i] << 16);
-                sn[i] = __uint_as_float((uint32_t)t[base + 32 + i] << 16);
+        for (int u = 0; u < kPB; ++u) {
+            const int pp = ws + g + 4 * (it + u);
+            st[u] = 0;
+            kk[u] = vv[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (it + u < niter && pp < we) {
+                if (pp == seq - 1) {
+                    st[u] = 2;
+                } else {
+                    st[u] = 1;
+                    const int blk = __ldg(p.block_table + b * p.bt_stride + pp / p.block_size);
+                    const long long e = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride +
+                                        (long long)kvh * p.head_stride + 8 * j;
+                    kk[u] = __ldcg(reinterpret_cast<const uint4*>(kvr + p.k_off + e));
+                    vv[u] = __ldcg(reinterpret_cast<const uint4*>(kvr + p.v_off + e));
+                }
             }
         }
+    };
+    if (c.prof) c.prof[10] = global_ns();
+    uint4 kc[kPB], vc[kPB];
+    int stc[kPB];
+    fetch(0, kc, vc, stc);
+
+    // q of the G heads sharing this kv head plus the new token's k and v: (G + 2) * 64 flagged words,
+    // one per thread, rotated (q, k) through shared memory and then read back by every lane
+    // the staging arrays are read with 16-byte loads: keep them on a 4-float boundary
+    constexpr int kPartWords = (kNW * G * 66 + 3) & ~3;
+    static_assert(kPartWords + 2 * (G + 2) * kD <= kAttnScratchWords, "attention scratch too small");
+    float* raw_s = c.attn + kPartWords;
+    float* rot_s = raw_s + (G + 2) * kD;
+    for (int t = threadIdx.x; t < (G + 2) * kD; t += kCT) {
+        const int which = t / kD, d = t % kD;     // which: 0..G-1 = q head, G = k, G+1 = v
+        const int row = which < G ? (kvh * G + which) * kD + d
+                                  : (which == G ? (p.QH + kvh) * kD + d : (p.QH + p.KVH + kvh) * kD + d);
+        raw_s[t] = __uint_as_float(wait_flagged(c, qkv + row, tag) << 16);
     }
-    // rotated queries of the G heads sharing this kv head
+    consumer_bar();
+    if (c.prof) c.prof[11] = global_ns();
+    for (int t = threadIdx.x; t < (G + 2) * kD; t += kCT) {
+        const int which = t / kD, d = t % kD;
+        float out = raw_s[t];
+        if (which <= G) {
+            float cv, sv;
+            const int ci = pos * kD + (d & 31);
+            if (p.cs_fp32) {
+                cv = __ldg(reinterpret_cast<const float*>(p.cos_sin) + ci);
+                sv = __ldg(reinterpret_cast<const float*>(p.cos_sin) + ci + 32);
+            } else {
+                cv = __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(p.cos_sin) + ci) << 16);
+                sv = __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(p.cos_sin) + ci + 32) << 16);
+            }
+            out = rope_elem(out, raw_s[t ^ 32], cv, sv, d < 32);
+        }
+        rot_s[t] = out;
+    }
+    consumer_bar();
+    if (c.prof) c.prof[12] = global_ns();
     float q[G][8];
 #pragma unroll
     for (int hh = 0; hh < G; ++hh) {
-        const int hq = kvh * G + hh;
-        uint32_t rawb[8];
-        wait_flagged_vec<8>(c, qkv + hq * kD + 8 * j, tag, rawb);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float x = __uint_as_float(rawb[i] << 16);
-            const float partner = __shfl_xor_sync(kFullMask, x, 4);
-            q[hh][i] = rope_elem(x, partner, cs[i], sn[i], j < 4);
-        }
+        const float4 lo = *reinterpret_cast<const float4*>(rot_s + hh * kD + 8 * j);
+        const float4 hi = *reinterpret_cast<const float4*>(rot_s + hh * kD + 8 * j + 4);
+        q[hh][0] = lo.x; q[hh][1] = lo.y; q[hh][2] = lo.z; q[hh][3] = lo.w;
+        q[hh][4] = hi.x; q[hh][5] = hi.y; q[hh][6] = hi.z; q[hh][7] = hi.w;
     }
-    // the new token's K (rotated) and V; appended to the paged cache by the item that owns seq-1
     float kn[8], vn[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) kn[i] = vn[i] = 0.f;
-    if (has_new) {
-        uint32_t rawk[8], rawv[8];
-        wait_flagged_vec<8>(c, qkv + (p.QH + kvh) * kD + 8 * j, tag, rawk);
-        wait_flagged_vec<8>(c, qkv + (p.QH + p.KVH + kvh) * kD + 8 * j, tag, rawv);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float x = __uint_as_float(rawk[i] << 16);
-            const float partner = __shfl_xor_sync(kFullMask, x, 4);
-            kn[i] = rope_elem(x, partner, cs[i], sn[i], j < 4);
-            vn[i] = __uint_as_float(rawv[i] << 16);
-        }
+    for (int i = 0; i < 8; ++i) {
+        kn[i] = rot_s[G * kD + 8 * j + i];
+        vn[i] = rot_s[(G + 1) * kD + 8 * j + i];
+    }
+    if (has_new) {   // warp-uniform
+        // append the new token's K/V to the paged cache (slot -1 = padded row: skip)
         const long long slot = sh.slot[b];
         if (slot >= 0 && g == 0) {
             uint16_t* kvw = reinterpret_cast<uint16_t*>(p.kv[layer]);
             const long long blk = slot / p.block_size, off = slot % p.block_size;
             const long long e = blk * p.block_stride + off * p.token_stride + (long long)kvh * p.head_stride + 8 * j;
-            uint4 kw, vw;
-            kw.x = pack_bf16x2(kn[0], kn[1]);
-            kw.y = pack_bf16x2(kn[2], kn[3]);
-            kw.z = pack_bf16x2(kn[4], kn[5]);
-            kw.w = pack_bf16x2(kn[6], kn[7]);
-            vw.x = pack_bf16x2(vn[0], vn[1]);
-            vw.y = pack_bf16x2(vn[2], vn[3]);
-            vw.z = pack_bf16x2(vn[4], vn[5]);
-            vw.w = pack_bf16x2(vn[6], vn[7]);
-            *reinterpret_cast<uint4*>(kvw + p.k_off + e) = kw;
-            *reinterpret_cast<uint4*>(kvw + p.v_off + e) = vw;
+            uint4 ko, vo;
+            ko.x = pack_bf16x2(kn[0], kn[1]); ko.y = pack_bf16x2(kn[2], kn[3]);
+            ko.z = pack_bf16x2(kn[4], kn[5]); ko.w = pack_bf16x2(kn[6], kn[7]);
+            vo.x = pack_bf16x2(vn[0], vn[1]); vo.y = pack_bf16x2(vn[2], vn[3]);
+            vo.z = pack_bf16x2(vn[4], vn[5]); vo.w = pack_bf16x2(vn[6], vn[7]);
+            *reinterpret_cast<uint4*>(kvw + p.k_off + e) = ko;
+            *reinterpret_cast<uint4*>(kvw + p.v_off + e) = vo;
         }
     }
 
-    const uint16_t* kvr = reinterpret_cast<const uint16_t*>(p.kv[layer]);
     float m[G], l[G], acc[G][8];
 #pragma unroll
     for (int hh = 0; hh < G; ++hh) {
@@ -760,40 +886,24 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[hh][i] = 0.f;
     }
-    const int niter = (end - start + 3) >> 2;   // positions per lane group, uniform over the warp
-    for (int it0 = 0; it0 < niter; it0 += 4) {
-        uint4 kk[4], vv[4];
-        int st[4];   // 0 = out of range, 1 = from cache, 2 = the new token (registers)
+    for (int it0 = 0; it0 < niter; it0 += kPB) {
+        uint4 kn2[kPB], vn2[kPB];
+        int stn[kPB];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int pp = start + g + 4 * (it0 + u);
-            st[u] = 0;
-            kk[u] = vv[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (it0 + u < niter && pp < end) {
-                if (pp == seq - 1) {
-                    st[u] = 2;
-                } else {
-                    st[u] = 1;
-                    const int blk = p.block_table[b * p.bt_stride + pp / p.block_size];
-                    const long long e = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride +
-                                        (long long)kvh * p.head_stride + 8 * j;
-                    kk[u] = __ldcg(reinterpret_cast<const uint4*>(kvr + p.k_off + e));
-                    vv[u] = __ldcg(reinterpret_cast<const uint4*>(kvr + p.v_off + e));
-                }
-            }
+        for (int u = 0; u < kPB; ++u) {
+            stn[u] = 0;
+            kn2[u] = vn2[u] = make_uint4(0u, 0u, 0u, 0u);
         }
-        float sc[4][G];
+        if (it0 + kPB < niter) fetch(it0 + kPB, kn2, vn2, stn);      // next batch in flight during the math
+        float sc[kPB][G];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kPB; ++u) {
             float kf[8];
-            if (st[u] == 2) {
+            if (stc[u] == 2) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) kf[i] = kn[i];
             } else {
-                kf[0] = bf16_lo(kk[u].x); kf[1] = bf16_hi(kk[u].x);
-                kf[2] = bf16_lo(kk[u].y); kf[3] = bf16_hi(kk[u].y);
-                kf[4] = bf16_lo(kk[u].z); kf[5] = bf16_hi(kk[u].z);
-                kf[6] = bf16_lo(kk[u].w); kf[7] = bf16_hi(kk[u].w);
+                unpack8(kc[u], kf);
             }
 #pragma unroll
             for (int hh = 0; hh < G; ++hh) {
@@ -804,20 +914,20 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
                 dsum += __shfl_xor_sync(kFullMask, dsum, 2);
                 dsum += __shfl_xor_sync(kFullMask, dsum, 1);
                 // bf16 matmul output, then the exact 1/8 scale (HF eager_attention_forward)
-                sc[u][hh] = st[u] ? round_bf16(dsum) * 0.125f : -INFINITY;
+                sc[u][hh] = stc[u] ? round_bf16(dsum) * 0.125f : -INFINITY;
             }
         }
-        float ev[4][G];
+        float ev[kPB][G];
 #pragma unroll
         for (int hh = 0; hh < G; ++hh) {
             float mx = m[hh];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) mx = fmaxf(mx, sc[u][hh]);
-            const float alpha = (mx == -INFINITY) ? 1.f : expf(m[hh] - mx);
+            for (int u = 0; u < kPB; ++u) mx = fmaxf(mx, sc[u][hh]);
+            const float alpha = (mx == -INFINITY) ? 1.f : __expf(m[hh] - mx);
             float es = 0.f;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                ev[u][hh] = (sc[u][hh] == -INFINITY) ? 0.f : expf(sc[u][hh] - mx);
+            for (int u = 0; u < kPB; ++u) {
+                ev[u][hh] = (sc[u][hh] == -INFINITY) ? 0.f : __expf(sc[u][hh] - mx);
                 es += ev[u][hh];
             }
             l[hh] = l[hh] * alpha + es;
@@ -826,31 +936,34 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
             for (int i = 0; i < 8; ++i) acc[hh][i] *= alpha;
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kPB; ++u) {
             float vf[8];
-            if (st[u] == 2) {
+            if (stc[u] == 2) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) vf[i] = vn[i];
             } else {
-                vf[0] = bf16_lo(vv[u].x); vf[1] = bf16_hi(vv[u].x);
-                vf[2] = bf16_lo(vv[u].y); vf[3] = bf16_hi(vv[u].y);
-                vf[4] = bf16_lo(vv[u].z); vf[5] = bf16_hi(vv[u].z);
-                vf[6] = bf16_lo(vv[u].w); vf[7] = bf16_hi(vv[u].w);
+                unpack8(vc[u], vf);
             }
 #pragma unroll
             for (int hh = 0; hh < G; ++hh)
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[hh][i] = fmaf(ev[u][hh], vf[i], acc[hh][i]);
         }
+#pragma unroll
+        for (int u = 0; u < kPB; ++u) {
+            kc[u] = kn2[u];
+            vc[u] = vn2[u];
+            stc[u] = stn[u];
+        }
     }
-    // combine the 4 lane groups, publish the partial of every head of the group
-    const size_t item = ((size_t)(b * p.KVH + kvh) * kNCMax + chunk) * G;
-    unsigned long long* part = p.ll_part + ((size_t)par * p.B * p.KVH * kNCMax * G + item) * 66;
+    if (c.prof) c.prof[13] = global_ns();
+    // combine the 4 lane groups of the warp; lanes 0..7 park the warp's partial in shared memory
+    float* wpart = c.attn + (size_t)c.warp * G * 66;
 #pragma unroll
     for (int hh = 0; hh < G; ++hh) {
         float mm = fmaxf(m[hh], __shfl_xor_sync(kFullMask, m[hh], 8));
         mm = fmaxf(mm, __shfl_xor_sync(kFullMask, mm, 16));
-        const float f = (m[hh] == -INFINITY) ? 0.f : expf(m[hh] - mm);
+        const float f = (m[hh] == -INFINITY) ? 0.f : __expf(m[hh] - mm);
         float lt = l[hh] * f;
         lt += __shfl_xor_sync(kFullMask, lt, 8);
         lt += __shfl_xor_sync(kFullMask, lt, 16);
@@ -862,19 +975,46 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
             acc[hh][i] = a;
         }
         if (g == 0) {
-            unsigned long long* dst = part + hh * 66;
+            float* dst = wpart + hh * 66;
             if (j == 0) {
-                st_flagged(dst + 0, __float_as_uint(mm), tag);
-                st_flagged(dst + 1, __float_as_uint(lt), tag);
+                dst[0] = mm;
+                dst[1] = lt;
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) st_flagged(dst + 2 + 8 * j + i, __float_as_uint(acc[hh][i]), tag);
+            for (int i = 0; i < 8; ++i) dst[2 + 8 * j + i] = acc[hh][i];
         }
     }
+    consumer_bar();
+    if (c.prof) c.prof[14] = global_ns();
+    // combine the 16 warps; thread (hh, d) publishes one accumulator word, d == 0 also m and l
+    const size_t item = ((size_t)(b * p.KVH + kvh) * kNCMax + chunk) * G;
+    unsigned long long* part = p.ll_part + ((size_t)par * p.B * p.KVH * kNCMax * G + item) * 66;
+    for (int t = threadIdx.x; t < G * kD; t += kCT) {
+        const int hh = t / kD, d = t % kD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kNW; ++w) M = fmaxf(M, c.attn[(w * G + hh) * 66]);
+        float lt = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < kNW; ++w) {
+            const float* src = c.attn + (w * G + hh) * 66;
+            const float f = (src[0] == -INFINITY) ? 0.f : __expf(src[0] - M);
+            lt = fmaf(src[1], f, lt);
+            a = fmaf(src[2 + d], f, a);
+        }
+        unsigned long long* dst = part + hh * 66;
+        if (d == 0) {
+            st_flagged(dst + 0, __float_as_uint(M), tag);
+            st_flagged(dst + 1, __float_as_uint(lt), tag);
+        }
+        st_flagged(dst + 2 + d, __float_as_uint(a), tag);
+    }
+    consumer_bar();   // c.attn is reused by the next item / the merge staging
+    if (c.prof) c.prof[15] = global_ns();
 }
 
-// Log-sum-exp merge of the chunk partials of one (request, query head); output rounded to bf16
-// (the attention output dtype) and published two values per flagged word.
+// Two-level mode only: log-sum-exp merge of the chunk partials of one (request, query head) by one
+// warp; output rounded to bf16 (the attention output dtype), two values per flagged word.
 __device__ void merge_task(Ctx& c, int layer, int b, int hq) {
     const DecodeParams& p = c.p;
     Shared& sh = c.sh;
@@ -887,43 +1027,43 @@ __device__ void merge_task(Ctx& c, int layer, int b, int hq) {
     const unsigned long long* part =
         p.ll_part + ((size_t)par * p.B * p.KVH * kNCMax * G + ((size_t)(b * p.KVH + kvh) * kNCMax) * G + hh) * 66;
     const size_t cstride = (size_t)G * 66;
+    uint32_t mlw[4];
+    wait_flagged_multi<4>(
+        c,
+        [&](int u) -> const unsigned long long* {
+            const int ch = lane + 32 * (u >> 1);
+            return ch < nc ? part + ch * cstride + (u & 1) : nullptr;
+        },
+        tag, mlw);
     float mc[2], lc[2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
         const int ch = lane + 32 * u;
-        mc[u] = -INFINITY;
-        lc[u] = 0.f;
-        if (ch < nc) {
-            mc[u] = __uint_as_float(wait_flagged(c, part + ch * cstride + 0, tag));
-            lc[u] = __uint_as_float(wait_flagged(c, part + ch * cstride + 1, tag));
-        }
+        mc[u] = ch < nc ? __uint_as_float(mlw[2 * u]) : -INFINITY;
+        lc[u] = ch < nc ? __uint_as_float(mlw[2 * u + 1]) : 0.f;
     }
     const float M = warp_max(fmaxf(mc[0], mc[1]));
     float wc[2];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) wc[u] = (mc[u] == -INFINITY) ? 0.f : expf(mc[u] - M);
+    for (int u = 0; u < 2; ++u) wc[u] = (mc[u] == -INFINITY) ? 0.f : __expf(mc[u] - M);
     const float den = warp_sum(lc[0] * wc[0] + lc[1] * wc[1]);
     float a0 = 0.f, a1 = 0.f;
     for (int ch0 = 0; ch0 < nc; ch0 += 8) {
-        unsigned long long v[8][2];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            if (ch0 + u < nc) {
-                v[u][0] = ld_flagged(part + (ch0 + u) * cstride + 2 + 2 * lane);
-                v[u][1] = ld_flagged(part + (ch0 + u) * cstride + 3 + 2 * lane);
-            }
-        }
+        uint32_t av[16];
+        wait_flagged_multi<16>(
+            c,
+            [&](int u) -> const unsigned long long* {
+                const int ch = ch0 + (u >> 1);
+                return ch < nc ? part + ch * cstride + 2 + 2 * lane + (u & 1) : nullptr;
+            },
+            tag, av);
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const int ch = ch0 + u;
             if (ch < nc) {   // warp-uniform
                 const float wgt = __shfl_sync(kFullMask, ch < 32 ? wc[0] : wc[1], ch & 31);
-                const uint32_t b0 = ((uint32_t)(v[u][0] >> 32) == tag) ? (uint32_t)v[u][0]
-                                                                        : wait_flagged(c, part + ch * cstride + 2 + 2 * lane, tag);
-                const uint32_t b1 = ((uint32_t)(v[u][1] >> 32) == tag) ? (uint32_t)v[u][1]
-                                                                        : wait_flagged(c, part + ch * cstride + 3 + 2 * lane, tag);
-                a0 = fmaf(wgt, __uint_as_float(b0), a0);
-                a1 = fmaf(wgt, __uint_as_float(b1), a1);
+                a0 = fmaf(wgt, __uint_as_float(av[2 * u]), a0);
+                a1 = fmaf(wgt, __uint_as_float(av[2 * u + 1]), a1);
             }
         }
     }
@@ -933,23 +1073,138 @@ __device__ void merge_task(Ctx& c, int layer, int b, int hq) {
     st_flagged(p.ll_attn + (size_t)par * p.B * nattn + (size_t)b * nattn + hq * (kD / 2) + lane, packed, tag);
 }
 
-template <int G>
-__device__ void attention_phase(Ctx& c, int layer) {
+// Top of a layer: the CTAs that own attention items pull their chunk's K/V rows (256 contiguous bytes
+// per position and kv head) towards L2 while the QKV projection is still being computed.
+__device__ void attention_prefetch(Ctx& c, int layer) {
     const DecodeParams& p = c.p;
     Shared& sh = c.sh;
-    const int total_warps = c.ncta * kNW;
-    const int gw = c.warp * c.ncta + c.cta;
     const int nslots = kNCMax * p.B * p.KVH;
-    for (int s = gw; s < nslots; s += total_warps) {
+    const unsigned char* kvr = reinterpret_cast<const unsigned char*>(p.kv[layer]);
+    for (int s = c.cta; s < nslots; s += c.ncta) {
         const int kvh = s % p.KVH;
         const int rest = s / p.KVH;
         const int b = rest % p.B;
         const int chunk = rest / p.B;
+        if (chunk >= sh.ncmax) break;
+        if (chunk >= sh.nc[b]) continue;
+        const int start = chunk * sh.lc[b];
+        const int end = min(start + sh.lc[b], sh.seq[b] - 1);
+        for (int i = start * 2 + (int)threadIdx.x; i < end * 2; i += kCT) {
+            const int pp = i >> 1;
+            const int blk = __ldg(p.block_table + b * p.bt_stride + pp / p.block_size);
+            const long long e = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride +
+                                (long long)kvh * p.head_stride;
+            const unsigned char* a = kvr + ((i & 1) ? p.v_off + e : p.k_off + e) * 2;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+        }
+    }
+}
+
+template <int G>
+__device__ void attention_phase(Ctx& c, int layer) {
+    const DecodeParams& p = c.p;
+    Shared& sh = c.sh;
+    // items (chunk-major so that the always-present chunk 0 of every (request, kv head) comes first),
+    // dealt round-robin to CTAs
+    const int nslots = kNCMax * p.B * p.KVH;
+    for (int s = c.cta; s < nslots; s += c.ncta) {
+        const int kvh = s % p.KVH;
+        const int rest = s / p.KVH;
+        const int b = rest % p.B;
+        const int chunk = rest / p.B;
+        if (chunk >= sh.ncmax) break;
         if (chunk < sh.nc[b]) attention_item<G>(c, layer, b, kvh, chunk);
     }
-    // merge tasks go to the highest warps first so they rarely queue behind an attention item
-    const int gm = (kNW - 1 - c.warp) * c.ncta + c.cta;
-    for (int t = gm; t < p.B * p.QH; t += total_warps) merge_task(c, layer, t / p.QH, t % p.QH);
+    if (sh.two_level) {
+        const int total_warps = c.ncta * kNW;
+        const int gm = (kNW - 1 - c.warp) * c.ncta + c.cta;
+        for (int t = gm; t < p.B * p.QH; t += total_warps) merge_task(c, layer, t / p.QH, t % p.QH);
+    }
+}
+
+// Direct mode: every CTA pulls all chunk partials (at most kDirectWords words), merges them with
+// log-sum-exp in shared memory and writes the bf16 attention output straight into c.act -- one
+// hand-off between the attention items and the O projection instead of two.
+template <int B>
+__device__ void stage_attn_direct(Ctx& c, int layer) {
+    const DecodeParams& p = c.p;
+    Shared& sh = c.sh;
+    const int ct = threadIdx.x;
+    const uint32_t tag = layer_tag(c, layer);
+    const int par = layer & 1;
+    const int G = p.G;
+    const unsigned long long* base = p.ll_part + (size_t)par * p.B * p.KVH * kNCMax * G * 66;
+    float* wts = c.attn + kDirectWords;          // [B * QH * nc] merge weights (<= 512 words)
+    consumer_bar();
+    // stage: shared layout [b][kvh][chunk < nc_b][hh][66], source layout [b][kvh][kNCMax][hh][66]
+    int soff = 0;
+    for (int b = 0; b < B; ++b) {
+        const int nc = sh.nc[b];
+        const int per_kvh = nc * G * 66;
+        const int n = p.KVH * per_kvh;
+        for (int i0 = ct; i0 < n; i0 += 8 * kCT) {
+            uint32_t bits[8];
+            wait_flagged_multi<8>(
+                c,
+                [&](int u) -> const unsigned long long* {
+                    const int i = i0 + u * kCT;
+                    if (i >= n) return nullptr;
+                    const int kvh = i / per_kvh, r = i - kvh * per_kvh;
+                    return base + ((size_t)(b * p.KVH + kvh) * kNCMax) * G * 66 + r;
+                },
+                tag, bits);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * kCT;
+                if (i < n) c.attn[soff + i] = __uint_as_float(bits[u]);
+            }
+        }
+        soff += n;
+    }
+    consumer_bar();
+    // merge weights once per (request, head, chunk): w = exp(m_c - M) / sum_c l_c exp(m_c - M)
+    soff = 0;
+    int woff = 0;
+    for (int b = 0; b < B; ++b) {
+        const int nc = sh.nc[b];
+        for (int hq = ct; hq < p.QH; hq += kCT) {
+            const int kvh = hq / G, hh = hq - kvh * G;
+            const float* src = c.attn + soff + ((kvh * nc) * G + hh) * 66;
+            const int cs = G * 66;
+            float M = -INFINITY;
+            for (int ch = 0; ch < nc; ++ch) M = fmaxf(M, src[ch * cs]);
+            float den = 0.f;
+            for (int ch = 0; ch < nc; ++ch) {
+                const float w = (src[ch * cs] == -INFINITY) ? 0.f : __expf(src[ch * cs] - M);
+                wts[woff + hq * nc + ch] = w;
+                den = fmaf(src[ch * cs + 1], w, den);
+            }
+            const float inv = 1.f / den;
+            for (int ch = 0; ch < nc; ++ch) wts[woff + hq * nc + ch] *= inv;
+        }
+        soff += p.KVH * nc * G * 66;
+        woff += p.QH * nc;
+    }
+    consumer_bar();
+    uint16_t* act16 = reinterpret_cast<uint16_t*>(c.act);
+    soff = 0;
+    woff = 0;
+    for (int b = 0; b < B; ++b) {
+        const int nc = sh.nc[b];
+        for (int o = ct; o < p.QH * kD; o += kCT) {
+            const int hq = o / kD, d = o - hq * kD;
+            const int kvh = hq / G, hh = hq - kvh * G;
+            const float* src = c.attn + soff + ((kvh * nc) * G + hh) * 66 + 2 + d;
+            const float* w = wts + woff + hq * nc;
+            const int cs = G * 66;
+            float a = 0.f;
+            for (int ch = 0; ch < nc; ++ch) a = fmaf(src[ch * cs], w[ch], a);
+            act16[(size_t)b * p.act_elems + o] = (uint16_t)f32_to_bf16_bits(a);
+        }
+        soff += p.KVH * nc * G * 66;
+        woff += p.QH * nc;
+    }
+    consumer_bar();
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -962,6 +1217,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
     off += ((size_t)B * p.act_elems * 2 + 127) & ~size_t(127);
     float* res = reinterpret_cast<float*>(smem_raw + off);
     off += ((size_t)B * p.H * 4 + 127) & ~size_t(127);
+    float* attn_scratch = reinterpret_cast<float*>(smem_raw + off);
+    off += (size_t)kAttnScratchWords * 4;
     unsigned char* ring_base = smem_raw + off;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -989,16 +1246,53 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
         sh.slot[tid] = p.slot_mapping[tid];
         sh.tok[tid] = p.ids_i64 ? reinterpret_cast<const long long*>(p.input_ids)[tid]
                                 : (long long)reinterpret_cast<const int*>(p.input_ids)[tid];
-        // chunk length: whole 16-position blocks, at most kNCMax chunks per (request, kv head)
-        int lc = ((seq + kNCMax - 1) / kNCMax + 15) & ~15;
-        if (lc < 16) lc = 16;
+        // Split-KV chunking.  Direct mode: chunks of 16 positions per warp (one load batch per lane
+        // group), longer only when B*QH*nc*66 would exceed kDirectWords.  When that would make chunks longer than 1024 positions,
+        // switch to two-level mode: 256-position chunks (up to kNCMax, longer only past 16K) and a
+        // separate merge hand-off.  The mode is decided on the longest request so it is CTA-uniform.
+        int smax = 1;
+        for (int bb = 0; bb < B; ++bb) smax = max(smax, max(p.seq_lens[bb], 1));
+        int ncd = kDirectWords / (B * p.QH * 66);
+        ncd = max(1, min(ncd, kNCMax));
+        int lcd = max(16 * kNW, (((smax + ncd - 1) / ncd) + 15) & ~15);
+        const int two = lcd > 1024 ? 1 : 0;
+        int lc = lcd;
+        if (two) lc = max(256, (((smax + kNCMax - 1) / kNCMax) + 15) & ~15);
         sh.lc[tid] = lc;
         sh.nc[tid] = (seq + lc - 1) / lc;
+        if (tid == 0) {
+            sh.two_level = two;
+            sh.ncmax = (smax + lc - 1) / lc;
+        }
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
+    if (warp < kNW) {
+        // this warp's entry table: lanes fill entries in parallel (closed form per entry)
+        int base = 0;
+        for (int t = 0; t < 4; ++t) {
+            const int n = phase_entries(p.ph[t], sh.row_a[t][warp], sh.row_b[t][warp]);
+            for (int e = lane; e < n; e += 32)
+                if (base + e < kMaxLayerEntries)
+                    sh.ent_table[warp][base + e] = phase_entry(p.ph[t], sh.row_a[t][warp], sh.row_b[t][warp], e);
+            base += n;
+        }
+        const int nlm = p.lm_head ? phase_entries(p.ph[kLM], sh.row_a[kLM][warp], sh.row_b[kLM][warp]) : 0;
+        for (int e = lane; e < nlm; e += 32)
+            if (e < kMaxLmEntries)
+                sh.ent_table[warp][kMaxLayerEntries + e] = phase_entry(p.ph[kLM], sh.row_a[kLM][warp], sh.row_b[kLM][warp], e);
+        if (lane == 0) {
+            sh.ent_count[warp][0] = base;
+            sh.ent_count[warp][1] = nlm;
+            if (base > kMaxLayerEntries || nlm > kMaxLmEntries) {
+                sh.abort_flag = 1;
+                atomicCAS(p.ctrl + kCtrlStatus, 0u, (unsigned)kErrShape);
+            }
+        }
+    }
+    __syncthreads();
 
-    Ctx c{p, sh, act, res, ring_base + (size_t)(warp < kNW ? warp : 0) * p.ring_bytes, 0u, warp, lane, cta, ncta};
+    Ctx c{p, sh, act, res, attn_scratch, ring_base + (size_t)(warp < kNW ? warp : 0) * p.ring_bytes, 0u, warp, lane, cta, ncta, nullptr};
     c.tag_base = (sh.epoch + 1u) << 7;
 
     if (warp == kNW) {
@@ -1014,15 +1308,30 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
             const int par = layer & 1;
             const uint16_t* norm1 = reinterpret_cast<const uint16_t*>(p.layers[layer * 6 + 0]);
             const uint16_t* norm2 = reinterpret_cast<const uint16_t*>(p.layers[layer * 6 + 3]);
+            unsigned long long* prof =
+                (p.profile && tid == 0) ? p.profile + ((size_t)cta * p.L + layer) * kProfSlots : nullptr;
+            c.prof = prof;
+            if (prof) prof[0] = global_ns();
+            attention_prefetch(c, layer);
             stage_norm<B>(c, p.ll_x + (size_t)par * B * p.H, tag, norm1, layer == 0);
+            if (prof) prof[1] = global_ns();
             gemv_phase<B, kQKV>(c, layer, consumed);
+            if (prof) prof[2] = global_ns();
             attention_phase<G>(c, layer);
-            stage_copy<B>(c, p.ll_attn + (size_t)par * B * (p.QH * kD / 2), tag, p.QH * kD, true);
+            if (prof) prof[3] = global_ns();
+            if (sh.two_level) stage_copy<B>(c, p.ll_attn + (size_t)par * B * (p.QH * kD / 2), tag, p.QH * kD, true);
+            else stage_attn_direct<B>(c, layer);
+            if (prof) prof[4] = global_ns();
             gemv_phase<B, kO>(c, layer, consumed);
+            if (prof) prof[5] = global_ns();
             stage_norm<B>(c, p.ll_h1 + (size_t)par * B * p.H, tag, norm2, false);
+            if (prof) prof[6] = global_ns();
             gemv_phase<B, kGU>(c, layer, consumed);
+            if (prof) prof[7] = global_ns();
             stage_copy<B>(c, p.ll_act + (size_t)par * B * p.I, tag, p.I, false);
+            if (prof) prof[8] = global_ns();
             gemv_phase<B, kDown>(c, layer, consumed);
+            if (prof) prof[9] = global_ns();
         }
         if (p.lm_head || cta == 0) {
             stage_norm<B>(c, p.ll_x + (size_t)(p.L & 1) * B * p.H, layer_tag(c, p.L), p.final_norm, false);
@@ -1111,6 +1420,8 @@ struct DeviceInfo {
     int sm_count = 0, coop = 0, major = 0, minor = 0, smem_optin = 0;
 };
 static std::mutex g_mu;
+static unsigned long long* g_profile = nullptr;   // optional stage-timestamp buffer (debug aid)
+static size_t g_profile_bytes = 0;
 static std::unordered_map<int, DeviceInfo> g_devinfo;
 static std::unordered_map<const void*, size_t> g_ws_ready;      // workspace pointers already zeroed
 static std::unordered_map<const void*, int> g_kernel_smem;      // largest dynamic smem opted in per kernel
@@ -1145,8 +1456,7 @@ static KernelFn pick_kernel(int B, int G) {
 }
 
 // Fill the per-phase staging descriptors for a ring of `rw` bytes per consumer warp.
-static int make_phases(const ModelGeom& g, int rw, PhaseDesc (&ph)[kNumPhaseTypes]) {
-    const int entry_max = rw / 2;
+static int make_phases_with(const ModelGeom& g, int entry_max, PhaseDesc (&ph)[kNumPhaseTypes]) {
     auto rowbytes = [&](int K) { return g.wfmt ? (int)align_up((size_t)K + K / 32, 16) : K * 2; };
     struct Spec { int nrows, K, pair, widx; long long pair_rows; };
     const int nqkv = (g.QH + 2 * g.KVH) * kD;
@@ -1186,6 +1496,36 @@ static int make_phases(const ModelGeom& g, int rw, PhaseDesc (&ph)[kNumPhaseType
     return 0;
 }
 
+// Entries per consumer warp (worst CTA) for one layer / for the lm_head under the given descriptors.
+static void worst_entry_counts(const PhaseDesc (&ph)[kNumPhaseTypes], int ncta, int& per_layer, int& lm) {
+    auto count = [&](const PhaseDesc& d) {
+        const int rows_cta = (d.nrows + ncta - 1) / ncta;
+        const int rpw = (rows_cta + kNW - 1) / kNW;
+        return d.nseg == 1 ? (rpw + d.rows_per_entry - 1) / d.rows_per_entry : rpw * d.nseg;
+    };
+    per_layer = 0;
+    for (int t = 0; t < 4; ++t) per_layer += count(ph[t]);
+    lm = count(ph[kLM]);
+}
+
+// Pick the smallest entry size (small entries lose little ring space at the wrap point, which an
+// entry never straddles) whose per-warp schedule still fits the in-kernel entry tables.
+static int make_phases(const ModelGeom& g, int rw, int ncta, PhaseDesc (&ph)[kNumPhaseTypes]) {
+    int rc = kErrShape;
+    int first = rw / 2 / 512 * 512;
+    if (first > 8192) first = 8192;
+    if (first < 1024) return kErrResidency;
+    for (int entry_max = first; entry_max <= rw / 2; entry_max *= 2) {
+        rc = make_phases_with(g, entry_max, ph);
+        if (rc) continue;
+        int per_layer = 0, lm = 0;
+        worst_entry_counts(ph, ncta, per_layer, lm);
+        if (per_layer <= kMaxLayerEntries && lm <= kMaxLmEntries) return 0;
+        rc = kErrShape;
+    }
+    return rc;
+}
+
 struct StepArgs {
     cudaStream_t stream;
     int B;
@@ -1205,7 +1545,7 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
         !a.final_norm || !a.kv || !a.cos_sin || !a.out_hidden || !a.ws)
         return kErrNull;
     if (g.H <= 0 || g.I <= 0 || g.L < 1 || g.L > kMaxLayers || g.QH <= 0 || g.KVH <= 0 || g.QH % g.KVH || g.V <= 0 ||
-        g.H % 32 || g.I % 32 || (g.QH * kD) % 32)
+        g.H % 32 || g.I % 32 || (g.QH * kD) % 32 || g.H > kNormRegs * kCT)
         return kErrShape;
     const int G = g.QH / g.KVH;
     KernelFn fn = pick_kernel(a.B, G);
@@ -1231,11 +1571,19 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
     // shared memory: fixed part + per-warp rings
     const int act_elems = g.H > g.I ? g.H : g.I;
     const size_t fixed = align_up(sizeof(Shared), 128) + align_up((size_t)a.B * act_elems * 2, 128) +
-                         align_up((size_t)a.B * g.H * 4, 128);
+                         align_up((size_t)a.B * g.H * 4, 128) + (size_t)kAttnScratchWords * 4;
     if ((size_t)di.smem_optin < fixed + (size_t)kNW * 2048) return kErrResidency;
     int rw = (int)(((size_t)di.smem_optin - fixed) / kNW / 512 * 512);
     DecodeParams p{};
-    rc = make_phases(g, rw, p.ph);
+    // grid: one CTA per SM, but never more CTAs than rows in the smallest projection, so every
+    // CTA takes part in every hand-off (which bounds how far any CTA can run ahead of another)
+    int ncta = di.sm_count;
+    {
+        const int rows[4] = {(g.QH + 2 * g.KVH) * kD, g.H, g.I, g.H};
+        for (int t = 0; t < 4; ++t) ncta = rows[t] < ncta ? rows[t] : ncta;
+    }
+    if (ncta < 1) return kErrShape;
+    rc = make_phases(g, rw, ncta, p.ph);
     if (rc) return rc;
     const size_t smem = fixed + (size_t)kNW * rw;
 
@@ -1255,12 +1603,6 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
             g_ws_ready[a.ws] = a.ws_bytes;
         }
     }
-
-    // grid: one CTA per SM, but never more CTAs than rows in the smallest projection, so every
-    // CTA takes part in every hand-off (which bounds how far any CTA can run ahead of another)
-    int ncta = di.sm_count;
-    for (int t = 0; t < 4; ++t) ncta = p.ph[t].nrows < ncta ? p.ph[t].nrows : ncta;
-    if (ncta < 1) return kErrShape;
 
     unsigned char* ws = static_cast<unsigned char*>(a.ws);
     p.layers = static_cast<const unsigned long long*>(a.layers);
@@ -1301,6 +1643,7 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
     p.advance = (a.advance && p.lm_head && a.next_ids) ? 1 : 0;
     p.max_seq_len = a.max_seq_len;
     p.ring_bytes = rw;
+    p.profile = (g_profile && g_profile_bytes >= (size_t)ncta * g.L * kProfSlots * 8) ? g_profile : nullptr;
     p.act_elems = act_elems;
     p.eps = g.eps;
 
@@ -1414,6 +1757,14 @@ extern "C" int pk_decode_status(void* workspace, void* stream) {
 }
 
 extern "C" const char* pk_status_string(int status) { return status_string(status); }
+
+// Debug aid: when set (device buffer of at least ctas * layers * 24 * 8 bytes), thread 0 of every CTA
+// stamps %globaltimer at each phase boundary of each layer: [cta][layer][12].  Pass null to disable.
+extern "C" void pk_decode_set_profile(void* buffer, size_t bytes) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_profile = static_cast<unsigned long long*>(buffer);
+    g_profile_bytes = buffer ? bytes : 0;
+}
 
 extern "C" int pk_decode_query(int* sm_count, int* coop, int* major, int* minor, int* smem_optin, int* threads,
                                int* consumer_warps) {
