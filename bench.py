@@ -136,9 +136,13 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--workload", default="smollm2-360m-b1", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--prompt-tokens", type=int, default=None, help="override the workload's prompt length")
     args = ap.parse_args()
     wl = args.workload
     gname, batch, prompt_len, default_steps = WORKLOADS[wl]
+    if args.prompt_tokens:
+        prompt_len = args.prompt_tokens
     if args.steps is None:
         args.steps = default_steps
     if args.impl == "reference":
@@ -211,46 +215,51 @@ def main():
     seq_last = seq_first + K - 1
 
     # ---- end to end through the public API with host buffers
-    kv2, sess2 = new_session()
-    prefill(sess2)
-    h_ids = torch.empty(batch, dtype=torch.int64).pin_memory()
-    h_pos = torch.empty(batch, dtype=torch.int64).pin_memory()
-    h_seq = torch.empty(batch, dtype=torch.int32).pin_memory()
-    h_slot = torch.empty(batch, dtype=torch.int64).pin_memory()
-    h_next = torch.empty(batch, dtype=torch.int64).pin_memory()
-    d_ids, d_pos = torch.empty_like(h_ids, device=dev), torch.empty_like(h_pos, device=dev)
-    d_seq, d_slot = torch.empty_like(h_seq, device=dev), torch.empty_like(h_slot, device=dev)
-    bt_host = kv2.block_table.cpu()
-    cur = prompt[:, -1].clone()
-    pos0 = prompt_len - 1
+    def run_e2e():
+        kv2, sess2 = new_session()
+        prefill(sess2)
+        h_ids = torch.empty(batch, dtype=torch.int64).pin_memory()
+        h_pos = torch.empty(batch, dtype=torch.int64).pin_memory()
+        h_seq = torch.empty(batch, dtype=torch.int32).pin_memory()
+        h_slot = torch.empty(batch, dtype=torch.int64).pin_memory()
+        h_next = torch.empty(batch, dtype=torch.int64).pin_memory()
+        d_ids, d_pos = torch.empty_like(h_ids, device=dev), torch.empty_like(h_pos, device=dev)
+        d_seq, d_slot = torch.empty_like(h_seq, device=dev), torch.empty_like(h_slot, device=dev)
+        bt_host = kv2.block_table.cpu()
+        cur = prompt[:, -1].clone()
+        pos0 = prompt_len - 1
 
-    def e2e_step(t):
-        pos = pos0 + t
-        h_ids.copy_(cur)
-        h_pos.fill_(pos)
-        h_seq.fill_(pos + 1)
-        h_slot.copy_(bt_host[:batch, pos // 16].to(torch.int64) * 16 + pos % 16)
-        d_ids.copy_(h_ids, non_blocking=True)
-        d_pos.copy_(h_pos, non_blocking=True)
-        d_seq.copy_(h_seq, non_blocking=True)
-        d_slot.copy_(h_slot, non_blocking=True)
-        _, _, nxt = D.decode_step(geom, input_ids=d_ids, positions=d_pos, seq_lens=d_seq, block_table=kv2.block_table,
-                                  slot_mapping=d_slot, embed=weights["embed"], layers=weights["layers"],
-                                  final_norm=weights["final_norm"], kv_caches=kv2.kv_caches, cos_sin_cache=cos_sin,
-                                  eps=geom.eps, lm_head=True)
-        h_next.copy_(nxt, non_blocking=True)
-        torch.cuda.current_stream(dev).synchronize()
-        cur.copy_(h_next)
+        def e2e_step(t):
+            pos = pos0 + t
+            h_ids.copy_(cur)
+            h_pos.fill_(pos)
+            h_seq.fill_(pos + 1)
+            h_slot.copy_(bt_host[:batch, pos // 16].to(torch.int64) * 16 + pos % 16)
+            d_ids.copy_(h_ids, non_blocking=True)
+            d_pos.copy_(h_pos, non_blocking=True)
+            d_seq.copy_(h_seq, non_blocking=True)
+            d_slot.copy_(h_slot, non_blocking=True)
+            _, _, nxt = D.decode_step(geom, input_ids=d_ids, positions=d_pos, seq_lens=d_seq,
+                                      block_table=kv2.block_table, slot_mapping=d_slot, embed=weights["embed"],
+                                      layers=weights["layers"], final_norm=weights["final_norm"],
+                                      kv_caches=kv2.kv_caches, cos_sin_cache=cos_sin, eps=geom.eps, lm_head=True)
+            h_next.copy_(nxt, non_blocking=True)
+            torch.cuda.current_stream(dev).synchronize()
+            cur.copy_(h_next)
 
-    for t in range(W):
-        e2e_step(t)
-    barrier()
-    t0 = time.perf_counter()
-    for t in range(W, W + K):
-        e2e_step(t)
-    torch.cuda.synchronize(dev)
-    e2e_s = time.perf_counter() - t0
-    barrier()
+        for t in range(W):
+            e2e_step(t)
+        barrier()
+        t0 = time.perf_counter()
+        for t in range(W, W + K):
+            e2e_step(t)
+        torch.cuda.synchronize(dev)
+        dt = time.perf_counter() - t0
+        barrier()
+        D.check_status(geom, dev)
+        return dt
+
+    e2e_s = float("nan") if args.no_e2e else run_e2e()
 
     times = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
     if world > 1:
@@ -277,7 +286,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": peak_src, "frac_of_8TBs_nominal": achieved / 8000.0,
                          "algorithmic_bytes_per_step": mean_bytes},
-            "e2e": {"value": world * batch * K / (e2e_ms_max * 1e-3), "unit": "tok/s",
+            "e2e": {"value": None if args.no_e2e else world * batch * K / (e2e_ms_max * 1e-3), "unit": "tok/s",
                     "h2d_bytes_per_step": batch * (8 + 8 + 4 + 8), "d2h_bytes_per_step": batch * 8},
             "gpu_launches": K,
             "clocks": clocks.summary(),

@@ -52,8 +52,8 @@ constexpr int kMaxSeq = 8192;
 constexpr int kMaxLayerEntries = 40;       // ring entries per consumer warp and layer
 constexpr int kMaxLmEntries = 56;          // ring entries per consumer warp for the lm_head
 constexpr int kNormRegs = 10;              // norm weights held per thread: hidden <= kNormRegs * kCT
-constexpr int kDirectWords = 8192;         // direct-merge limit: partial words every CTA stages per layer
-constexpr int kAttnScratchWords = 8192 + 512;   // staged partials + merge weights; also >= kNW * 4 * 66 + staging
+constexpr int kDirectWords = 2048;         // direct-merge limit: partial words every CTA stages per layer
+constexpr int kAttnScratchWords = 3072;        // staged partials + merge weights; also >= kNW * 4 * 66 + staging
 constexpr int kMaxLayers = 120;
 constexpr unsigned kSpinLimit = 1u << 22;  // bounded waits: ~1-2 s of L2 polling
 
@@ -421,15 +421,21 @@ __device__ void producer_loop(Ctx& c, unsigned char* ring_base) {
 }
 
 // ------------------------------------------------------------------ math helpers
+// acc += w.lo * a.lo + w.hi * a.hi for one packed bf16 pair per operand, with the sm_100 mixed-precision
+// FMA (bf16 x bf16 product exact, fp32 accumulate, one rounding: the same result as widening both
+// operands and using an fp32 FMA, without the four unpack instructions).
+__device__ __forceinline__ float fma2_bf16(uint32_t w, uint32_t a, float acc) {
+    asm("{\n.reg .b16 wl, wh, al, ah;\nmov.b32 {wl, wh}, %1;\nmov.b32 {al, ah}, %2;\n"
+        "fma.rn.f32.bf16 %0, wl, al, %0;\nfma.rn.f32.bf16 %0, wh, ah, %0;\n}"
+        : "+f"(acc)
+        : "r"(w), "r"(a));
+    return acc;
+}
 __device__ __forceinline__ float dot8_bf16(const uint4 w, const uint4 a, float acc) {
-    acc = fmaf(bf16_lo(w.x), bf16_lo(a.x), acc);
-    acc = fmaf(bf16_hi(w.x), bf16_hi(a.x), acc);
-    acc = fmaf(bf16_lo(w.y), bf16_lo(a.y), acc);
-    acc = fmaf(bf16_hi(w.y), bf16_hi(a.y), acc);
-    acc = fmaf(bf16_lo(w.z), bf16_lo(a.z), acc);
-    acc = fmaf(bf16_hi(w.z), bf16_hi(a.z), acc);
-    acc = fmaf(bf16_lo(w.w), bf16_lo(a.w), acc);
-    acc = fmaf(bf16_hi(w.w), bf16_hi(a.w), acc);
+    acc = fma2_bf16(w.x, a.x, acc);
+    acc = fma2_bf16(w.y, a.y, acc);
+    acc = fma2_bf16(w.z, a.z, acc);
+    acc = fma2_bf16(w.w, a.w, acc);
     return acc;
 }
 
@@ -543,8 +549,8 @@ __device__ __forceinline__ void gemv_rows_mxfp8(const uint4* ep, int rc, int kac
 // ------------------------------------------------------------------ GEMV phase (consumer warps)
 // Consumes this warp's ring entries of phase type T at `layer`, multiplying the staged rows with
 // the bf16 activations in c.act, and hands each finished row to the phase epilogue.
-template <int B, int T>
-__device__ void gemv_phase(Ctx& c, int layer, uint32_t& consumed) {
+template <int B, int WF>
+__device__ void gemv_phase(Ctx& c, const int T, int layer, uint32_t& consumed) {
     const DecodeParams& p = c.p;
     Shared& sh = c.sh;
     const PhaseDesc& d = p.ph[T];
@@ -553,7 +559,7 @@ __device__ void gemv_phase(Ctx& c, int layer, uint32_t& consumed) {
     const int actc = p.act_elems >> 3;                 // uint4 per request in c.act
     const uint32_t tag = layer_tag(c, layer);
     const int par = layer & 1;
-    constexpr bool kPair = (T == kGU);
+    const bool kPair = (T == kGU);
     for (int row = ra; row < rb; row += d.rows_per_entry) {
         const int nre = min(d.rows_per_entry, rb - row);
         float acc[kRMax][B], acc2[kRMax][B];
@@ -568,7 +574,7 @@ __device__ void gemv_phase(Ctx& c, int layer, uint32_t& consumed) {
             const uint4* ep = reinterpret_cast<const uint4*>(c.ring + sh.ent_off[w][slot]);
             // accumulator r <- staged row r; a gate/up entry stages nre gate rows, then nre up rows
             const int nmem = kPair ? 2 * nre : nre;
-            if (p.wfmt == 0) {
+            if (WF == 0) {
                 const int sc = d.nseg == 1 ? d.kchunks : min(d.segchunks, d.kchunks - seg * d.segchunks);
                 const int kc0 = seg * d.segchunks;
                 switch (nmem) {
@@ -617,7 +623,7 @@ __device__ void gemv_phase(Ctx& c, int layer, uint32_t& consumed) {
                         // up row of pair i sits right after the nre gate rows: static selects, no dynamic register index
                         const float upv = nre == 1 ? acc[1][b] : acc[(i + 2) & (kRMax - 1)][b];
                         const float u = round_bf16(upv);
-                        const float silu = round_bf16(g / (1.f + expf(-g)));
+                        const float silu = round_bf16(__fdividef(g, 1.f + __expf(-g)));
                         const float a = round_bf16(__fmul_rn(silu, u));
                         st_flagged(p.ll_act + (size_t)par * B * p.I + b * p.I + r, f32_to_bf16_bits(a), tag);
                     } else if (T == kDown) {
@@ -1027,20 +1033,26 @@ __device__ void merge_task(Ctx& c, int layer, int b, int hq) {
     const unsigned long long* part =
         p.ll_part + ((size_t)par * p.B * p.KVH * kNCMax * G + ((size_t)(b * p.KVH + kvh) * kNCMax) * G + hh) * 66;
     const size_t cstride = (size_t)G * 66;
-    uint32_t mlw[4];
-    wait_flagged_multi<4>(
+    // one round of loads: m and l of chunks lane, lane+32, and this lane's accumulator pair of the
+    // first 8 chunks
+    uint32_t w20[20];
+    wait_flagged_multi<20>(
         c,
         [&](int u) -> const unsigned long long* {
-            const int ch = lane + 32 * (u >> 1);
-            return ch < nc ? part + ch * cstride + (u & 1) : nullptr;
+            if (u < 4) {
+                const int ch = lane + 32 * (u >> 1);
+                return ch < nc ? part + ch * cstride + (u & 1) : nullptr;
+            }
+            const int ch = (u - 4) >> 1;
+            return ch < nc ? part + ch * cstride + 2 + 2 * lane + (u & 1) : nullptr;
         },
-        tag, mlw);
+        tag, w20);
     float mc[2], lc[2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
         const int ch = lane + 32 * u;
-        mc[u] = ch < nc ? __uint_as_float(mlw[2 * u]) : -INFINITY;
-        lc[u] = ch < nc ? __uint_as_float(mlw[2 * u + 1]) : 0.f;
+        mc[u] = ch < nc ? __uint_as_float(w20[2 * u]) : -INFINITY;
+        lc[u] = ch < nc ? __uint_as_float(w20[2 * u + 1]) : 0.f;
     }
     const float M = warp_max(fmaxf(mc[0], mc[1]));
     float wc[2];
@@ -1048,7 +1060,15 @@ __device__ void merge_task(Ctx& c, int layer, int b, int hq) {
     for (int u = 0; u < 2; ++u) wc[u] = (mc[u] == -INFINITY) ? 0.f : __expf(mc[u] - M);
     const float den = warp_sum(lc[0] * wc[0] + lc[1] * wc[1]);
     float a0 = 0.f, a1 = 0.f;
-    for (int ch0 = 0; ch0 < nc; ch0 += 8) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        if (u < nc) {   // warp-uniform
+            const float wgt = __shfl_sync(kFullMask, wc[0], u);
+            a0 = fmaf(wgt, __uint_as_float(w20[4 + 2 * u]), a0);
+            a1 = fmaf(wgt, __uint_as_float(w20[5 + 2 * u]), a1);
+        }
+    }
+    for (int ch0 = 8; ch0 < nc; ch0 += 8) {
         uint32_t av[16];
         wait_flagged_multi<16>(
             c,
@@ -1208,7 +1228,7 @@ __device__ void stage_attn_direct(Ctx& c, int layer) {
 }
 
 // ------------------------------------------------------------------ the kernel
-template <int B, int G>
+template <int B, int G, int WF>
 __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Shared& sh = *reinterpret_cast<Shared*>(smem_raw);
@@ -1246,18 +1266,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
         sh.slot[tid] = p.slot_mapping[tid];
         sh.tok[tid] = p.ids_i64 ? reinterpret_cast<const long long*>(p.input_ids)[tid]
                                 : (long long)reinterpret_cast<const int*>(p.input_ids)[tid];
-        // Split-KV chunking.  Direct mode: chunks of 16 positions per warp (one load batch per lane
-        // group), longer only when B*QH*nc*66 would exceed kDirectWords.  When that would make chunks longer than 1024 positions,
-        // switch to two-level mode: 256-position chunks (up to kNCMax, longer only past 16K) and a
-        // separate merge hand-off.  The mode is decided on the longest request so it is CTA-uniform.
+        // Split-KV chunking: 16 positions per warp and chunk (one load batch per lane group), longer
+        // only when that would need more than kNCMax chunks.  With few partials (short contexts) every
+        // CTA merges them itself while staging the O projection input (direct mode, one hand-off);
+        // otherwise one warp per (request, head) merges and publishes the result (two hand-offs, but
+        // no redundant staging).  The mode is decided on the longest request so it is CTA-uniform.
         int smax = 1;
         for (int bb = 0; bb < B; ++bb) smax = max(smax, max(p.seq_lens[bb], 1));
-        int ncd = kDirectWords / (B * p.QH * 66);
-        ncd = max(1, min(ncd, kNCMax));
-        int lcd = max(16 * kNW, (((smax + ncd - 1) / ncd) + 15) & ~15);
-        const int two = lcd > 1024 ? 1 : 0;
-        int lc = lcd;
-        if (two) lc = max(256, (((smax + kNCMax - 1) / kNCMax) + 15) & ~15);
+        const int lc = max(16 * kNW, (((smax + kNCMax - 1) / kNCMax) + 15) & ~15);
+        const int two = (B * p.QH * ((smax + lc - 1) / lc) * 66 > kDirectWords) ? 1 : 0;
         sh.lc[tid] = lc;
         sh.nc[tid] = (seq + lc - 1) / lc;
         if (tid == 0) {
@@ -1301,46 +1318,50 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
         // reset the argmax cells the *next* launch will use
         if (cta == 0 && tid < kMaxB && p.next_ids) p.argkey[(size_t)((sh.epoch + 1u) & 1u) * kMaxB + tid] = 0ull;
         uint32_t consumed = 0;
-        const int nqkv = (p.QH + 2 * p.KVH) * kD;
-        (void)nqkv;
-        for (int layer = 0; layer < p.L; ++layer) {
+        // One loop over the global phase index (4 per layer, then the lm_head) with a single call site
+        // for every building block, so each is instantiated once and the instruction footprint of a
+        // layer stays small enough for the instruction cache.
+        const int nphases = p.L * 4 + 1;
+        for (int gp = 0; gp < nphases; ++gp) {
+            const int layer = gp >> 2;
+            const int t = gp < p.L * 4 ? (gp & 3) : (int)kLM;
+            if (t == kLM && !(p.lm_head || cta == 0)) break;
             const uint32_t tag = layer_tag(c, layer);
             const int par = layer & 1;
-            const uint16_t* norm1 = reinterpret_cast<const uint16_t*>(p.layers[layer * 6 + 0]);
-            const uint16_t* norm2 = reinterpret_cast<const uint16_t*>(p.layers[layer * 6 + 3]);
-            unsigned long long* prof =
-                (p.profile && tid == 0) ? p.profile + ((size_t)cta * p.L + layer) * kProfSlots : nullptr;
+            unsigned long long* prof = nullptr;
+            if (p.profile && tid == 0 && t != kLM) prof = p.profile + ((size_t)cta * p.L + layer) * kProfSlots;
             c.prof = prof;
-            if (prof) prof[0] = global_ns();
-            attention_prefetch(c, layer);
-            stage_norm<B>(c, p.ll_x + (size_t)par * B * p.H, tag, norm1, layer == 0);
-            if (prof) prof[1] = global_ns();
-            gemv_phase<B, kQKV>(c, layer, consumed);
-            if (prof) prof[2] = global_ns();
-            attention_phase<G>(c, layer);
-            if (prof) prof[3] = global_ns();
-            if (sh.two_level) stage_copy<B>(c, p.ll_attn + (size_t)par * B * (p.QH * kD / 2), tag, p.QH * kD, true);
-            else stage_attn_direct<B>(c, layer);
-            if (prof) prof[4] = global_ns();
-            gemv_phase<B, kO>(c, layer, consumed);
-            if (prof) prof[5] = global_ns();
-            stage_norm<B>(c, p.ll_h1 + (size_t)par * B * p.H, tag, norm2, false);
-            if (prof) prof[6] = global_ns();
-            gemv_phase<B, kGU>(c, layer, consumed);
-            if (prof) prof[7] = global_ns();
-            stage_copy<B>(c, p.ll_act + (size_t)par * B * p.I, tag, p.I, false);
-            if (prof) prof[8] = global_ns();
-            gemv_phase<B, kDown>(c, layer, consumed);
-            if (prof) prof[9] = global_ns();
-        }
-        if (p.lm_head || cta == 0) {
-            stage_norm<B>(c, p.ll_x + (size_t)(p.L & 1) * B * p.H, layer_tag(c, p.L), p.final_norm, false);
-            if (cta == 0) {
+            if (t == kQKV) {
+                if (prof) prof[0] = global_ns();
+                attention_prefetch(c, layer);
+            }
+            if (t == kO) {
+                attention_phase<G>(c, layer);
+                if (prof) prof[3] = global_ns();
+            }
+            // ---- stage the phase input into c.act
+            const bool norm = (t == kQKV || t == kGU || t == kLM);
+            if (norm) {
+                const unsigned long long* src =
+                    (t == kGU) ? p.ll_h1 + (size_t)par * B * p.H : p.ll_x + (size_t)par * B * p.H;
+                const uint16_t* w = (t == kLM) ? p.final_norm
+                                               : reinterpret_cast<const uint16_t*>(p.layers[layer * 6 + (t == kQKV ? 0 : 3)]);
+                stage_norm<B>(c, src, tag, w, gp == 0);
+            } else if (t == kO && !sh.two_level) {
+                stage_attn_direct<B>(c, layer);
+            } else {
+                const bool attn = (t == kO);
+                stage_copy<B>(c, attn ? p.ll_attn + (size_t)par * B * (p.QH * kD / 2) : p.ll_act + (size_t)par * B * p.I, tag,
+                              attn ? p.QH * kD : p.I, attn);
+            }
+            if (prof) prof[1 + 2 * t + (t >= kO ? 1 : 0)] = global_ns();     // slots 1, 4, 6, 8
+            if (t == kLM && cta == 0) {
                 const uint16_t* act16 = reinterpret_cast<const uint16_t*>(c.act);
                 for (int b = 0; b < B; ++b)
                     for (int i = tid; i < p.H; i += kCT) p.out_hidden[b * p.H + i] = act16[(size_t)b * p.act_elems + i];
             }
-            if (p.lm_head) gemv_phase<B, kLM>(c, p.L, consumed);
+            if (t != kLM || p.lm_head) gemv_phase<B, WF>(c, t, layer, consumed);
+            if (prof) prof[2 + 2 * t + (t >= kO ? 1 : 0)] = global_ns();     // slots 2, 5, 7, 9
         }
     }
     __syncthreads();
@@ -1446,9 +1467,10 @@ static int device_info(DeviceInfo& out) {
 }
 
 typedef void (*KernelFn)(const DecodeParams);
-static KernelFn pick_kernel(int B, int G) {
-#define PK_CASE(b, g) \
-    if (B == b && G == g) return decode_step_kernel<b, g>;
+static KernelFn pick_kernel(int B, int G, int WF) {
+#define PK_CASE(b, g)                                            \
+    if (B == b && G == g && WF == 0) return decode_step_kernel<b, g, 0>; \
+    if (B == b && G == g && WF == 1) return decode_step_kernel<b, g, 1>;
     PK_CASE(1, 1) PK_CASE(2, 1) PK_CASE(3, 1) PK_CASE(4, 1)
     PK_CASE(1, 3) PK_CASE(2, 3) PK_CASE(3, 3) PK_CASE(4, 3)
 #undef PK_CASE
@@ -1548,7 +1570,8 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
         g.H % 32 || g.I % 32 || (g.QH * kD) % 32 || g.H > kNormRegs * kCT)
         return kErrShape;
     const int G = g.QH / g.KVH;
-    KernelFn fn = pick_kernel(a.B, G);
+    if (g.wfmt != 0 && g.wfmt != 1) return kErrShape;
+    KernelFn fn = pick_kernel(a.B, G, g.wfmt);
     if (!fn) return kErrShape;
     if (a.block_size <= 0 || a.bt_stride < 1 || (long long)a.bt_stride * a.block_size < a.max_seq_len) return kErrBlock;
     if (a.k_off % 8 || a.v_off % 8 || a.block_stride % 8 || a.token_stride % 8 || a.head_stride % 8 || a.k_off < 0 ||
@@ -1789,7 +1812,7 @@ extern "C" int mk_query(int* sm_count, int* coop, int* active_per_sm, int* major
     const int rc = device_info(di);
     if (rc) return rc;
     cudaFuncAttributes fa{};
-    cudaError_t e = cudaFuncGetAttributes(&fa, decode_step_kernel<4, 3>);
+    cudaError_t e = cudaFuncGetAttributes(&fa, decode_step_kernel<4, 3, 0>);
     if (e != cudaSuccess) return (int)e;
     *sm_count = di.sm_count;
     *coop = di.coop;
