@@ -41,6 +41,13 @@ int pk_fused_rmsnorm_residual_forward_ex(void* vals, void* scales, float* rrms, 
  * (scale_numel in prime_kernels/rmsnorm/csrc/torch_interface.cpp:18-20, extended to ragged shapes). */
 long long pk_rmsnorm_scale_bytes(int N, int C);
 
+/* MXFP8 weight packing for the decode GEMVs.  No counterpart in the reference (its kernels take
+ * pre-quantised weights, prime_kernels/flash_moe/__init__.py:165-170).  Quantises bf16 [rows, K] along K
+ * with the quantiser above (one E8M0 scale per 32 values, round-up scale) into packed rows
+ * [K e4m3][K/32 e8m0][zero pad to 16 B]; pk_mxfp8_packed_row_bytes(K) is the row stride (-1: bad K). */
+long long pk_mxfp8_packed_row_bytes(int K);
+int pk_pack_weights_mxfp8(const void* weights_bf16, void* packed, long long rows, int K, void* stream);
+
 /* ---------------------------------------------------------------- decode megakernel, generic geometry */
 
 typedef struct PkDecodeModel {

@@ -46,7 +46,8 @@ def decode_step(geometry, weights, token_ids, positions, keys, values, cos_sin_c
     g = geometry
     B = len(token_ids)
     G = g.q_heads // g.kv_heads
-    x = weights["embed"][token_ids].float()                       # [B, H]
+    # input lookup: bf16 embedding rows (kept separately when the tied lm_head matrix is quantised)
+    x = weights.get("embed_lookup", weights["embed"])[token_ids].float()      # [B, H]
     cs = cos_sin_cache.float()
     layer_outs = []
     for l, (n1, qkv_w, o_w, n2, gu_w, down_w) in enumerate(weights["layers"]):

@@ -40,6 +40,8 @@ SYMBOLS = {
     "pk_fused_rmsnorm_residual_forward": (ci, [vp, vp, vp, vp, vp, vp, cf, ci, ci, vp]),
     "pk_fused_rmsnorm_residual_forward_ex": (ci, [vp, vp, vp, vp, vp, vp, vp, cf, ci, ci, ci, vp]),
     "pk_rmsnorm_scale_bytes": (ll, [ci, ci]),
+    "pk_mxfp8_packed_row_bytes": (ll, [ci]),
+    "pk_pack_weights_mxfp8": (ci, [vp, vp, ll, ci, vp]),
     "pk_decode_workspace_bytes": (sz, [ctypes.POINTER(PkDecodeModel), ci]),
     "pk_decode_step": (ci, [ctypes.POINTER(PkDecodeModel), ctypes.POINTER(PkDecodeArgs)]),
     "pk_decode_workspace_init": (ci, [vp, sz, vp]),

@@ -280,3 +280,64 @@ extern "C" int pk_fused_rmsnorm_residual_forward_ex(void* vals, void* scales, fl
 extern "C" long long pk_rmsnorm_scale_bytes(int N, int C) {
     return (long long)((N + 127) / 128) * ((C + 127) / 128) * 512;
 }
+
+// ---------------------------------------------------------------- MXFP8 weight packing
+// Quantises a row-major bf16 matrix [rows, K] with the same per-32 recipe as the activation quantiser
+// (scale = 2^ceil(log2(amax/448)), value = e4m3(bf16(w * 2^-scale))) along K and writes the packed-row
+// format the decode GEMV streams: [K e4m3][K/32 e8m0][zero pad to a multiple of 16 bytes].
+// One warp per row; lane owns whole 32-element groups (group g handled by lane g % 32).
+namespace pk {
+
+__global__ void __launch_bounds__(256) pack_weights_mxfp8_kernel(const uint16_t* __restrict__ w, uint8_t* __restrict__ out,
+                                                                 long long rows, int K, int rowbytes) {
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const uint16_t* src = w + row * K;
+    uint8_t* dst = out + row * rowbytes;
+    const int groups = K >> 5;
+    for (int g = lane; g < groups; g += 32) {
+        const uint4* p = reinterpret_cast<const uint4*>(src + g * 32);
+        uint32_t v[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 q = __ldg(p + i);
+            v[4 * i] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(v[i])), fabsf(bf16_hi(v[i]))));
+        const uint32_t sf = e8m0_roundup(__fmul_rn(amax, 1.f / 448.f));
+        const uint32_t e = 254u - sf;
+        const float inv = __uint_as_float(e ? (e << 23) : 0x00400000u);
+        uint32_t q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            q[i] = e4m3x2(bf16_lo(v[2 * i]) * inv, bf16_hi(v[2 * i]) * inv) |
+                   (e4m3x2(bf16_lo(v[2 * i + 1]) * inv, bf16_hi(v[2 * i + 1]) * inv) << 16);
+        uint4* o = reinterpret_cast<uint4*>(dst + g * 32);
+        o[0] = make_uint4(q[0], q[1], q[2], q[3]);
+        o[1] = make_uint4(q[4], q[5], q[6], q[7]);
+        dst[K + g] = (uint8_t)sf;
+    }
+    for (int i = K + groups + lane; i < rowbytes; i += 32) dst[i] = 0;
+}
+
+}  // namespace pk
+
+extern "C" long long pk_mxfp8_packed_row_bytes(int K) { return K % 32 ? -1 : ((long long)K + K / 32 + 15) / 16 * 16; }
+
+// No counterpart in the reference (it consumes pre-quantised weights, flash_moe/__init__.py:165-170).
+extern "C" int pk_pack_weights_mxfp8(const void* weights_bf16, void* packed, long long rows, int K, void* stream) {
+    using namespace pk;
+    if (rows < 0 || K <= 0 || (K % 32) != 0) return kErrShape;
+    if (rows == 0) return kOk;
+    if (!weights_bf16 || !packed) return kErrNull;
+    if ((reinterpret_cast<uintptr_t>(weights_bf16) % 16) || (reinterpret_cast<uintptr_t>(packed) % 16)) return kErrAlign;
+    const int rowbytes = (int)pk_mxfp8_packed_row_bytes(K);
+    const long long blocks = (rows + 7) / 8;
+    if (blocks > 0x7fffffffLL) return kErrShape;
+    pack_weights_mxfp8_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(weights_bf16), static_cast<uint8_t*>(packed), rows, K, rowbytes);
+    return (int)cudaPeekAtLastError();
+}

@@ -21,7 +21,8 @@ from .._cabi import library, load_ops
 load_ops()
 
 __all__ = ["Geometry", "SMOLLM2_135M", "SMOLLM2_360M", "SMOLLM2_1P7B", "GEOMETRIES", "MAX_BATCH", "MAX_SEQ",
-           "HEAD_DIM", "decode_step", "check_status", "DecodeSession", "workspace_bytes"]
+           "HEAD_DIM", "decode_step", "check_status", "DecodeSession", "workspace_bytes", "pack_matrix_mxfp8", "pack_weights_mxfp8",
+           "unpack_matrix_mxfp8", "packed_row_bytes"]
 
 MAX_BATCH = 4
 MAX_SEQ = 8192
@@ -117,6 +118,44 @@ def _runtime(geometry: Geometry, device: torch.device) -> _Runtime:
     if key not in _runtimes:
         _runtimes[key] = _Runtime(geometry, device)
     return _runtimes[key]
+
+
+def packed_row_bytes(k: int) -> int:
+    return int(library().pk_mxfp8_packed_row_bytes(int(k)))
+
+
+def pack_matrix_mxfp8(w: torch.Tensor) -> torch.Tensor:
+    """Quantise a bf16 CUDA matrix ``[rows, K]`` to the packed MXFP8 row format the decode GEMV streams:
+    ``[K e4m3][K/32 e8m0][zero pad to 16 B]`` per row (uint8 ``[rows, packed_row_bytes(K)]``)."""
+    if w.dtype != torch.bfloat16 or w.dim() != 2 or not w.is_cuda or not w.is_contiguous():
+        raise ValueError("expected a contiguous 2-D BF16 CUDA tensor")
+    rows, k = w.shape
+    rb = packed_row_bytes(k)
+    if rb < 0:
+        raise ValueError("K must be a multiple of 32")
+    out = torch.empty((rows, rb), dtype=torch.uint8, device=w.device)
+    with torch.cuda.device(w.device):
+        rc = library().pk_pack_weights_mxfp8(w.data_ptr(), out.data_ptr(), rows, k,
+                                             torch.cuda.current_stream(w.device).cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"pack_weights_mxfp8 failed: {status_string(rc)}")
+    return out
+
+
+def pack_weights_mxfp8(weights: dict) -> dict:
+    """MXFP8 variant of a weight dict (``embed``, ``layers``, ``final_norm``): every projection matrix and
+    the tied lm_head are packed; norm weights stay bf16; ``embed_lookup`` keeps the bf16 embedding rows."""
+    layers = [(n1, pack_matrix_mxfp8(qkv), pack_matrix_mxfp8(o), n2, pack_matrix_mxfp8(gu), pack_matrix_mxfp8(down))
+              for (n1, qkv, o, n2, gu, down) in weights["layers"]]
+    return {"embed": pack_matrix_mxfp8(weights["embed"]), "embed_lookup": weights["embed"], "layers": layers,
+            "final_norm": weights["final_norm"]}
+
+
+def unpack_matrix_mxfp8(packed: torch.Tensor, k: int) -> torch.Tensor:
+    """Exact bf16 de-quantisation of a packed matrix (plain PyTorch; for checks and oracles)."""
+    vals = packed[:, :k].contiguous().view(torch.float8_e4m3fn).float().view(-1, k // 32, 32)
+    scale = torch.exp2(packed[:, k:k + k // 32].float() - 127.0)
+    return (vals * scale[..., None]).view(-1, k).to(torch.bfloat16)
 
 
 def status_string(rc: int) -> str:

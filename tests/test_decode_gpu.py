@@ -158,3 +158,61 @@ def test_smollm2_135m_against_hf_golden(cuda_device):
                          cos_sin_cache=csd, eps=MK.EPS)
     assert hid.shape == (1, MK.HIDDEN)
     assert (hid[0].float().cpu() - want_hidden[0]).abs().max() <= 2 ** -3
+
+
+def test_mxfp8_weight_packing_is_bit_exact(cuda_device):
+    """Packed MXFP8 rows against the CPU oracle's weight quantiser (bytes and scale bytes)."""
+    from oracle import mxfp8
+    from prime_kernels_b200 import decode as D
+
+    g = torch.Generator().manual_seed(3)
+    for rows, k in [(7, 960), (64, 2560), (33, 32), (5, 8192)]:
+        w = (torch.randn(rows, k, generator=g) * 0.02).to(torch.bfloat16)
+        w[0, :32] = 0                                            # zero group -> scale byte 0
+        packed = D.pack_matrix_mxfp8(w.to(cuda_device)).cpu().numpy()
+        vals, scales = mxfp8.quantise_weight(w.view(torch.int16).numpy().view(np.uint16))
+        assert packed.shape[1] == D.packed_row_bytes(k) and packed.shape[1] % 16 == 0
+        assert np.array_equal(packed[:, :k], vals)
+        assert np.array_equal(packed[:, k:k + k // 32], scales)
+        assert (packed[:, k + k // 32:] == 0).all()
+        deq = D.unpack_matrix_mxfp8(torch.from_numpy(packed), k).float()
+        assert ((deq - w.float()).abs() <= w.float().abs().view(rows, -1, 32).amax(-1, keepdim=True).expand(-1, -1, 32)
+                .reshape(rows, k) * 2 ** -3 + 1e-30).all()
+
+
+@pytest.mark.parametrize("B", [1, 4])
+def test_mxfp8_weights_decode_against_restatement(cuda_device, B):
+    """MXFP8 weights (E4M3 + E8M0 per 32 along K), bf16 activations and KV: the oracle runs the same step on
+    the exactly de-quantised weights."""
+    from prime_kernels_b200 import decode as D
+
+    geom = D.Geometry("mx", 192, 512, 3, 3, 1, 1024, weight_format=1)
+    w = harness.make_weights(geom, 0, norm_weights="random")
+    wd = harness.weights_to(w, cuda_device)
+    wq = D.pack_weights_mxfp8(wd)
+    # oracle weights = exact de-quantisation of the packed bytes
+    wo = {"embed": D.unpack_matrix_mxfp8(wq["embed"], geom.hidden).cpu(), "embed_lookup": w["embed"],
+          "final_norm": w["final_norm"], "layers": []}
+    for (n1, qkv, o, n2, gu, down), (_, qkv_p, o_p, _, gu_p, down_p) in zip(w["layers"], wq["layers"]):
+        wo["layers"].append((n1, D.unpack_matrix_mxfp8(qkv_p, geom.hidden).cpu(), D.unpack_matrix_mxfp8(o_p, geom.q_heads * 64).cpu(),
+                             n2, D.unpack_matrix_mxfp8(gu_p, geom.hidden).cpu(), D.unpack_matrix_mxfp8(down_p, geom.intermediate).cpu()))
+    cs = harness.make_cos_sin_cache(geom, 256)
+    gen = torch.Generator().manual_seed(11)
+    ctx = 70
+    cur = torch.randint(0, geom.vocab, (B,), generator=gen)
+    keys = [[torch.randn(geom.kv_heads, ctx, 64, generator=gen).to(torch.bfloat16) for _ in range(B)] for _ in range(geom.layers)]
+    vals = [[torch.randn(geom.kv_heads, ctx, 64, generator=gen).to(torch.bfloat16) for _ in range(B)] for _ in range(geom.layers)]
+    kv = harness.PagedKV(geom, B, 128, cuda_device)
+    kv.load_prefix([torch.stack(k) for k in keys], [torch.stack(v) for v in vals])
+    for s in range(2):
+        pos = torch.full((B,), ctx + s, dtype=torch.int64)
+        hid, logits, nxt = D.decode_step(geom, input_ids=cur.to(cuda_device), positions=pos.to(cuda_device),
+                                         seq_lens=(pos + 1).to(torch.int32).to(cuda_device), block_table=kv.block_table,
+                                         slot_mapping=kv.slots(pos), embed=wq["embed"], embed_lookup=wq["embed_lookup"],
+                                         layers=wq["layers"], final_norm=wq["final_norm"], kv_caches=kv.kv_caches,
+                                         cos_sin_cache=cs.to(cuda_device), eps=geom.eps, lm_head=True)
+        D.check_status(geom, cuda_device)
+        rh, rl, _ = R.decode_step(geom, wo, cur, pos, keys, vals, cs)
+        assert (logits.cpu().float() - rl).abs().max() <= LOGIT_TOL
+        assert (hid.cpu().float() - rh.float()).abs().max() <= 2 ** -4
+        cur = rl.argmax(-1)
