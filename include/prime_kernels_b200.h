@@ -86,6 +86,21 @@ int pk_decode_workspace_init(void* workspace, size_t bytes, void* stream);
 void pk_decode_workspace_forget(void* workspace);
 /* Synchronise `stream` and return the device-side status word (9110 = a bounded wait gave up). */
 int pk_decode_status(void* workspace, void* stream);
+/* Decode step for callers that cannot allocate device memory.  No counterpart in the reference (its
+ * Python surface always allocates the scratch with torch).  Inference servers usually give all memory
+ * left after start-up to their KV-cache pool, and some embedders run where the CUDA allocator must not
+ * be called; for them the library holds a scratch area of its own, a 2 MiB device array that every GPU
+ * loading the library keeps until the process exits.  Same arguments as pk_decode_step except that
+ * args->workspace / workspace_bytes are ignored.  Status 9112 when the step needs more than
+ * pk_decode_static_scratch_bytes() (fits: SmolLM2-360M at batch 1, SmolLM2-135M up to batch 2).
+ * The first call on a device resolves the array's device address: make it before any stream capture.
+ * All calls on a device share the array (it keeps the previous call's contents; status and completion
+ * words are cleared per call), so calls that overlap on the GPU race -- serialise them.
+ * Nothing on this path calls cudaMalloc, cudaFree or an allocating library routine. */
+int pk_decode_step_static(const PkDecodeModel* model, const PkDecodeArgs* args);
+size_t pk_decode_static_scratch_bytes(void);
+/* Synchronise `stream` and return the status word of the built-in scratch of the current device. */
+int pk_decode_static_status(void* stream);
 /* Generic form of mk_query (prime_kernels/decode_megakernel/csrc/megakernel.cu:833-836). */
 int pk_decode_query(int* sm_count, int* coop, int* major, int* minor, int* smem_optin, int* threads,
                     int* consumer_warps);

@@ -44,6 +44,9 @@ SYMBOLS = {
     "pk_pack_weights_mxfp8": (ci, [vp, vp, ll, ci, vp]),
     "pk_decode_workspace_bytes": (sz, [ctypes.POINTER(PkDecodeModel), ci]),
     "pk_decode_step": (ci, [ctypes.POINTER(PkDecodeModel), ctypes.POINTER(PkDecodeArgs)]),
+    "pk_decode_step_static": (ci, [ctypes.POINTER(PkDecodeModel), ctypes.POINTER(PkDecodeArgs)]),
+    "pk_decode_static_scratch_bytes": (sz, []),
+    "pk_decode_static_status": (ci, [vp]),
     "pk_decode_workspace_init": (ci, [vp, sz, vp]),
     "pk_decode_workspace_forget": (None, [vp]),
     "pk_decode_status": (ci, [vp, vp]),

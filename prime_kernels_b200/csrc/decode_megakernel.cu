@@ -1694,6 +1694,7 @@ static const char* status_string(int status) {
         case kErrBlock: return "block_size_or_stride_invalid";
         case kErrBarrierTimeout: return "device_wait_timed_out";
         case kErrShape: return "unsupported_model_geometry";
+        case kErrStaticScratch: return "request_needs_more_than_the_2_MiB_built_in_scratch";
         default: return cudaGetErrorString(static_cast<cudaError_t>(status));
     }
 }
@@ -1867,3 +1868,82 @@ extern "C" int decode360(void* stream, int B, const void* input_ids, const void*
 }
 
 extern "C" const char* decode360_status_string(int status) { return status_string(status); }
+
+// ---- decode step for callers that must not allocate device memory ------------------------------
+// The workspace of pk_decode_step normally comes from the caller (the Python surface allocates it with
+// torch).  Inference servers typically hand every byte that is left after start-up to their KV-cache
+// pool, and some embedders call the C ABI from places where the CUDA allocator is off limits (for
+// example a pre-sized arena with no allocator behind it); neither can produce a scratch buffer later.
+// For them the library carries a small scratch area of its own: a file-scope device array, resident on
+// every GPU that loads the library until the process exits.
+//
+// Limits and rules:
+//  * the step's workspace must fit kStaticScratchBytes (2 MiB): SmolLM2-360M at batch 1 and SmolLM2-135M
+//    up to batch 2 fit, SmolLM2-1.7B does not; larger requests are refused with status 9112;
+//  * the first call on a device looks the array's device address up (cudaGetSymbolAddress, with that
+//    device current) and remembers it; make that first call outside any stream capture;
+//  * all calls on a device share the one array.  It keeps what the previous call left (the launch epoch
+//    must survive from call to call); the status and completion words are cleared in stream order on
+//    every call.  Calls that overlap on the GPU (different streams) race on it: serialise them;
+//  * nothing on this path calls cudaMalloc, cudaFree or any allocating library routine.
+namespace pk {
+constexpr size_t kStaticScratchBytes = size_t(2) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static std::unordered_map<int, void*> g_static_scratch_addr;   // device ordinal -> device address
+}  // namespace pk
+
+extern "C" size_t pk_decode_static_scratch_bytes() { return kStaticScratchBytes; }
+
+extern "C" int pk_decode_step_static(const PkDecodeModel* m, const PkDecodeArgs* a) {
+    if (!m || !a) return kErrNull;
+    if (m->kv_heads <= 0 || a->batch < 1) return kErrBatch;
+    const ModelGeom g = to_geom(m);
+    if (ws_layout(g, a->batch).total > kStaticScratchBytes) return kErrStaticScratch;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    void* ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        auto it = g_static_scratch_addr.find(dev);
+        if (it == g_static_scratch_addr.end()) {
+            // In host code the array's name is only a handle; the kernel needs its device address.
+            e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+            if (e != cudaSuccess) return (int)e;
+            g_static_scratch_addr[dev] = ptr;
+            g_ws_ready[ptr] = kStaticScratchBytes;   // zero-initialised at module load: no first-use memset
+        } else {
+            ptr = it->second;
+        }
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+    // status and completion counter start every call at zero; the epoch word before them is kept
+    e = cudaMemsetAsync(static_cast<unsigned int*>(ptr) + kCtrlStatus, 0, 2 * sizeof(unsigned int), stream);
+    if (e != cudaSuccess) return (int)e;
+    StepArgs s{stream, a->batch, a->input_ids, a->ids_i64, a->positions, a->seq_lens, a->block_table, a->bt_stride,
+               a->slot_mapping, a->layers, a->embed, a->embed_lookup, a->final_norm, a->kv_layers, a->k_off, a->v_off,
+               a->block_stride, a->token_stride, a->head_stride, a->block_size, a->cos_sin, a->cs_fp32, a->out_hidden,
+               a->logits, a->next_ids, a->layer_outputs, ptr, kStaticScratchBytes, a->max_seq_len, a->lm_head, a->advance};
+    return decode_launch(g, s);
+}
+
+// Status word of the built-in scratch on the current device (synchronises `stream`).
+extern "C" int pk_decode_static_status(void* stream) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    void* ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        auto it = g_static_scratch_addr.find(dev);
+        if (it == g_static_scratch_addr.end()) return 0;
+        ptr = it->second;
+    }
+    unsigned int word = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    e = cudaMemcpyAsync(&word, static_cast<unsigned int*>(ptr) + kCtrlStatus, sizeof(word), cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return (int)e;
+    return (int)word;
+}

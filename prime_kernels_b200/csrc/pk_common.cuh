@@ -22,6 +22,7 @@ enum Status : int {
     kErrBlock = 9109,       // KV block size / stride invalid
     kErrBarrierTimeout = 9110,  // a bounded device-side wait gave up
     kErrShape = 9111,       // unsupported geometry
+    kErrStaticScratch = 9112,   // request does not fit the library's built-in scratch area
 };
 
 // ---- bf16 <-> fp32 bit helpers (bf16 carried as the high half of an fp32 pattern) ----
