@@ -57,8 +57,28 @@ __device__ __forceinline__ uint32_t e4m3x2(float lo, float hi) {
     return r;
 }
 
+// d = a * b + c per packed bf16 half (a, b: two bf16 each; product exact, fp32 add, one rounding) with the
+// sm_100 mixed-precision FMA -- no unpacking of the bf16 operands.
+__device__ __forceinline__ void fma2_bf16(uint32_t a, uint32_t b, float c_lo, float c_hi, float& d_lo, float& d_hi) {
+    asm("{\n.reg .b16 al, ah, bl, bh;\nmov.b32 {al, ah}, %2;\nmov.b32 {bl, bh}, %3;\n"
+        "fma.rn.f32.bf16 %0, al, bl, %4;\nfma.rn.f32.bf16 %1, ah, bh, %5;\n}"
+        : "=f"(d_lo), "=f"(d_hi)
+        : "r"(a), "r"(b), "f"(c_lo), "f"(c_hi));
+}
+__device__ __forceinline__ uint32_t abs_bf16x2(uint32_t a) {
+    uint32_t r;
+    asm("abs.bf16x2 %0, %1;" : "=r"(r) : "r"(a));
+    return r;
+}
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+constexpr uint32_t kOnesBf16x2 = 0x3f803f80u;
+
 template <int U>
-__global__ void __launch_bounds__(512) rmsnorm_mxfp8_kernel(const RmsParams p) {
+__global__ void __launch_bounds__(256, U == 4 ? 4 : 2) rmsnorm_mxfp8_kernel(const RmsParams p) {
     extern __shared__ float red_s[];   // [rows_per_block][W]
     const int W = p.warps_per_row;
     const int T = W * 32;
@@ -71,7 +91,7 @@ __global__ void __launch_bounds__(512) rmsnorm_mxfp8_kernel(const RmsParams p) {
     const bool live = row < p.n;
 
     uint4 br[U], rs[U], wt[U];
-    float ss = 0.f;
+    float ss = 0.f, ss2 = 0.f;
     if (live) {
         const uint4* bp = p.branch + (size_t)row * nch;
         const uint4* rp = p.residual + (size_t)row * nch;
@@ -94,23 +114,23 @@ __global__ void __launch_bounds__(512) rmsnorm_mxfp8_kernel(const RmsParams p) {
             if (c < nch) {
                 uint32_t a[4] = {br[i].x, br[i].y, br[i].z, br[i].w};
                 if (p.mode) {
+                    // sum = bf16(branch + residual): both addends exact in fp32, one rounding
                     const uint32_t r4[4] = {rs[i].x, rs[i].y, rs[i].z, rs[i].w};
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        a[k] = pack_bf16x2(__fadd_rn(bf16_lo(a[k]), bf16_lo(r4[k])),
-                                           __fadd_rn(bf16_hi(a[k]), bf16_hi(r4[k])));
+                    for (int k = 0; k < 4; ++k) {
+                        float lo, hi;
+                        fma2_bf16(r4[k], kOnesBf16x2, 0.f, 0.f, lo, hi);
+                        fma2_bf16(a[k], kOnesBf16x2, lo, hi, lo, hi);
+                        a[k] = pack_bf16x2(lo, hi);
+                    }
                     br[i] = make_uint4(a[0], a[1], a[2], a[3]);
                 }
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float lo = bf16_lo(a[k]), hi = bf16_hi(a[k]);
-                    ss = fmaf(lo, lo, ss);
-                    ss = fmaf(hi, hi, ss);
-                }
+                for (int k = 0; k < 4; ++k) fma2_bf16(a[k], a[k], ss, ss2, ss, ss2);
             }
         }
     }
-    ss = warp_sum(ss);
+    ss = warp_sum(ss + ss2);
     if (W > 1) {
         if (lane == 0) red_s[team * W + warp_in_team] = ss;
         __syncthreads();
@@ -126,44 +146,44 @@ __global__ void __launch_bounds__(512) rmsnorm_mxfp8_kernel(const RmsParams p) {
     for (int i = 0; i < U; ++i) {
         const int c = tt + i * T;
         const bool has = live && c < nch;       // uniform over each aligned group of 4 lanes
-        float v[8];
-        float amax = 0.f;
+        uint32_t packed[4] = {0u, 0u, 0u, 0u};
+        uint32_t amax2 = 0u;                    // packed bf16 pair, both halves >= 0
         if (has) {
             const uint32_t a[4] = {br[i].x, br[i].y, br[i].z, br[i].w};
             const uint32_t r4[4] = {rs[i].x, rs[i].y, rs[i].z, rs[i].w};
             const uint32_t w4[4] = {wt[i].x, wt[i].y, wt[i].z, wt[i].w};
-            uint32_t packed[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const float pl = __fmul_rn(bf16_lo(a[k]), bf16_lo(w4[k]));   // exact
-                const float ph = __fmul_rn(bf16_hi(a[k]), bf16_hi(w4[k]));
+                float pl, ph;
+                fma2_bf16(a[k], w4[k], 0.f, 0.f, pl, ph);          // exact bf16 x bf16 products
                 float ol = __fmul_rn(s, pl), oh = __fmul_rn(s, ph);
-                if (!p.mode) {
-                    ol = __fadd_rn(ol, bf16_lo(r4[k]));
-                    oh = __fadd_rn(oh, bf16_hi(r4[k]));
-                }
+                // residual added after the norm in fp32 (r * 1 + x: exact product, one rounding, the same
+                // as widening r and adding; never contracted with the multiply above)
+                if (!p.mode) fma2_bf16(r4[k], kOnesBf16x2, ol, oh, ol, oh);
                 packed[k] = pack_bf16x2(ol, oh);
-                v[2 * k] = bf16_lo(packed[k]);
-                v[2 * k + 1] = bf16_hi(packed[k]);
+                amax2 = max_bf16x2(amax2, abs_bf16x2(packed[k]));
             }
             if (p.res_out) {
                 const uint4 o = p.mode ? br[i] : make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 st_stream_16(p.res_out + ((size_t)row * nch + c) * 8, o);
             }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
         }
         // group amax over the 4 lanes of a 32-element group (executed by the whole warp)
+        float amax = fmaxf(bf16_lo(amax2), bf16_hi(amax2));
         amax = fmaxf(amax, __shfl_xor_sync(kFullMask, amax, 1));
         amax = fmaxf(amax, __shfl_xor_sync(kFullMask, amax, 2));
         uint32_t sf = 0;
         if (has) {
             sf = e8m0_roundup(__fmul_rn(amax, 1.f / 448.f));
             const uint32_t e = 254u - sf;
-            const float inv = __uint_as_float(e ? (e << 23) : 0x00400000u);   // 2^(127 - sf)
+            const uint32_t invb = e ? (e << 7) : 0x0040u;          // bf16 bits of 2^(127 - sf)
+            const uint32_t inv2 = invb | (invb << 16);
+            float v[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) fma2_bf16(packed[k], inv2, 0.f, 0.f, v[2 * k], v[2 * k + 1]);   // exact scaling
             uint2 q;
-            q.x = e4m3x2(v[0] * inv, v[1] * inv) | (e4m3x2(v[2] * inv, v[3] * inv) << 16);
-            q.y = e4m3x2(v[4] * inv, v[5] * inv) | (e4m3x2(v[6] * inv, v[7] * inv) << 16);
+            q.x = e4m3x2(v[0], v[1]) | (e4m3x2(v[2], v[3]) << 16);
+            q.y = e4m3x2(v[4], v[5]) | (e4m3x2(v[6], v[7]) << 16);
             st_stream_8(p.vals + ((size_t)row * nch + c) * 8, q);
         }
         // four consecutive groups (16 lanes) -> one 32-bit store of scale bytes; groups past the
@@ -185,18 +205,15 @@ __global__ void __launch_bounds__(512) rmsnorm_mxfp8_kernel(const RmsParams p) {
 static int launch_rmsnorm(const RmsParams& p0, cudaStream_t stream) {
     RmsParams p = p0;
     const int nch = p.c / 8;
-    int U = 4;
-    int W = (nch + 32 * U - 1) / (32 * U);
-    if (W > 16) {
-        U = 8;
-        W = (nch + 32 * U - 1) / (32 * U);
-    }
-    if (W > 16) return kErrShape;
-    // teams must tile the block exactly: W in {1,2,4,8,16} after rounding up to a power of two
+    // a team is at most 8 warps (256 threads): 4 chunks per thread up to C = 8192, 8 chunks up to 16384
+    int U = nch <= 1024 ? 4 : 8;
+    const int W = (nch + 32 * U - 1) / (32 * U);
+    if (W > 8) return kErrShape;
+    // teams must tile the block exactly: W rounded up to a power of two
     int Wp = 1;
     while (Wp < W) Wp <<= 1;
     p.warps_per_row = Wp;
-    p.rows_per_block = (Wp * 32 >= 256) ? 1 : 256 / (Wp * 32);
+    p.rows_per_block = 8 / Wp;
     const int threads = p.rows_per_block * Wp * 32;
     const int grid = (p.n_pad + p.rows_per_block - 1) / p.rows_per_block;
     if (grid == 0) return kOk;
