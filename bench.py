@@ -95,6 +95,8 @@ def cpu_reference(geom, batch, prompt_len, sample_steps, seed=1234):
     from oracle import decode_hf
     from prime_kernels_b200 import harness
 
+    # all host cores (torchrun pins OMP_NUM_THREADS=1 in its children; undo that for the CPU arm)
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)))
     weights = harness.make_weights(geom, 0)
     prompt = torch.randint(0, geom.vocab, (batch, prompt_len), generator=torch.Generator().manual_seed(seed))
     res = decode_hf.run(geom, weights, prompt, sample_steps)
