@@ -87,6 +87,26 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
+def max_over_ranks(values, world, device="cpu"):
+    """Element-wise maximum of `values` (list of floats) over all ranks of the default process group;
+    with one rank it is the identity.  The timings of a replica run are reduced with this, so the
+    reported throughput is bounded by the slowest replica."""
+    import torch
+
+    t = torch.tensor(values, dtype=torch.float64, device=device)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def aggregate_throughput(world, batch, steps, ms_max):
+    """Whole-job tokens/s of `world` independent replicas that each decoded `steps` tokens for `batch`
+    requests within `ms_max` milliseconds (the slowest replica's time)."""
+    return world * batch * steps / (ms_max * 1e-3)
+
+
 def cpu_reference(geom, batch, prompt_len, sample_steps, seed=1234):
     """HuggingFace eager bf16 decode on the host cores: prefill the prompt, then time `sample_steps`
     decode steps.  Returns (tok/s, threads, description)."""
@@ -263,10 +283,7 @@ def main():
 
     e2e_s = float("nan") if args.no_e2e else run_e2e()
 
-    times = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_max, e2e_ms_max = times.tolist()
+    ms_max, e2e_ms_max = max_over_ranks([ms, e2e_s * 1e3], world, dev)
 
     if rank == 0:
         peaks_file = ROOT / "MEASURED_PEAKS.json"
@@ -278,7 +295,7 @@ def main():
         step_ms = ms_max / K
         achieved = mean_bytes / (step_ms * 1e-3) / 1e9
         line = {
-            "metric": METRIC, "value": world * batch * K / (ms_max * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "metric": METRIC, "value": aggregate_throughput(world, batch, K, ms_max), "unit": "tok/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": wl, "geometry": gname, "batch": batch, "prompt_tokens": prompt_len,
@@ -288,7 +305,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": peak_src, "frac_of_8TBs_nominal": achieved / 8000.0,
                          "algorithmic_bytes_per_step": mean_bytes},
-            "e2e": {"value": None if args.no_e2e else world * batch * K / (e2e_ms_max * 1e-3), "unit": "tok/s",
+            "e2e": {"value": None if args.no_e2e else aggregate_throughput(world, batch, K, e2e_ms_max), "unit": "tok/s",
                     "h2d_bytes_per_step": batch * (8 + 8 + 4 + 8), "d2h_bytes_per_step": batch * 8},
             "gpu_launches": K,
             "clocks": clocks.summary(),

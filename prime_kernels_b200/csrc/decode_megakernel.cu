@@ -274,10 +274,11 @@ __device__ __forceinline__ void wait_flagged_multi(Ctx& c, PtrFn ptr, uint32_t t
     }
 }
 
-// Up to 4 words at indices first, first+stride, ... (< n).
-__device__ __forceinline__ void wait_flagged_strided4(Ctx& c, const unsigned long long* base, int first, int stride,
-                                                      int n, uint32_t tag, uint32_t (&out)[4]) {
-    wait_flagged_multi<4>(
+// Up to N words at indices first, first+stride, ... (< n), fetched in one round.
+template <int N>
+__device__ __forceinline__ void wait_flagged_strided(Ctx& c, const unsigned long long* base, int first, int stride,
+                                                     int n, uint32_t tag, uint32_t (&out)[N]) {
+    wait_flagged_multi<N>(
         c, [&](int u) { const int idx = first + u * stride; return idx < n ? base + idx : nullptr; }, tag, out);
 }
 
@@ -673,19 +674,19 @@ __device__ void stage_norm(Ctx& c, const unsigned long long* src_words, uint32_t
 #pragma unroll
     for (int b = 0; b < B; ++b) {
         ss[b] = 0.f;
-        for (int i0 = ct; i0 < H; i0 += 4 * kCT) {
-            uint32_t xv[4];
+        for (int i0 = ct; i0 < H; i0 += 8 * kCT) {
+            uint32_t xv[8];
             if (from_embed) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < 8; ++u) {
                     const int i = i0 + u * kCT;
                     xv[u] = i < H ? (uint32_t)p.embed_bf16[(size_t)sh.tok[b] * H + i] : 0u;
                 }
             } else {
-                wait_flagged_strided4(c, src_words + b * H, i0, kCT, H, tag, xv);
+                wait_flagged_strided<8>(c, src_words + b * H, i0, kCT, H, tag, xv);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 const int i = i0 + u * kCT;
                 if (i < H) {
                     const float x = __uint_as_float(xv[u] << 16);
@@ -729,7 +730,7 @@ __device__ void stage_copy(Ctx& c, const unsigned long long* src_words, uint32_t
         for (int b = 0; b < B; ++b)
             for (int i0 = ct; i0 < nw; i0 += 4 * kCT) {
                 uint32_t v[4];
-                wait_flagged_strided4(c, src_words + b * nw, i0, kCT, nw, tag, v);
+                wait_flagged_strided<4>(c, src_words + b * nw, i0, kCT, nw, tag, v);
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
                     if (i0 + u * kCT < nw) act32[(size_t)b * (p.act_elems >> 1) + i0 + u * kCT] = v[u];
@@ -737,11 +738,11 @@ __device__ void stage_copy(Ctx& c, const unsigned long long* src_words, uint32_t
     } else {
         uint16_t* act16 = reinterpret_cast<uint16_t*>(c.act);
         for (int b = 0; b < B; ++b)
-            for (int i0 = ct; i0 < n; i0 += 4 * kCT) {
-                uint32_t v[4];
-                wait_flagged_strided4(c, src_words + b * n, i0, kCT, n, tag, v);
+            for (int i0 = ct; i0 < n; i0 += 16 * kCT) {
+                uint32_t v[16];
+                wait_flagged_strided<16>(c, src_words + b * n, i0, kCT, n, tag, v);
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
+                for (int u = 0; u < 16; ++u)
                     if (i0 + u * kCT < n) act16[(size_t)b * p.act_elems + i0 + u * kCT] = (uint16_t)v[u];
             }
     }
@@ -793,7 +794,7 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
 
     // K/V fetch of kPB positions per lane group; st: 0 = out of range, 1 = from the cache,
     // 2 = the new token (taken from registers).
-    constexpr int kPB = 4;
+    constexpr int kPB = 2;
     auto fetch = [&](int it, uint4* kk, uint4* vv, int* st) {
 #pragma unroll
         for (int u = 0; u < kPB; ++u) {
@@ -826,11 +827,26 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
     static_assert(kPartWords + 2 * (G + 2) * kD <= kAttnScratchWords, "attention scratch too small");
     float* raw_s = c.attn + kPartWords;
     float* rot_s = raw_s + (G + 2) * kD;
-    for (int t = threadIdx.x; t < (G + 2) * kD; t += kCT) {
-        const int which = t / kD, d = t % kD;     // which: 0..G-1 = q head, G = k, G+1 = v
-        const int row = which < G ? (kvh * G + which) * kD + d
-                                  : (which == G ? (p.QH + kvh) * kD + d : (p.QH + p.KVH + kvh) * kD + d);
-        raw_s[t] = __uint_as_float(wait_flagged(c, qkv + row, tag) << 16);
+    {
+        constexpr int kPer = ((G + 2) * kD + kCT - 1) / kCT;      // words per thread
+        auto word_row = [&](int t) {
+            const int which = t / kD, d = t % kD;     // which: 0..G-1 = q head, G = k, G+1 = v
+            return which < G ? (kvh * G + which) * kD + d
+                             : (which == G ? (p.QH + kvh) * kD + d : (p.QH + p.KVH + kvh) * kD + d);
+        };
+        uint32_t bits[kPer];
+        wait_flagged_multi<kPer>(
+            c,
+            [&](int u) -> const unsigned long long* {
+                const int t = (int)threadIdx.x + u * kCT;
+                return t < (G + 2) * kD ? qkv + word_row(t) : nullptr;
+            },
+            tag, bits);
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int t = (int)threadIdx.x + u * kCT;
+            if (t < (G + 2) * kD) raw_s[t] = __uint_as_float(bits[u] << 16);
+        }
     }
     consumer_bar();
     if (c.prof) c.prof[11] = global_ns();
