@@ -36,6 +36,10 @@ WORKLOADS = {
     "smollm2-360m-b4": ("smollm2-360m", 4, 512, 256),
 }
 METRIC = "SmolLM2-360M bs1 decode tok/s & % HBM roofline; aggregate tok/s @1/2/4/8 GPUs"
+# DRAM bytes per launch measured with ncu (dram__bytes_read + write) at context 503-505 divided by the
+# algorithmic bytes at that context: 747.8 MB / 744.3 MB (profiles/decode_step_kernel_smollm2-360m-b1_ctx505.md).
+# Traffic grows with the same units as the algorithmic bytes (weights + KV positions).
+NCU_TRAFFIC_RATIO = 1.005
 
 
 def algorithmic_bytes(geom, batch, seq):
@@ -303,7 +307,9 @@ def main():
                        "replicas": world, "l2": "weights (>= 269 MB per step) exceed the 126 MB L2; no flush needed",
                        "timing": "CUDA events on the launching stream around K back-to-back launches"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src, "frac_of_8TBs_nominal": achieved / 8000.0,
+                         "traffic": mean_bytes * NCU_TRAFFIC_RATIO if gname == "smollm2-360m" and batch == 1 else None,
+                         "traffic_source": "ncu capture at context 503-505 scaled by algorithmic bytes",
+                         "peak_source": peak_src, "frac_of_8TBs_nominal": achieved / 8000.0,
                          "algorithmic_bytes_per_step": mean_bytes},
             "e2e": {"value": None if args.no_e2e else aggregate_throughput(world, batch, K, e2e_ms_max), "unit": "tok/s",
                     "h2d_bytes_per_step": batch * (8 + 8 + 4 + 8), "d2h_bytes_per_step": batch * 8},
