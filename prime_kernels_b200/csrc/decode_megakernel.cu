@@ -45,7 +45,8 @@ constexpr int kCT = kNW * 32;              // consumer threads
 constexpr int kThreads = kCT + 32;         // + one producer warp
 constexpr int kD = 64;                     // head dim (fixed)
 constexpr int kE = 8;                      // ring entries in flight per consumer warp
-constexpr int kRMax = 4;                   // max weight rows staged per ring entry
+// max weight rows staged per ring entry (8 was measured slower: more registers live across the phase)
+__host__ __device__ constexpr int row_cap(int) { return 4; }
 constexpr int kMaxB = 8;
 constexpr int kNCMax = 64;                 // max split-KV chunks per (request, kv head)
 constexpr int kMaxSeq = 8192;
@@ -489,8 +490,8 @@ __device__ __forceinline__ uint32_t layer_tag(const Ctx& c, int layer) { return 
 // as independent chains (two accumulators per row and request).
 template <int B, int NR>
 __device__ __forceinline__ void gemv_rows_bf16(const uint4* ep, int sc, const uint4* act, int actc, int kc0, int lane,
-                                               float (&acc)[kRMax][B], float (&acc2)[kRMax][B]) {
-    constexpr int U = (NR * B <= 2) ? 4 : 2;     // lane-chunks in flight; bounded by the register budget
+                                               float (&acc)[row_cap(B)][B], float (&acc2)[row_cap(B)][B], int nlive = NR) {
+    constexpr int U = (NR * B <= 2) ? 4 : (NR * B <= 8 ? 2 : 1);     // lane-chunks in flight; bounded by the register budget
     for (int it0 = 0; it0 < sc; it0 += 32 * U) {
         uint4 av[U][B], wv[NR][U];
 #pragma unroll
@@ -500,7 +501,7 @@ __device__ __forceinline__ void gemv_rows_bf16(const uint4* ep, int sc, const ui
 #pragma unroll
             for (int b = 0; b < B; ++b) av[u][b] = ok ? act[b * actc + kc0 + ch] : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-            for (int r = 0; r < NR; ++r) wv[r][u] = ok ? ep[r * sc + ch] : make_uint4(0u, 0u, 0u, 0u);
+            for (int r = 0; r < NR; ++r) wv[r][u] = (ok && r < nlive) ? ep[r * sc + ch] : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u)
@@ -517,7 +518,7 @@ __device__ __forceinline__ void gemv_rows_bf16(const uint4* ep, int sc, const ui
 // MXFP8 packed rows: [K e4m3][K/32 e8m0][pad to 16 B]; one lane-chunk = 16 values, scale per 32.
 template <int B, int NR>
 __device__ __forceinline__ void gemv_rows_mxfp8(const uint4* ep, int rc, int kact, const uint4* act, int actc, int lane,
-                                                float (&acc)[kRMax][B], float (&acc2)[kRMax][B]) {
+                                                float (&acc)[row_cap(B)][B], float (&acc2)[row_cap(B)][B], int nlive = NR) {
     const int vc = kact >> 4;
     for (int it0 = 0; it0 < vc; it0 += 64) {
 #pragma unroll
@@ -532,6 +533,7 @@ __device__ __forceinline__ void gemv_rows_mxfp8(const uint4* ep, int rc, int kac
                 }
 #pragma unroll
                 for (int r = 0; r < NR; ++r) {
+                    if (r >= nlive) continue;
                     const uint4 wq = ep[r * rc + ch];
                     const unsigned char sb = reinterpret_cast<const unsigned char*>(ep + r * rc)[kact + (ch >> 1)];
                     const float scale = __uint_as_float(sb ? ((uint32_t)sb << 23) : 0x00400000u);
@@ -563,9 +565,10 @@ __device__ void gemv_phase(Ctx& c, const int T, int layer, uint32_t& consumed) {
     const bool kPair = (T == kGU);
     for (int row = ra; row < rb; row += d.rows_per_entry) {
         const int nre = min(d.rows_per_entry, rb - row);
-        float acc[kRMax][B], acc2[kRMax][B];
+        constexpr int RM = row_cap(B);
+        float acc[RM][B], acc2[RM][B];
 #pragma unroll
-        for (int i = 0; i < kRMax; ++i)
+        for (int i = 0; i < RM; ++i)
 #pragma unroll
             for (int b = 0; b < B; ++b) acc[i][b] = acc2[i][b] = 0.f;
         for (int seg = 0; seg < d.nseg; ++seg) {
@@ -582,14 +585,26 @@ __device__ void gemv_phase(Ctx& c, const int T, int layer, uint32_t& consumed) {
                     case 1: gemv_rows_bf16<B, 1>(ep, sc, c.act, actc, kc0, lane, acc, acc2); break;
                     case 2: gemv_rows_bf16<B, 2>(ep, sc, c.act, actc, kc0, lane, acc, acc2); break;
                     case 3: gemv_rows_bf16<B, 3>(ep, sc, c.act, actc, kc0, lane, acc, acc2); break;
-                    default: gemv_rows_bf16<B, 4>(ep, sc, c.act, actc, kc0, lane, acc, acc2); break;
+                    case 4: gemv_rows_bf16<B, 4>(ep, sc, c.act, actc, kc0, lane, acc, acc2); break;
+                    default:
+                        if constexpr (RM > 4) {
+                            if (nmem <= 6) gemv_rows_bf16<B, 6>(ep, sc, c.act, actc, kc0, lane, acc, acc2, nmem);
+                            else gemv_rows_bf16<B, 8>(ep, sc, c.act, actc, kc0, lane, acc, acc2, nmem);
+                        }
+                        break;
                 }
             } else {
                 switch (nmem) {
                     case 1: gemv_rows_mxfp8<B, 1>(ep, d.kchunks, d.kact, c.act, actc, lane, acc, acc2); break;
                     case 2: gemv_rows_mxfp8<B, 2>(ep, d.kchunks, d.kact, c.act, actc, lane, acc, acc2); break;
                     case 3: gemv_rows_mxfp8<B, 3>(ep, d.kchunks, d.kact, c.act, actc, lane, acc, acc2); break;
-                    default: gemv_rows_mxfp8<B, 4>(ep, d.kchunks, d.kact, c.act, actc, lane, acc, acc2); break;
+                    case 4: gemv_rows_mxfp8<B, 4>(ep, d.kchunks, d.kact, c.act, actc, lane, acc, acc2); break;
+                    default:
+                        if constexpr (RM > 4) {
+                            if (nmem <= 6) gemv_rows_mxfp8<B, 6>(ep, d.kchunks, d.kact, c.act, actc, lane, acc, acc2, nmem);
+                            else gemv_rows_mxfp8<B, 8>(ep, d.kchunks, d.kact, c.act, actc, lane, acc, acc2, nmem);
+                        }
+                        break;
                 }
             }
             __syncwarp();
@@ -597,53 +612,57 @@ __device__ void gemv_phase(Ctx& c, const int T, int layer, uint32_t& consumed) {
             ++consumed;
             if (T == kGU && c.prof) c.prof[17] = global_ns();
         }
-        // warp-reduce every accumulator, then lane i finishes row i
+        // warp-reduce every accumulator; then lane i finishes row i -- all rows at once, each lane picking
+        // its row's sums with selects (no divergent per-row branches, no dynamic register indexing)
 #pragma unroll
-        for (int i = 0; i < kRMax; ++i)
+        for (int i = 0; i < RM; ++i)
 #pragma unroll
             for (int b = 0; b < B; ++b) acc[i][b] = warp_sum(acc[i][b] + acc2[i][b]);
         if (T == kGU && c.prof) c.prof[18] = global_ns();
+        float mine[B], mine_up[B];
 #pragma unroll
-        for (int i = 0; i < kRMax; ++i) {
-            if (i < nre && lane == i) {
-                const int r = row + i;
+        for (int b = 0; b < B; ++b) {
+            mine[b] = mine_up[b] = 0.f;
 #pragma unroll
-                for (int b = 0; b < B; ++b) {
-                    if (T == kQKV) {
-                        // projection output rounded to bf16 (HF linear output dtype)
-                        st_flagged(p.ll_qkv + (size_t)par * B * d.nrows + b * d.nrows + r,
-                                   f32_to_bf16_bits(acc[i][b]), tag);
-                    } else if (T == kO) {
-                        // h1 = bf16( x + bf16(o_proj) )
-                        const float o = round_bf16(acc[i][b]);
-                        const float h = round_bf16(__fadd_rn(c.res[b * p.H + r], o));
-                        st_flagged(p.ll_h1 + (size_t)par * B * p.H + b * p.H + r, f32_to_bf16_bits(h), tag);
-                    } else if (T == kGU) {
-                        // act = bf16( bf16(silu(bf16 gate)) * bf16 up )   (HF LlamaMLP rounding)
-                        const float g = round_bf16(acc[i][b]);
-                        // up row of pair i sits right after the nre gate rows: static selects, no dynamic register index
-                        const float upv = nre == 1 ? acc[1][b] : acc[(i + 2) & (kRMax - 1)][b];
-                        const float u = round_bf16(upv);
-                        const float silu = round_bf16(__fdividef(g, 1.f + __expf(-g)));
-                        const float a = round_bf16(__fmul_rn(silu, u));
-                        st_flagged(p.ll_act + (size_t)par * B * p.I + b * p.I + r, f32_to_bf16_bits(a), tag);
-                    } else if (T == kDown) {
-                        // x' = bf16( h1 + bf16(down_proj) ), handed to the next layer's parity slot
-                        const float dn = round_bf16(acc[i][b]);
-                        const uint32_t xb = f32_to_bf16_bits(__fadd_rn(c.res[b * p.H + r], dn));
-                        st_flagged(p.ll_x + (size_t)((layer + 1) & 1) * B * p.H + b * p.H + r, xb,
-                                   layer_tag(c, layer + 1));
-                        if (p.layer_outputs) p.layer_outputs[((size_t)layer * B + b) * p.H + r] = (uint16_t)xb;
-                    } else {
-                        // logits rounded to bf16; argmax breaks ties toward the lowest index
-                        const uint32_t lb = f32_to_bf16_bits(acc[i][b]);
-                        if (p.logits) p.logits[(size_t)b * p.V + r] = (uint16_t)lb;
-                        if (p.next_ids) {
-                            const uint32_t ord = (lb & 0x8000u) ? (~lb & 0xffffu) : (lb | 0x8000u);
-                            const unsigned long long key =
-                                ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - (uint32_t)r);
-                            atomicMax(p.argkey + (size_t)(sh.epoch & 1u) * kMaxB + b, key);
-                        }
+            for (int i = 0; i < RM; ++i) {
+                if (i == lane) mine[b] = acc[i][b];
+                if (i == lane + nre) mine_up[b] = acc[i][b];      // gate/up entries: up row of pair `lane`
+            }
+        }
+        if (lane < nre) {
+            const int r = row + lane;
+#pragma unroll
+            for (int b = 0; b < B; ++b) {
+                if (T == kQKV) {
+                    // projection output rounded to bf16 (HF linear output dtype)
+                    st_flagged(p.ll_qkv + (size_t)par * B * d.nrows + b * d.nrows + r, f32_to_bf16_bits(mine[b]), tag);
+                } else if (T == kO) {
+                    // h1 = bf16( x + bf16(o_proj) )
+                    const float o = round_bf16(mine[b]);
+                    const float h = round_bf16(__fadd_rn(c.res[b * p.H + r], o));
+                    st_flagged(p.ll_h1 + (size_t)par * B * p.H + b * p.H + r, f32_to_bf16_bits(h), tag);
+                } else if (T == kGU) {
+                    // act = bf16( bf16(silu(bf16 gate)) * bf16 up )   (HF LlamaMLP rounding)
+                    const float g = round_bf16(mine[b]);
+                    const float u = round_bf16(mine_up[b]);
+                    const float silu = round_bf16(__fdividef(g, 1.f + __expf(-g)));
+                    const float a = round_bf16(__fmul_rn(silu, u));
+                    st_flagged(p.ll_act + (size_t)par * B * p.I + b * p.I + r, f32_to_bf16_bits(a), tag);
+                } else if (T == kDown) {
+                    // x' = bf16( h1 + bf16(down_proj) ), handed to the next layer's parity slot
+                    const float dn = round_bf16(mine[b]);
+                    const uint32_t xb = f32_to_bf16_bits(__fadd_rn(c.res[b * p.H + r], dn));
+                    st_flagged(p.ll_x + (size_t)((layer + 1) & 1) * B * p.H + b * p.H + r, xb, layer_tag(c, layer + 1));
+                    if (p.layer_outputs) p.layer_outputs[((size_t)layer * B + b) * p.H + r] = (uint16_t)xb;
+                } else {
+                    // logits rounded to bf16; argmax breaks ties toward the lowest index
+                    const uint32_t lb = f32_to_bf16_bits(mine[b]);
+                    if (p.logits) p.logits[(size_t)b * p.V + r] = (uint16_t)lb;
+                    if (p.next_ids) {
+                        const uint32_t ord = (lb & 0x8000u) ? (~lb & 0xffffu) : (lb | 0x8000u);
+                        const unsigned long long key =
+                            ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - (uint32_t)r);
+                        atomicMax(p.argkey + (size_t)(sh.epoch & 1u) * kMaxB + b, key);
                     }
                 }
             }
@@ -764,19 +783,24 @@ __device__ __forceinline__ void unpack8(const uint4 v, float (&f)[8]) {
     f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
 }
 
-// One CTA = one (request b, kv head, chunk) item over cache positions [start, end).  The 16 consumer
-// warps split the chunk; inside a warp lane j = lane & 7 owns dims 8j..8j+7 and lane group
-// g = lane >> 3 takes positions ws+g, ws+g+4, ... so one 128-byte K (or V) row is one coalesced
-// 8-lane 16-byte load.  fp32 online softmax per lane group; lane groups, then warps (through shared
-// memory), are combined with log-sum-exp, and one partial (m, l, acc[64]) per query head of the GQA
-// group leaves the CTA as flagged words.  Every global load this needs is issued before the first
-// dependent use: K/V of the first positions and cos/sin do not depend on q, and the q/k/v words of
-// the new token are fetched in one batch.
+// One CTA = one (request b, kv head, chunk) item over cache positions [start, end); the consumer warps
+// split the chunk into runs of 16 positions.  Each run is processed in two phases so that no value
+// has to be reduced across more than two lanes:
+//   scores: lane = (position, half) -- a lane reads 32 dims of its position's K row (four 16-byte
+//           loads; a lane pair covers the 128-byte row) and dots them with the G rotated queries kept
+//           as packed bf16 in shared memory (mixed-precision FMA, no unpacking); one shuffle joins the
+//           halves.  The softmax statistics of the run are warp reductions over the 16 positions.
+//   P.V:    lane = two output dims -- the V rows of the 16 positions are read as coalesced 128-byte
+//           rows (one 4-byte load per lane and position) and accumulated with the probabilities
+//           broadcast from shared memory.
+// All K and V loads of a run are issued before the new token's q/k/v words are waited for.  Warps are
+// combined through shared memory with log-sum-exp and one partial (m, l, acc[64]) per query head of the
+// GQA group leaves the CTA as flagged words.
 template <int G>
 __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
     const DecodeParams& p = c.p;
     Shared& sh = c.sh;
-    const int lane = c.lane, j = lane & 7, g = lane >> 3;
+    const int lane = c.lane;
     const uint32_t tag = layer_tag(c, layer);
     const int par = layer & 1;
     const int nqkv = (p.QH + 2 * p.KVH) * kD;
@@ -784,49 +808,61 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
     const int seq = sh.seq[b], pos = sh.pos[b];
     const int start = chunk * sh.lc[b];
     const int end = min(start + sh.lc[b], seq);
-    // this warp's share of the chunk, a multiple of 4 positions
-    const int ppw = (((end - start + kNW - 1) / kNW) + 3) & ~3;
+    // this warp's share of the chunk, a multiple of 16 positions
+    const int ppw = (((end - start + kNW - 1) / kNW) + 15) & ~15;
     const int ws = min(start + c.warp * ppw, end);
     const int we = min(ws + ppw, end);
     const bool has_new = (seq - 1 >= ws) && (seq - 1 < we);
     const uint16_t* kvr = reinterpret_cast<const uint16_t*>(p.kv[layer]);
-    const int niter = (we - ws + 3) >> 2;   // positions per lane group, uniform over the warp
+    const int pl = lane >> 1, half = lane & 1;      // scores phase: position in the run, half of the head dim
 
-    // K/V fetch of kPB positions per lane group; st: 0 = out of range, 1 = from the cache,
-    // 2 = the new token (taken from registers).
-    constexpr int kPB = 2;
-    auto fetch = [&](int it, uint4* kk, uint4* vv, int* st) {
+    // shared-memory staging (all on 16-byte boundaries)
+    constexpr int kPartWords = (kNW * G * 66 + 3) & ~3;
+    static_assert(kPartWords + (G + 2) * kD + (G + 2) * 32 + kNW * G * 16 <= kAttnScratchWords, "attention scratch too small");
+    float* raw_s = c.attn + kPartWords;                                  // [(G+2)*64] un-rotated q, k, v
+    uint32_t* qkvb_s = reinterpret_cast<uint32_t*>(raw_s + (G + 2) * kD);   // [(G+2)*32] packed bf16: rotated q, k; v
+    float* prob_s = reinterpret_cast<float*>(qkvb_s + (G + 2) * 32) + c.warp * G * 16;   // [G][16] per warp
+
+    // element offset of position pp of this (request, kv head) in the paged cache
+    auto kv_offset = [&](int pp) -> long long {
+        const int blk = __ldg(p.block_table + b * p.bt_stride + pp / p.block_size);
+        return (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride +
+               (long long)kvh * p.head_stride;
+    };
+    // loads of one run of 16 positions starting at r0: K (this lane's position and half), V (all 16
+    // positions, this lane's two dims); the position seq-1 is taken from shared memory later
+    uint4 kq[4];
+    uint32_t vw[16];
+    auto fetch_run = [&](int r0) {
+        const int pp = r0 + pl;
+        long long e_own = 0;
+        const bool own_ok = pp < we && pp != seq - 1;
+        if (pp < we) e_own = kv_offset(pp);
 #pragma unroll
-        for (int u = 0; u < kPB; ++u) {
-            const int pp = ws + g + 4 * (it + u);
-            st[u] = 0;
-            kk[u] = vv[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (it + u < niter && pp < we) {
-                if (pp == seq - 1) {
-                    st[u] = 2;
-                } else {
-                    st[u] = 1;
-                    const int blk = __ldg(p.block_table + b * p.bt_stride + pp / p.block_size);
-                    const long long e = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride +
-                                        (long long)kvh * p.head_stride + 8 * j;
-                    kk[u] = __ldcg(reinterpret_cast<const uint4*>(kvr + p.k_off + e));
-                    vv[u] = __ldcg(reinterpret_cast<const uint4*>(kvr + p.v_off + e));
-                }
+        for (int i = 0; i < 4; ++i)
+            kq[i] = own_ok ? __ldcg(reinterpret_cast<const uint4*>(kvr + p.k_off + e_own + 32 * half) + i)
+                           : make_uint4(0u, 0u, 0u, 0u);
+        // V rows: when the run lies inside one cache block the offsets are an arithmetic sequence
+        const bool one_block = (r0 % p.block_size) + 15 < p.block_size;
+        const long long e0 = __shfl_sync(kFullMask, e_own, 0);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int pj = r0 + j;
+            long long ej;
+            if (one_block) {
+                ej = e0 + (long long)j * p.token_stride;
+            } else {
+                ej = __shfl_sync(kFullMask, e_own, 2 * j);
             }
+            vw[j] = (pj < we && pj != seq - 1)
+                        ? __ldcg(reinterpret_cast<const uint32_t*>(kvr + p.v_off + ej) + lane)
+                        : 0u;
         }
     };
     if (c.prof) c.prof[10] = global_ns();
-    uint4 kc[kPB], vc[kPB];
-    int stc[kPB];
-    fetch(0, kc, vc, stc);
+    if (ws < we) fetch_run(ws);
 
-    // q of the G heads sharing this kv head plus the new token's k and v: (G + 2) * 64 flagged words,
-    // one per thread, rotated (q, k) through shared memory and then read back by every lane
-    // the staging arrays are read with 16-byte loads: keep them on a 4-float boundary
-    constexpr int kPartWords = (kNW * G * 66 + 3) & ~3;
-    static_assert(kPartWords + 2 * (G + 2) * kD <= kAttnScratchWords, "attention scratch too small");
-    float* raw_s = c.attn + kPartWords;
-    float* rot_s = raw_s + (G + 2) * kD;
+    // q of the G heads sharing this kv head plus the new token's k and v: (G + 2) * 64 flagged words
     {
         constexpr int kPer = ((G + 2) * kD + kCT - 1) / kCT;      // words per thread
         auto word_row = [&](int t) {
@@ -850,165 +886,141 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
     }
     consumer_bar();
     if (c.prof) c.prof[11] = global_ns();
-    for (int t = threadIdx.x; t < (G + 2) * kD; t += kCT) {
-        const int which = t / kD, d = t % kD;
-        float out = raw_s[t];
+    // rotate q and k (two adjacent dims per thread) and pack everything to bf16 pairs
+    for (int t = threadIdx.x; t < (G + 2) * 32; t += kCT) {
+        const int which = t >> 5, dp = t & 31, d = 2 * dp;
+        float o0 = raw_s[which * kD + d], o1 = raw_s[which * kD + d + 1];
         if (which <= G) {
-            float cv, sv;
+            float c0, s0, c1, s1;
             const int ci = pos * kD + (d & 31);
             if (p.cs_fp32) {
-                cv = __ldg(reinterpret_cast<const float*>(p.cos_sin) + ci);
-                sv = __ldg(reinterpret_cast<const float*>(p.cos_sin) + ci + 32);
+                const float* t32 = reinterpret_cast<const float*>(p.cos_sin);
+                c0 = __ldg(t32 + ci); c1 = __ldg(t32 + ci + 1);
+                s0 = __ldg(t32 + ci + 32); s1 = __ldg(t32 + ci + 33);
             } else {
-                cv = __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(p.cos_sin) + ci) << 16);
-                sv = __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(p.cos_sin) + ci + 32) << 16);
+                const uint32_t cw = __ldg(reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.cos_sin) + ci));
+                const uint32_t sw = __ldg(reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.cos_sin) + ci + 32));
+                c0 = bf16_lo(cw); c1 = bf16_hi(cw);
+                s0 = bf16_lo(sw); s1 = bf16_hi(sw);
             }
-            out = rope_elem(out, raw_s[t ^ 32], cv, sv, d < 32);
+            const float p0 = raw_s[which * kD + (d ^ 32)], p1 = raw_s[which * kD + ((d + 1) ^ 32)];
+            o0 = rope_elem(o0, p0, c0, s0, d < 32);
+            o1 = rope_elem(o1, p1, c1, s1, d < 32);
         }
-        rot_s[t] = out;
+        qkvb_s[t] = pack_bf16x2(o0, o1);
     }
     consumer_bar();
     if (c.prof) c.prof[12] = global_ns();
-    float q[G][8];
-#pragma unroll
-    for (int hh = 0; hh < G; ++hh) {
-        const float4 lo = *reinterpret_cast<const float4*>(rot_s + hh * kD + 8 * j);
-        const float4 hi = *reinterpret_cast<const float4*>(rot_s + hh * kD + 8 * j + 4);
-        q[hh][0] = lo.x; q[hh][1] = lo.y; q[hh][2] = lo.z; q[hh][3] = lo.w;
-        q[hh][4] = hi.x; q[hh][5] = hi.y; q[hh][6] = hi.z; q[hh][7] = hi.w;
-    }
-    float kn[8], vn[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        kn[i] = rot_s[G * kD + 8 * j + i];
-        vn[i] = rot_s[(G + 1) * kD + 8 * j + i];
-    }
-    if (has_new) {   // warp-uniform
-        // append the new token's K/V to the paged cache (slot -1 = padded row: skip)
+    if (has_new) {   // warp-uniform: append the new token's K/V to the paged cache (slot -1 = padded row: skip)
         const long long slot = sh.slot[b];
-        if (slot >= 0 && g == 0) {
+        if (slot >= 0 && lane < 8) {
             uint16_t* kvw = reinterpret_cast<uint16_t*>(p.kv[layer]);
             const long long blk = slot / p.block_size, off = slot % p.block_size;
-            const long long e = blk * p.block_stride + off * p.token_stride + (long long)kvh * p.head_stride + 8 * j;
-            uint4 ko, vo;
-            ko.x = pack_bf16x2(kn[0], kn[1]); ko.y = pack_bf16x2(kn[2], kn[3]);
-            ko.z = pack_bf16x2(kn[4], kn[5]); ko.w = pack_bf16x2(kn[6], kn[7]);
-            vo.x = pack_bf16x2(vn[0], vn[1]); vo.y = pack_bf16x2(vn[2], vn[3]);
-            vo.z = pack_bf16x2(vn[4], vn[5]); vo.w = pack_bf16x2(vn[6], vn[7]);
-            *reinterpret_cast<uint4*>(kvw + p.k_off + e) = ko;
-            *reinterpret_cast<uint4*>(kvw + p.v_off + e) = vo;
+            const long long e = blk * p.block_stride + off * p.token_stride + (long long)kvh * p.head_stride + 8 * lane;
+            *reinterpret_cast<uint4*>(kvw + p.k_off + e) = *reinterpret_cast<const uint4*>(qkvb_s + G * 32 + 4 * lane);
+            *reinterpret_cast<uint4*>(kvw + p.v_off + e) = *reinterpret_cast<const uint4*>(qkvb_s + (G + 1) * 32 + 4 * lane);
         }
     }
 
-    float m[G], l[G], acc[G][8];
+    float m[G], l[G], acc[G][2];
 #pragma unroll
     for (int hh = 0; hh < G; ++hh) {
         m[hh] = -INFINITY;
         l[hh] = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[hh][i] = 0.f;
+        acc[hh][0] = acc[hh][1] = 0.f;
     }
-    for (int it0 = 0; it0 < niter; it0 += kPB) {
-        uint4 kn2[kPB], vn2[kPB];
-        int stn[kPB];
+    for (int r0 = ws; r0 < we; r0 += 16) {
+        if (r0 != ws) fetch_run(r0);
+        const int pp = r0 + pl;
+        const bool valid = pp < we;
+        // ---- scores of this lane's position (half of the dims), joined with the other half
+        uint32_t kwd[16];
+        if (pp == seq - 1) {
 #pragma unroll
-        for (int u = 0; u < kPB; ++u) {
-            stn[u] = 0;
-            kn2[u] = vn2[u] = make_uint4(0u, 0u, 0u, 0u);
-        }
-        if (it0 + kPB < niter) fetch(it0 + kPB, kn2, vn2, stn);      // next batch in flight during the math
-        float sc[kPB][G];
-#pragma unroll
-        for (int u = 0; u < kPB; ++u) {
-            float kf[8];
-            if (stc[u] == 2) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) kf[i] = kn[i];
-            } else {
-                unpack8(kc[u], kf);
+            for (int i = 0; i < 4; ++i) {
+                const uint4 t4 = *reinterpret_cast<const uint4*>(qkvb_s + G * 32 + 16 * half + 4 * i);
+                kwd[4 * i] = t4.x; kwd[4 * i + 1] = t4.y; kwd[4 * i + 2] = t4.z; kwd[4 * i + 3] = t4.w;
             }
+        } else {
 #pragma unroll
-            for (int hh = 0; hh < G; ++hh) {
-                float dsum = 0.f;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) dsum = fmaf(q[hh][i], kf[i], dsum);
-                dsum += __shfl_xor_sync(kFullMask, dsum, 4);
-                dsum += __shfl_xor_sync(kFullMask, dsum, 2);
-                dsum += __shfl_xor_sync(kFullMask, dsum, 1);
-                // bf16 matmul output, then the exact 1/8 scale (HF eager_attention_forward)
-                sc[u][hh] = stc[u] ? round_bf16(dsum) * 0.125f : -INFINITY;
+            for (int i = 0; i < 4; ++i) {
+                kwd[4 * i] = kq[i].x; kwd[4 * i + 1] = kq[i].y; kwd[4 * i + 2] = kq[i].z; kwd[4 * i + 3] = kq[i].w;
             }
         }
-        float ev[kPB][G];
+        float sc[G];
 #pragma unroll
         for (int hh = 0; hh < G; ++hh) {
-            float mx = m[hh];
+            float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-            for (int u = 0; u < kPB; ++u) mx = fmaxf(mx, sc[u][hh]);
-            const float alpha = (mx == -INFINITY) ? 1.f : __expf(m[hh] - mx);
-            float es = 0.f;
-#pragma unroll
-            for (int u = 0; u < kPB; ++u) {
-                ev[u][hh] = (sc[u][hh] == -INFINITY) ? 0.f : __expf(sc[u][hh] - mx);
-                es += ev[u][hh];
+            for (int i = 0; i < 4; ++i) {
+                const uint4 q4 = *reinterpret_cast<const uint4*>(qkvb_s + hh * 32 + 16 * half + 4 * i);
+                d0 = fma2_bf16(kwd[4 * i], q4.x, d0);
+                d1 = fma2_bf16(kwd[4 * i + 1], q4.y, d1);
+                d0 = fma2_bf16(kwd[4 * i + 2], q4.z, d0);
+                d1 = fma2_bf16(kwd[4 * i + 3], q4.w, d1);
             }
-            l[hh] = l[hh] * alpha + es;
-            m[hh] = mx;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[hh][i] *= alpha;
+            float dsum = d0 + d1;
+            dsum += __shfl_xor_sync(kFullMask, dsum, 1);
+            // bf16 matmul output, then the exact 1/8 scale (HF eager_attention_forward)
+            sc[hh] = valid ? round_bf16(dsum) * 0.125f : -INFINITY;
         }
+        // ---- running softmax statistics over the 16 positions of the run
+        float pr[G];
 #pragma unroll
-        for (int u = 0; u < kPB; ++u) {
-            float vf[8];
-            if (stc[u] == 2) {
+        for (int hh = 0; hh < G; ++hh) {
+            float mx = sc[hh];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) vf[i] = vn[i];
-            } else {
-                unpack8(vc[u], vf);
+            for (int o = 2; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(kFullMask, mx, o));
+            const float mn = fmaxf(m[hh], mx);
+            const float alpha = (mn == -INFINITY) ? 1.f : __expf(m[hh] - mn);
+            pr[hh] = (sc[hh] == -INFINITY) ? 0.f : __expf(sc[hh] - mn);
+            float ps = pr[hh];
+#pragma unroll
+            for (int o = 2; o < 32; o <<= 1) ps += __shfl_xor_sync(kFullMask, ps, o);
+            l[hh] = l[hh] * alpha + ps;
+            m[hh] = mn;
+            acc[hh][0] *= alpha;
+            acc[hh][1] *= alpha;
+            if (half == 0) prob_s[hh * 16 + pl] = pr[hh];
+        }
+        __syncwarp();
+        // ---- P.V: this lane accumulates dims 2*lane, 2*lane+1 over the 16 positions
+        const uint32_t vnew = qkvb_s[(G + 1) * 32 + lane];
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) {
+            float a0 = acc[hh][0], a1 = acc[hh][1];
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4) {
+                const float4 p4 = *reinterpret_cast<const float4*>(prob_s + hh * 16 + 4 * j4);
+                const float pj[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int j = 4 * j4 + jj;
+                    const uint32_t v = (r0 + j == seq - 1) ? vnew : vw[j];
+                    a0 = fmaf(pj[jj], bf16_lo(v), a0);
+                    a1 = fmaf(pj[jj], bf16_hi(v), a1);
+                }
             }
-#pragma unroll
-            for (int hh = 0; hh < G; ++hh)
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc[hh][i] = fmaf(ev[u][hh], vf[i], acc[hh][i]);
+            acc[hh][0] = a0;
+            acc[hh][1] = a1;
         }
-#pragma unroll
-        for (int u = 0; u < kPB; ++u) {
-            kc[u] = kn2[u];
-            vc[u] = vn2[u];
-            stc[u] = stn[u];
-        }
+        __syncwarp();
     }
     if (c.prof) c.prof[13] = global_ns();
-    // combine the 4 lane groups of the warp; lanes 0..7 park the warp's partial in shared memory
+    // park the warp's partial in shared memory: lanes hold two dims each, nothing to shuffle
     float* wpart = c.attn + (size_t)c.warp * G * 66;
 #pragma unroll
     for (int hh = 0; hh < G; ++hh) {
-        float mm = fmaxf(m[hh], __shfl_xor_sync(kFullMask, m[hh], 8));
-        mm = fmaxf(mm, __shfl_xor_sync(kFullMask, mm, 16));
-        const float f = (m[hh] == -INFINITY) ? 0.f : __expf(m[hh] - mm);
-        float lt = l[hh] * f;
-        lt += __shfl_xor_sync(kFullMask, lt, 8);
-        lt += __shfl_xor_sync(kFullMask, lt, 16);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            float a = acc[hh][i] * f;
-            a += __shfl_xor_sync(kFullMask, a, 8);
-            a += __shfl_xor_sync(kFullMask, a, 16);
-            acc[hh][i] = a;
+        float* dst = wpart + hh * 66;
+        if (lane == 0) {
+            dst[0] = m[hh];
+            dst[1] = l[hh];
         }
-        if (g == 0) {
-            float* dst = wpart + hh * 66;
-            if (j == 0) {
-                dst[0] = mm;
-                dst[1] = lt;
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) dst[2 + 8 * j + i] = acc[hh][i];
-        }
+        *reinterpret_cast<float2*>(dst + 2 + 2 * lane) = make_float2(acc[hh][0], acc[hh][1]);
     }
     consumer_bar();
     if (c.prof) c.prof[14] = global_ns();
-    // combine the 16 warps; thread (hh, d) publishes one accumulator word, d == 0 also m and l
+    // combine the warps; thread (hh, d) publishes one accumulator word, d == 0 also m and l
     const size_t item = ((size_t)(b * p.KVH + kvh) * kNCMax + chunk) * G;
     unsigned long long* part = p.ll_part + ((size_t)par * p.B * p.KVH * kNCMax * G + item) * 66;
     for (int t = threadIdx.x; t < G * kD; t += kCT) {
@@ -1494,7 +1506,7 @@ static KernelFn pick_kernel(int B, int G, int WF) {
 }
 
 // Fill the per-phase staging descriptors for a ring of `rw` bytes per consumer warp.
-static int make_phases_with(const ModelGeom& g, int entry_max, PhaseDesc (&ph)[kNumPhaseTypes]) {
+static int make_phases_with(const ModelGeom& g, int entry_max, int rm, PhaseDesc (&ph)[kNumPhaseTypes]) {
     auto rowbytes = [&](int K) { return g.wfmt ? (int)align_up((size_t)K + K / 32, 16) : K * 2; };
     struct Spec { int nrows, K, pair, widx; long long pair_rows; };
     const int nqkv = (g.QH + 2 * g.KVH) * kD;
@@ -1513,7 +1525,7 @@ static int make_phases_with(const ModelGeom& g, int entry_max, PhaseDesc (&ph)[k
         d.pair_off = spec[t].pair_rows * (long long)d.rowbytes;
         const int unit = d.rowbytes * (d.pair ? 2 : 1);
         int R = entry_max / unit;
-        const int rcap = d.pair ? kRMax / 2 : kRMax;
+        const int rcap = d.pair ? rm / 2 : rm;
         if (R > rcap) R = rcap;
         if (R >= 1) {
             d.rows_per_entry = R;
@@ -1548,13 +1560,13 @@ static void worst_entry_counts(const PhaseDesc (&ph)[kNumPhaseTypes], int ncta, 
 
 // Pick the smallest entry size (small entries lose little ring space at the wrap point, which an
 // entry never straddles) whose per-warp schedule still fits the in-kernel entry tables.
-static int make_phases(const ModelGeom& g, int rw, int ncta, PhaseDesc (&ph)[kNumPhaseTypes]) {
+static int make_phases(const ModelGeom& g, int rw, int ncta, int rm, PhaseDesc (&ph)[kNumPhaseTypes]) {
     int rc = kErrShape;
     int first = rw / 2 / 512 * 512;
     if (first > 8192) first = 8192;
     if (first < 1024) return kErrResidency;
     for (int entry_max = first; entry_max <= rw / 2; entry_max *= 2) {
-        rc = make_phases_with(g, entry_max, ph);
+        rc = make_phases_with(g, entry_max, rm, ph);
         if (rc) continue;
         int per_layer = 0, lm = 0;
         worst_entry_counts(ph, ncta, per_layer, lm);
@@ -1622,7 +1634,7 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
         for (int t = 0; t < 4; ++t) ncta = rows[t] < ncta ? rows[t] : ncta;
     }
     if (ncta < 1) return kErrShape;
-    rc = make_phases(g, rw, ncta, p.ph);
+    rc = make_phases(g, rw, ncta, row_cap(a.B), p.ph);
     if (rc) return rc;
     const size_t smem = fixed + (size_t)kNW * rw;
 
