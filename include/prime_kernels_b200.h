@@ -41,6 +41,22 @@ int pk_fused_rmsnorm_residual_forward_ex(void* vals, void* scales, float* rrms, 
  * (scale_numel in prime_kernels/rmsnorm/csrc/torch_interface.cpp:18-20, extended to ragged shapes). */
 long long pk_rmsnorm_scale_bytes(int N, int C);
 
+/* ---------------------------------------------------------------- forward ops the megakernel absorbs, standalone */
+
+/* Forward of triton_rope.apply_rotary (prime_kernels/triton_rope/__init__.py:41-82,373-377) for one tensor:
+ * x, y bf16 [batch*heads*seq, D] contiguous, head-major ([B, heads, S, D]; unsqueeze_dim 1) or sequence-major
+ * ([B, S, heads, D]; unsqueeze_dim 2); cos, sin bf16 [cos_batch (1 or B), S, rot]; the first `rot` dims rotate. */
+int pk_apply_rotary(const void* x, void* y, const void* cos, const void* sin, long long batch, int heads, int seq,
+                    int D, int rot, int head_major, int cos_batch, void* stream);
+/* Forward of triton_rmsnorm.rmsnorm / residual_rmsnorm (prime_kernels/triton_rmsnorm/rmsnorm.py:701-722):
+ * out = bf16(w * bf16(v * rstd)), v = x or bf16(x + residual); residual and sum_out may be NULL. */
+int pk_rmsnorm_forward(const void* x, const void* residual, const void* weight, void* out, void* sum_out,
+                       long long rows, int H, float eps, void* stream);
+/* Forward of triton_swiglu.swiglu (prime_kernels/triton_swiglu/swiglu.py:31-59,195-202):
+ * out = bf16(bf16(silu(gate)) * up); gate/up row strides in elements. */
+int pk_swiglu_forward(const void* gate, const void* up, void* out, long long rows, int cols, long long gate_stride,
+                      long long up_stride, void* stream);
+
 /* MXFP8 weight packing for the decode GEMVs.  No counterpart in the reference (its kernels take
  * pre-quantised weights, prime_kernels/flash_moe/__init__.py:165-170).  Quantises bf16 [rows, K] along K
  * with the quantiser above (one E8M0 scale per 32 values, round-up scale) into packed rows

@@ -20,7 +20,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib"
 OBJ = LIB / "obj"
-CUDA_SOURCES = ["rmsnorm_mxfp8.cu", "decode_megakernel.cu"]
+CUDA_SOURCES = ["rmsnorm_mxfp8.cu", "decode_megakernel.cu", "elementwise_ops.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--use_fast_math=false"]
 

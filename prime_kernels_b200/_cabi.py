@@ -40,6 +40,9 @@ SYMBOLS = {
     "pk_fused_rmsnorm_residual_forward": (ci, [vp, vp, vp, vp, vp, vp, cf, ci, ci, vp]),
     "pk_fused_rmsnorm_residual_forward_ex": (ci, [vp, vp, vp, vp, vp, vp, vp, cf, ci, ci, ci, vp]),
     "pk_rmsnorm_scale_bytes": (ll, [ci, ci]),
+    "pk_apply_rotary": (ci, [vp, vp, vp, vp, ll, ci, ci, ci, ci, ci, ci, vp]),
+    "pk_rmsnorm_forward": (ci, [vp, vp, vp, vp, vp, ll, ci, cf, vp]),
+    "pk_swiglu_forward": (ci, [vp, vp, vp, ll, ci, ll, ll, vp]),
     "pk_mxfp8_packed_row_bytes": (ll, [ci]),
     "pk_pack_weights_mxfp8": (ci, [vp, vp, ll, ci, vp]),
     "pk_decode_workspace_bytes": (sz, [ctypes.POINTER(PkDecodeModel), ci]),

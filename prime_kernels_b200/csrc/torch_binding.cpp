@@ -128,7 +128,86 @@ int64_t decode_step(const torch::Tensor& input_ids, const torch::Tensor& positio
     return pk_decode_step(&m, &a);
 }
 
+void check_bf16_cuda(const torch::Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.dtype() == torch::kBFloat16, name, " must be a CUDA bfloat16 tensor");
+}
+
+std::tuple<torch::Tensor, torch::Tensor> apply_rotary(const torch::Tensor& q, const torch::Tensor& k,
+                                                      const torch::Tensor& cos, const torch::Tensor& sin,
+                                                      int64_t unsqueeze_dim) {
+    check_bf16_cuda(q, "q"); check_bf16_cuda(k, "k"); check_bf16_cuda(cos, "cos"); check_bf16_cuda(sin, "sin");
+    TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && cos.dim() == 3 && sin.sizes() == cos.sizes(), "expected 4-D q, k and 3-D cos, sin");
+    TORCH_CHECK(unsqueeze_dim == 1 || unsqueeze_dim == 2, "unsqueeze_dim must be 1 or 2");
+    TORCH_CHECK(q.is_contiguous() && k.is_contiguous() && cos.is_contiguous() && sin.is_contiguous(), "inputs must be contiguous");
+    at::cuda::OptionalCUDAGuard guard{device_of(q)};
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    const bool hm = unsqueeze_dim == 1;
+    const int64_t B = q.size(0), S = hm ? q.size(2) : q.size(1), D = q.size(3), rot = cos.size(2);
+    TORCH_CHECK(cos.size(1) == S && (cos.size(0) == 1 || cos.size(0) == B), "cos must be [1 or B, S, rot]");
+    TORCH_CHECK(k.size(0) == B && k.size(3) == D && (hm ? k.size(2) : k.size(1)) == S, "k must match q in batch, seq and head dim");
+    torch::Tensor oq = torch::empty_like(q), ok = torch::empty_like(k);
+    int rc = pk_apply_rotary(q.const_data_ptr(), oq.data_ptr(), cos.const_data_ptr(), sin.const_data_ptr(), B,
+                             (int)(hm ? q.size(1) : q.size(2)), (int)S, (int)D, (int)rot, hm, (int)cos.size(0), stream);
+    TORCH_CHECK(rc == 0, "apply_rotary failed: ", pk_status_string(rc));
+    rc = pk_apply_rotary(k.const_data_ptr(), ok.data_ptr(), cos.const_data_ptr(), sin.const_data_ptr(), B,
+                         (int)(hm ? k.size(1) : k.size(2)), (int)S, (int)D, (int)rot, hm, (int)cos.size(0), stream);
+    TORCH_CHECK(rc == 0, "apply_rotary failed: ", pk_status_string(rc));
+    return {oq, ok};
+}
+
+torch::Tensor rmsnorm_fwd(const torch::Tensor& x, const torch::Tensor& weight, double eps) {
+    check_bf16_cuda(x, "x"); check_bf16_cuda(weight, "weight");
+    TORCH_CHECK(x.is_contiguous() && weight.dim() == 1 && weight.size(0) == x.size(-1), "x contiguous, weight [H]");
+    at::cuda::OptionalCUDAGuard guard{device_of(x)};
+    torch::Tensor out = torch::empty_like(x);
+    const int64_t H = x.size(-1), rows = x.numel() / H;
+    const int rc = pk_rmsnorm_forward(x.const_data_ptr(), nullptr, weight.const_data_ptr(), out.data_ptr(), nullptr, rows,
+                                      (int)H, (float)eps, at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "rmsnorm failed: ", pk_status_string(rc));
+    return out;
+}
+
+std::tuple<torch::Tensor, torch::Tensor> residual_rmsnorm_fwd(const torch::Tensor& branch, const torch::Tensor& residual,
+                                                              const torch::Tensor& weight, double eps) {
+    check_bf16_cuda(branch, "branch"); check_bf16_cuda(residual, "residual"); check_bf16_cuda(weight, "weight");
+    TORCH_CHECK(branch.is_contiguous() && residual.is_contiguous() && residual.sizes() == branch.sizes(), "branch and residual must be contiguous and match");
+    TORCH_CHECK(weight.dim() == 1 && weight.size(0) == branch.size(-1), "weight must be [H]");
+    at::cuda::OptionalCUDAGuard guard{device_of(branch)};
+    torch::Tensor out = torch::empty_like(branch), sum = torch::empty_like(branch);
+    const int64_t H = branch.size(-1), rows = branch.numel() / H;
+    const int rc = pk_rmsnorm_forward(branch.const_data_ptr(), residual.const_data_ptr(), weight.const_data_ptr(),
+                                      out.data_ptr(), sum.data_ptr(), rows, (int)H, (float)eps, at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "residual_rmsnorm failed: ", pk_status_string(rc));
+    return {out, sum};
+}
+
+torch::Tensor swiglu_fwd(const torch::Tensor& gate, const torch::Tensor& up) {
+    check_bf16_cuda(gate, "gate"); check_bf16_cuda(up, "up");
+    TORCH_CHECK(gate.sizes() == up.sizes() && gate.dim() >= 1 && gate.stride(-1) == 1 && up.stride(-1) == 1, "gate and up must match, contiguous last dim");
+    at::cuda::OptionalCUDAGuard guard{device_of(gate)};
+    const int64_t cols = gate.size(-1);
+    // leading dims may be a strided view of a larger tensor: flatten to rows with one row stride
+    torch::Tensor g2 = gate.dim() == 2 ? gate : gate.reshape({-1, cols});
+    torch::Tensor u2 = up.dim() == 2 ? up : up.reshape({-1, cols});
+    torch::Tensor out = torch::empty(gate.sizes(), gate.options());
+    const int rc = pk_swiglu_forward(g2.const_data_ptr(), u2.const_data_ptr(), out.data_ptr(), g2.size(0), (int)cols,
+                                     g2.stride(0), u2.stride(0), at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "swiglu failed: ", pk_status_string(rc));
+    return out;
+}
+
 }  // namespace
+
+TORCH_LIBRARY_FRAGMENT(prime_elementwise, m) {
+    m.def("apply_rotary(Tensor q, Tensor k, Tensor cos, Tensor sin, int unsqueeze_dim) -> (Tensor, Tensor)");
+    m.impl("apply_rotary", torch::kCUDA, &apply_rotary);
+    m.def("rmsnorm(Tensor x, Tensor weight, float eps) -> Tensor");
+    m.impl("rmsnorm", torch::kCUDA, &rmsnorm_fwd);
+    m.def("residual_rmsnorm(Tensor branch, Tensor residual, Tensor weight, float eps) -> (Tensor, Tensor)");
+    m.impl("residual_rmsnorm", torch::kCUDA, &residual_rmsnorm_fwd);
+    m.def("swiglu(Tensor gate, Tensor up) -> Tensor");
+    m.impl("swiglu", torch::kCUDA, &swiglu_fwd);
+}
 
 TORCH_LIBRARY_FRAGMENT(prime_rmsnorm, m) {
     m.def("fused_rmsnorm_residual(Tensor branch, Tensor residual, Tensor weight, float epsilon) -> (Tensor, Tensor, Tensor)");
