@@ -216,3 +216,82 @@ def test_mxfp8_weights_decode_against_restatement(cuda_device, B):
         assert (logits.cpu().float() - rl).abs().max() <= LOGIT_TOL
         assert (hid.cpu().float() - rh.float()).abs().max() <= 2 ** -4
         cur = rl.argmax(-1)
+
+
+@pytest.mark.parametrize("case", ["long-context", "fp32-cos-int32-ids", "block8-straddle", "ragged-batch"])
+def test_edge_cases_against_restatement(cuda_device, case):
+    """Maximum context (two-level merge, 64 chunks), fp32 rotary table with int32 ids, a KV block size that
+    makes a 16-position run straddle cache blocks, and a batch whose requests have different lengths."""
+    from prime_kernels_b200 import decode as D
+
+    geom = D.Geometry("edge-" + case, 192, 512, 2, 3, 1, 1024)
+    w = harness.make_weights(geom, 2, norm_weights="random")
+    wd = harness.weights_to(w, cuda_device)
+    gen = torch.Generator().manual_seed(21)
+    block_size, cap = 16, 256
+    cs_dtype, id_dtype = torch.bfloat16, torch.int64
+    if case == "long-context":
+        ctxs, cap = [8100], 8192
+    elif case == "fp32-cos-int32-ids":
+        ctxs, cs_dtype, id_dtype = [40], torch.float32, torch.int32
+    elif case == "block8-straddle":
+        ctxs, block_size = [150], 8
+    else:
+        ctxs = [1, 117, 230]
+    B = len(ctxs)
+    cs = harness.make_cos_sin_cache(geom, cap, dtype=cs_dtype)
+    keys = [[torch.randn(geom.kv_heads, c, 64, generator=gen).to(torch.bfloat16) for c in ctxs] for _ in range(geom.layers)]
+    vals = [[torch.randn(geom.kv_heads, c, 64, generator=gen).to(torch.bfloat16) for c in ctxs] for _ in range(geom.layers)]
+    kv = harness.PagedKV(geom, B, cap, cuda_device, block_size=block_size, shuffle=True)
+    for layer in range(geom.layers):                        # ragged prefix: load request by request
+        for b, c in enumerate(ctxs):
+            kvb = torch.cat([keys[layer][b], vals[layer][b]], -1).to(cuda_device)
+            for t0 in range(0, c, block_size):
+                n = min(block_size, c - t0)
+                kv.kv_caches[layer][int(kv.block_table[b, t0 // block_size]), :, :n, :] = kvb[:, t0:t0 + n, :]
+    cur = torch.randint(0, geom.vocab, (B,), generator=gen)
+    for s in range(2):
+        pos = torch.tensor([c + s for c in ctxs], dtype=torch.int64)
+        hid, logits, nxt = D.decode_step(geom, input_ids=cur.to(id_dtype).to(cuda_device), positions=pos.to(cuda_device),
+                                         seq_lens=(pos + 1).to(torch.int32).to(cuda_device), block_table=kv.block_table,
+                                         slot_mapping=kv.slots(pos), embed=wd["embed"], layers=wd["layers"],
+                                         final_norm=wd["final_norm"], kv_caches=kv.kv_caches,
+                                         cos_sin_cache=cs.to(cuda_device), eps=geom.eps, lm_head=True)
+        D.check_status(geom, cuda_device)
+        rh, rl, _ = R.decode_step(geom, w, cur, pos, keys, vals, cs)
+        assert (logits.cpu().float() - rl).abs().max() <= LOGIT_TOL
+        margin = rl.topk(2, -1).values
+        sure = (margin[:, 0] - margin[:, 1]) > 2 * LOGIT_TOL
+        assert (nxt.cpu()[sure] == rl.argmax(-1)[sure]).all()
+        cur = rl.argmax(-1)
+
+
+def test_device_driven_generation_matches_stepwise(cuda_device):
+    """`advance=True` (ids, positions, seq_lens and slot_mapping rewritten by the kernel) gives the same
+    greedy sequence as feeding every step from the host."""
+    from prime_kernels_b200 import decode as D
+
+    geom = D.Geometry("gen", 192, 512, 3, 3, 1, 1024)
+    wd = harness.weights_to(harness.make_weights(geom, 5, norm_weights="random"), cuda_device)
+    csd = harness.make_cos_sin_cache(geom, 128, cuda_device)
+    B, steps = 2, 20
+    first = torch.tensor([11, 500])
+
+    def fresh():
+        return harness.PagedKV(geom, B, 128, cuda_device, shuffle=True, seed=3)
+
+    kv_a = fresh()
+    sess = D.DecodeSession(geom, embed=wd["embed"], layers=wd["layers"], final_norm=wd["final_norm"],
+                           kv_caches=kv_a.kv_caches, cos_sin_cache=csd, block_table=kv_a.block_table)
+    sess.start(first, torch.zeros(B, dtype=torch.int64))
+    ids_a = sess.generate(steps).cpu()
+    kv_b = fresh()
+    cur, ids_b = first.clone(), []
+    for s in range(steps):
+        pos = torch.full((B,), s, dtype=torch.int64)
+        _, _, nxt = _step(D, geom, wd, kv_b, csd, cur, pos)
+        cur = nxt.cpu().clone()
+        ids_b.append(cur)
+    assert torch.equal(ids_a, torch.stack(ids_b))
+    for ca, cb in zip(kv_a.kv_caches, kv_b.kv_caches):
+        assert torch.equal(ca, cb)
