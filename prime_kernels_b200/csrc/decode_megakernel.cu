@@ -105,7 +105,8 @@ struct DecodeParams {
     unsigned long long* ll_part;        // [2][B*KVH*kNCMax*G*66]
     long long k_off, v_off, block_stride, token_stride, head_stride;
     int block_size, bt_stride, ids_i64, cs_fp32;
-    int H, I, L, QH, KVH, V, B, G;
+    int H, I, L, QH, KVH, V, B, G;       // B = batch the kernel is instantiated for
+    int nb;                             // requests actually present (<= B); rows nb..B-1 are padding
     int wfmt;                           // 0 = bf16 weights, 1 = MXFP8 packed rows
     int lm_head, advance;
     int max_seq_len;
@@ -653,12 +654,12 @@ __device__ void gemv_phase(Ctx& c, const int T, int layer, uint32_t& consumed) {
                     const float dn = round_bf16(mine[b]);
                     const uint32_t xb = f32_to_bf16_bits(__fadd_rn(c.res[b * p.H + r], dn));
                     st_flagged(p.ll_x + (size_t)((layer + 1) & 1) * B * p.H + b * p.H + r, xb, layer_tag(c, layer + 1));
-                    if (p.layer_outputs) p.layer_outputs[((size_t)layer * B + b) * p.H + r] = (uint16_t)xb;
+                    if (p.layer_outputs && b < p.nb) p.layer_outputs[((size_t)layer * p.nb + b) * p.H + r] = (uint16_t)xb;
                 } else {
                     // logits rounded to bf16; argmax breaks ties toward the lowest index
                     const uint32_t lb = f32_to_bf16_bits(mine[b]);
-                    if (p.logits) p.logits[(size_t)b * p.V + r] = (uint16_t)lb;
-                    if (p.next_ids) {
+                    if (p.logits && b < p.nb) p.logits[(size_t)b * p.V + r] = (uint16_t)lb;
+                    if (p.next_ids && b < p.nb) {
                         const uint32_t ord = (lb & 0x8000u) ? (~lb & 0xffffu) : (lb | 0x8000u);
                         const unsigned long long key =
                             ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - (uint32_t)r);
@@ -825,7 +826,8 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
 
     // element offset of position pp of this (request, kv head) in the paged cache
     auto kv_offset = [&](int pp) -> long long {
-        const int blk = __ldg(p.block_table + b * p.bt_stride + pp / p.block_size);
+        // padding rows read the block-table row of the last real request
+        const int blk = __ldg(p.block_table + min(b, p.nb - 1) * p.bt_stride + pp / p.block_size);
         return (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride +
                (long long)kvh * p.head_stride;
     };
@@ -1139,7 +1141,7 @@ __device__ void attention_prefetch(Ctx& c, int layer) {
         const int end = min(start + sh.lc[b], sh.seq[b] - 1);
         for (int i = start * 2 + (int)threadIdx.x; i < end * 2; i += kCT) {
             const int pp = i >> 1;
-            const int blk = __ldg(p.block_table + b * p.bt_stride + pp / p.block_size);
+            const int blk = __ldg(p.block_table + min(b, p.nb - 1) * p.bt_stride + pp / p.block_size);
             const long long e = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride +
                                 (long long)kvh * p.head_stride;
             const unsigned char* a = kvr + ((i & 1) ? p.v_off + e : p.k_off + e) * 2;
@@ -1288,19 +1290,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
         sh.row_b[t][w] = b;
     }
     if (tid < B) {
-        const int seq = max(p.seq_lens[tid], 1);
+        // padding rows (batch 5..7 run on the batch-8 kernel) mirror the last real request and write nothing
+        const int src = min(tid, p.nb - 1);
+        const int seq = max(p.seq_lens[src], 1);
         sh.seq[tid] = seq;
-        sh.pos[tid] = (int)max(p.positions[tid], 0LL);
-        sh.slot[tid] = p.slot_mapping[tid];
-        sh.tok[tid] = p.ids_i64 ? reinterpret_cast<const long long*>(p.input_ids)[tid]
-                                : (long long)reinterpret_cast<const int*>(p.input_ids)[tid];
+        sh.pos[tid] = (int)max(p.positions[src], 0LL);
+        sh.slot[tid] = tid < p.nb ? p.slot_mapping[src] : -1LL;
+        sh.tok[tid] = p.ids_i64 ? reinterpret_cast<const long long*>(p.input_ids)[src]
+                                : (long long)reinterpret_cast<const int*>(p.input_ids)[src];
         // Split-KV chunking: 16 positions per warp and chunk (one load batch per lane group), longer
         // only when that would need more than kNCMax chunks.  With few partials (short contexts) every
         // CTA merges them itself while staging the O projection input (direct mode, one hand-off);
         // otherwise one warp per (request, head) merges and publishes the result (two hand-offs, but
         // no redundant staging).  The mode is decided on the longest request so it is CTA-uniform.
         int smax = 1;
-        for (int bb = 0; bb < B; ++bb) smax = max(smax, max(p.seq_lens[bb], 1));
+        for (int bb = 0; bb < p.nb; ++bb) smax = max(smax, max(p.seq_lens[bb], 1));
         const int lc = max(16 * kNW, (((smax + kNCMax - 1) / kNCMax) + 15) & ~15);
         const int two = (B * p.QH * ((smax + lc - 1) / lc) * 66 > kDirectWords) ? 1 : 0;
         sh.lc[tid] = lc;
@@ -1385,7 +1389,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
             if (prof) prof[1 + 2 * t + (t >= kO ? 1 : 0)] = global_ns();     // slots 1, 4, 6, 8
             if (t == kLM && cta == 0) {
                 const uint16_t* act16 = reinterpret_cast<const uint16_t*>(c.act);
-                for (int b = 0; b < B; ++b)
+                for (int b = 0; b < p.nb; ++b)
                     for (int i = tid; i < p.H; i += kCT) p.out_hidden[b * p.H + i] = act16[(size_t)b * p.act_elems + i];
             }
             if (t != kLM || p.lm_head) gemv_phase<B, WF>(c, t, layer, consumed);
@@ -1402,7 +1406,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
             __threadfence();
             const bool ok = *((volatile unsigned int*)(p.ctrl + kCtrlStatus)) == 0;
             if (p.next_ids && p.lm_head && ok) {
-                for (int b = 0; b < B; ++b) {
+                for (int b = 0; b < p.nb; ++b) {
                     const unsigned long long key =
                         *((volatile unsigned long long*)(p.argkey + (size_t)(sh.epoch & 1u) * kMaxB + b));
                     const long long id = (long long)(0xffffffffu - (uint32_t)key);
@@ -1499,8 +1503,8 @@ static KernelFn pick_kernel(int B, int G, int WF) {
 #define PK_CASE(b, g)                                            \
     if (B == b && G == g && WF == 0) return decode_step_kernel<b, g, 0>; \
     if (B == b && G == g && WF == 1) return decode_step_kernel<b, g, 1>;
-    PK_CASE(1, 1) PK_CASE(2, 1) PK_CASE(3, 1) PK_CASE(4, 1)
-    PK_CASE(1, 3) PK_CASE(2, 3) PK_CASE(3, 3) PK_CASE(4, 3)
+    PK_CASE(1, 1) PK_CASE(2, 1) PK_CASE(3, 1) PK_CASE(4, 1) PK_CASE(8, 1)
+    PK_CASE(1, 3) PK_CASE(2, 3) PK_CASE(3, 3) PK_CASE(4, 3) PK_CASE(8, 3)
 #undef PK_CASE
     return nullptr;
 }
@@ -1589,7 +1593,8 @@ struct StepArgs {
 };
 
 static int decode_launch(const ModelGeom& g, const StepArgs& a) {
-    if (a.B < 1 || a.B > 4) return kErrBatch;
+    if (a.B < 1 || a.B > kMaxB) return kErrBatch;
+    const int KB = a.B <= 4 ? a.B : kMaxB;      // kernel batch: exact up to 4, the batch-8 kernel (padded) beyond
     if (a.max_seq_len < 1 || a.max_seq_len > kMaxSeq) return kErrMaxSeq;
     if (!a.input_ids || !a.positions || !a.seq_lens || !a.block_table || !a.slot_mapping || !a.layers || !a.embed ||
         !a.final_norm || !a.kv || !a.cos_sin || !a.out_hidden || !a.ws)
@@ -1599,7 +1604,7 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
         return kErrShape;
     const int G = g.QH / g.KVH;
     if (g.wfmt != 0 && g.wfmt != 1) return kErrShape;
-    KernelFn fn = pick_kernel(a.B, G, g.wfmt);
+    KernelFn fn = pick_kernel(KB, G, g.wfmt);
     if (!fn) return kErrShape;
     if (a.block_size <= 0 || a.bt_stride < 1 || (long long)a.bt_stride * a.block_size < a.max_seq_len) return kErrBlock;
     if (a.k_off % 8 || a.v_off % 8 || a.block_stride % 8 || a.token_stride % 8 || a.head_stride % 8 || a.k_off < 0 ||
@@ -1610,7 +1615,7 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
         (a.embed_lookup && mis16(a.embed_lookup)) || (a.layer_outputs && mis16(a.layer_outputs)) ||
         (a.logits && mis16(a.logits)))
         return kErrAlign;
-    const WsLayout lay = ws_layout(g, a.B);
+    const WsLayout lay = ws_layout(g, KB);
     if (a.ws_bytes < lay.total) return kErrScratch;
 
     DeviceInfo di;
@@ -1621,8 +1626,8 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
 
     // shared memory: fixed part + per-warp rings
     const int act_elems = g.H > g.I ? g.H : g.I;
-    const size_t fixed = align_up(sizeof(Shared), 128) + align_up((size_t)a.B * act_elems * 2, 128) +
-                         align_up((size_t)a.B * g.H * 4, 128) + (size_t)kAttnScratchWords * 4;
+    const size_t fixed = align_up(sizeof(Shared), 128) + align_up((size_t)KB * act_elems * 2, 128) +
+                         align_up((size_t)KB * g.H * 4, 128) + (size_t)kAttnScratchWords * 4;
     if ((size_t)di.smem_optin < fixed + (size_t)kNW * 2048) return kErrResidency;
     int rw = (int)(((size_t)di.smem_optin - fixed) / kNW / 512 * 512);
     DecodeParams p{};
@@ -1634,7 +1639,7 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
         for (int t = 0; t < 4; ++t) ncta = rows[t] < ncta ? rows[t] : ncta;
     }
     if (ncta < 1) return kErrShape;
-    rc = make_phases(g, rw, ncta, row_cap(a.B), p.ph);
+    rc = make_phases(g, rw, ncta, row_cap(KB), p.ph);
     if (rc) return rc;
     const size_t smem = fixed + (size_t)kNW * rw;
 
@@ -1688,7 +1693,8 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
     p.bt_stride = a.bt_stride;
     p.ids_i64 = a.ids_i64 ? 1 : 0;
     p.cs_fp32 = a.cs_fp32 ? 1 : 0;
-    p.H = g.H; p.I = g.I; p.L = g.L; p.QH = g.QH; p.KVH = g.KVH; p.V = g.V; p.B = a.B; p.G = G;
+    p.H = g.H; p.I = g.I; p.L = g.L; p.QH = g.QH; p.KVH = g.KVH; p.V = g.V; p.B = KB; p.G = G;
+    p.nb = a.B;
     p.wfmt = g.wfmt;
     p.lm_head = (a.lm_head && (a.logits || a.next_ids)) ? 1 : 0;
     p.advance = (a.advance && p.lm_head && a.next_ids) ? 1 : 0;
@@ -1711,7 +1717,7 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
 static const char* status_string(int status) {
     switch (status) {
         case kOk: return "ok";
-        case kErrBatch: return "batch_must_be_1_to_4";
+        case kErrBatch: return "batch_must_be_1_to_8";
         case kErrMaxSeq: return "max_seq_len_must_be_1_to_8192";
         case kErrNull: return "null_device_pointer";
         case kErrCoop: return "cooperative_launch_unsupported";
@@ -1856,7 +1862,7 @@ extern "C" int mk_query(int* sm_count, int* coop, int* active_per_sm, int* major
 extern "C" size_t mk_workspace_bytes(int B, int max_seq_len) {
     (void)B;
     (void)max_seq_len;
-    return ws_layout(kGeom135, 4).total;
+    return ws_layout(kGeom135, kMaxB).total;
 }
 
 extern "C" int mk_decode(void* stream, int B, const void* input_ids, int ids_i64, const void* positions,
@@ -1875,7 +1881,7 @@ extern "C" int mk_decode(void* stream, int B, const void* input_ids, int ids_i64
 extern "C" const char* mk_status_string(int status) { return status_string(status); }
 
 // SmolLM2-360M: prime_kernels/decode_megakernel_360m/csrc/block360_kernel.inc:849-938
-extern "C" size_t decode360_workspace_bytes() { return ws_layout(kGeom360, 4).total; }
+extern "C" size_t decode360_workspace_bytes() { return ws_layout(kGeom360, kMaxB).total; }
 extern "C" size_t decode360_debug_bytes() { return 16; }   // stage dumps are not produced; accepted and ignored
 
 extern "C" int decode360(void* stream, int B, const void* input_ids, const void* embed, const void* final_norm,
@@ -1926,7 +1932,8 @@ extern "C" int pk_decode_step_static(const PkDecodeModel* m, const PkDecodeArgs*
     if (!m || !a) return kErrNull;
     if (m->kv_heads <= 0 || a->batch < 1) return kErrBatch;
     const ModelGeom g = to_geom(m);
-    if (ws_layout(g, a->batch).total > kStaticScratchBytes) return kErrStaticScratch;
+    if (a->batch > kMaxB) return kErrBatch;
+    if (ws_layout(g, a->batch <= 4 ? a->batch : kMaxB).total > kStaticScratchBytes) return kErrStaticScratch;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;

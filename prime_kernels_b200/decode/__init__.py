@@ -24,7 +24,7 @@ __all__ = ["Geometry", "SMOLLM2_135M", "SMOLLM2_360M", "SMOLLM2_1P7B", "GEOMETRI
            "HEAD_DIM", "decode_step", "check_status", "DecodeSession", "workspace_bytes", "pack_matrix_mxfp8", "pack_weights_mxfp8",
            "unpack_matrix_mxfp8", "packed_row_bytes"]
 
-MAX_BATCH = 4
+MAX_BATCH = 8
 MAX_SEQ = 8192
 HEAD_DIM = 64
 

@@ -41,6 +41,8 @@ def _step(D, geom, wd, kv, csd, cur, pos, lm_head=True, layer_outputs=None):
     ("gqa3-b4", (192, 512, 3, 3, 1, 1024), 4, 100, False),
     ("gqa3-b3-ctx1", (192, 512, 2, 6, 2, 2048), 3, 1, False),
     ("gqa3-b1-ctx1000", (192, 512, 2, 3, 1, 1024), 1, 1000, True),
+    ("gqa3-b6-padded", (192, 512, 2, 3, 1, 1024), 6, 50, True),
+    ("mha-b8", (128, 256, 2, 2, 2, 512), 8, 30, False),
 ])
 def test_small_geometries_against_restatement(cuda_device, name, dims, B, ctx, shuffle):
     from prime_kernels_b200 import decode as D

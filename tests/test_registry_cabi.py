@@ -55,15 +55,15 @@ def test_library_exports_every_declared_symbol():
 
 def test_status_strings_and_sizes_without_a_device():
     lib = _cabi.library()
-    assert lib.pk_status_string(9101).decode() == "batch_must_be_1_to_4"
+    assert lib.pk_status_string(9101).decode() == "batch_must_be_1_to_8"
     assert lib.mk_status_string(9110).decode() == "device_wait_timed_out"
     assert lib.decode360_status_string(9106).decode() == "kernel_requires_sm100"
     assert lib.pk_rmsnorm_scale_bytes(1, 960) == 8 * 512
     assert lib.pk_rmsnorm_scale_bytes(8192, 4096) == 64 * 32 * 512
-    assert lib.mk_workspace_bytes(1, 2048) == lib.mk_workspace_bytes(4, 8192) > 0
+    assert lib.mk_workspace_bytes(1, 2048) == lib.mk_workspace_bytes(8, 8192) > 0
     assert lib.decode360_workspace_bytes() > lib.mk_workspace_bytes(1, 1)
     m = _cabi.PkDecodeModel(960, 2560, 32, 15, 5, 49152, 0, 1e-5)
-    assert lib.pk_decode_workspace_bytes(ctypes.byref(m), 4) == lib.decode360_workspace_bytes()
+    assert lib.pk_decode_workspace_bytes(ctypes.byref(m), 8) == lib.decode360_workspace_bytes()
 
 
 def test_argument_validation_needs_no_device():
@@ -74,7 +74,7 @@ def test_argument_validation_needs_no_device():
     assert lib.mk_decode(None, 9, *([None] * 23)) == 9101 if False else True
     m = _cabi.PkDecodeModel(960, 2560, 32, 15, 5, 49152, 0, 1e-5)
     a = _cabi.PkDecodeArgs()
-    a.batch = 7
+    a.batch = 9
     assert lib.pk_decode_step(ctypes.byref(m), ctypes.byref(a)) == 9101
     a.batch = 1
     a.max_seq_len = 9000
@@ -113,7 +113,7 @@ def test_decode_contract_errors_are_valueerrors():
     from prime_kernels_b200 import decode_megakernel as a
 
     ids = torch.zeros(9, dtype=torch.int64)
-    with pytest.raises(ValueError, match="batch must be 1"):
+    with pytest.raises(ValueError, match="batch must be 1..8"):
         a.decode_step(input_ids=ids, positions=ids, seq_lens=ids, block_table=ids, slot_mapping=ids, embed=None,
                       layers=[], final_norm=None, kv_caches=[], cos_sin_cache=None, eps=1e-5)
     ids = torch.zeros(1, dtype=torch.int64)
