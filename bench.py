@@ -29,11 +29,16 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 WORKLOADS = {
-    # name: (geometry name, batch, prompt tokens, default steps, weight format)
-    "smollm2-360m-b1": ("smollm2-360m", 1, 512, 256),
-    "smollm2-135m-b1": ("smollm2-135m", 1, 32, 64),
-    "smollm2-1.7b-b1": ("smollm2-1.7b", 1, 1024, 256),
+    # name: (geometry name, batch, context tokens before timing, default steps)
+    "smollm2-360m-b1": ("smollm2-360m", 1, 512, 256),            # BASELINE config 2 (headline)
+    "smollm2-135m-b1": ("smollm2-135m", 1, 32, 64),              # config 1
+    "smollm2-1.7b-b1": ("smollm2-1.7b", 1, 1024, 256),           # config 5
+    "smollm2-1.7b-b8": ("smollm2-1.7b", 8, 1024, 256),
     "smollm2-360m-b4": ("smollm2-360m", 4, 512, 256),
+    "smollm2-360m-b8": ("smollm2-360m", 8, 512, 256),
+    # config 4: MXFP8 weights (E4M3 + E8M0 per 32 along K), context pre-filled to 4096 with normal(0,1) K/V
+    "smollm2-360m-mxfp8-b1": ("smollm2-360m", 1, 4096, 128),
+    "smollm2-360m-mxfp8-b4": ("smollm2-360m", 4, 4096, 128),
 }
 METRIC = "SmolLM2-360M bs1 decode tok/s & % HBM roofline; aggregate tok/s @1/2/4/8 GPUs"
 # DRAM bytes per launch measured with ncu (dram__bytes_read + write) at context 503-505 divided by the
@@ -42,13 +47,16 @@ METRIC = "SmolLM2-360M bs1 decode tok/s & % HBM roofline; aggregate tok/s @1/2/4
 NCU_TRAFFIC_RATIO = 1.005
 
 
-def algorithmic_bytes(geom, batch, seq):
-    """Bytes one decode step must move: every weight once (bf16) + K/V of `seq` positions per request."""
-    per_layer = geom.qkv_rows * geom.hidden + geom.hidden * geom.q_heads * 64 + 3 * geom.intermediate * geom.hidden \
-        + 2 * geom.hidden
-    params = geom.layers * per_layer + geom.vocab * geom.hidden + geom.hidden
+def algorithmic_bytes(geom, batch, seq, mxfp8=False):
+    """Bytes one decode step must move: every weight once (bf16, or E4M3 + one E8M0 per 32 for the matrices
+    when `mxfp8`) + K/V of `seq` positions per request."""
+    matrices = geom.layers * (geom.qkv_rows * geom.hidden + geom.hidden * geom.q_heads * 64
+                              + 3 * geom.intermediate * geom.hidden) + geom.vocab * geom.hidden
+    norms = geom.layers * 2 * geom.hidden + geom.hidden
     kv = 2 * geom.layers * geom.kv_heads * 64 * 2 * seq * batch
-    return 2 * params + kv
+    if mxfp8:
+        return matrices + matrices // 32 + 2 * norms + kv
+    return 2 * (matrices + norms) + kv
 
 
 class ClockSampler:
@@ -199,7 +207,11 @@ def main():
         torch.cuda.synchronize(dev)
 
     # ---- synthetic model + prompt (replica r decodes its own stream: seed 1234 + r)
+    mxfp8 = "mxfp8" in wl
     weights = harness.weights_to(harness.make_weights(geom, 0), dev)
+    if mxfp8:
+        geom = geom.with_format(1)
+        weights = D.pack_weights_mxfp8(weights)
     K, W = args.steps, max(args.warmup, 3)
     capacity = prompt_len + 2 * (K + W) + 64
     capacity = min(D.MAX_SEQ, (capacity + 15) // 16 * 16)
@@ -209,10 +221,18 @@ def main():
     def new_session():
         kv = harness.PagedKV(geom, batch, capacity, dev)
         sess = D.DecodeSession(geom, embed=weights["embed"], layers=weights["layers"], final_norm=weights["final_norm"],
-                               kv_caches=kv.kv_caches, cos_sin_cache=cos_sin, block_table=kv.block_table)
+                               kv_caches=kv.kv_caches, cos_sin_cache=cos_sin, block_table=kv.block_table,
+                               embed_lookup=weights.get("embed_lookup"))
         return kv, sess
 
     def prefill(sess):
+        if mxfp8:
+            # config 4: the context is pre-filled with normal(0,1) bf16 K/V (seed 3), not computed from a prompt
+            g3 = torch.Generator(device=dev).manual_seed(3)
+            for cache in sess.kv_caches:
+                cache.copy_(torch.randn(cache.shape, generator=g3, device=dev, dtype=torch.float32).to(torch.bfloat16))
+            sess.start(prompt[:, -1], torch.full((batch,), prompt_len - 1, dtype=torch.int64))
+            return
         # the prompt goes through the same kernel, token by token (teacher forced), which fills the cache
         sess.start(prompt[:, 0], torch.zeros(batch, dtype=torch.int64))
         for t in range(prompt_len - 1):
@@ -268,7 +288,8 @@ def main():
             _, _, nxt = D.decode_step(geom, input_ids=d_ids, positions=d_pos, seq_lens=d_seq,
                                       block_table=kv2.block_table, slot_mapping=d_slot, embed=weights["embed"],
                                       layers=weights["layers"], final_norm=weights["final_norm"],
-                                      kv_caches=kv2.kv_caches, cos_sin_cache=cos_sin, eps=geom.eps, lm_head=True)
+                                      kv_caches=kv2.kv_caches, cos_sin_cache=cos_sin, eps=geom.eps, lm_head=True,
+                                      embed_lookup=weights.get("embed_lookup"))
             h_next.copy_(nxt, non_blocking=True)
             torch.cuda.current_stream(dev).synchronize()
             cur.copy_(h_next)
@@ -295,19 +316,19 @@ def main():
             peak, peak_src = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
         else:
             peak, peak_src = 6650.0, "fallback (earlier pool measurement)"
-        mean_bytes = statistics.mean(algorithmic_bytes(geom, batch, s) for s in (seq_first, seq_last))
+        mean_bytes = statistics.mean(algorithmic_bytes(geom, batch, s, mxfp8) for s in (seq_first, seq_last))
         step_ms = ms_max / K
         achieved = mean_bytes / (step_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": aggregate_throughput(world, batch, K, ms_max), "unit": "tok/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": None, "dtype": "bf16 activations, MXFP8 weights" if mxfp8 else "bf16", "data": "synthetic",
             "config": {"workload": wl, "geometry": gname, "batch": batch, "prompt_tokens": prompt_len,
                        "context_during_timing": [seq_first, seq_last], "kv_block": 16,
                        "replicas": world, "l2": "weights (>= 269 MB per step) exceed the 126 MB L2; no flush needed",
                        "timing": "CUDA events on the launching stream around K back-to-back launches"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": mean_bytes * NCU_TRAFFIC_RATIO if gname == "smollm2-360m" and batch == 1 else None,
+                         "traffic": mean_bytes * NCU_TRAFFIC_RATIO if gname == "smollm2-360m" and batch == 1 and not mxfp8 else None,
                          "traffic_source": "ncu capture at context 503-505 scaled by algorithmic bytes",
                          "peak_source": peak_src, "frac_of_8TBs_nominal": achieved / 8000.0,
                          "algorithmic_bytes_per_step": mean_bytes},

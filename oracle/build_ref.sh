@@ -1,8 +1,12 @@
 #!/usr/bin/env bash
-# TEST INFRASTRUCTURE. Compiles the reference project's own CPU reference for the MXFP8
-# quantiser from the reference checkout into oracle/_ref/ (git-ignored). Needs nvcc only
-# because the reference's host code uses CUDA's host-callable conversion intrinsics; no GPU
-# is needed to build or to run the result.
+# TEST INFRASTRUCTURE. Compiles, from the reference checkout where it lies, into oracle/_ref/
+# (git-ignored):
+#   libref_rmsnorm.so       the reference's own CPU reference() for the MXFP8 quantiser (needs nvcc only
+#                           because its host code uses CUDA's host-callable conversion intrinsics; runs
+#                           without a GPU)
+#   libref_rmsnorm_gpu.so   the reference's own GPU kernels behind a C entry point (GPU parity tests)
+#   ref_rmsnorm_bench       the reference's own benchmark executable (same-box timing of its kernels)
+# The reference's cmake project is not run: its sources are handed to nvcc directly.
 #   usage: oracle/build_ref.sh [/path/to/reference/checkout]
 set -euo pipefail
 here="$(cd "$(dirname "$0")" && pwd)"
@@ -10,9 +14,22 @@ ref="${1:-/root/reference}"
 src="$ref/prime_kernels/rmsnorm"
 [ -f "$src/test.cu" ] || { echo "reference checkout not found at $ref; keeping any prebuilt oracle/_ref" >&2; exit 0; }
 mkdir -p "$here/_ref"
+# fresh OUT IN...: true when OUT exists and is newer than every input
+fresh() { local out="$1"; shift; [ -f "$out" ] || return 1; for f in "$@"; do [ "$out" -nt "$f" ] || return 1; done; }
+fresh "$here/_ref/libref_rmsnorm.so" "$src/test.cu" "$here/ref_rmsnorm_wrapper.cu" || \
 nvcc -O2 -std=c++17 -shared -Xcompiler -fPIC -w \
   -gencode arch=compute_100a,code=sm_100a \
   -I"$src" -I"$src/src/include" \
   -DREF_TEST_CU="\"$src/test.cu\"" \
   -o "$here/_ref/libref_rmsnorm.so" "$here/ref_rmsnorm_wrapper.cu"
 echo "built $here/_ref/libref_rmsnorm.so"
+kernels=("$src/rmsnorm.cu" "$src"/src/kernels/rmsnorm_0[0-5]_*.cu)
+common=(-O3 -std=c++20 -w -gencode arch=compute_100a,code=sm_100a -I"$src" -I"$src/src/include")
+headers=("$src/rmsnorm.cuh" "$src"/src/include/*)
+fresh "$here/_ref/libref_rmsnorm_gpu.so" "${kernels[@]}" "${headers[@]}" "$here/ref_rmsnorm_gpu_wrapper.cu" || \
+nvcc "${common[@]}" -shared -Xcompiler -fPIC -o "$here/_ref/libref_rmsnorm_gpu.so" \
+  "${kernels[@]}" "$here/ref_rmsnorm_gpu_wrapper.cu" -lcuda
+echo "built $here/_ref/libref_rmsnorm_gpu.so"
+fresh "$here/_ref/ref_rmsnorm_bench" "${kernels[@]}" "${headers[@]}" "$src/bench.cu" || \
+nvcc "${common[@]}" -o "$here/_ref/ref_rmsnorm_bench" "${kernels[@]}" "$src/bench.cu" -lcuda
+echo "built $here/_ref/ref_rmsnorm_bench"

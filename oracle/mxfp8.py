@@ -87,6 +87,26 @@ def ref() -> ctypes.CDLL:
     return _REF
 
 
+_REF_GPU = None
+
+
+def ref_gpu_available() -> bool:
+    return (HERE / "_ref" / "libref_rmsnorm_gpu.so").exists()
+
+
+def ref_gpu() -> ctypes.CDLL:
+    """The reference's own GPU kernels (oracle/ref_rmsnorm_gpu_wrapper.cu); device pointers as integers."""
+    global _REF_GPU
+    if _REF_GPU is None:
+        lib = ctypes.CDLL(str(HERE / "_ref" / "libref_rmsnorm_gpu.so"))
+        vp = ctypes.c_void_p
+        lib.ref_rmsnorm_gpu.argtypes = [ctypes.c_char_p, vp, vp, vp, vp, vp, vp, ctypes.c_float, ctypes.c_int,
+                                        ctypes.c_int, vp]
+        lib.ref_rmsnorm_gpu.restype = ctypes.c_int
+        _REF_GPU = lib
+    return _REF_GPU
+
+
 def scale_bytes(n: int, c: int) -> int:
     return ((n + 127) // 128) * ((c + 127) // 128) * 512
 

@@ -484,6 +484,32 @@ __device__ __forceinline__ float dot16_e4m3(const uint4 w, const uint4 a0, const
 
 __device__ __forceinline__ uint32_t layer_tag(const Ctx& c, int layer) { return c.tag_base + (uint32_t)layer + 1u; }
 
+__host__ __device__ constexpr int pow2_ceil(int n) { return n <= 1 ? 1 : 2 * pow2_ceil((n + 1) / 2); }
+__host__ __device__ constexpr int ilog2(int n) { return n <= 1 ? 0 : 1 + ilog2(n / 2); }
+
+// Warp reduction of NV values per lane that also transposes: on return lane L holds the sum over
+// all lanes of v[L >> (5 - log2 NV)].  Step t exchanges one half of the remaining values with the
+// lane at distance 16 >> t and keeps the other half, so the number of live values halves each step.
+template <int NV>
+__device__ __forceinline__ float transpose_reduce(float (&v)[NV], int lane) {
+    static_assert(NV >= 1 && NV <= 32 && (NV & (NV - 1)) == 0, "NV must be a power of two up to 32");
+#pragma unroll
+    for (int k = NV / 2; k >= 1; k >>= 1) {
+        const int off = 16 / (NV / (2 * k));
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < k; ++i) {
+            const float send = upper ? v[i] : v[i + k];
+            const float keep = upper ? v[i + k] : v[i];
+            v[i] = keep + __shfl_xor_sync(kFullMask, send, off);
+        }
+    }
+    float r = v[0];
+#pragma unroll
+    for (int off = 16 / NV; off >= 1; off >>= 1) r += __shfl_xor_sync(kFullMask, r, off);
+    return r;
+}
+
 // ------------------------------------------------------------------ GEMV row kernels
 // NR staged rows (row r at ep + r * stride chunks) times B activation vectors, K-split over the lanes.
 // A lone warp cannot hide instruction latency behind other warps, so the loops are unrolled four
@@ -613,51 +639,50 @@ __device__ void gemv_phase(Ctx& c, const int T, int layer, uint32_t& consumed) {
             ++consumed;
             if (T == kGU && c.prof) c.prof[17] = global_ns();
         }
-        // warp-reduce every accumulator; then lane i finishes row i -- all rows at once, each lane picking
-        // its row's sums with selects (no divergent per-row branches, no dynamic register indexing)
+        // Transposing warp reduction: afterwards lane L holds the total of value L >> SH, where value
+        // j = (request j / RM, staged row j % RM), so every (row, request) pair is finished by its
+        // own lane at once (no dynamic register indexing, 31 shuffles at most instead of 5 per value).
+        constexpr int NV = pow2_ceil(RM * B);
+        constexpr int SH = 5 - ilog2(NV);
+        float v[NV];
 #pragma unroll
-        for (int i = 0; i < RM; ++i)
-#pragma unroll
-            for (int b = 0; b < B; ++b) acc[i][b] = warp_sum(acc[i][b] + acc2[i][b]);
-        if (T == kGU && c.prof) c.prof[18] = global_ns();
-        float mine[B], mine_up[B];
-#pragma unroll
-        for (int b = 0; b < B; ++b) {
-            mine[b] = mine_up[b] = 0.f;
-#pragma unroll
-            for (int i = 0; i < RM; ++i) {
-                if (i == lane) mine[b] = acc[i][b];
-                if (i == lane + nre) mine_up[b] = acc[i][b];      // gate/up entries: up row of pair `lane`
-            }
+        for (int j = 0; j < NV; ++j) {
+            const int bb = j / RM < B ? j / RM : 0;     // NV > RM * B only for batch 3: those values are zero
+            v[j] = (j / RM < B) ? acc[j % RM][bb] + acc2[j % RM][bb] : 0.f;
         }
-        if (lane < nre) {
-            const int r = row + lane;
-#pragma unroll
-            for (int b = 0; b < B; ++b) {
+        const float mine = transpose_reduce<NV>(v, lane);
+        if (T == kGU && c.prof) c.prof[18] = global_ns();
+        const int vj = lane >> SH;
+        const int ri = vj % RM, b = vj / RM;
+        // gate/up entries: the lane that owns gate row ri also needs up row ri, staged at nre + ri
+        const float mine_up = __shfl_sync(kFullMask, mine, ((vj + nre) << SH) & 31);
+        if ((lane & ((1 << SH) - 1)) == 0 && b < B && ri < nre) {
+            const int r = row + ri;
+            {
                 if (T == kQKV) {
                     // projection output rounded to bf16 (HF linear output dtype)
-                    st_flagged(p.ll_qkv + (size_t)par * B * d.nrows + b * d.nrows + r, f32_to_bf16_bits(mine[b]), tag);
+                    st_flagged(p.ll_qkv + (size_t)par * B * d.nrows + b * d.nrows + r, f32_to_bf16_bits(mine), tag);
                 } else if (T == kO) {
                     // h1 = bf16( x + bf16(o_proj) )
-                    const float o = round_bf16(mine[b]);
+                    const float o = round_bf16(mine);
                     const float h = round_bf16(__fadd_rn(c.res[b * p.H + r], o));
                     st_flagged(p.ll_h1 + (size_t)par * B * p.H + b * p.H + r, f32_to_bf16_bits(h), tag);
                 } else if (T == kGU) {
                     // act = bf16( bf16(silu(bf16 gate)) * bf16 up )   (HF LlamaMLP rounding)
-                    const float g = round_bf16(mine[b]);
-                    const float u = round_bf16(mine_up[b]);
+                    const float g = round_bf16(mine);
+                    const float u = round_bf16(mine_up);
                     const float silu = round_bf16(__fdividef(g, 1.f + __expf(-g)));
                     const float a = round_bf16(__fmul_rn(silu, u));
                     st_flagged(p.ll_act + (size_t)par * B * p.I + b * p.I + r, f32_to_bf16_bits(a), tag);
                 } else if (T == kDown) {
                     // x' = bf16( h1 + bf16(down_proj) ), handed to the next layer's parity slot
-                    const float dn = round_bf16(mine[b]);
+                    const float dn = round_bf16(mine);
                     const uint32_t xb = f32_to_bf16_bits(__fadd_rn(c.res[b * p.H + r], dn));
                     st_flagged(p.ll_x + (size_t)((layer + 1) & 1) * B * p.H + b * p.H + r, xb, layer_tag(c, layer + 1));
                     if (p.layer_outputs && b < p.nb) p.layer_outputs[((size_t)layer * p.nb + b) * p.H + r] = (uint16_t)xb;
                 } else {
                     // logits rounded to bf16; argmax breaks ties toward the lowest index
-                    const uint32_t lb = f32_to_bf16_bits(mine[b]);
+                    const uint32_t lb = f32_to_bf16_bits(mine);
                     if (p.logits && b < p.nb) p.logits[(size_t)b * p.V + r] = (uint16_t)lb;
                     if (p.next_ids && b < p.nb) {
                         const uint32_t ord = (lb & 0x8000u) ? (~lb & 0xffffu) : (lb | 0x8000u);
@@ -690,24 +715,35 @@ __device__ void stage_norm(Ctx& c, const unsigned long long* src_words, uint32_t
         wreg[u] = i < H ? __uint_as_float((uint32_t)__ldg(weight + i) << 16) : 0.f;
     }
     consumer_bar();   // everyone is done with the previous phase's act/res
+    // Up to RG requests are polled in one round, so the wait costs one L2 round trip per RG requests
+    // instead of one per request.
+    constexpr int RG = B < 4 ? B : 4;
     float ss[B];
 #pragma unroll
-    for (int b = 0; b < B; ++b) {
-        ss[b] = 0.f;
-        for (int i0 = ct; i0 < H; i0 += 8 * kCT) {
-            uint32_t xv[8];
+    for (int b = 0; b < B; ++b) ss[b] = 0.f;
+    for (int i0 = ct; i0 < H; i0 += 8 * kCT) {
+#pragma unroll
+        for (int bg = 0; bg < B; bg += RG) {
+            uint32_t xv[RG * 8];
             if (from_embed) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int i = i0 + u * kCT;
-                    xv[u] = i < H ? (uint32_t)p.embed_bf16[(size_t)sh.tok[b] * H + i] : 0u;
+                for (int u = 0; u < RG * 8; ++u) {
+                    const int i = i0 + (u & 7) * kCT;
+                    xv[u] = i < H ? (uint32_t)p.embed_bf16[(size_t)sh.tok[bg + (u >> 3)] * H + i] : 0u;
                 }
             } else {
-                wait_flagged_strided<8>(c, src_words + b * H, i0, kCT, H, tag, xv);
+                wait_flagged_multi<RG * 8>(
+                    c,
+                    [&](int u) {
+                        const int i = i0 + (u & 7) * kCT;
+                        return i < H ? src_words + (bg + (u >> 3)) * H + i : nullptr;
+                    },
+                    tag, xv);
             }
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int i = i0 + u * kCT;
+            for (int u = 0; u < RG * 8; ++u) {
+                const int i = i0 + (u & 7) * kCT;
+                const int b = bg + (u >> 3);
                 if (i < H) {
                     const float x = __uint_as_float(xv[u] << 16);
                     c.res[b * H + i] = x;
@@ -715,6 +751,9 @@ __device__ void stage_norm(Ctx& c, const unsigned long long* src_words, uint32_t
                 }
             }
         }
+    }
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
         ss[b] = warp_sum(ss[b]);
         if (c.lane == 0) sh.red[b][c.warp] = ss[b];
     }
@@ -726,11 +765,18 @@ __device__ void stage_norm(Ctx& c, const unsigned long long* src_words, uint32_t
 #pragma unroll
         for (int w = 0; w < kNW; ++w) tot += sh.red[b][w];
         const float s = rsqrtf(tot * (1.f / (float)H) + p.eps);
+        // all loads first: the stores below may alias them as far as the compiler knows
+        float xr[kNormRegs];
+#pragma unroll
+        for (int u = 0; u < kNormRegs; ++u) {
+            const int i = ct + u * kCT;
+            xr[u] = i < H ? c.res[b * H + i] : 0.f;
+        }
 #pragma unroll
         for (int u = 0; u < kNormRegs; ++u) {
             const int i = ct + u * kCT;
             if (i < H) {
-                const float n = round_bf16(__fmul_rn(c.res[b * H + i], s));
+                const float n = round_bf16(__fmul_rn(xr[u], s));
                 act16[(size_t)b * p.act_elems + i] = (uint16_t)f32_to_bf16_bits(__fmul_rn(n, wreg[u]));
             }
         }
@@ -1298,14 +1344,18 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
         sh.slot[tid] = tid < p.nb ? p.slot_mapping[src] : -1LL;
         sh.tok[tid] = p.ids_i64 ? reinterpret_cast<const long long*>(p.input_ids)[src]
                                 : (long long)reinterpret_cast<const int*>(p.input_ids)[src];
-        // Split-KV chunking: 16 positions per warp and chunk (one load batch per lane group), longer
-        // only when that would need more than kNCMax chunks.  With few partials (short contexts) every
-        // CTA merges them itself while staging the O projection input (direct mode, one hand-off);
-        // otherwise one warp per (request, head) merges and publishes the result (two hand-offs, but
-        // no redundant staging).  The mode is decided on the longest request so it is CTA-uniform.
+        // Split-KV chunking: one CTA per (request, kv head, chunk) item.  The chunk length is the
+        // shortest multiple of 16 positions, at least one 16-position run per warp, that keeps the
+        // number of items within one round of the grid (and the chunks per request within kNCMax);
+        // when there are more (request, kv head) pairs than CTAs a chunk covers the whole context.
+        // With few partials (short contexts) every CTA merges them itself while staging the O
+        // projection input (direct mode, one hand-off); otherwise one warp per (request, head) merges
+        // and publishes the result (two hand-offs, but no redundant staging).  The mode is decided on
+        // the longest request so it is CTA-uniform.
         int smax = 1;
         for (int bb = 0; bb < p.nb; ++bb) smax = max(smax, max(p.seq_lens[bb], 1));
-        const int lc = max(16 * kNW, (((smax + kNCMax - 1) / kNCMax) + 15) & ~15);
+        const int nct = min(max(ncta / (B * p.KVH), 1), kNCMax);
+        const int lc = max(16 * kNW, (((smax + nct - 1) / nct) + 15) & ~15);
         const int two = (B * p.QH * ((smax + lc - 1) / lc) * 66 > kDirectWords) ? 1 : 0;
         sh.lc[tid] = lc;
         sh.nc[tid] = (seq + lc - 1) / lc;
