@@ -40,6 +40,9 @@ int pk_fused_rmsnorm_residual_forward_ex(void* vals, void* scales, float* rrms, 
 /* Size in bytes of the blocked scale buffer: ceil(N/128) * ceil(C/128) * 512
  * (scale_numel in prime_kernels/rmsnorm/csrc/torch_interface.cpp:18-20, extended to ragged shapes). */
 long long pk_rmsnorm_scale_bytes(int N, int C);
+/* Bounded barrier waits of the pipelined kernel that expired since load (0 = healthy; -1 = CUDA error).
+ * No counterpart in the reference (its TMA kernels wait without a bound, rmsnorm_05_tma.cu). Synchronises. */
+long long pk_rmsnorm_wait_timeouts(void);
 
 /* ---------------------------------------------------------------- forward ops the megakernel absorbs, standalone */
 

@@ -1,5 +1,13 @@
 // Fused RMSNorm + residual + MXFP8 quantisation for sm_100a.
 //
+// Two kernels share the arithmetic:
+//  * rmsnorm_pipe_kernel (large power-of-two shapes): persistent CTAs; a producer warp streams tiles of
+//    whole rows into a 3-stage shared-memory ring with bulk async copies (completion on mbarriers), the
+//    consumer warps take one 1024-element unit each -- a lane owns one 32-element MXFP8 group, so the group
+//    amax needs no shuffle -- and the fp8 bytes leave through a bulk shared->global store.  The bytes in
+//    flight are set by the ring (two stages), not by registers or occupancy.
+//  * rmsnorm_mxfp8_kernel (every other shape): the row stays in registers, described next.
+//
 // One row is handled by a team of W warps.  Every thread owns U 16-byte chunks (8 bf16) of the
 // row at chunk indices t, t+T, t+2T, ... (T = 32*W), so every load and store instruction of a
 // warp touches one contiguous 512-byte (loads) / 256-byte (fp8 stores) span: fully coalesced
@@ -65,11 +73,6 @@ __device__ __forceinline__ void fma2_bf16(uint32_t a, uint32_t b, float c_lo, fl
         : "=f"(d_lo), "=f"(d_hi)
         : "r"(a), "r"(b), "f"(c_lo), "f"(c_hi));
 }
-__device__ __forceinline__ uint32_t abs_bf16x2(uint32_t a) {
-    uint32_t r;
-    asm("abs.bf16x2 %0, %1;" : "=r"(r) : "r"(a));
-    return r;
-}
 __device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
     uint32_t r;
     asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
@@ -77,7 +80,10 @@ __device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
 }
 constexpr uint32_t kOnesBf16x2 = 0x3f803f80u;
 
-template <int U>
+// LW: fetch the norm weights after the reduction (fewer live registers while the row's loads are in flight:
+// better for large inputs) instead of together with the row (shorter dependent chain: better when one
+// wave of blocks covers the whole input).
+template <int U, int LW>
 __global__ void __launch_bounds__(256, U == 4 ? 4 : 2) rmsnorm_mxfp8_kernel(const RmsParams p) {
     extern __shared__ float red_s[];   // [rows_per_block][W]
     const int W = p.warps_per_row;
@@ -103,10 +109,12 @@ __global__ void __launch_bounds__(256, U == 4 ? 4 : 2) rmsnorm_mxfp8_kernel(cons
                 rs[i] = ld_stream_16(rp + c);
             }
         }
+        if (!LW) {
 #pragma unroll
-        for (int i = 0; i < U; ++i) {
-            const int c = tt + i * T;
-            if (c < nch) wt[i] = __ldg(p.weight + c);
+            for (int i = 0; i < U; ++i) {
+                const int c = tt + i * T;
+                if (c < nch) wt[i] = __ldg(p.weight + c);
+            }
         }
 #pragma unroll
         for (int i = 0; i < U; ++i) {
@@ -133,7 +141,8 @@ __global__ void __launch_bounds__(256, U == 4 ? 4 : 2) rmsnorm_mxfp8_kernel(cons
     ss = warp_sum(ss + ss2);
     if (W > 1) {
         if (lane == 0) red_s[team * W + warp_in_team] = ss;
-        __syncthreads();
+        // one named barrier per team: the rows of a block do not wait for each other
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "r"(T) : "memory");
         float tot = 0.f;
         for (int w = 0; w < W; ++w) tot += red_s[team * W + w];
         ss = tot;
@@ -141,6 +150,15 @@ __global__ void __launch_bounds__(256, U == 4 ? 4 : 2) rmsnorm_mxfp8_kernel(cons
     const float s = rsqrtf(ss * p.inv_c + p.eps);
 
     if (row >= p.n_pad) return;
+    // late weights (an L1/L2 hit): holding them across the reduction would cost 4*U registers during
+    // the phase in which the row's loads are in flight
+    if (LW && live) {
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            const int c = tt + i * T;
+            if (c < nch) wt[i] = __ldg(p.weight + c);
+        }
+    }
     uint32_t* sc32 = reinterpret_cast<uint32_t*>(p.scales);
 #pragma unroll
     for (int i = 0; i < U; ++i) {
@@ -161,7 +179,7 @@ __global__ void __launch_bounds__(256, U == 4 ? 4 : 2) rmsnorm_mxfp8_kernel(cons
                 // as widening r and adding; never contracted with the multiply above)
                 if (!p.mode) fma2_bf16(r4[k], kOnesBf16x2, ol, oh, ol, oh);
                 packed[k] = pack_bf16x2(ol, oh);
-                amax2 = max_bf16x2(amax2, abs_bf16x2(packed[k]));
+                amax2 = max_bf16x2(amax2, packed[k] & 0x7fff7fffu);    // |x| by mask: abs.bf16x2 issues at half rate
             }
             if (p.res_out) {
                 const uint4 o = p.mode ? br[i] : make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -202,7 +220,208 @@ __global__ void __launch_bounds__(256, U == 4 ? 4 : 2) rmsnorm_mxfp8_kernel(cons
     if (live && tt == 0) p.rrms[row] = s;
 }
 
+
+// ---------------------------------------------------------------- pipelined kernel
+constexpr int kPipeStages = 3;
+constexpr int kPipeUnit = 1024;                 // elements per consumer warp and tile
+constexpr unsigned kPipeSpinLimit = 1u << 26;   // bounded mbarrier waits (~seconds)
+__device__ unsigned int g_rms_wait_timeouts;    // waits that gave up (results of that launch are invalid)
+
+__device__ __forceinline__ void pipe_wait(uint64_t* bar, uint32_t parity) {
+    for (unsigned spins = 0; !mbar_test(bar, parity); ++spins)
+        if (spins > kPipeSpinLimit) {
+            atomicAdd(&g_rms_wait_timeouts, 1u);
+            return;
+        }
+}
+// global -> this CTA's shared memory (never multicast), completion counted in bytes on an mbarrier
+__device__ __forceinline__ void pipe_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void pipe_s2g(void* dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+struct PipeShared {
+    uint64_t full[kPipeStages], empty[kPipeStages];
+    float part[2][16];            // per-unit sums of squares, double-buffered by tile parity
+};
+constexpr size_t pipe_smem_bytes(int pw) { return 256 + (size_t)kPipeStages * pw * kPipeUnit * 4 + (size_t)pw * 2048; }
+
+// C = 1024 * M; PW consumer warps (one unit each) + one producer warp; a tile is PW / M consecutive rows, so
+// its branch and residual bytes are one contiguous range each.  16 / PW CTAs per SM.
+template <int M, int PW>
+__global__ void __launch_bounds__(PW * 32 + 32, 16 / PW) rmsnorm_pipe_kernel(const RmsParams p, int ntiles) {
+    constexpr int kTile = PW * kPipeUnit;
+    extern __shared__ __align__(128) unsigned char pipe_smem[];
+    PipeShared& sh = *reinterpret_cast<PipeShared*>(pipe_smem);
+    unsigned char* stages = pipe_smem + 256;                                  // kPipeStages x (branch, residual)
+    unsigned char* outs = stages + (size_t)kPipeStages * kTile * 4;           // PW x 2 x 1 KB of fp8
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kPipeStages; ++s) {
+            mbar_init(&sh.full[s], 1);
+            mbar_init(&sh.empty[s], PW);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == PW) {
+        if (lane == 0) {
+            int it = 0;
+            for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+                const int s = it % kPipeStages;
+                if (it >= kPipeStages) pipe_wait(&sh.empty[s], ((it / kPipeStages) - 1) & 1);
+                mbar_expect_tx(&sh.full[s], kTile * 4);
+                unsigned char* dst = stages + (size_t)s * kTile * 4;
+                pipe_g2s(dst, reinterpret_cast<const uint16_t*>(p.branch) + (size_t)t * kTile, kTile * 2, &sh.full[s]);
+                pipe_g2s(dst + kTile * 2, reinterpret_cast<const uint16_t*>(p.residual) + (size_t)t * kTile, kTile * 2,
+                         &sh.full[s]);
+            }
+        }
+        return;
+    }
+    constexpr int R = PW / M;                         // rows per tile
+    const int row_in_tile = warp / M, seg = warp % M;
+    // A lane owns 64 contiguous bytes (one 32-element group) of each input.  Its four 16-byte chunks are
+    // visited in an order rotated by lane / 2, which makes every 8-lane phase of a 128-bit shared-memory
+    // access hit eight different 16-byte bank groups.
+    const int rot = lane >> 1;
+    const uint4* wsrc = p.weight + seg * 128 + 4 * lane;
+    uint32_t* sc32 = reinterpret_cast<uint32_t*>(p.scales);
+    unsigned char* myout = outs + (size_t)warp * 2048;
+    int it = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+        const int s = it % kPipeStages;
+        pipe_wait(&sh.full[s], (it / kPipeStages) & 1);
+        const uint4* sb = reinterpret_cast<const uint4*>(stages + (size_t)s * kTile * 4) + warp * 128 + 4 * lane;
+        const uint4* sr = sb + kTile / 8;
+        uint4 br[4], rs[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int cj = (j + rot) & 3;
+            br[j] = sb[cj];
+            rs[j] = sr[cj];
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.empty[s]);      // the unit is in registers: the stage can be refilled
+        float ss = 0.f, ss2 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            fma2_bf16(br[j].x, br[j].x, ss, ss2, ss, ss2);
+            fma2_bf16(br[j].y, br[j].y, ss, ss2, ss, ss2);
+            fma2_bf16(br[j].z, br[j].z, ss, ss2, ss, ss2);
+            fma2_bf16(br[j].w, br[j].w, ss, ss2, ss, ss2);
+        }
+        ss = warp_sum(ss + ss2);
+        if (M > 1) {
+            // the M warps of a row meet on the row's own named barrier; partials are summed in unit order
+            if (lane == 0) sh.part[it & 1][warp] = ss;
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + row_in_tile), "n"(32 * M) : "memory");
+            float tot = 0.f;
+#pragma unroll
+            for (int j = 0; j < M; ++j) tot += sh.part[it & 1][row_in_tile * M + j];
+            ss = tot;
+        }
+        const float sc = rsqrtf(ss * p.inv_c + p.eps);
+        uint4 wt[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wt[j] = __ldg(wsrc + ((j + rot) & 3));
+        uint32_t amax2 = 0u;
+        uint32_t res[16];                              // bf16 pairs of the pre-quantisation values
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t a[4] = {br[j].x, br[j].y, br[j].z, br[j].w};
+            const uint32_t r4[4] = {rs[j].x, rs[j].y, rs[j].z, rs[j].w};
+            const uint32_t w4[4] = {wt[j].x, wt[j].y, wt[j].z, wt[j].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float pl, ph;
+                fma2_bf16(a[k], w4[k], 0.f, 0.f, pl, ph);                 // exact bf16 x bf16 products
+                float ol = __fmul_rn(sc, pl), oh = __fmul_rn(sc, ph);
+                fma2_bf16(r4[k], kOnesBf16x2, ol, oh, ol, oh);            // + residual in fp32, one rounding
+                res[4 * j + k] = pack_bf16x2(ol, oh);
+                amax2 = max_bf16x2(amax2, res[4 * j + k] & 0x7fff7fffu);
+            }
+        }
+        const float amax = fmaxf(bf16_lo(amax2), bf16_hi(amax2));
+        const uint32_t sf = e8m0_roundup(__fmul_rn(amax, 1.f / 448.f));
+        const uint32_t e = 254u - sf;
+        const uint32_t invb = e ? (e << 7) : 0x0040u;                     // bf16 bits of 2^(127 - sf)
+        const uint32_t inv2 = invb | (invb << 16);
+        // the bulk store issued from this output buffer two tiles ago must have finished reading it
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        __syncwarp();
+        unsigned char* ob = myout + (it & 1) * 1024 + lane * 32;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) fma2_bf16(res[4 * j + k], inv2, 0.f, 0.f, v[2 * k], v[2 * k + 1]);
+            uint2 q;
+            q.x = e4m3x2(v[0], v[1]) | (e4m3x2(v[2], v[3]) << 16);
+            q.y = e4m3x2(v[4], v[5]) | (e4m3x2(v[6], v[7]) << 16);
+            *reinterpret_cast<uint2*>(ob + 8 * ((j + rot) & 3)) = q;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) pipe_s2g(p.vals + (size_t)t * kTile + warp * kPipeUnit, myout + (it & 1) * 1024, 1024);
+        // scale bytes of four adjacent groups -> one 32-bit store into the blocked layout
+        uint32_t w2 = sf | (__shfl_xor_sync(kFullMask, sf, 1) << 8);
+        w2 |= __shfl_xor_sync(kFullMask, w2, 2) << 16;
+        const int row = t * R + row_in_tile;
+        if ((lane & 3) == 0) {
+            const int k = seg * 32 + lane;
+            const size_t off = ((size_t)(row >> 7) * p.nkt + (k >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
+            sc32[off >> 2] = w2;
+        }
+        if (seg == 0 && lane == 0) p.rrms[row] = sc;
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+template <int M, int PW>
+static int launch_pipe_mp(const RmsParams& p, cudaStream_t stream) {
+    static int sms[64] = {0};        // per device: SM count, read once (and the kernel's shared-memory opt-in)
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return kErrShape;
+    constexpr size_t smem = pipe_smem_bytes(PW);
+    if (!sms[dev]) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        cudaError_t e = cudaFuncSetAttribute(rmsnorm_pipe_kernel<M, PW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        sms[dev] = n;
+    }
+    const int ntiles = p.n / (PW / M);
+    const int grid = ntiles < sms[dev] * (16 / PW) ? ntiles : sms[dev] * (16 / PW);
+    rmsnorm_pipe_kernel<M, PW><<<grid, PW * 32 + 32, smem, stream>>>(p, ntiles);
+    return (int)cudaPeekAtLastError();
+}
+
+// Shapes the pipelined kernel takes: reference semantics only (mode 0, no residual output), whole 128-row
+// tiles, C a power of two from 1024 to 16384, and enough rows to give every CTA several tiles.
+static bool pipe_eligible(const RmsParams& p) {
+    if (p.mode != 0 || p.res_out != nullptr || (p.n % 128) != 0) return false;
+    if (p.c != 1024 && p.c != 2048 && p.c != 4096 && p.c != 8192 && p.c != 16384) return false;
+    return (long long)p.n * p.c >= (1ll << 24);
+}
+static int launch_pipe(const RmsParams& p, cudaStream_t stream) {
+    switch (p.c) {
+        case 1024: return launch_pipe_mp<1, 8>(p, stream);
+        case 2048: return launch_pipe_mp<2, 8>(p, stream);
+        case 4096: return launch_pipe_mp<4, 8>(p, stream);
+        case 8192: return launch_pipe_mp<8, 8>(p, stream);
+        default: return launch_pipe_mp<16, 16>(p, stream);
+    }
+}
+
 static int launch_rmsnorm(const RmsParams& p0, cudaStream_t stream) {
+    if (pipe_eligible(p0)) return launch_pipe(p0, stream);
     RmsParams p = p0;
     const int nch = p.c / 8;
     // a team is at most 8 warps (256 threads): 4 chunks per thread up to C = 8192, 8 chunks up to 16384
@@ -218,10 +437,13 @@ static int launch_rmsnorm(const RmsParams& p0, cudaStream_t stream) {
     const int grid = (p.n_pad + p.rows_per_block - 1) / p.rows_per_block;
     if (grid == 0) return kOk;
     const size_t smem = (size_t)p.rows_per_block * Wp * sizeof(float);
-    if (U == 4)
-        rmsnorm_mxfp8_kernel<4><<<grid, threads, smem, stream>>>(p);
-    else
-        rmsnorm_mxfp8_kernel<8><<<grid, threads, smem, stream>>>(p);
+    const bool late = (long long)p.n * p.c >= (1ll << 23);
+    if (U == 4) {
+        if (late) rmsnorm_mxfp8_kernel<4, 1><<<grid, threads, smem, stream>>>(p);
+        else rmsnorm_mxfp8_kernel<4, 0><<<grid, threads, smem, stream>>>(p);
+    } else {
+        rmsnorm_mxfp8_kernel<8, 0><<<grid, threads, smem, stream>>>(p);
+    }
     return (int)cudaPeekAtLastError();
 }
 
@@ -292,6 +514,14 @@ extern "C" int pk_fused_rmsnorm_residual_forward_ex(void* vals, void* scales, fl
     p.nkt = (C + 127) / 128;
     p.mode = mode;
     return launch_rmsnorm(p, static_cast<cudaStream_t>(stream));
+}
+
+// Number of bounded shared-memory-barrier waits of the pipelined kernel that gave up since the library was
+// loaded (0 in normal operation; a launch that counted one produced invalid output).  Synchronises the device.
+extern "C" long long pk_rmsnorm_wait_timeouts(void) {
+    unsigned int n = 0;
+    if (cudaMemcpyFromSymbol(&n, pk::g_rms_wait_timeouts, sizeof(n)) != cudaSuccess) return -1;
+    return (long long)n;
 }
 
 extern "C" long long pk_rmsnorm_scale_bytes(int N, int C) {
