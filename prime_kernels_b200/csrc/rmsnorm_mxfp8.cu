@@ -403,12 +403,14 @@ static int launch_pipe_mp(const RmsParams& p, cudaStream_t stream) {
     return (int)cudaPeekAtLastError();
 }
 
-// Shapes the pipelined kernel takes: reference semantics only (mode 0, no residual output), whole 128-row
-// tiles, C a power of two from 1024 to 16384, and enough rows to give every CTA several tiles.
+// Shapes the pipelined kernel takes (chosen by measurement against the lane-owns-group kernel): reference
+// semantics only (mode 0, no residual output), whole 128-row tiles, C = 8192 or 16384, and enough rows to give
+// every CTA several tiles.  The templates also cover C = 1024, 2048 and 4096, where the other kernel is as fast.
 static bool pipe_eligible(const RmsParams& p) {
     if (p.mode != 0 || p.res_out != nullptr || (p.n % 128) != 0) return false;
-    if (p.c != 1024 && p.c != 2048 && p.c != 4096 && p.c != 8192 && p.c != 16384) return false;
-    return (long long)p.n * p.c >= (1ll << 24);
+    if (p.c == 8192) return p.n >= 8192;
+    if (p.c == 16384) return p.n >= 2048;
+    return false;
 }
 static int launch_pipe(const RmsParams& p, cudaStream_t stream) {
     switch (p.c) {
@@ -420,8 +422,199 @@ static int launch_pipe(const RmsParams& p, cudaStream_t stream) {
     }
 }
 
+
+// ---------------------------------------------------------------- lane-owns-group kernel (256-bit accesses)
+// A row is handled by M = ceil(C / 1024) warps and a lane owns one whole 32-element MXFP8 group: it reads the
+// group's 64 bytes of each input with two 256-bit loads (sm_100 `ld.global.v8.b32`), needs no cross-lane
+// traffic for the amax, the E8M0 conversion or the scale byte, and writes its 32 fp8 bytes with one 256-bit
+// store.  Blocks are small (ROWS rows of M warps, at most TMAX threads), so a launch fills the machine at
+// once and its tail is short.  Handles every shape of the op (ragged N, C % 32 == 0 up to 16384, both modes,
+// optional bf16 output); needs 32-byte aligned pointers.
+struct u32x8 {
+    uint32_t v[8];
+};
+__device__ __forceinline__ u32x8 ld_stream_32(const void* p) {
+    u32x8 r;
+    asm volatile("ld.global.cs.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]),
+                   "=r"(r.v[7])
+                 : "l"(p));
+    return r;
+}
+__device__ __forceinline__ u32x8 ld_keep_32(const void* p) {
+    u32x8 r;
+    asm volatile("ld.global.nc.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]),
+                   "=r"(r.v[7])
+                 : "l"(p));
+    return r;
+}
+__device__ __forceinline__ void st_stream_32(void* p, const u32x8& r) {
+    asm volatile("st.global.cs.v8.u32 [%8], {%0,%1,%2,%3,%4,%5,%6,%7};" ::"r"(r.v[0]), "r"(r.v[1]), "r"(r.v[2]),
+                 "r"(r.v[3]), "r"(r.v[4]), "r"(r.v[5]), "r"(r.v[6]), "r"(r.v[7]), "l"(p)
+                 : "memory");
+}
+
+// MT > 0: C == 1024 * MT, N % 128 == 0, reference semantics -- every lane is live and nothing is optional
+// (the common large shapes); MT == 0: the general form with a run-time warp count and masks.
+template <int TMAX, int MT>
+__global__ void __launch_bounds__(TMAX, 1024 / TMAX) rmsnorm_group_kernel(const RmsParams p) {
+    __shared__ float part[16];
+    constexpr bool kFull = MT > 0;
+    const int M = kFull ? MT : p.warps_per_row;
+    const int mode = kFull ? 0 : p.mode;
+    uint16_t* const res_out = kFull ? nullptr : p.res_out;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row_in_block = warp / M, seg = warp - row_in_block * M;
+    const int row = blockIdx.x * p.rows_per_block + row_in_block;
+    const int g = seg * 32 + lane;                     // group index inside the row
+    const bool live = kFull || row < p.n;
+    const bool has = kFull || (live && g < (p.c >> 5));
+    const size_t ebase = (size_t)row * p.c + (size_t)g * 32;
+    u32x8 br[2], rs[2], wt[2];
+    if (has) {
+        const uint16_t* gb = reinterpret_cast<const uint16_t*>(p.branch) + ebase;
+        const uint16_t* gr = reinterpret_cast<const uint16_t*>(p.residual) + ebase;
+        const uint16_t* gw = reinterpret_cast<const uint16_t*>(p.weight) + g * 32;
+        br[0] = ld_stream_32(gb);
+        br[1] = ld_stream_32(gb + 16);
+        rs[0] = ld_stream_32(gr);
+        rs[1] = ld_stream_32(gr + 16);
+        wt[0] = ld_keep_32(gw);
+        wt[1] = ld_keep_32(gw + 16);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) br[j].v[k] = rs[j].v[k] = wt[j].v[k] = 0u;
+    }
+    if (mode) {
+        // sum = bf16(branch + residual): both addends exact in fp32, one rounding
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                float lo, hi;
+                fma2_bf16(rs[j].v[k], kOnesBf16x2, 0.f, 0.f, lo, hi);
+                fma2_bf16(br[j].v[k], kOnesBf16x2, lo, hi, lo, hi);
+                br[j].v[k] = pack_bf16x2(lo, hi);
+            }
+    }
+    float ss = 0.f, ss2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) fma2_bf16(br[j].v[k], br[j].v[k], ss, ss2, ss, ss2);
+    ss = warp_sum(ss + ss2);
+    if (M > 1) {
+        // the warps of a row meet on the row's own named barrier; partials are added in segment order
+        if (lane == 0) part[warp] = ss;
+        // Barrier ids are immediates: a barrier id held in a register makes the compiler reserve all 16
+        // hardware barriers for the block, which caps the number of resident blocks per SM.
+        if (p.rows_per_block == 1) {
+            __syncthreads();
+        } else {
+            switch (row_in_block) {
+                case 0: asm volatile("bar.sync 1, %0;" ::"r"(32 * M) : "memory"); break;
+                case 1: asm volatile("bar.sync 2, %0;" ::"r"(32 * M) : "memory"); break;
+                case 2: asm volatile("bar.sync 3, %0;" ::"r"(32 * M) : "memory"); break;
+                default: asm volatile("bar.sync 4, %0;" ::"r"(32 * M) : "memory"); break;
+            }
+        }
+        float tot = 0.f;
+#pragma unroll
+        for (int j = 0; j < (kFull ? MT : 16); ++j)
+            if (kFull || j < M) tot += part[row_in_block * M + j];
+        ss = tot;
+    }
+    const float sc = rsqrtf(ss * p.inv_c + p.eps);
+    if (!kFull && row >= p.n_pad) return;
+    uint32_t sf = 0u;
+    if (has) {
+        uint32_t amax2 = 0u;
+        uint32_t res[16];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                float pl, ph;
+                fma2_bf16(br[j].v[k], wt[j].v[k], 0.f, 0.f, pl, ph);             // exact bf16 x bf16 products
+                float ol = __fmul_rn(sc, pl), oh = __fmul_rn(sc, ph);
+                if (!mode) fma2_bf16(rs[j].v[k], kOnesBf16x2, ol, oh, ol, oh);   // + residual in fp32, one rounding
+                res[8 * j + k] = pack_bf16x2(ol, oh);
+                amax2 = max_bf16x2(amax2, res[8 * j + k] & 0x7fff7fffu);
+            }
+        if (res_out) {
+            u32x8 o0, o1;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                o0.v[k] = mode ? br[0].v[k] : res[k];
+                o1.v[k] = mode ? br[1].v[k] : res[8 + k];
+            }
+            st_stream_32(res_out + ebase, o0);
+            st_stream_32(res_out + ebase + 16, o1);
+        }
+        const float amax = fmaxf(bf16_lo(amax2), bf16_hi(amax2));
+        sf = e8m0_roundup(__fmul_rn(amax, 1.f / 448.f));
+        const uint32_t e = 254u - sf;
+        const uint32_t invb = e ? (e << 7) : 0x0040u;                            // bf16 bits of 2^(127 - sf)
+        const uint32_t inv2 = invb | (invb << 16);
+        u32x8 q;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float v0, v1, v2, v3;
+            fma2_bf16(res[2 * k], inv2, 0.f, 0.f, v0, v1);                       // exact scaling
+            fma2_bf16(res[2 * k + 1], inv2, 0.f, 0.f, v2, v3);
+            q.v[k] = e4m3x2(v0, v1) | (e4m3x2(v2, v3) << 16);
+        }
+        st_stream_32(p.vals + ebase, q);
+    }
+    // scale bytes of four adjacent groups -> one 32-bit store into the blocked layout; groups past the end of
+    // the row and rows past N carry 0, so padded tiles are fully defined
+    uint32_t w2 = sf | (__shfl_xor_sync(kFullMask, sf, 1) << 8);
+    w2 |= __shfl_xor_sync(kFullMask, w2, 2) << 16;
+    if ((lane & 3) == 0 && (kFull || g < p.nkt * 4)) {
+        const size_t off = ((size_t)(row >> 7) * p.nkt + (g >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
+        reinterpret_cast<uint32_t*>(p.scales)[off >> 2] = w2;
+    }
+    if (live && seg == 0 && lane == 0) p.rrms[row] = sc;
+}
+
+static bool aligned32(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; }
+static bool group_eligible(const RmsParams& p) {
+    return p.c <= 16384 && aligned32(p.vals) && aligned32(p.branch) && aligned32(p.residual) && aligned32(p.weight) &&
+           (p.res_out == nullptr || aligned32(p.res_out));
+}
+static int launch_group(const RmsParams& p0, cudaStream_t stream) {
+    RmsParams p = p0;
+    const int M = (p.c + 1023) / 1024;
+    // rows per block, chosen by measurement: small blocks; 2048-wide rows prefer four rows per block once
+    // the input is large
+    int rows = 1;
+    if (M == 1) rows = 2;
+    else if (M == 2 && p.n >= 16384) rows = 4;
+    p.warps_per_row = M;
+    p.rows_per_block = rows;
+    const int threads = rows * M * 32;
+    const int grid = (p.n_pad + rows - 1) / rows;
+    if (grid == 0) return kOk;
+    const bool full = p.mode == 0 && p.res_out == nullptr && (p.n % 128) == 0 && (p.c % 1024) == 0;
+    if (full && M == 1) rmsnorm_group_kernel<64, 1><<<grid, threads, 0, stream>>>(p);
+    else if (full && M == 2 && rows == 1) rmsnorm_group_kernel<64, 2><<<grid, threads, 0, stream>>>(p);
+    else if (full && M == 2) rmsnorm_group_kernel<256, 2><<<grid, threads, 0, stream>>>(p);
+    else if (full && M == 4) rmsnorm_group_kernel<128, 4><<<grid, threads, 0, stream>>>(p);
+    else if (full && M == 8) rmsnorm_group_kernel<256, 8><<<grid, threads, 0, stream>>>(p);
+    else if (full && M == 16) rmsnorm_group_kernel<512, 16><<<grid, threads, 0, stream>>>(p);
+    else if (threads <= 64) rmsnorm_group_kernel<64, 0><<<grid, threads, 0, stream>>>(p);
+    else if (threads <= 128) rmsnorm_group_kernel<128, 0><<<grid, threads, 0, stream>>>(p);
+    else if (threads <= 256) rmsnorm_group_kernel<256, 0><<<grid, threads, 0, stream>>>(p);
+    else rmsnorm_group_kernel<512, 0><<<grid, threads, 0, stream>>>(p);
+    return (int)cudaPeekAtLastError();
+}
+
 static int launch_rmsnorm(const RmsParams& p0, cudaStream_t stream) {
     if (pipe_eligible(p0)) return launch_pipe(p0, stream);
+    if (group_eligible(p0)) return launch_group(p0, stream);
     RmsParams p = p0;
     const int nch = p.c / 8;
     // a team is at most 8 warps (256 threads): 4 chunks per thread up to C = 8192, 8 chunks up to 16384
