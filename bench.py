@@ -264,13 +264,18 @@ def main():
     def run_e2e():
         kv2, sess2 = new_session()
         prefill(sess2)
-        h_ids = torch.empty(batch, dtype=torch.int64).pin_memory()
-        h_pos = torch.empty(batch, dtype=torch.int64).pin_memory()
-        h_seq = torch.empty(batch, dtype=torch.int32).pin_memory()
-        h_slot = torch.empty(batch, dtype=torch.int64).pin_memory()
+        # one pinned staging buffer and one device buffer hold the four per-step inputs (ids, positions and slot
+        # mapping as int64, then seq_lens as int32), so a step costs one host-to-device copy of 28 bytes per request
+        h_buf = torch.empty(batch * 28, dtype=torch.uint8).pin_memory()
+        d_buf = torch.empty(batch * 28, dtype=torch.uint8, device=dev)
+
+        def views(buf):
+            i64 = buf[: batch * 24].view(torch.int64)
+            return i64[:batch], i64[batch: 2 * batch], i64[2 * batch: 3 * batch], buf[batch * 24:].view(torch.int32)
+
+        h_ids, h_pos, h_slot, h_seq = views(h_buf)
+        d_ids, d_pos, d_slot, d_seq = views(d_buf)
         h_next = torch.empty(batch, dtype=torch.int64).pin_memory()
-        d_ids, d_pos = torch.empty_like(h_ids, device=dev), torch.empty_like(h_pos, device=dev)
-        d_seq, d_slot = torch.empty_like(h_seq, device=dev), torch.empty_like(h_slot, device=dev)
         bt_host = kv2.block_table.cpu()
         cur = prompt[:, -1].clone()
         pos0 = prompt_len - 1
@@ -281,10 +286,7 @@ def main():
             h_pos.fill_(pos)
             h_seq.fill_(pos + 1)
             h_slot.copy_(bt_host[:batch, pos // 16].to(torch.int64) * 16 + pos % 16)
-            d_ids.copy_(h_ids, non_blocking=True)
-            d_pos.copy_(h_pos, non_blocking=True)
-            d_seq.copy_(h_seq, non_blocking=True)
-            d_slot.copy_(h_slot, non_blocking=True)
+            d_buf.copy_(h_buf, non_blocking=True)
             _, _, nxt = D.decode_step(geom, input_ids=d_ids, positions=d_pos, seq_lens=d_seq,
                                       block_table=kv2.block_table, slot_mapping=d_slot, embed=weights["embed"],
                                       layers=weights["layers"], final_norm=weights["final_norm"],
