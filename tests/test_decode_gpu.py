@@ -297,3 +297,67 @@ def test_device_driven_generation_matches_stepwise(cuda_device):
     assert torch.equal(ids_a, torch.stack(ids_b))
     for ca, cb in zip(kv_a.kv_caches, kv_b.kv_caches):
         assert torch.equal(ca, cb)
+
+
+def test_router_drives_the_real_kernel(cuda_device):
+    """The caller-side router (decode_backend) on a vLLM-shaped model object: a pure-decode step goes through
+    the fused kernel and gives the same hidden state as calling decode_step directly; a mixed step is repaired
+    row by row."""
+    from types import SimpleNamespace
+
+    from prime_kernels_b200 import decode as D, decode_backend as db, harness
+
+    class FlashAttentionMetadata:
+        def __init__(self, **kw):
+            self.__dict__.update(kw)
+
+    geom = D.Geometry("router", 192, 512, 2, 3, 1, 1024)
+    wd = harness.weights_to(harness.make_weights(geom, 3), cuda_device)
+    B, ctx = 3, 21
+    kv = harness.PagedKV(geom, B, 64, cuda_device)
+    g = torch.Generator().manual_seed(5)
+    for cache in kv.kv_caches:
+        cache.copy_((torch.randn(cache.shape, generator=g) * 0.5).to(torch.bfloat16))
+    snapshot = [c.clone() for c in kv.kv_caches]
+    csd = harness.make_cos_sin_cache(geom, 64, cuda_device)
+    layers = []
+    for i, (n1, qkv, o, n2, gu, dn) in enumerate(wd["layers"]):
+        layers.append(SimpleNamespace(
+            input_layernorm=SimpleNamespace(weight=n1), post_attention_layernorm=SimpleNamespace(weight=n2),
+            self_attn=SimpleNamespace(qkv_proj=SimpleNamespace(weight=qkv), o_proj=SimpleNamespace(weight=o),
+                                      attn=SimpleNamespace(kv_cache=kv.kv_caches[i], layer_name=f"l{i}"),
+                                      rotary_emb=SimpleNamespace(cos_sin_cache=csd)),
+            mlp=SimpleNamespace(gate_up_proj=SimpleNamespace(weight=gu), down_proj=SimpleNamespace(weight=dn))))
+    config = SimpleNamespace(hidden_size=192, intermediate_size=512, num_hidden_layers=2, num_attention_heads=3,
+                             num_key_value_heads=1, rms_norm_eps=geom.eps, vocab_size=1024, rope_theta=geom.rope_theta)
+    model = SimpleNamespace(config=config, layers=layers, aux_hidden_state_layers=(),
+                            embed_tokens=SimpleNamespace(weight=wd["embed"]),
+                            norm=SimpleNamespace(weight=wd["final_norm"], variance_epsilon=geom.eps))
+    ids = torch.tensor([7, 400, 33], device=cuda_device)
+    pos = torch.full((B,), ctx, dtype=torch.int64, device=cuda_device)
+    meta = FlashAttentionMetadata(max_query_len=1, num_actual_tokens=B,
+                                  seq_lens=torch.full((B,), ctx + 1, dtype=torch.int32, device=cuda_device),
+                                  block_table=kv.block_table, slot_mapping=kv.slots(pos),
+                                  query_start_loc=torch.arange(B + 1, dtype=torch.int32, device=cuda_device))
+    db.stats.clear()
+    routed = db.route(model, ids, pos, meta).clone()
+    assert db.stats["backend_decode"] == 1
+    for c, s in zip(kv.kv_caches, snapshot):
+        c.copy_(s)
+    direct = D.decode_step(db.model_geometry(model), input_ids=ids, positions=pos, seq_lens=meta.seq_lens,
+                           block_table=kv.block_table, slot_mapping=meta.slot_mapping, embed=wd["embed"],
+                           layers=wd["layers"], final_norm=wd["final_norm"], kv_caches=kv.kv_caches,
+                           cos_sin_cache=csd, eps=geom.eps).clone()
+    assert torch.equal(routed, direct)
+    # mixed step: request 0 is a 2-token prefill, requests 1 and 2 decode -> rows 2 and 3 are recomputed
+    for c, s in zip(kv.kv_caches, snapshot):
+        c.copy_(s)
+    mixed = FlashAttentionMetadata(max_query_len=2, num_actual_tokens=4, seq_lens=meta.seq_lens, block_table=kv.block_table,
+                                   slot_mapping=torch.cat([kv.slots(pos)[:1], kv.slots(pos)]),
+                                   query_start_loc=torch.tensor([0, 2, 3, 4], dtype=torch.int32, device=cuda_device))
+    ids4 = torch.tensor([1, 7, 400, 33], device=cuda_device)
+    pos4 = torch.full((4,), ctx, dtype=torch.int64, device=cuda_device)
+    stock = torch.zeros(4, 192, dtype=torch.bfloat16, device=cuda_device)
+    fixed = db.repair_mixed_decode(model, D.decode_step, db.model_geometry(model), ids4, pos4, stock, mixed)
+    assert torch.equal(fixed[2:], direct[1:]) and fixed[:2].abs().sum() == 0
+    D.check_status(db.model_geometry(model), cuda_device)
