@@ -117,6 +117,7 @@ struct DecodeParams {
 };
 
 constexpr int kProfSlots = 24;
+constexpr unsigned kProducerIdleNs = 100;   // producer back-off when its rings are full
 enum CtrlWord { kCtrlEpoch = 0, kCtrlStatus = 1, kCtrlDone = 2, kCtrlWords = 16 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -375,6 +376,8 @@ __device__ void producer_loop(Ctx& c, unsigned char* ring_base) {
         const bool done = issued >= total;      // everything issued; outstanding copies are drained below
         if (__all_sync(kFullMask, done)) break;
         idle = (progressed || done) ? 0 : idle + 1;
+        // nothing to retire or issue: yield the issue slots to the consumer warp that shares this scheduler
+        if (!__any_sync(kFullMask, progressed)) __nanosleep(kProducerIdleNs);
         if ((idle & 255u) == 255u) {
             if (idle >= kSpinLimit) raise_abort(c, kErrBarrierTimeout);
         }
