@@ -162,6 +162,7 @@ struct Shared {
     float red[kMaxB][kNW];
     int seq[kMaxB], pos[kMaxB], nc[kMaxB], lc[kMaxB];
     int ncmax, two_level;
+    uint32_t lm_best[kNW][32];          // lm_head: running argmax per consumer lane
     long long slot[kMaxB];
     long long tok[kMaxB];
     volatile int abort_flag;
@@ -562,6 +563,13 @@ __device__ void gemv_phase(Ctx& c, const int T, int layer, uint32_t& consumed) {
     const uint32_t tag = layer_tag(c, layer);
     const int par = layer & 1;
     const bool kPair = (T == kGU);
+    // lm_head: running argmax over this lane's rows in one word: bf16 order key << 16 | (0xffff - local row).
+    // One atomic per warp at the end instead of one per vocabulary row (49152 atomics on one address
+    // serialise in L2 and took longer than streaming the embedding matrix).
+    // The running value lives in shared memory, not in a register, so that the other phases (which share this
+    // code) do not carry it.
+    uint32_t& best = sh.lm_best[w][lane];
+    if (T == kLM) best = 0u;
     for (int row = ra; row < rb; row += d.rows_per_entry) {
         const int nre = min(d.rows_per_entry, rb - row);
         constexpr int RM = row_cap(B);
@@ -658,12 +666,25 @@ __device__ void gemv_phase(Ctx& c, const int T, int layer, uint32_t& consumed) {
                     if (p.logits && b < p.nb) p.logits[(size_t)b * p.V + r] = (uint16_t)lb;
                     if (p.next_ids && b < p.nb) {
                         const uint32_t ord = (lb & 0x8000u) ? (~lb & 0xffffu) : (lb | 0x8000u);
-                        const unsigned long long key =
-                            ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - (uint32_t)r);
-                        atomicMax(p.argkey + (size_t)(sh.epoch & 1u) * kMaxB + b, key);
+                        best = max(best, (ord << 16) | (0xffffu - (uint32_t)(r - ra)));
                     }
                 }
             }
+        }
+    }
+    if (T == kLM && p.next_ids) {
+        // lanes that hold rows of the same request sit in one aligned group of RM << SH lanes
+        constexpr int RM = row_cap(B);
+        constexpr int SH = 5 - ilog2(pow2_ceil(RM * B));
+        constexpr int kGroup = (RM << SH) < 32 ? (RM << SH) : 32;
+        uint32_t top = best;
+#pragma unroll
+        for (int off = 1; off < kGroup; off <<= 1) top = max(top, __shfl_xor_sync(kFullMask, top, off));
+        const int b = (lane >> SH) / RM;
+        if ((lane & (kGroup - 1)) == 0 && b < p.nb && top != 0u) {
+            const uint32_t r = (uint32_t)ra + (0xffffu - (top & 0xffffu));
+            const unsigned long long key = ((unsigned long long)(top >> 16) << 32) | (unsigned long long)(0xffffffffu - r);
+            atomicMax(p.argkey + (size_t)(sh.epoch & 1u) * kMaxB + b, key);
         }
     }
 }
