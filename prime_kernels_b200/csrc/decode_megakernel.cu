@@ -163,6 +163,8 @@ struct Shared {
     int seq[kMaxB], pos[kMaxB], nc[kMaxB], lc[kMaxB];
     int ncmax, two_level;
     uint32_t lm_best[kNW][32];          // lm_head: running argmax per consumer lane
+    long long kv_off[kNW][16];          // cache element offsets (without the kv-head term) of the 16 positions of
+                                        // each warp's first run of this CTA's first attention item; -1 = none
     long long slot[kMaxB];
     long long tok[kMaxB];
     volatile int abort_flag;
@@ -837,7 +839,7 @@ __device__ __forceinline__ void unpack8(const uint4 v, float (&f)[8]) {
 // combined through shared memory with log-sum-exp and one partial (m, l, acc[64]) per query head of the
 // GQA group leaves the CTA as flagged words.
 template <int G>
-__device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
+__device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk, bool first_item) {
     const DecodeParams& p = c.p;
     Shared& sh = c.sh;
     const int lane = c.lane;
@@ -878,6 +880,24 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk) {
         const int pp = r0 + pl;
         long long e_own = 0;
         const bool own_ok = pp < we && pp != seq - 1;
+        if (first_item && r0 == ws) {
+            // offsets resolved at kernel start (shared memory, no dependent global load)
+            const long long hs = (long long)kvh * p.head_stride;
+            if (pp < we) e_own = sh.kv_off[c.warp][pl] + hs;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                kq[i] = own_ok ? __ldcg(reinterpret_cast<const uint4*>(kvr + p.k_off + e_own + 32 * half) + i)
+                               : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int pj = r0 + j;
+                const long long ej = sh.kv_off[c.warp][j] + hs;
+                vw[j] = (pj < we && pj != seq - 1)
+                            ? __ldcg(reinterpret_cast<const uint32_t*>(kvr + p.v_off + ej) + lane)
+                            : 0u;
+            }
+            return;
+        }
         if (pp < we) e_own = kv_offset(pp);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
@@ -1202,7 +1222,7 @@ __device__ void attention_phase(Ctx& c, int layer) {
         const int b = rest % p.B;
         const int chunk = rest / p.B;
         if (chunk >= sh.ncmax) break;
-        if (chunk < sh.nc[b]) attention_item<G>(c, layer, b, kvh, chunk);
+        if (chunk < sh.nc[b]) attention_item<G>(c, layer, b, kvh, chunk, s == c.cta);
     }
     if (sh.two_level) {
         const int total_warps = c.ncta * kNW;
@@ -1360,6 +1380,31 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
     if (warp < kNW) {
+        // The block-table look-ups of an attention item do not depend on the layer: resolve them once per
+        // launch for this CTA's first item (the only one at moderate contexts), so that a layer's K/V loads
+        // can be issued without a dependent global load and integer divisions in front of them.
+        if (lane < 16) {
+            long long off = -1;
+            const int sidx = cta;
+            if (sidx < kNCMax * B * p.KVH) {
+                const int rest = sidx / p.KVH;
+                const int b = rest % B, chunk = rest / B;
+                if (chunk < sh.nc[b]) {
+                    const int seq = sh.seq[b];
+                    const int start = chunk * sh.lc[b];
+                    const int end = min(start + sh.lc[b], seq);
+                    const int ppw = (((end - start + kNW - 1) / kNW) + 15) & ~15;
+                    const int ws = min(start + warp * ppw, end);
+                    const int we = min(ws + ppw, end);
+                    const int pp = ws + lane;
+                    if (pp < we) {
+                        const int blk = p.block_table[min(b, p.nb - 1) * p.bt_stride + pp / p.block_size];
+                        off = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride;
+                    }
+                }
+            }
+            sh.kv_off[warp][lane] = off;
+        }
         // this warp's entry table: lanes fill entries in parallel (closed form per entry)
         int base = 0;
         for (int t = 0; t < 4; ++t) {
