@@ -163,6 +163,8 @@ struct Shared {
     int seq[kMaxB], pos[kMaxB], nc[kMaxB], lc[kMaxB];
     int ncmax, two_level;
     uint32_t lm_best[kNW][32];          // lm_head: running argmax per consumer lane
+    int item0_kvh;                      // kv head of this CTA's first attention item when every warp's share of it is
+                                        // one 16-position run (so kv_off covers the whole chunk), else -1
     long long kv_off[kNW][16];          // cache element offsets (without the kv-head term) of the 16 positions of
                                         // each warp's first run of this CTA's first attention item; -1 = none
     long long slot[kMaxB];
@@ -1189,7 +1191,19 @@ __device__ void attention_prefetch(Ctx& c, int layer) {
     Shared& sh = c.sh;
     const int nslots = kNCMax * p.B * p.KVH;
     const unsigned char* kvr = reinterpret_cast<const unsigned char*>(p.kv[layer]);
-    for (int s = c.cta; s < nslots; s += c.ncta) {
+    int first = c.cta;
+    if (sh.item0_kvh >= 0) {
+        // first item, offsets already resolved: thread = (warp share, position, K or V), no look-ups
+        const int t = (int)threadIdx.x;
+        const long long off = sh.kv_off[t >> 5][(t & 31) >> 1];
+        if (off >= 0) {
+            const long long e = off + (long long)sh.item0_kvh * p.head_stride;
+            const unsigned char* a = kvr + ((t & 1) ? p.v_off + e : p.k_off + e) * 2;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+        }
+        first += c.ncta;
+    }
+    for (int s = first; s < nslots; s += c.ncta) {
         const int kvh = s % p.KVH;
         const int rest = s / p.KVH;
         const int b = rest % p.B;
@@ -1404,6 +1418,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
                 }
             }
             sh.kv_off[warp][lane] = off;
+            if (warp == 0 && lane == 0) {
+                int kvh0 = -1;
+                if (sidx < kNCMax * B * p.KVH) {
+                    const int rest = sidx / p.KVH;
+                    const int b = rest % B;
+                    if (rest / B < sh.nc[b] && sh.lc[b] == 16 * kNW) kvh0 = sidx % p.KVH;
+                }
+                sh.item0_kvh = kvh0;
+            }
         }
         // this warp's entry table: lanes fill entries in parallel (closed form per entry)
         int base = 0;
