@@ -117,6 +117,7 @@ struct DecodeParams {
 };
 
 constexpr int kProfSlots = 24;
+constexpr int kPreRuns = 4;                // runs per warp whose block-table look-ups are resolved at kernel start
 constexpr unsigned kProducerIdleNs = 100;   // producer back-off when its rings are full
 enum CtrlWord { kCtrlEpoch = 0, kCtrlStatus = 1, kCtrlDone = 2, kCtrlWords = 16 };
 
@@ -163,10 +164,12 @@ struct Shared {
     int seq[kMaxB], pos[kMaxB], nc[kMaxB], lc[kMaxB];
     int ncmax, two_level;
     uint32_t lm_best[kNW][32];          // lm_head: running argmax per consumer lane
-    int item0_kvh;                      // kv head of this CTA's first attention item when every warp's share of it is
-                                        // one 16-position run (so kv_off covers the whole chunk), else -1
-    long long kv_off[kNW][16];          // cache element offsets (without the kv-head term) of the 16 positions of
-                                        // each warp's first run of this CTA's first attention item; -1 = none
+    // This CTA's first attention item, resolved once per launch (nothing in it depends on the layer):
+    int item0_b, item0_kvh, item0_chunk;   // its coordinates; item0_b < 0: this CTA has no item
+    int item0_all;                         // 1 when kv_off covers every position of the item's chunk
+    long long slot_off[kMaxB];             // cache element offset (without the kv-head term) of each request's new token; -1 = skip
+    long long kv_off[kNW][kPreRuns * 16];  // cache element offsets (without the kv-head term) of the first kPreRuns
+                                           // 16-position runs of each warp's share of the item; -1 = none
     long long slot[kMaxB];
     long long tok[kMaxB];
     volatile int abort_flag;
@@ -882,10 +885,11 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk, boo
         const int pp = r0 + pl;
         long long e_own = 0;
         const bool own_ok = pp < we && pp != seq - 1;
-        if (first_item && r0 == ws) {
+        if (first_item && r0 - ws < kPreRuns * 16) {
             // offsets resolved at kernel start (shared memory, no dependent global load)
             const long long hs = (long long)kvh * p.head_stride;
-            if (pp < we) e_own = sh.kv_off[c.warp][pl] + hs;
+            const long long* pre = sh.kv_off[c.warp] + (r0 - ws);
+            if (pp < we) e_own = pre[pl] + hs;
 #pragma unroll
             for (int i = 0; i < 4; ++i)
                 kq[i] = own_ok ? __ldcg(reinterpret_cast<const uint4*>(kvr + p.k_off + e_own + 32 * half) + i)
@@ -893,7 +897,7 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk, boo
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const int pj = r0 + j;
-                const long long ej = sh.kv_off[c.warp][j] + hs;
+                const long long ej = pre[j] + hs;
                 vw[j] = (pj < we && pj != seq - 1)
                             ? __ldcg(reinterpret_cast<const uint32_t*>(kvr + p.v_off + ej) + lane)
                             : 0u;
@@ -975,11 +979,10 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk, boo
     consumer_bar();
     if (c.prof) c.prof[12] = global_ns();
     if (has_new) {   // warp-uniform: append the new token's K/V to the paged cache (slot -1 = padded row: skip)
-        const long long slot = sh.slot[b];
-        if (slot >= 0 && lane < 8) {
+        const long long so = sh.slot_off[b];
+        if (so >= 0 && lane < 8) {
             uint16_t* kvw = reinterpret_cast<uint16_t*>(p.kv[layer]);
-            const long long blk = slot / p.block_size, off = slot % p.block_size;
-            const long long e = blk * p.block_stride + off * p.token_stride + (long long)kvh * p.head_stride + 8 * lane;
+            const long long e = so + (long long)kvh * p.head_stride + 8 * lane;
             *reinterpret_cast<uint4*>(kvw + p.k_off + e) = *reinterpret_cast<const uint4*>(qkvb_s + G * 32 + 4 * lane);
             *reinterpret_cast<uint4*>(kvw + p.v_off + e) = *reinterpret_cast<const uint4*>(qkvb_s + (G + 1) * 32 + 4 * lane);
         }
@@ -1192,16 +1195,20 @@ __device__ void attention_prefetch(Ctx& c, int layer) {
     const int nslots = kNCMax * p.B * p.KVH;
     const unsigned char* kvr = reinterpret_cast<const unsigned char*>(p.kv[layer]);
     int first = c.cta;
-    if (sh.item0_kvh >= 0) {
+    if (sh.item0_all) {
         // first item, offsets already resolved: thread = (warp share, position, K or V), no look-ups
-        const int t = (int)threadIdx.x;
-        const long long off = sh.kv_off[t >> 5][(t & 31) >> 1];
-        if (off >= 0) {
-            const long long e = off + (long long)sh.item0_kvh * p.head_stride;
-            const unsigned char* a = kvr + ((t & 1) ? p.v_off + e : p.k_off + e) * 2;
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+        const long long hs = (long long)sh.item0_kvh * p.head_stride;
+        for (int t = (int)threadIdx.x; t < kNW * kPreRuns * 32; t += kCT) {
+            const long long off = sh.kv_off[t / (kPreRuns * 32)][(t % (kPreRuns * 32)) >> 1];
+            if (off >= 0) {
+                const long long e = off + hs;
+                const unsigned char* a = kvr + ((t & 1) ? p.v_off + e : p.k_off + e) * 2;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+            }
         }
         first += c.ncta;
+    } else if (sh.item0_b < 0) {
+        first += c.ncta;       // the first slot holds no item (a short request); later slots are still visited
     }
     for (int s = first; s < nslots; s += c.ncta) {
         const int kvh = s % p.KVH;
@@ -1230,13 +1237,21 @@ __device__ void attention_phase(Ctx& c, int layer) {
     // items (chunk-major so that the always-present chunk 0 of every (request, kv head) comes first),
     // dealt round-robin to CTAs
     const int nslots = kNCMax * p.B * p.KVH;
+    // one call site (the item code is large): the first slot takes its coordinates from shared memory
     for (int s = c.cta; s < nslots; s += c.ncta) {
-        const int kvh = s % p.KVH;
-        const int rest = s / p.KVH;
-        const int b = rest % p.B;
-        const int chunk = rest / p.B;
-        if (chunk >= sh.ncmax) break;
-        if (chunk < sh.nc[b]) attention_item<G>(c, layer, b, kvh, chunk, s == c.cta);
+        const bool first = (s == c.cta);
+        int b = sh.item0_b, kvh = sh.item0_kvh, chunk = sh.item0_chunk;
+        if (first) {
+            if (b < 0) continue;
+        } else {
+            kvh = s % p.KVH;
+            const int rest = s / p.KVH;
+            b = rest % p.B;
+            chunk = rest / p.B;
+            if (chunk >= sh.ncmax) break;
+            if (chunk >= sh.nc[b]) continue;
+        }
+        attention_item<G>(c, layer, b, kvh, chunk, first);
     }
     if (sh.two_level) {
         const int total_warps = c.ncta * kNW;
@@ -1397,35 +1412,43 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
         // The block-table look-ups of an attention item do not depend on the layer: resolve them once per
         // launch for this CTA's first item (the only one at moderate contexts), so that a layer's K/V loads
         // can be issued without a dependent global load and integer divisions in front of them.
-        if (lane < 16) {
-            long long off = -1;
+        {
             const int sidx = cta;
+            int ib = -1, ikvh = 0, ichunk = 0, ws = 0, we = 0, ppw = 0;
             if (sidx < kNCMax * B * p.KVH) {
                 const int rest = sidx / p.KVH;
                 const int b = rest % B, chunk = rest / B;
                 if (chunk < sh.nc[b]) {
+                    ib = b;
+                    ikvh = sidx % p.KVH;
+                    ichunk = chunk;
                     const int seq = sh.seq[b];
                     const int start = chunk * sh.lc[b];
                     const int end = min(start + sh.lc[b], seq);
-                    const int ppw = (((end - start + kNW - 1) / kNW) + 15) & ~15;
-                    const int ws = min(start + warp * ppw, end);
-                    const int we = min(ws + ppw, end);
-                    const int pp = ws + lane;
-                    if (pp < we) {
-                        const int blk = p.block_table[min(b, p.nb - 1) * p.bt_stride + pp / p.block_size];
-                        off = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride;
-                    }
+                    ppw = (((end - start + kNW - 1) / kNW) + 15) & ~15;
+                    ws = min(start + warp * ppw, end);
+                    we = min(ws + ppw, end);
                 }
             }
-            sh.kv_off[warp][lane] = off;
-            if (warp == 0 && lane == 0) {
-                int kvh0 = -1;
-                if (sidx < kNCMax * B * p.KVH) {
-                    const int rest = sidx / p.KVH;
-                    const int b = rest % B;
-                    if (rest / B < sh.nc[b] && sh.lc[b] == 16 * kNW) kvh0 = sidx % p.KVH;
+            for (int j = lane; j < kPreRuns * 16; j += 32) {
+                long long off = -1;
+                const int pp = ws + j;
+                if (ib >= 0 && pp < we) {
+                    const int blk = p.block_table[min(ib, p.nb - 1) * p.bt_stride + pp / p.block_size];
+                    off = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride;
                 }
-                sh.item0_kvh = kvh0;
+                sh.kv_off[warp][j] = off;
+            }
+            if (warp == 0 && lane == 0) {
+                sh.item0_b = ib;
+                sh.item0_kvh = ikvh;
+                sh.item0_chunk = ichunk;
+                sh.item0_all = (ib >= 0 && ppw <= kPreRuns * 16) ? 1 : 0;
+            }
+            if (warp == 0 && lane < B) {
+                const long long slot = sh.slot[lane];
+                sh.slot_off[lane] = slot < 0 ? -1
+                                             : (slot / p.block_size) * p.block_stride + (slot % p.block_size) * p.token_stride;
             }
         }
         // this warp's entry table: lanes fill entries in parallel (closed form per entry)
