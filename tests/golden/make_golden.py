@@ -1,7 +1,7 @@
 """Generates the committed golden fixtures (run in a container that has the reference checkout and
 ``transformers``):
 
-    python tests/golden/make_golden.py [--only mxfp8|decode]
+    python tests/golden/make_golden.py [--only mxfp8|decode|decode360]
 
 * ``mxfp8_reference.json`` -- digests and samples of the outputs of the reference project's own CPU
   ``reference()`` (prime_kernels/rmsnorm/test.cu:82-150, compiled into oracle/_ref by
@@ -11,6 +11,10 @@
   seeded random weights (prime_kernels_b200.harness.make_weights seed 0), 32-token seeded prompt,
   64 greedy steps: the prompt, the KV cache after the prompt, and per step the greedy id, top-8
   logits, the logits at 512 fixed vocabulary positions and the final-normed hidden state.
+* ``decode_360m_b1.npz`` -- the same oracle on the headline configuration (SmolLM2-360M geometry, 512-token
+  prompt seeded like ``bench.py``, 256 greedy steps): the prompt and per step the greedy id, top-8 logits and
+  the logits at 128 fixed vocabulary positions (the prompt's KV cache is too large to commit; the GPU test
+  rebuilds it by running the prompt through the kernel).
 """
 from __future__ import annotations
 
@@ -77,9 +81,33 @@ def make_decode():
     print("wrote decode_135m_b1.npz; ids", res["ids"][:, 0].tolist()[:16], "s/step", res["seconds_per_step"])
 
 
+def make_decode_360m():
+    from oracle import decode_hf
+    from prime_kernels_b200 import harness
+    from prime_kernels_b200.decode import SMOLLM2_360M as geom
+
+    weights = harness.make_weights(geom, seed=0)
+    prompt = torch.randint(0, geom.vocab, (1, 512), generator=torch.Generator().manual_seed(1234))
+    res = decode_hf.run(geom, weights, prompt, 256)
+    logits = res["logits"][:, 0, :]                                  # [256, V] fp32
+    sample_idx = torch.randperm(geom.vocab, generator=torch.Generator().manual_seed(99))[:128].sort().values
+    top = logits.topk(8, dim=-1)
+    np.savez_compressed(
+        HERE / "decode_360m_b1.npz",
+        prompt=prompt.numpy(), ids=res["ids"][:, 0].numpy(),
+        top_values=top.values.numpy(), top_indices=top.indices.numpy(),
+        sample_idx=sample_idx.numpy(), sample_logits=logits[:, sample_idx].numpy(),
+    )
+    margin = (top.values[:, 0] - top.values[:, 1]).min().item()
+    print("wrote decode_360m_b1.npz; ids", res["ids"][:, 0].tolist()[:8], "min top-2 margin", margin,
+          "s/step", res["seconds_per_step"])
+
+
 if __name__ == "__main__":
     only = sys.argv[sys.argv.index("--only") + 1] if "--only" in sys.argv else None
     if only in (None, "mxfp8"):
         make_mxfp8()
     if only in (None, "decode"):
         make_decode()
+    if only in (None, "decode360"):
+        make_decode_360m()

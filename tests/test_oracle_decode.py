@@ -57,3 +57,27 @@ def test_restatement_against_committed_135m_golden_first_steps():
         if top_v[0] - top_v[1] > 4e-2:
             assert int(logits.argmax(-1)) == int(z["ids"][s])
         cur = torch.tensor([int(z["ids"][s])])
+
+
+def test_summation_order_noise_floor_on_the_headline_configuration():
+    """Two CPU implementations with identical rounding points and identical KV caches (HuggingFace eager and
+    the restatement, which differ only in fp32 summation order) on SmolLM2-360M with a 512-token context:
+    their bf16 logits differ by 3-5e-2 over the vocabulary while the greedy ids agree.  This is the floor any
+    independent implementation (the CUDA kernel included) sits on at this configuration; the per-step 2e-2
+    target is only reachable on the shallower 135M / short-context configuration."""
+    from prime_kernels_b200.decode import SMOLLM2_360M as geom
+
+    w = harness.make_weights(geom, 0)
+    prompt = torch.randint(0, geom.vocab, (1, 512), generator=torch.Generator().manual_seed(1234))
+    ref = decode_hf.run(geom, w, prompt, 2)
+    cs = harness.make_cos_sin_cache(geom, 640)
+    keys = [[ref["prefill_k"][l][0].clone()] for l in range(geom.layers)]
+    vals = [[ref["prefill_v"][l][0].clone()] for l in range(geom.layers)]
+    cur = prompt[:, -1]
+    worst = 0.0
+    for s in range(2):
+        _, logits, _ = R.decode_step(geom, w, cur, torch.tensor([511 + s]), keys, vals, cs)
+        worst = max(worst, (logits - ref["logits"][s]).abs().max().item())
+        assert (logits.argmax(-1) == ref["ids"][s]).all()
+        cur = ref["ids"][s]
+    assert 2e-2 < worst <= 1.25e-1
