@@ -516,7 +516,9 @@ __device__ __forceinline__ void gemv_rows_bf16(const uint4* ep, int sc, const ui
             for (int r = 0; r < NR; ++r)
 #pragma unroll
                 for (int b = 0; b < B; ++b) {
-                    if (u & 1) acc2[r][b] = dot8_bf16(wv[r][u], av[u][b], acc2[r][b]);
+                    // the second accumulator set (more independent chains) is only affordable at small batch:
+                    // at batch >= 4 it would cost RM * B registers that the kernel does not have
+                    if ((u & 1) && B < 4) acc2[r][b] = dot8_bf16(wv[r][u], av[u][b], acc2[r][b]);
                     else acc[r][b] = dot8_bf16(wv[r][u], av[u][b], acc[r][b]);
                 }
     }
@@ -547,7 +549,7 @@ __device__ __forceinline__ void gemv_rows_mxfp8(const uint4* ep, int rc, int kac
 #pragma unroll
                     for (int b = 0; b < B; ++b) {
                         const float part = dot16_e4m3(wq, a0[b], a1[b], 0.f);
-                        if (u & 1) acc2[r][b] = fmaf(scale, part, acc2[r][b]);
+                        if ((u & 1) && B < 4) acc2[r][b] = fmaf(scale, part, acc2[r][b]);
                         else acc[r][b] = fmaf(scale, part, acc[r][b]);
                     }
                 }
@@ -759,6 +761,41 @@ __device__ void stage_norm(Ctx& c, const unsigned long long* src_words, uint32_t
     }
     consumer_bar();
     uint16_t* act16 = reinterpret_cast<uint16_t*>(c.act);
+    if constexpr (B > 1) {
+        // Batched: requests are normalised in pairs; all shared-memory loads of a pair are issued before its
+        // stores (the compiler must assume they alias), so the two dependent chains overlap.
+#pragma unroll
+        for (int bg = 0; bg < B; bg += 2) {
+            float s2[2], xr[2][kNormRegs];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int bb = bg + j < B ? bg + j : B - 1;
+                float tot = 0.f;
+#pragma unroll
+                for (int w = 0; w < kNW; ++w) tot += sh.red[bb][w];
+                s2[j] = rsqrtf(tot * (1.f / (float)H) + p.eps);
+#pragma unroll
+                for (int u = 0; u < kNormRegs; ++u) {
+                    const int i = ct + u * kCT;
+                    xr[j][u] = i < H ? c.res[bb * H + i] : 0.f;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                if (bg + j >= B) continue;
+#pragma unroll
+                for (int u = 0; u < kNormRegs; ++u) {
+                    const int i = ct + u * kCT;
+                    if (i < H) {
+                        const float n = round_bf16(__fmul_rn(xr[j][u], s2[j]));
+                        act16[(size_t)(bg + j) * p.act_elems + i] = (uint16_t)f32_to_bf16_bits(__fmul_rn(n, wreg[u]));
+                    }
+                }
+            }
+        }
+        consumer_bar();
+        return;
+    }
 #pragma unroll
     for (int b = 0; b < B; ++b) {
         float tot = 0.f;
@@ -790,6 +827,40 @@ __device__ void stage_copy(Ctx& c, const unsigned long long* src_words, uint32_t
     const DecodeParams& p = c.p;
     const int ct = threadIdx.x;
     consumer_bar();
+    if constexpr (B > 1) {
+        // Batched: two requests are polled per round (one L2 round trip per pair of requests, not per request).
+        // Words are 32-bit payloads holding two bf16 values (packed) or one.
+        const int nw = packed ? n >> 1 : n;
+        constexpr int N = 8;                     // words per request and round
+        uint32_t* act32 = reinterpret_cast<uint32_t*>(c.act);
+        uint16_t* act16 = reinterpret_cast<uint16_t*>(c.act);
+        for (int i0 = ct; i0 < nw; i0 += N * kCT) {
+#pragma unroll
+            for (int bg = 0; bg < B; bg += 2) {
+                constexpr int kPairs = 2;
+                uint32_t v[kPairs * N];
+                wait_flagged_multi<kPairs * N>(
+                    c,
+                    [&](int u) {
+                        const int i = i0 + (u % N) * kCT;
+                        const int bb = bg + u / N;
+                        return (i < nw && bb < B) ? src_words + bb * nw + i : nullptr;
+                    },
+                    tag, v);
+#pragma unroll
+                for (int u = 0; u < kPairs * N; ++u) {
+                    const int i = i0 + (u % N) * kCT;
+                    const int bb = bg + u / N;
+                    if (i < nw && bb < B) {
+                        if (packed) act32[(size_t)bb * (p.act_elems >> 1) + i] = v[u];
+                        else act16[(size_t)bb * p.act_elems + i] = (uint16_t)v[u];
+                    }
+                }
+            }
+        }
+        consumer_bar();
+        return;
+    }
     if (packed) {
         uint32_t* act32 = reinterpret_cast<uint32_t*>(c.act);
         const int nw = n >> 1;
