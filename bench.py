@@ -60,29 +60,71 @@ def algorithmic_bytes(geom, batch, seq, mxfp8=False):
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    """SM clock / throttle-reason samples taken while the timed region runs.  Read-only NVML queries from a
+    thread of this process every 10 ms (an `nvidia-smi -lms` child needs longer to start than the timed
+    region lasts); falls back to an `nvidia-smi` child when the NVML binding is missing."""
+
+    REASONS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.thread = index, [], None, None
+        self.stop = threading.Event()
+        self.nvml = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.nvml = pynvml
+        except Exception:
+            self.nvml = None
+
+    def _poll_nvml(self):
+        n = self.nvml
+        while not self.stop.is_set():
+            try:
+                mhz = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                try:
+                    mask = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except AttributeError:
+                    mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.rows.append((mhz, self.max_mhz, mask))
+            except Exception:
+                pass
+            self.stop.wait(0.01)
+
+    def _read_smi(self):
+        for line in self.proc.stdout:
+            c = [x.strip() for x in line.split(",")]
+            if len(c) >= 6 and c[0].isdigit() and c[1].isdigit():
+                mask = 0
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[2:6]):
+                    if v.lower() == "active":
+                        mask |= self.REASONS[name]
+                self.rows.append((int(c[0]), int(c[1]), mask))
 
     def __enter__(self):
+        if self.nvml is not None:
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return self
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={q}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread = threading.Thread(target=self._read_smi, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
-
     def __exit__(self, *exc):
+        self.stop.set()
+        if self.nvml is not None and self.thread is not None:
+            self.thread.join(timeout=2)
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -91,12 +133,14 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
-        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower() == "active"})
+        sm = [r[0] for r in self.rows]
+        mx = [r[1] for r in self.rows]
+        mask = 0
+        for r in self.rows:
+            mask |= r[2]
+        reasons = sorted(n for n, bit in self.REASONS.items() if mask & bit)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+                "reasons": reasons, "samples": len(sm), "source": "nvml" if self.nvml is not None else "nvidia-smi"}
 
 
 def max_over_ranks(values, world, device="cpu"):
