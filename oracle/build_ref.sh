@@ -6,6 +6,9 @@
 #                           without a GPU)
 #   libref_rmsnorm_gpu.so   the reference's own GPU kernels behind a C entry point (GPU parity tests)
 #   ref_rmsnorm_bench       the reference's own benchmark executable (same-box timing of its kernels)
+#   libref_megakernel135.so, libref_megakernel360.so
+#                           the reference's own SmolLM2-135M / 360M decode megakernels (their sm_89-only device check
+#                           shimmed, see ref_megakernel_wrapper.cu): second decode oracle and same-box baseline
 # The reference's cmake project is not run: its sources are handed to nvcc directly.
 #   usage: oracle/build_ref.sh [/path/to/reference/checkout]
 set -euo pipefail
@@ -33,3 +36,18 @@ echo "built $here/_ref/libref_rmsnorm_gpu.so"
 fresh "$here/_ref/ref_rmsnorm_bench" "${kernels[@]}" "${headers[@]}" "$src/bench.cu" || \
 nvcc "${common[@]}" -o "$here/_ref/ref_rmsnorm_bench" "${kernels[@]}" "$src/bench.cu" -lcuda
 echo "built $here/_ref/ref_rmsnorm_bench"
+mk="$ref/prime_kernels/decode_megakernel/csrc/megakernel.cu"
+if [ -f "$mk" ]; then
+  fresh "$here/_ref/libref_megakernel135.so" "$mk" "$here/ref_megakernel_wrapper.cu" || \
+  nvcc -O3 -std=c++17 -w -gencode arch=compute_100a,code=sm_100a -shared -Xcompiler -fPIC -DMK_PREFETCH=1 \
+    -DREF_MEGAKERNEL_CU="\"$mk\"" -o "$here/_ref/libref_megakernel135.so" "$here/ref_megakernel_wrapper.cu"
+  echo "built $here/_ref/libref_megakernel135.so"
+fi
+mk360="$ref/prime_kernels/decode_megakernel_360m/csrc/block360.cu"
+if [ -f "$mk360" ]; then
+  fresh "$here/_ref/libref_megakernel360.so" "$mk360" "$ref/prime_kernels/decode_megakernel_360m/csrc/block360_kernel.inc" \
+        "$here/ref_megakernel_wrapper.cu" || \
+  nvcc -O3 -std=c++17 -w -gencode arch=compute_100a,code=sm_100a -shared -Xcompiler -fPIC \
+    -DREF_MEGAKERNEL_CU="\"$mk360\"" -o "$here/_ref/libref_megakernel360.so" "$here/ref_megakernel_wrapper.cu"
+  echo "built $here/_ref/libref_megakernel360.so"
+fi

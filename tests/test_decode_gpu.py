@@ -403,3 +403,147 @@ def test_smollm2_360m_headline_against_hf_golden(cuda_device):
     # (the golden run contains exact top-2 ties, which no independent implementation can be held to)
     assert all(margin <= 2 * max(dl.max(), dt.max()) for _, margin in wrong)
     assert len(wrong) <= 8
+
+
+def test_against_the_reference_projects_own_135m_kernel(cuda_device):
+    """The reference's own SmolLM2-135M megakernel (compiled for this GPU from the reference checkout, its
+    sm_89-only device check shimmed: oracle/ref_megakernel_wrapper.cu) and this library on the same device
+    inputs: final hidden states and the K/V rows both kernels append, for batch 1..4 at ragged contexts."""
+    from oracle import ref_megakernel as REF
+    from prime_kernels_b200 import decode as D
+    from prime_kernels_b200 import decode_megakernel as MK
+
+    if not REF.available():
+        pytest.skip("reference megakernel not built (oracle/build_ref.sh)")
+    geom = D.SMOLLM2_135M
+    wd = harness.weights_to(harness.make_weights(geom, 0, norm_weights="random"), cuda_device)
+    csd = harness.make_cos_sin_cache(geom, 256, cuda_device)
+    worst = 0.0
+    for B, ctxs in [(1, [31]), (2, [17, 100]), (4, [5, 64, 129, 200])]:
+        g = torch.Generator().manual_seed(7 + B)
+        kvs = []
+        for _ in range(2):                      # identical caches for the two kernels
+            kv = harness.PagedKV(geom, B, 256, cuda_device, shuffle=True, seed=3)
+            kvs.append(kv)
+        for l in range(geom.layers):
+            fill = (torch.randn(kvs[0].kv_caches[l].shape, generator=g) * 0.5).to(torch.bfloat16).to(cuda_device)
+            kvs[0].kv_caches[l].copy_(fill)
+            kvs[1].kv_caches[l].copy_(fill)
+        ids = torch.randint(0, geom.vocab, (B,), generator=g).to(cuda_device)
+        pos = torch.tensor(ctxs, dtype=torch.int64, device=cuda_device)
+        seq = (pos + 1).to(torch.int32)
+        outs = []
+        for kv, step in zip(kvs, (REF.decode_step, MK.decode_step)):
+            outs.append(step(input_ids=ids, positions=pos, seq_lens=seq, block_table=kv.block_table,
+                             slot_mapping=kv.slots(pos), embed=wd["embed"], layers=wd["layers"],
+                             final_norm=wd["final_norm"], kv_caches=kv.kv_caches, cos_sin_cache=csd, eps=1e-5).float().clone())
+        torch.cuda.synchronize()
+        diff = (outs[0] - outs[1]).abs().max().item()
+        scale = outs[0].abs().max().item()
+        worst = max(worst, diff / scale)
+        # appended K/V rows (position ctx of every request, every layer)
+        kdiff, kdiff0 = 0.0, 0.0
+        for l in (0, geom.layers // 2, geom.layers - 1):
+            for b in range(B):
+                a = kvs[0].gather(l, b, ctxs[b] + 1)[:, -1].float()
+                c = kvs[1].gather(l, b, ctxs[b] + 1)[:, -1].float()
+                d = (a - c).abs().max().item()
+                kdiff = max(kdiff, d)
+                if l == 0:
+                    kdiff0 = max(kdiff0, d / max(a.abs().max().item(), 1.0))
+        print(f"reference kernel vs this library, B={B}: hidden max-abs {diff:.4f} (scale {scale:.2f}), appended K/V max-abs layer 0 (relative) {kdiff0:.4f}, any layer {kdiff:.4f}")
+        assert diff <= 2 ** -4 * max(scale, 1.0)
+        # layer 0 sees identical inputs: the rows agree to a bf16 rounding or two (the 135M reference rounds RoPE
+        # once, this library three times like HF eager); deeper layers carry the usual one-ulp-flip drift
+        assert kdiff0 <= 2 ** -6 and kdiff <= 0.125
+    D.check_status(geom, cuda_device)
+
+
+def test_against_the_reference_projects_own_360m_kernel(cuda_device):
+    """The reference's packaged SmolLM2-360M kernel (decode_megakernel_360m, the strict-parity line; compiled for
+    this GPU like the 135M one) against this library at the headline geometry: batch 1 at context 520 and batch 2
+    at ragged contexts."""
+    from oracle import ref_megakernel as REF
+    from prime_kernels_b200 import decode as D
+    from prime_kernels_b200 import decode_megakernel_360m as MK360
+
+    if not REF.available_360m():
+        pytest.skip("reference 360M megakernel not built (oracle/build_ref.sh)")
+    geom = D.SMOLLM2_360M
+    wd = harness.weights_to(harness.make_weights(geom, 0, norm_weights="random"), cuda_device)
+    csd = harness.make_cos_sin_cache(geom, 640, cuda_device)
+    for B, ctxs in [(1, [520]), (2, [77, 300])]:
+        g = torch.Generator().manual_seed(11 + B)
+        kvs = [harness.PagedKV(geom, B, 640, cuda_device, shuffle=True, seed=5) for _ in range(2)]
+        for l in range(geom.layers):
+            fill = (torch.randn(kvs[0].kv_caches[l].shape, generator=g) * 0.5).to(torch.bfloat16).to(cuda_device)
+            kvs[0].kv_caches[l].copy_(fill)
+            kvs[1].kv_caches[l].copy_(fill)
+        ids = torch.randint(0, geom.vocab, (B,), generator=g).to(cuda_device)
+        pos = torch.tensor(ctxs, dtype=torch.int64, device=cuda_device)
+        seq = (pos + 1).to(torch.int32)
+        outs = []
+        for kv, step in zip(kvs, (REF.decode_step_360m, MK360.decode_step)):
+            outs.append(step(input_ids=ids, positions=pos, seq_lens=seq, block_table=kv.block_table,
+                             slot_mapping=kv.slots(pos), embed=wd["embed"], layers=wd["layers"],
+                             final_norm=wd["final_norm"], kv_caches=kv.kv_caches, cos_sin_cache=csd, eps=1e-5).float().clone())
+        torch.cuda.synchronize()
+        diff = (outs[0] - outs[1]).abs().max().item()
+        scale = outs[0].abs().max().item()
+        kdiff, kdiff0 = 0.0, 0.0
+        for l in (0, geom.layers - 1):
+            for b in range(B):
+                a = kvs[0].gather(l, b, ctxs[b] + 1)[:, -1].float()
+                c = kvs[1].gather(l, b, ctxs[b] + 1)[:, -1].float()
+                d = (a - c).abs().max().item()
+                kdiff = max(kdiff, d)
+                if l == 0:
+                    kdiff0 = max(kdiff0, d / max(a.abs().max().item(), 1.0))
+        print(f"reference 360M kernel vs this library, B={B}: hidden max-abs {diff:.4f} (scale {scale:.2f}), appended K/V max-abs layer 0 (relative) {kdiff0:.4f}, any layer {kdiff:.4f}")
+        assert diff <= 2 ** -4 * max(scale, 1.0)
+        # layer 0 sees identical inputs: the rows agree to a bf16 rounding or two (the 135M reference rounds RoPE
+        # once, this library three times like HF eager); deeper layers carry the usual one-ulp-flip drift
+        assert kdiff0 <= 2 ** -6 and kdiff <= 0.125
+    D.check_status(geom, cuda_device)
+
+
+def test_same_box_timing_against_the_reference_kernels(cuda_device):
+    """Step time of the reference project's own kernels (24-CTA sm_89 designs, compiled for this GPU) and of this
+    library on the same box and the same inputs: SmolLM2-135M batch 1 at context 64 and SmolLM2-360M batch 1 at
+    context 520 (CUDA events around 40 back-to-back steps at a fixed position)."""
+    from oracle import ref_megakernel as REF
+    from prime_kernels_b200 import decode as D
+    from prime_kernels_b200 import decode_megakernel as MK
+    from prime_kernels_b200 import decode_megakernel_360m as MK360
+
+    if not (REF.available() and REF.available_360m()):
+        pytest.skip("reference megakernels not built (oracle/build_ref.sh)")
+    for geom, ctx, ref_step, my_step in [(D.SMOLLM2_135M, 64, REF.decode_step, MK.decode_step),
+                                         (D.SMOLLM2_360M, 520, REF.decode_step_360m, MK360.decode_step)]:
+        wd = harness.weights_to(harness.make_weights(geom, 0), cuda_device)
+        csd = harness.make_cos_sin_cache(geom, 640, cuda_device)
+        kv = harness.PagedKV(geom, 1, 640, cuda_device)
+        for cache in kv.kv_caches:
+            cache.normal_()
+        ids = torch.tensor([17], device=cuda_device)
+        pos = torch.tensor([ctx], dtype=torch.int64, device=cuda_device)
+        seq = (pos + 1).to(torch.int32)
+        kw = dict(input_ids=ids, positions=pos, seq_lens=seq, block_table=kv.block_table, slot_mapping=kv.slots(pos),
+                  embed=wd["embed"], layers=wd["layers"], final_norm=wd["final_norm"], kv_caches=kv.kv_caches,
+                  cos_sin_cache=csd, eps=1e-5)
+        times = []
+        for step in (ref_step, my_step):
+            for _ in range(5):
+                step(**kw)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(40):
+                step(**kw)
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) / 40 * 1e3)
+        print(f"{geom.name} B=1 ctx {ctx}: reference kernel {times[0]:.0f} us/step, this library {times[1]:.0f} us/step "
+              f"({times[0] / times[1]:.1f}x)")
+        assert times[1] < times[0]
+    D.check_status(D.SMOLLM2_360M, cuda_device)
