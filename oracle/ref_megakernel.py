@@ -96,9 +96,10 @@ def library_360m() -> ctypes.CDLL:
 
 
 def decode_step_360m(*, input_ids, positions, seq_lens, block_table, slot_mapping, embed, layers, final_norm, kv_caches,
-                     cos_sin_cache, eps=1e-5):
+                     cos_sin_cache, eps=1e-5, layer_outputs=None):
     """One decode step of the reference's packaged 360M kernel (batch 1 or 2, KV block size 16); the call is the one
-    prime_kernels/decode_megakernel_360m/__init__.py:186-207 of the reference project makes.  Returns ``[B, 960]``."""
+    prime_kernels/decode_megakernel_360m/__init__.py:186-207 of the reference project makes.  Returns ``[B, 960]``;
+    ``layer_outputs`` (optional, bf16 ``[32, B, 960]``) receives the residual stream after every layer."""
     lib = library_360m()
     device = input_ids.device
     batch = input_ids.shape[0]
@@ -116,7 +117,8 @@ def decode_step_360m(*, input_ids, positions, seq_lens, block_table, slot_mappin
                        final_norm.data_ptr(), positions.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(),
                        block_table.stride(0), slot_mapping.data_ptr(), st["layers_t"].data_ptr(), st["kv_t"].data_ptr(),
                        0, 64, kv0.stride(0), kv0.stride(2), kv0.stride(1), 16, cos_sin_cache.data_ptr(),
-                       int(cos_sin_cache.dtype == torch.float32), st["out"].data_ptr(), None, st["scratch"].data_ptr(),
+                       int(cos_sin_cache.dtype == torch.float32), st["out"].data_ptr(),
+                       layer_outputs.data_ptr() if layer_outputs is not None else None, st["scratch"].data_ptr(),
                        st["scratch"].numel(), None, 0, block_table.shape[1] * 16, -1)
     if rc != 0:
         raise RuntimeError(f"reference decode_megakernel_360m failed: {lib.decode360_status_string(rc).decode()}")

@@ -482,12 +482,21 @@ def test_against_the_reference_projects_own_360m_kernel(cuda_device):
         ids = torch.randint(0, geom.vocab, (B,), generator=g).to(cuda_device)
         pos = torch.tensor(ctxs, dtype=torch.int64, device=cuda_device)
         seq = (pos + 1).to(torch.int32)
-        outs = []
+        outs, streams = [], []
         for kv, step in zip(kvs, (REF.decode_step_360m, MK360.decode_step)):
+            lo = torch.zeros((geom.layers, B, geom.hidden), dtype=torch.bfloat16, device=cuda_device)
             outs.append(step(input_ids=ids, positions=pos, seq_lens=seq, block_table=kv.block_table,
                              slot_mapping=kv.slots(pos), embed=wd["embed"], layers=wd["layers"],
-                             final_norm=wd["final_norm"], kv_caches=kv.kv_caches, cos_sin_cache=csd, eps=1e-5).float().clone())
+                             final_norm=wd["final_norm"], kv_caches=kv.kv_caches, cos_sin_cache=csd, eps=1e-5,
+                             layer_outputs=lo).float().clone())
+            streams.append(lo.float())
         torch.cuda.synchronize()
+        # residual stream after every layer: the first layer sees identical inputs and must agree to a rounding
+        per_layer = (streams[0] - streams[1]).abs().amax(dim=(1, 2))
+        rel0 = per_layer[0].item() / max(streams[0][0].abs().max().item(), 1.0)
+        print(f"  residual stream max-abs per layer: first {per_layer[0].item():.4f} (relative {rel0:.4f}), "
+              f"middle {per_layer[geom.layers // 2].item():.4f}, last {per_layer[-1].item():.4f}")
+        assert rel0 <= 2 ** -6
         diff = (outs[0] - outs[1]).abs().max().item()
         scale = outs[0].abs().max().item()
         kdiff, kdiff0 = 0.0, 0.0
