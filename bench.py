@@ -308,37 +308,24 @@ def main():
     def run_e2e():
         kv2, sess2 = new_session()
         prefill(sess2)
-        # one pinned staging buffer and one device buffer hold the four per-step inputs (ids, positions and slot
-        # mapping as int64, then seq_lens as int32), so a step costs one host-to-device copy of 28 bytes per request
-        h_buf = torch.empty(batch * 28, dtype=torch.uint8).pin_memory()
-        d_buf = torch.empty(batch * 28, dtype=torch.uint8, device=dev)
-
-        def views(buf):
-            i64 = buf[: batch * 24].view(torch.int64)
-            return i64[:batch], i64[batch: 2 * batch], i64[2 * batch: 3 * batch], buf[batch * 24:].view(torch.int32)
-
-        h_ids, h_pos, h_slot, h_seq = views(h_buf)
-        d_ids, d_pos, d_slot, d_seq = views(d_buf)
-        h_next = torch.empty(batch, dtype=torch.int64).pin_memory()
+        # D.HostStep: one pinned staging buffer + one device buffer for the four per-step inputs (28 bytes per
+        # request, one host-to-device copy), the fused step, and the device-to-host copy of the greedy ids,
+        # captured once into a CUDA graph and replayed every step; the inputs of every step come from the host
+        step = D.HostStep(geom, batch, embed=weights["embed"], layers=weights["layers"], final_norm=weights["final_norm"],
+                          kv_caches=kv2.kv_caches, cos_sin_cache=cos_sin, block_table=kv2.block_table,
+                          embed_lookup=weights.get("embed_lookup"))
         bt_host = kv2.block_table.cpu()
         cur = prompt[:, -1].clone()
         pos0 = prompt_len - 1
+        h_pos = torch.empty(batch, dtype=torch.int64)
+        h_seq = torch.empty(batch, dtype=torch.int32)
 
         def e2e_step(t):
             pos = pos0 + t
-            h_ids.copy_(cur)
             h_pos.fill_(pos)
             h_seq.fill_(pos + 1)
-            h_slot.copy_(bt_host[:batch, pos // 16].to(torch.int64) * 16 + pos % 16)
-            d_buf.copy_(h_buf, non_blocking=True)
-            _, _, nxt = D.decode_step(geom, input_ids=d_ids, positions=d_pos, seq_lens=d_seq,
-                                      block_table=kv2.block_table, slot_mapping=d_slot, embed=weights["embed"],
-                                      layers=weights["layers"], final_norm=weights["final_norm"],
-                                      kv_caches=kv2.kv_caches, cos_sin_cache=cos_sin, eps=geom.eps, lm_head=True,
-                                      embed_lookup=weights.get("embed_lookup"))
-            h_next.copy_(nxt, non_blocking=True)
-            torch.cuda.current_stream(dev).synchronize()
-            cur.copy_(h_next)
+            nxt = step(cur, h_pos, h_seq, bt_host[:batch, pos // 16].to(torch.int64) * 16 + pos % 16)
+            cur.copy_(nxt)
 
         for t in range(W):
             e2e_step(t)

@@ -21,7 +21,7 @@ from .._cabi import library, load_ops
 load_ops()
 
 __all__ = ["Geometry", "SMOLLM2_135M", "SMOLLM2_360M", "SMOLLM2_1P7B", "GEOMETRIES", "MAX_BATCH", "MAX_SEQ",
-           "HEAD_DIM", "decode_step", "check_status", "DecodeSession", "workspace_bytes", "pack_matrix_mxfp8", "pack_weights_mxfp8",
+           "HEAD_DIM", "decode_step", "check_status", "DecodeSession", "HostStep", "workspace_bytes", "pack_matrix_mxfp8", "pack_weights_mxfp8",
            "unpack_matrix_mxfp8", "packed_row_bytes"]
 
 MAX_BATCH = 8
@@ -286,3 +286,66 @@ class DecodeSession:
                 logs[t].copy_(logits)
         check_status(self.geometry, self.device)
         return (ids, logs) if collect_logits else ids
+
+
+class HostStep:
+    """One decode step driven from host buffers, for serving loops that produce the step inputs on the CPU.
+
+    The four per-step inputs (ids, positions, slot mapping as int64, sequence lengths as int32) live in one pinned
+    staging buffer and one device buffer, so a step is one host-to-device copy of 28 bytes per request, one kernel
+    launch (tied lm_head + argmax fused) and one device-to-host copy of the greedy ids; with ``graph=True`` the
+    three are captured once into a CUDA graph and replayed.  ``__call__`` returns the greedy next ids as a pinned
+    host tensor ``[B]`` after synchronising the stream."""
+
+    def __init__(self, geometry: Geometry, batch: int, *, embed, layers, final_norm, kv_caches, cos_sin_cache,
+                 block_table, embed_lookup=None, graph: bool = True):
+        self.geometry, self.batch = geometry, batch
+        dev = embed.device
+        self.device = dev
+        self.h_buf = torch.empty(batch * 28, dtype=torch.uint8).pin_memory()
+        self.d_buf = torch.empty(batch * 28, dtype=torch.uint8, device=dev)
+        self.h_ids, self.h_pos, self.h_slot, self.h_seq = self._views(self.h_buf)
+        d_ids, d_pos, d_slot, d_seq = self._views(self.d_buf)
+        self.h_next = torch.empty(batch, dtype=torch.int64).pin_memory()
+        self._kw = dict(input_ids=d_ids, positions=d_pos, seq_lens=d_seq, block_table=block_table, slot_mapping=d_slot,
+                        embed=embed, layers=layers, final_norm=final_norm, kv_caches=kv_caches,
+                        cos_sin_cache=cos_sin_cache, eps=geometry.eps, lm_head=True, embed_lookup=embed_lookup)
+        self.graph = None
+        if graph:
+            self.h_ids.zero_()
+            self.h_pos.zero_()
+            self.h_slot.fill_(-1)          # a padded row: the capture run writes nothing into the cache
+            self.h_seq.fill_(1)
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                self._enqueue()            # first call outside capture (workspace set-up, pointer tables)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    self._enqueue()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize(dev)
+            self.graph = g
+
+    def _views(self, buf):
+        b = self.batch
+        i64 = buf[: b * 24].view(torch.int64)
+        return i64[:b], i64[b: 2 * b], i64[2 * b: 3 * b], buf[b * 24:].view(torch.int32)
+
+    def _enqueue(self):
+        self.d_buf.copy_(self.h_buf, non_blocking=True)
+        _, _, nxt = decode_step(self.geometry, **self._kw)
+        self.h_next.copy_(nxt, non_blocking=True)
+
+    def __call__(self, ids, positions, seq_lens, slot_mapping):
+        self.h_ids.copy_(ids)
+        self.h_pos.copy_(positions)
+        self.h_seq.copy_(seq_lens)
+        self.h_slot.copy_(slot_mapping)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._enqueue()
+        torch.cuda.current_stream(self.device).synchronize()
+        return self.h_next
+

@@ -556,3 +556,38 @@ def test_same_box_timing_against_the_reference_kernels(cuda_device):
               f"({times[0] / times[1]:.1f}x)")
         assert times[1] < times[0]
     D.check_status(D.SMOLLM2_360M, cuda_device)
+
+
+@pytest.mark.parametrize("graph", [True, False])
+def test_host_driven_step_matches_device_driven_generation(cuda_device, graph):
+    """decode.HostStep (inputs from pinned host buffers, one packed copy, optionally a captured CUDA graph) produces
+    the same greedy ids as the device-driven session on the same prefix."""
+    from prime_kernels_b200 import decode as D
+
+    geom = D.Geometry("host", 192, 512, 3, 3, 1, 1024)
+    wd = harness.weights_to(harness.make_weights(geom, 2), cuda_device)
+    csd = harness.make_cos_sin_cache(geom, 128, cuda_device)
+    B, ctx, steps = 2, 19, 6
+    kvs = [harness.PagedKV(geom, B, 128, cuda_device, shuffle=True, seed=1) for _ in range(2)]
+    g = torch.Generator().manual_seed(4)
+    for l in range(geom.layers):
+        fill = (torch.randn(kvs[0].kv_caches[l].shape, generator=g) * 0.5).to(torch.bfloat16).to(cuda_device)
+        kvs[0].kv_caches[l].copy_(fill)
+        kvs[1].kv_caches[l].copy_(fill)
+    first = torch.tensor([5, 900])
+    sess = D.DecodeSession(geom, embed=wd["embed"], layers=wd["layers"], final_norm=wd["final_norm"],
+                           kv_caches=kvs[0].kv_caches, cos_sin_cache=csd, block_table=kvs[0].block_table)
+    sess.start(first, torch.full((B,), ctx, dtype=torch.int64))
+    want = sess.generate(steps).cpu()
+    step = D.HostStep(geom, B, embed=wd["embed"], layers=wd["layers"], final_norm=wd["final_norm"],
+                      kv_caches=kvs[1].kv_caches, cos_sin_cache=csd, block_table=kvs[1].block_table, graph=graph)
+    bt = kvs[1].block_table.cpu()
+    cur, got = first.clone(), []
+    for t in range(steps):
+        pos = ctx + t
+        nxt = step(cur, torch.full((B,), pos, dtype=torch.int64), torch.full((B,), pos + 1, dtype=torch.int32),
+                   bt[:, pos // 16].to(torch.int64) * 16 + pos % 16)
+        got.append(nxt.clone())
+        cur = nxt.clone()
+    assert torch.equal(torch.stack(got), want)
+    D.check_status(geom, cuda_device)
