@@ -33,12 +33,14 @@ WORKLOADS = {
     "smollm2-360m-b1": ("smollm2-360m", 1, 512, 256),            # BASELINE config 2 (headline)
     "smollm2-135m-b1": ("smollm2-135m", 1, 32, 64),              # config 1
     "smollm2-1.7b-b1": ("smollm2-1.7b", 1, 1024, 256),           # config 5
-    "smollm2-1.7b-b8": ("smollm2-1.7b", 8, 1024, 256),
+    "smollm2-1.7b-b8": ("smollm2-1.7b", 8, 1024, 64),            # config 5, two launches of 4 requests per step
+    "smollm2-1.7b-b64": ("smollm2-1.7b", 64, 1024, 16),          # config 5, sixteen launches per step
     "smollm2-360m-b4": ("smollm2-360m", 4, 512, 256),
     "smollm2-360m-b8": ("smollm2-360m", 8, 512, 256),
     # config 4: MXFP8 weights (E4M3 + E8M0 per 32 along K), context pre-filled to 4096 with normal(0,1) K/V
     "smollm2-360m-mxfp8-b1": ("smollm2-360m", 1, 4096, 128),
     "smollm2-360m-mxfp8-b4": ("smollm2-360m", 4, 4096, 128),
+    "smollm2-360m-mxfp8-b16": ("smollm2-360m", 16, 4096, 32),    # config 4, two launches of 8 requests per step
 }
 METRIC = "SmolLM2-360M bs1 decode tok/s & % HBM roofline; aggregate tok/s @1/2/4/8 GPUs"
 # DRAM bytes per launch measured with ncu (dram__bytes_read + write) at context 503-505 divided by the

@@ -20,11 +20,12 @@ from .._cabi import library, load_ops
 
 load_ops()
 
-__all__ = ["Geometry", "SMOLLM2_135M", "SMOLLM2_360M", "SMOLLM2_1P7B", "GEOMETRIES", "MAX_BATCH", "MAX_SEQ",
+__all__ = ["Geometry", "SMOLLM2_135M", "SMOLLM2_360M", "SMOLLM2_1P7B", "GEOMETRIES", "MAX_BATCH", "MAX_REQUESTS", "MAX_SEQ",
            "HEAD_DIM", "decode_step", "check_status", "DecodeSession", "HostStep", "workspace_bytes", "pack_matrix_mxfp8", "pack_weights_mxfp8",
            "unpack_matrix_mxfp8", "packed_row_bytes"]
 
-MAX_BATCH = 8
+MAX_BATCH = 8          # requests one kernel launch takes
+MAX_REQUESTS = 64      # requests one decode_step call takes (larger batches run as several launches)
 MAX_SEQ = 8192
 HEAD_DIM = 64
 
@@ -81,7 +82,8 @@ class _Runtime:
         self.geometry = geometry
         self.device = device
         self.scratch = torch.zeros(workspace_bytes(geometry, MAX_BATCH), dtype=torch.uint8, device=device)
-        self.out = torch.empty((MAX_BATCH, geometry.hidden), dtype=torch.bfloat16, device=device)
+        self.out = torch.empty((MAX_REQUESTS, geometry.hidden), dtype=torch.bfloat16, device=device)
+        self.group = MAX_BATCH          # requests per launch; lowered when the geometry does not fit at that batch
         self.logits = None
         self.next_ids = None
         self.table_key = None
@@ -91,8 +93,8 @@ class _Runtime:
 
     def lm_buffers(self):
         if self.logits is None:
-            self.logits = torch.empty((MAX_BATCH, self.geometry.vocab), dtype=torch.bfloat16, device=self.device)
-            self.next_ids = torch.zeros((MAX_BATCH,), dtype=torch.int64, device=self.device)
+            self.logits = torch.empty((MAX_REQUESTS, self.geometry.vocab), dtype=torch.bfloat16, device=self.device)
+            self.next_ids = torch.zeros((MAX_REQUESTS,), dtype=torch.int64, device=self.device)
         return self.logits, self.next_ids
 
     def tables(self, layers, kv_caches):
@@ -190,10 +192,12 @@ def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_tab
                 final_norm, kv_caches, cos_sin_cache, eps, layer_outputs=None, lm_head=False, advance=False,
                 embed_lookup=None, name="decode"):
     """One decode step for ``geometry``.  Returns the final-normed hidden ``[B, hidden]`` (a view of a
-    shared buffer), or ``(hidden, logits, next_ids)`` when ``lm_head`` is true."""
+    shared buffer), or ``(hidden, logits, next_ids)`` when ``lm_head`` is true.  Up to ``MAX_BATCH`` requests run in
+    one launch; up to ``MAX_REQUESTS`` are accepted and run as consecutive launches (micro-batches), each of which
+    streams the weights again."""
     batch = input_ids.shape[0]
-    if not 1 <= batch <= MAX_BATCH:
-        raise ValueError(f"batch must be 1..{MAX_BATCH}, got {batch}")
+    if not 1 <= batch <= MAX_REQUESTS:
+        raise ValueError(f"batch must be 1..{MAX_REQUESTS}, got {batch}")
     if eps != geometry.eps:
         raise ValueError(f"the kernel is built for rms eps {geometry.eps}, got {eps}")
     if len(layers) != geometry.layers or len(kv_caches) != geometry.layers:
@@ -218,14 +222,36 @@ def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_tab
     logits = next_ids = None
     if lm_head:
         logits, next_ids = rt.lm_buffers()
-    rc = torch.ops.prime_decode.decode_step(
-        input_ids, positions, seq_lens, block_table, slot_mapping, embed, embed_lookup, layers_t, final_norm, kv_t,
-        0, kv0.shape[3] // 2, kv0.stride(0), kv0.stride(2), kv0.stride(1), block_size, cos_sin_cache, rt.out,
-        logits, next_ids, layer_outputs, rt.scratch, geometry.hidden, geometry.intermediate, geometry.layers,
-        geometry.q_heads, geometry.kv_heads, geometry.vocab, geometry.weight_format, float(eps), max_seq,
-        bool(lm_head), bool(advance))
-    if rc != 0:
-        raise RuntimeError(f"{name} failed: {status_string(rc)}")
+
+    def launch(g0, g1, lo):
+        whole = g0 == 0 and g1 == batch                 # the common case: no slicing on the hot path
+        cut = (lambda t: t) if whole else (lambda t: t[g0:g1])
+        return torch.ops.prime_decode.decode_step(
+            cut(input_ids), cut(positions), cut(seq_lens), cut(block_table), cut(slot_mapping), embed, embed_lookup,
+            layers_t, final_norm, kv_t, 0, kv0.shape[3] // 2, kv0.stride(0), kv0.stride(2), kv0.stride(1), block_size,
+            cos_sin_cache, rt.out if whole else rt.out[g0:g1], (logits if whole else logits[g0:g1]) if lm_head else None,
+            (next_ids if whole else next_ids[g0:g1]) if lm_head else None, lo, rt.scratch, geometry.hidden,
+            geometry.intermediate, geometry.layers, geometry.q_heads, geometry.kv_heads, geometry.vocab,
+            geometry.weight_format, float(eps), max_seq, bool(lm_head), bool(advance))
+
+    # A launch takes up to rt.group requests (MAX_BATCH, fewer when the geometry's activation staging does not fit
+    # shared memory at that batch: status 9111 / 9105 lowers the group once and for all).  Larger batches run as
+    # consecutive launches over slices of the request arrays: every launch streams the weights again.
+    g0 = 0
+    while g0 < batch:
+        g1 = min(batch, g0 + rt.group)
+        whole = g0 == 0 and g1 == batch
+        lo = layer_outputs if whole or layer_outputs is None else \
+            torch.empty((geometry.layers, g1 - g0, geometry.hidden), dtype=torch.bfloat16, device=device)
+        rc = launch(g0, g1, lo)
+        if rc in (9111, 9105) and g1 - g0 > 1 and rt.group > 1:
+            rt.group = max(1, (g1 - g0) // 2)
+            continue
+        if rc != 0:
+            raise RuntimeError(f"{name} failed: {status_string(rc)}")
+        if lo is not None and lo is not layer_outputs:
+            layer_outputs[:, g0:g1].copy_(lo)
+        g0 = g1
     if lm_head:
         return rt.out[:batch], logits[:batch], next_ids[:batch]
     return rt.out[:batch]

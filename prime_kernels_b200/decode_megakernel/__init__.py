@@ -33,6 +33,9 @@ EPS = GEOMETRY.eps
 
 def decode_step(*, input_ids, positions, seq_lens, block_table, slot_mapping, embed, layers, final_norm,
                 kv_caches, cos_sin_cache, eps, lm_head=False):
+    batch = input_ids.shape[0]
+    if not 1 <= batch <= MAX_BATCH:      # one launch, like the reference entry (the generic op micro-batches beyond)
+        raise ValueError(f"batch must be 1..{MAX_BATCH}, got {batch}")
     return _generic.decode_step(GEOMETRY, input_ids=input_ids, positions=positions, seq_lens=seq_lens,
                                 block_table=block_table, slot_mapping=slot_mapping, embed=embed, layers=layers,
                                 final_norm=final_norm, kv_caches=kv_caches, cos_sin_cache=cos_sin_cache, eps=eps,

@@ -43,6 +43,8 @@ def _step(D, geom, wd, kv, csd, cur, pos, lm_head=True, layer_outputs=None):
     ("gqa3-b1-ctx1000", (192, 512, 2, 3, 1, 1024), 1, 1000, True),
     ("gqa3-b6-padded", (192, 512, 2, 3, 1, 1024), 6, 50, True),
     ("mha-b8", (128, 256, 2, 2, 2, 512), 8, 30, False),
+    ("gqa3-b16-two-launches", (192, 512, 2, 3, 1, 1024), 16, 40, True),       # BASELINE config 4's batch 16
+    ("gqa3-b19-ragged-groups", (192, 512, 2, 3, 1, 1024), 19, 33, False),     # 8 + 8 + 3 requests
 ])
 def test_small_geometries_against_restatement(cuda_device, name, dims, B, ctx, shuffle):
     from prime_kernels_b200 import decode as D
@@ -591,3 +593,33 @@ def test_host_driven_step_matches_device_driven_generation(cuda_device, graph):
         cur = nxt.clone()
     assert torch.equal(torch.stack(got), want)
     D.check_status(geom, cuda_device)
+
+
+def test_wide_geometry_falls_back_to_smaller_launch_groups(cuda_device):
+    """A geometry whose 8-request activation staging does not fit shared memory (SmolLM2-1.7B's widths, two layers):
+    the step runs as launches of 4 requests and still matches the restatement (BASELINE config 5's batch 8)."""
+    from prime_kernels_b200 import decode as D
+
+    geom = D.Geometry("wide", 2048, 8192, 2, 32, 32, 2048, rope_theta=130000.0)
+    w = harness.make_weights(geom, 0)
+    wd = harness.weights_to(w, cuda_device)
+    cs = harness.make_cos_sin_cache(geom, 128)
+    B, ctx = 8, 20
+    gen = torch.Generator().manual_seed(3)
+    cur = torch.randint(0, geom.vocab, (B,), generator=gen)
+    keys = [[torch.randn(geom.kv_heads, ctx, 64, generator=gen).to(torch.bfloat16) for _ in range(B)] for _ in range(geom.layers)]
+    vals = [[torch.randn(geom.kv_heads, ctx, 64, generator=gen).to(torch.bfloat16) for _ in range(B)] for _ in range(geom.layers)]
+    kv = harness.PagedKV(geom, B, 64, cuda_device)
+    kv.load_prefix([torch.stack(k) for k in keys], [torch.stack(v) for v in vals])
+    pos = torch.full((B,), ctx, dtype=torch.int64)
+    hid, logits, nxt = _step(D, geom, wd, kv, cs.to(cuda_device), cur, pos)
+    D.check_status(geom, cuda_device)
+    assert D._runtime(geom, torch.device(cuda_device)).group < D.MAX_BATCH
+    rh, rl, _ = R.decode_step(geom, w, cur, pos, keys, vals, cs)
+    # 2048- and 8192-long dot products: the summation-order noise is larger than on the small geometries
+    wide_tol = 5e-2
+    assert (logits.cpu().float() - rl).abs().max() <= wide_tol
+    margin = rl.topk(2, -1).values
+    sure = (margin[:, 0] - margin[:, 1]) > 2 * wide_tol
+    assert (nxt.cpu()[sure] == rl.argmax(-1)[sure]).all()
+
