@@ -121,7 +121,6 @@ int main() {
     run<9>("fma.rn.bf16x2", 1);
     run<10>("mul.rn.bf16x2", 1);
     run<11>("2x prmt + 2 xor", 1);
-    run<13>("and.b32", 1);
     run<14>("cvt bf16.f32 + shl/or", 1);
     run<15>("rsqrt.approx", 1);
     run<16>("shfl.bfly", 1);
