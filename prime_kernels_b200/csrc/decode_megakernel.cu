@@ -263,6 +263,7 @@ __device__ __forceinline__ void wait_flagged_strided(Ctx& c, const unsigned long
 }
 
 __device__ __forceinline__ bool wait_mbar(Ctx& c, uint64_t* bar, uint32_t parity) {
+    if (mbar_probe(bar, parity)) return true;      // the common case: the entry landed long ago
     if (aborted(c)) return false;
     unsigned spins = 0;
     while (!mbar_test(bar, parity)) {
