@@ -117,6 +117,7 @@ struct DecodeParams {
 };
 
 constexpr int kProfSlots = 24;
+constexpr int kKvPtrCache = 64;            // per-layer KV base pointers kept in shared memory (deeper models read the table)
 constexpr int kPreRuns = 4;                // runs per warp whose block-table look-ups are resolved at kernel start
 constexpr unsigned kProducerIdleNs = 100;   // producer back-off when its rings are full
 enum CtrlWord { kCtrlEpoch = 0, kCtrlStatus = 1, kCtrlDone = 2, kCtrlWords = 16 };
@@ -163,6 +164,8 @@ struct Shared {
     float red[kMaxB][kNW];
     int seq[kMaxB], pos[kMaxB], nc[kMaxB], lc[kMaxB];
     int ncmax, two_level;
+    PhaseDesc ph[kNumPhaseTypes];       // copy of the phase descriptors (indexed with a run-time phase type)
+    unsigned long long kv_ptr[kKvPtrCache];   // copy of the per-layer KV base pointers: no dependent global load per layer
     uint32_t lm_best[kNW][32];          // lm_head: running argmax per consumer lane
     // This CTA's first attention item, resolved once per launch (nothing in it depends on the layer):
     int item0_b, item0_kvh, item0_chunk;   // its coordinates; item0_b < 0: this CTA has no item
@@ -566,7 +569,7 @@ template <int B, int WF>
 __device__ void gemv_phase(Ctx& c, const int T, int layer, uint32_t& consumed) {
     const DecodeParams& p = c.p;
     Shared& sh = c.sh;
-    const PhaseDesc& d = p.ph[T];
+    const PhaseDesc& d = sh.ph[T];      // shared-memory copy: T is a run-time index
     const int w = c.warp, lane = c.lane;
     const int ra = sh.row_a[T][w], rb = sh.row_b[T][w];
     const int actc = p.act_elems >> 3;                 // uint4 per request in c.act
@@ -932,7 +935,7 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk, boo
     const int ws = min(start + c.warp * ppw, end);
     const int we = min(ws + ppw, end);
     const bool has_new = (seq - 1 >= ws) && (seq - 1 < we);
-    const uint16_t* kvr = reinterpret_cast<const uint16_t*>(p.kv[layer]);
+    const uint16_t* kvr = reinterpret_cast<const uint16_t*>(layer < kKvPtrCache ? sh.kv_ptr[layer] : p.kv[layer]);
     const int pl = lane >> 1, half = lane & 1;      // scores phase: position in the run, half of the head dim
 
     // shared-memory staging (all on 16-byte boundaries)
@@ -1053,7 +1056,7 @@ __device__ void attention_item(Ctx& c, int layer, int b, int kvh, int chunk, boo
     if (has_new) {   // warp-uniform: append the new token's K/V to the paged cache (slot -1 = padded row: skip)
         const long long so = sh.slot_off[b];
         if (so >= 0 && lane < 8) {
-            uint16_t* kvw = reinterpret_cast<uint16_t*>(p.kv[layer]);
+            uint16_t* kvw = reinterpret_cast<uint16_t*>(layer < kKvPtrCache ? sh.kv_ptr[layer] : p.kv[layer]);
             const long long e = so + (long long)kvh * p.head_stride + 8 * lane;
             *reinterpret_cast<uint4*>(kvw + p.k_off + e) = *reinterpret_cast<const uint4*>(qkvb_s + G * 32 + 4 * lane);
             *reinterpret_cast<uint4*>(kvw + p.v_off + e) = *reinterpret_cast<const uint4*>(qkvb_s + (G + 1) * 32 + 4 * lane);
@@ -1265,7 +1268,7 @@ __device__ void attention_prefetch(Ctx& c, int layer) {
     const DecodeParams& p = c.p;
     Shared& sh = c.sh;
     const int nslots = kNCMax * p.B * p.KVH;
-    const unsigned char* kvr = reinterpret_cast<const unsigned char*>(p.kv[layer]);
+    const unsigned char* kvr = reinterpret_cast<const unsigned char*>(layer < kKvPtrCache ? sh.kv_ptr[layer] : p.kv[layer]);
     int first = c.cta;
     if (sh.item0_all) {
         // first item, offsets already resolved: thread = (warp share, position, K or V), no look-ups
@@ -1442,6 +1445,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
         mbar_init(&sh.full[tid / kE][tid % kE], 1);
         mbar_init(&sh.empty[tid / kE][tid % kE], 1);
     }
+    if (tid < kNumPhaseTypes) sh.ph[tid] = p.ph[tid];
+    for (int l = tid; l < p.L && l < kKvPtrCache; l += kThreads) sh.kv_ptr[l] = p.kv[l];
     if (tid < kNumPhaseTypes * kNW) {
         const int t = tid / kNW, w = tid % kNW;
         int a = 0, b = 0;
