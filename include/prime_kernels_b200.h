@@ -3,7 +3,7 @@
  *
  * Plain pointers and sizes only; every pointer is a CUDA device pointer unless stated otherwise,
  * `stream` is a cudaStream_t passed as void*.  Every function that can fail returns an int:
- * 0 = ok, 9101..9111 = contract violations (see pk_status_string), any other value is a
+ * 0 = ok, 9101..9112 = contract violations (see pk_status_string), any other value is a
  * cudaError_t.  Nothing here allocates device memory; nothing here falls back to the CPU.
  *
  * Each entry cites the reference interface it replaces (paths inside the reference project).
@@ -130,6 +130,19 @@ int pk_decode_query(int* sm_count, int* coop, int* major, int* minor, int* smem_
 void pk_decode_set_profile(void* buffer, size_t bytes);
 /* Replaces mk_status_string / decode360_status_string for every code above. */
 const char* pk_status_string(int status);
+/* Tuning and test knobs, process-wide; no counterpart in the reference.
+ * pk_decode_set_fast_path: batch-1 bf16 steps of the SmolLM2-135M / 360M widths run on a kernel specialised
+ * for those widths with `warps` (8 or 16) warps per CTA; 0 sends every step to the generic kernel
+ * (default: environment variable PK_DECODE_FAST, else 16).  Both kernels keep the same rounding points.
+ * pk_decode_set_spin_limit: bound, in polling rounds, of every device-side wait of later launches (the
+ * reference spins without a bound, prime_kernels/decode_megakernel/csrc/megakernel.cu:109-122); 0 = default.
+ * pk_decode_wait_probe: failure-path check in the form of the reference's harness watchdog
+ * (prime_kernels/rmsnorm/test.cu:180-192) moved onto the device: one CTA polls a word of `workspace` that
+ * nothing writes, gives up after `rounds` polls and records status 9110, which pk_decode_status() then
+ * returns and clears.  It cannot hang and writes nothing else. */
+int pk_decode_set_fast_path(int warps);
+void pk_decode_set_spin_limit(unsigned rounds);
+int pk_decode_wait_probe(void* workspace, size_t bytes, unsigned rounds, void* stream);
 
 /* ---------------------------------------------------------------- drop-in signatures of the reference */
 

@@ -6,9 +6,14 @@ Rounding points follow the reference's HF-parity kernel line
 (prime_kernels/decode_megakernel_360m_lossless/csrc/block360.cu:121-166 RMSNorm, :239-255 RoPE;
 block360_kernel.inc:166-167 bf16 score then exact 1/8 scale, :403-408 bf16 attention output,
 :422-436 O + residual, :487-559 SwiGLU, :566-582 down + residual) which mirror
-transformers/models/llama/modeling_llama.py.  One deliberate difference from HF, shared with the
-reference's fast line and the CUDA kernel: softmax probabilities stay fp32 (HF rounds them to bf16
-before the PV product).
+transformers/models/llama/modeling_llama.py.
+
+Softmax probabilities: HuggingFace eager normalises in fp32 and rounds the probabilities to bf16 before
+the P.V product (the reference's strict line does the same,
+prime_kernels/decode_megakernel_360m/csrc/block360_kernel.inc:252,311-312,346-347); ``probs="bf16"``
+restates that.  ``probs="fp32"`` keeps them in fp32 like the reference's fast line
+(prime_kernels/decode_megakernel_360m_lossless/csrc/block360_kernel.inc:166-234) and the CUDA kernel's
+split-KV path, which only know un-normalised weights until the chunk partials are merged.
 """
 from __future__ import annotations
 
@@ -36,7 +41,7 @@ def rope(x, cos, sin):
 
 
 @torch.no_grad()
-def decode_step(geometry, weights, token_ids, positions, keys, values, cos_sin_cache):
+def decode_step(geometry, weights, token_ids, positions, keys, values, cos_sin_cache, probs="fp32"):
     """One decode step on the CPU.
 
     ``keys[l]`` / ``values[l]``: per-layer lists of per-request tensors ``[kv_heads, T_b, 64]`` (bf16) holding
@@ -67,6 +72,8 @@ def decode_step(geometry, weights, token_ids, positions, keys, values, cos_sin_c
             V = values[l][b].float().repeat_interleave(G, 0)
             sc = bf(torch.einsum("hd,htd->ht", q, K)) * 0.125
             p = torch.softmax(sc, -1)
+            if probs == "bf16":
+                p = bf(p)
             attn[b] = bf(torch.einsum("ht,htd->hd", p, V)).reshape(-1)
         h1 = bf(x + bf(attn @ o_w.float().T))
         hn = rms_norm(h1, n2, g.eps)

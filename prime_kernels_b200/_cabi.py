@@ -57,6 +57,9 @@ SYMBOLS = {
     "pk_decode_query": (ci, [ip] * 7),
     "pk_decode_set_profile": (None, [vp, sz]),
     "pk_status_string": (ctypes.c_char_p, [ci]),
+    "pk_decode_set_fast_path": (ci, [ci]),
+    "pk_decode_set_spin_limit": (None, [ctypes.c_uint]),
+    "pk_decode_wait_probe": (ci, [vp, sz, ctypes.c_uint, vp]),
     "mk_query": (ci, [ip] * 7),
     "mk_workspace_bytes": (sz, [ci, ci]),
     "mk_decode": (ci, [vp, ci, vp, ci, vp, vp, vp, ci, vp, vp, vp, vp, vp, ll, ll, ll, ll, ll, ci, vp, ci, vp, vp, sz, ci]),

@@ -1,0 +1,1121 @@
+// Batch-1 bf16 decode step with compile-time model widths (included by decode_megakernel.cu).
+//
+// Same arithmetic contract and the same dataflow idea as decode_step_kernel (weights streamed through
+// per-warp shared-memory rings with bulk async copies, activations handed from CTA to CTA through
+// self-validating words in L2, no grid barrier, every wait bounded), specialised so that one step of a
+// small model is a short chain of short phases:
+//
+//  * hidden / intermediate / head counts are template constants: every loop bound, divisor and stride
+//    folds, and the whole kernel is a few thousand instructions, so a layer iteration stays inside the
+//    instruction cache (the generic kernel is ~200 KB of code per instantiation and refetches it from L2
+//    every layer);
+//  * every warp is a consumer and refills its own ring: right after it has used an entry it issues the
+//    bulk copies of the next entries that fit (the freed bytes are exactly what the next copy needs, so a
+//    separate producer warp would act at the same moment), which removes the producer warp, the "empty"
+//    barriers and their polling;
+//  * bf16 activations travel as 32-bit words [tag:16 | bf16:16] and are polled with 16-byte loads: four
+//    values per load, each word validating itself (no reliance on 16-byte atomicity).  fp32 split-KV
+//    partials travel as 64-bit words [tag:32 | fp32] polled two per 16-byte load;
+//  * five hand-offs per layer instead of six: split-KV partials are always merged by the consumers while
+//    they stage the O-projection input (at most Widths::NC chunks per kv head; longer contexts get
+//    longer chunks), so there is no separate merge stage;
+//  * activation and residual staging buffers alternate between phases, which removes the barrier that
+//    protected them from the previous phase's stragglers (two barriers per norm phase, one per copy phase).
+//
+// Reference behaviour followed: see the header of decode_megakernel.cu (same rounding points).
+#pragma once
+
+namespace pk {
+namespace fast {
+
+constexpr int kFE = 8;             // ring entries in flight per warp
+constexpr int kPre = 2;            // 16-position runs per warp whose cache offsets are resolved at kernel start
+constexpr int kKvPtrs = 64;        // per-layer KV base pointers cached in shared memory
+constexpr int kNominalCtas = 128;  // compile-time lower bound of the grid (the host checks it)
+
+template <int H_, int I_, int QH_, int KVH_>
+struct Widths {
+    static constexpr int H = H_, I = I_, QH = QH_, KVH = KVH_, G = QH_ / KVH_;
+    static constexpr int NQKV = (QH_ + 2 * KVH_) * kD;
+    static constexpr int AD = QH_ * kD;                           // attention output width (K of the O projection)
+    static constexpr int NC = (kNominalCtas / KVH_) < 6 ? (kNominalCtas / KVH_) : 6;   // max chunks per kv head
+    static_assert(QH_ % KVH_ == 0 && H_ % 32 == 0 && I_ % 32 == 0, "unsupported widths");
+};
+
+struct FastParams {
+    const unsigned long long* layers;   // device table [L][6]
+    const unsigned long long* kv;       // device table [L]
+    const uint16_t* embed;              // [V, H] bf16 (tied lm_head)
+    const uint16_t* final_norm;
+    const void* input_ids;
+    const long long* positions;
+    const int* seq_lens;
+    const int* block_table;
+    const long long* slot_mapping;
+    const void* cos_sin;
+    uint16_t* out_hidden;
+    uint16_t* logits;
+    long long* next_ids;
+    uint16_t* layer_outputs;
+    unsigned long long* profile;
+    unsigned int* ctrl;                 // control words shared with the generic kernel (status)
+    unsigned int* fctrl;                // this kernel's own control words: epoch, completion counter
+    unsigned long long* argkey;         // [2]
+    uint32_t* w_x;                      // [2][H]      words [tag16 | bf16]
+    uint32_t* w_qkv;                    // [2][NQKV]
+    uint32_t* w_h1;                     // [2][H]
+    uint32_t* w_act;                    // [2][I]
+    unsigned long long* w_part;         // [2][KVH][NC][G][66]  words [tag32 | fp32]
+    unsigned long long* w_gate;         // [2][KVH * NC]        one word [tag32 | 1] per attention item, written after its partials
+    long long k_off, v_off, block_stride, token_stride, head_stride;
+    int block_size, bt_stride, ids_i64, cs_fp32;
+    int L, V, lm_head, advance, max_seq_len, ring_bytes;
+    unsigned spin_limit;
+    int dbg;                            // development switches (bit 0: CTA barrier after every GEMV phase; bit 1: poll back-off)
+    float eps;
+};
+
+enum { kFctrlEpoch = 0, kFctrlDone = 1 };
+
+template <int NW>
+struct FShared {
+    uint64_t full[NW][kFE];
+    uint32_t ent_off[NW][kFE];
+    uint32_t ent_foot[NW][kFE];
+    int row_a[kNumPhaseTypes][NW];
+    int row_b[kNumPhaseTypes][NW];
+    float red[NW];
+    float cs[64];                          // cos[32], sin[32] of this step's position
+    unsigned long long lm_key[NW];
+    unsigned long long kv_ptr[kKvPtrs];
+    unsigned long long norm_ptr[2 * kMaxLayers + 1];   // norm1 / norm2 weight pointers of every layer, then the final norm
+    unsigned long long mat_ptr[kMaxLayers][4];         // qkv, o, gate_up, down weight pointers of every layer
+    long long kv_off[NW][kPre * 16];       // cache element offsets (without the kv-head term) of the warp's first runs
+    long long slot_off;                    // cache element offset of the new token; -1 = skip the write
+    long long tok;
+    int seq, pos, nc, lc;
+    int item_kvh, item_chunk;              // this CTA's attention item; item_kvh < 0: none
+    volatile int abort_flag;
+    uint32_t epoch;
+};
+
+// ------------------------------------------------------------------ hand-off words
+__device__ __forceinline__ uint4 ld_packet(const void* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_word(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void ld_flagged2(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+// all four words of a packet carry the tag T (= tag16 << 16)
+__device__ __forceinline__ bool packet_ok(const uint4 v, uint32_t T) {
+    return ((((v.x ^ T) | (v.y ^ T)) | ((v.z ^ T) | (v.w ^ T))) >> 16) == 0u;
+}
+
+// ------------------------------------------------------------------ per-thread kernel state
+template <int NW>
+struct FC {
+    const FastParams& p;
+    FShared<NW>& sh;
+    uint4* act[2];      // bf16 activations of the current phase, alternating between phases
+    float* res[2];      // fp32 copy of the residual stream: [0] = x (layer input), [1] = h1
+    float* attn;        // attention scratch / staged split-KV partials
+    unsigned char* ring;
+    uint32_t T16;       // ((epoch % 511) + 1) << 23: the epoch part of a 16-bit tag, already in the high half
+    uint32_t T32;       // (epoch + 1) << 7: the epoch part of a 32-bit tag
+    int warp, lane, cta, ncta;
+    // ring state (warp-uniform)
+    uint32_t issued, consumed, head, used;
+    int i_layer, i_t, i_row;    // issue cursor; i_t == kNumPhaseTypes: nothing left
+    uint2 nwv[2];               // this thread's norm weights of the *next* norm phase (fetched one phase ahead)
+    unsigned long long* prof;
+#ifdef PK_FAST_WPROF
+    unsigned long long* wprof;  // development builds: this warp's stamps of the current phase (lane 0, one layer)
+#endif
+};
+
+#ifdef PK_FAST_WPROF
+constexpr int kWprofLayer = 5;
+#define PK_WSTAMP(c, i) do { if ((c).wprof) (c).wprof[i] = global_ns(); } while (0)
+#else
+#define PK_WSTAMP(c, i) do { } while (0)
+#endif
+
+template <int NW>
+__device__ __forceinline__ bool f_aborted(const FC<NW>& c) { return c.sh.abort_flag != 0; }
+template <int NW>
+__device__ __forceinline__ void f_raise(FC<NW>& c, int code) {
+    c.sh.abort_flag = 1;
+    atomicCAS(c.p.ctrl + kCtrlStatus, 0u, (unsigned)code);
+}
+// periodic check inside a spin loop; returns true when the wait must be given up
+template <int NW>
+__device__ __forceinline__ bool f_give_up(FC<NW>& c, unsigned spins) {
+    if (f_aborted(c)) return true;
+    if (*((volatile unsigned int*)(c.p.ctrl + kCtrlStatus)) != 0) {
+        c.sh.abort_flag = 1;
+        return true;
+    }
+    if (spins >= c.p.spin_limit) {
+        f_raise(c, kErrBarrierTimeout);
+        return true;
+    }
+    return false;
+}
+
+template <int NW>
+__device__ __forceinline__ uint32_t tag16(const FC<NW>& c, int layer) { return c.T16 | ((uint32_t)(layer + 1) << 16); }
+template <int NW>
+__device__ __forceinline__ uint32_t tag32(const FC<NW>& c, int layer) { return c.T32 + (uint32_t)layer + 1u; }
+
+// Wait for up to N packets (ptr[u] == nullptr: slot unused).  While nothing has arrived only the first
+// packet is polled (the CTAs that have no other work in a phase would otherwise multiply the polling
+// traffic in L2 by N); once it is there all remaining ones are fetched together.
+template <int N, int NW>
+__device__ __forceinline__ void poll_packets(FC<NW>& c, const uint32_t* const (&ptr)[N], uint32_t T, uint4 (&out)[N]) {
+    unsigned need = 0;
+#pragma unroll
+    for (int u = 0; u < N; ++u) {
+        out[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (ptr[u] != nullptr) need |= 1u << u;
+    }
+    if (f_aborted(c)) return;
+    unsigned spins = 0;
+    bool first_only = N > 1;
+    while (need) {
+        const unsigned cur = first_only ? (need & (0u - need)) : need;
+        uint4 v[N];
+#pragma unroll
+        for (int u = 0; u < N; ++u)
+            if (cur & (1u << u)) v[u] = ld_packet(ptr[u]);
+#pragma unroll
+        for (int u = 0; u < N; ++u)
+            if ((cur & (1u << u)) && packet_ok(v[u], T)) {
+                out[u] = v[u];
+                need &= ~(1u << u);
+                first_only = false;
+            }
+        if (need && (c.p.dbg & 2)) __nanosleep(200);
+        if (need && (++spins & 255u) == 0 && f_give_up(c, spins)) return;
+    }
+}
+
+// Same for pairs of 64-bit flagged words [tag32 | fp32]; out[2u], out[2u+1] receive the payloads.
+template <int N, int NW>
+__device__ __forceinline__ void poll_flagged_pairs(FC<NW>& c, const unsigned long long* const (&ptr)[N], uint32_t tag,
+                                                   uint32_t (&out)[2 * N]) {
+    unsigned need = 0;
+#pragma unroll
+    for (int u = 0; u < N; ++u) {
+        out[2 * u] = out[2 * u + 1] = 0u;
+        if (ptr[u] != nullptr) need |= 1u << u;
+    }
+    if (f_aborted(c)) return;
+    unsigned spins = 0;
+    bool first_only = N > 1;
+    while (need) {
+        const unsigned cur = first_only ? (need & (0u - need)) : need;
+        unsigned long long a[N], b[N];
+#pragma unroll
+        for (int u = 0; u < N; ++u)
+            if (cur & (1u << u)) ld_flagged2(ptr[u], a[u], b[u]);
+#pragma unroll
+        for (int u = 0; u < N; ++u)
+            if ((cur & (1u << u)) && (uint32_t)(a[u] >> 32) == tag && (uint32_t)(b[u] >> 32) == tag) {
+                out[2 * u] = (uint32_t)a[u];
+                out[2 * u + 1] = (uint32_t)b[u];
+                need &= ~(1u << u);
+                first_only = false;
+            }
+        if (need && (++spins & 255u) == 0 && f_give_up(c, spins)) return;
+    }
+}
+
+template <int NW>
+__device__ __forceinline__ bool f_wait_mbar(FC<NW>& c, uint64_t* bar, uint32_t parity) {
+    if (mbar_probe(bar, parity)) return true;
+    if (f_aborted(c)) return false;
+    unsigned spins = 0;
+    while (!mbar_test(bar, parity)) {
+        if ((++spins & 255u) == 0 && f_give_up(c, spins)) return false;
+    }
+    return true;
+}
+
+// ------------------------------------------------------------------ weight schedule
+// Phase constants.  Rows are dealt in contiguous shares: CTA, then warp (same rule as the generic kernel).
+template <class W, int NW, int T>
+struct Ph;
+template <class W, int NW>
+struct Ph<W, NW, kQKV> { static constexpr int K = W::H, WIDX = 1, PAIR = 1, RPE = 1; };   // unit = rows (d, d + 32) of a head
+template <class W, int NW>
+struct Ph<W, NW, kO> { static constexpr int K = W::AD, WIDX = 2, PAIR = 0, RPE = 2; };
+template <class W, int NW>
+struct Ph<W, NW, kGU> { static constexpr int K = W::H, WIDX = 4, PAIR = 1, RPE = (NW >= 12 ? 1 : 2); };
+template <class W, int NW>
+struct Ph<W, NW, kDown> { static constexpr int K = W::I, WIDX = 5, PAIR = 0, RPE = (W::I * 2 > 4096 ? 1 : 2); };
+template <class W, int NW>
+struct Ph<W, NW, kLM> { static constexpr int K = W::H, WIDX = -1, PAIR = 0, RPE = (NW >= 12 ? 2 : 4); };
+
+template <class W, int NW>
+__device__ __forceinline__ void phase_consts(int t, int& rowbytes, int& rpe, int& widx) {
+    switch (t) {
+        case kQKV: rowbytes = Ph<W, NW, kQKV>::K * 2; rpe = Ph<W, NW, kQKV>::RPE; widx = Ph<W, NW, kQKV>::WIDX; break;
+        case kO: rowbytes = Ph<W, NW, kO>::K * 2; rpe = Ph<W, NW, kO>::RPE; widx = Ph<W, NW, kO>::WIDX; break;
+        case kGU: rowbytes = Ph<W, NW, kGU>::K * 2; rpe = Ph<W, NW, kGU>::RPE; widx = Ph<W, NW, kGU>::WIDX; break;
+        case kDown: rowbytes = Ph<W, NW, kDown>::K * 2; rpe = Ph<W, NW, kDown>::RPE; widx = Ph<W, NW, kDown>::WIDX; break;
+        default: rowbytes = Ph<W, NW, kLM>::K * 2; rpe = Ph<W, NW, kLM>::RPE; widx = Ph<W, NW, kLM>::WIDX; break;
+    }
+}
+
+template <int NW>
+__device__ __forceinline__ void warp_share(int nrows, int cta, int ncta, int warp, int& a, int& b) {
+    const int r0 = (int)((long long)nrows * cta / ncta);
+    const int r1 = (int)((long long)nrows * (cta + 1) / ncta);
+    const int n = r1 - r0;
+    a = r0 + n * warp / NW;
+    b = r0 + n * (warp + 1) / NW;
+}
+
+// Move the issue cursor to the next phase of this warp that owns rows (or to the end).
+template <int NW>
+__device__ __forceinline__ void cursor_next_phase(FC<NW>& c) {
+    for (;;) {
+        if (c.i_t == kLM) {
+            c.i_t = kNumPhaseTypes;
+            return;
+        }
+        if (++c.i_t == 4) {
+            ++c.i_layer;
+            if (c.i_layer < c.p.L) {
+                c.i_t = 0;
+            } else if (c.p.lm_head) {
+                c.i_t = kLM;
+            } else {
+                c.i_t = kNumPhaseTypes;
+                return;
+            }
+        }
+        c.i_row = c.sh.row_a[c.i_t][c.warp];
+        if (c.i_row < c.sh.row_b[c.i_t][c.warp]) return;
+    }
+}
+
+// Issue the bulk copies of as many upcoming entries as the ring has room for.  Warp-uniform; lane 0 issues.
+template <class W, int NW>
+__device__ __forceinline__ void issue_more(FC<NW>& c, uint64_t pol) {
+    const uint32_t RW = (uint32_t)c.p.ring_bytes;
+    while (c.i_t < kNumPhaseTypes) {
+        int rowbytes, rpe, widx;
+        phase_consts<W, NW>(c.i_t, rowbytes, rpe, widx);
+        const int nre = min(rpe, c.sh.row_b[c.i_t][c.warp] - c.i_row);
+        const uint32_t part = (uint32_t)(nre * rowbytes);
+        const bool pair = c.i_t == kGU || c.i_t == kQKV;
+        const uint32_t bytes = pair ? 2u * part : part;
+        const uint32_t gap = (c.head + bytes > RW) ? RW - c.head : 0u;
+        const uint32_t foot = bytes + gap;
+        if (c.issued - c.consumed >= (uint32_t)kFE || c.used + foot > RW) break;
+        const uint32_t off = gap ? 0u : c.head;
+        if (c.lane == 0) {
+            const uint32_t slot = c.issued % kFE;
+            c.sh.ent_off[c.warp][slot] = off;
+            c.sh.ent_foot[c.warp][slot] = foot;
+            // weight pointers come from the shared-memory copy of the table: no global load in front of the copy
+            const unsigned char* base = widx < 0 ? reinterpret_cast<const unsigned char*>(c.p.embed)
+                                                 : reinterpret_cast<const unsigned char*>(c.sh.mat_ptr[c.i_layer][c.i_t]);
+            // QKV units pair row d with row d + 32 of the same head; gate/up units pair row r with row I + r
+            const int row0 = c.i_t == kQKV ? ((c.i_row >> 5) << 6) + (c.i_row & 31) : c.i_row;
+            const size_t pair_off = (size_t)(c.i_t == kQKV ? 32 : W::I) * rowbytes;
+            const unsigned char* src = base + (size_t)row0 * rowbytes;
+            // the generic-proxy reads of the bytes being overwritten are ordered before the async-proxy writes
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(&c.sh.full[c.warp][slot], bytes);
+            bulk_g2s(c.ring + off, src, part, &c.sh.full[c.warp][slot], pol);
+            if (pair) bulk_g2s(c.ring + off + part, src + pair_off, part, &c.sh.full[c.warp][slot], pol);
+        }
+        c.head = off + bytes;
+        if (c.head >= RW) c.head = 0;
+        c.used += foot;
+        ++c.issued;
+        c.i_row += rpe;
+        if (c.i_row >= c.sh.row_b[c.i_t][c.warp]) cursor_next_phase(c);
+    }
+    __syncwarp();
+}
+
+// ------------------------------------------------------------------ GEMV
+// NR staged rows of KC 16-byte chunks each times the activation vector, K split over the lanes.
+template <int KC, int NR>
+__device__ __forceinline__ void gemv_rows(const uint4* ep, const uint4* act, int lane, int nlive, float (&v)[4]) {
+    constexpr int IT = (KC + 31) / 32;
+    float acc[NR], acc2[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) acc[r] = acc2[r] = 0.f;
+#pragma unroll 4
+    for (int it = 0; it < IT; ++it) {
+        const int ch = it * 32 + lane;
+        const bool ok = (it + 1) * 32 <= KC || ch < KC;
+        const uint4 a = ok ? act[ch] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const uint4 wv = (ok && r < nlive) ? ep[r * KC + ch] : make_uint4(0u, 0u, 0u, 0u);
+            if (it & 1) acc2[r] = dot8_bf16(wv, a, acc2[r]);
+            else acc[r] = dot8_bf16(wv, a, acc[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) v[r] = acc[r] + acc2[r];
+}
+
+// One GEMV phase of one warp: its ring entries of phase type t at `layer`.  One body for all phase types
+// (run-time t) so that the wait, the reduction and the ring refill exist once in the instruction stream;
+// only the dot products (compile-time K) and the epilogues are switched.
+template <class W, int NW>
+__device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, const uint4* act, const float* res, uint64_t pol) {
+    const FastParams& p = c.p;
+    FShared<NW>& sh = c.sh;
+    const int w = c.warp, lane = c.lane;
+    const int ra = sh.row_a[t][w], rb = sh.row_b[t][w];
+    const int par = layer & 1;
+    int rowbytes, rpe, widx;
+    phase_consts<W, NW>(t, rowbytes, rpe, widx);
+    uint32_t best = 0u;      // lm_head: bf16 order key << 16 | (0xffff - local row)
+#pragma unroll 1
+    for (int row = ra; row < rb; row += rpe) {
+        const int nre = min(rpe, rb - row);
+        const uint32_t slot = c.consumed % kFE;
+        // after an abort the staged bytes are undefined: leave the phase (warp-uniform)
+        if (!__all_sync(kFullMask, f_wait_mbar(c, &sh.full[w][slot], (c.consumed / kFE) & 1))) break;
+        if (row == ra) PK_WSTAMP(c, 4);
+        const uint4* ep = reinterpret_cast<const uint4*>(c.ring + sh.ent_off[w][slot]);
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        switch (t) {
+            case kQKV: gemv_rows<Ph<W, NW, kQKV>::K / 8, 2 * Ph<W, NW, kQKV>::RPE>(ep, act, lane, 2 * nre, v); break;
+            case kO: gemv_rows<Ph<W, NW, kO>::K / 8, Ph<W, NW, kO>::RPE>(ep, act, lane, nre, v); break;
+            case kGU: gemv_rows<Ph<W, NW, kGU>::K / 8, 2 * Ph<W, NW, kGU>::RPE>(ep, act, lane, 2 * nre, v); break;
+            case kDown: gemv_rows<Ph<W, NW, kDown>::K / 8, Ph<W, NW, kDown>::RPE>(ep, act, lane, nre, v); break;
+            default: gemv_rows<Ph<W, NW, kLM>::K / 8, Ph<W, NW, kLM>::RPE>(ep, act, lane, nre, v); break;
+        }
+        __syncwarp();
+        c.used -= sh.ent_foot[w][slot];
+        ++c.consumed;
+        // lane 8 j ends up with the total of staged row j (j < 4)
+        const float mine = transpose_reduce<4>(v, lane);
+        const int vj = lane >> 3;
+        // pair entries stage nre first rows (gate / dim d), then nre second rows (up / dim d + 32)
+        const float mine_up = __shfl_sync(kFullMask, mine, ((vj + nre) << 3) & 31);
+        if ((lane & 7) == 0 && vj < nre) {
+            const int r = row + vj;
+            if (t == kQKV) {
+                // unit r = (head, j): projection outputs of dims j and j + 32 rounded to bf16 (HF linear output),
+                // q and k heads rotated here (HF apply_rotary_pos_emb rounding), v passed through
+                const int hd = r >> 5, j = r & 31;
+                float x0 = round_bf16(mine), x1 = round_bf16(mine_up);
+                if (hd < W::QH + W::KVH) {
+                    const float cs = sh.cs[j], sn = sh.cs[32 + j];
+                    const float y0 = rope_elem(x0, x1, cs, sn, true);
+                    x1 = rope_elem(x1, x0, cs, sn, false);
+                    x0 = y0;
+                }
+                uint32_t* dst = p.w_qkv + par * W::NQKV + hd * kD + j;
+                st_word(dst, f32_to_bf16_bits(x0) | tag16(c, layer));
+                st_word(dst + 32, f32_to_bf16_bits(x1) | tag16(c, layer));
+            } else if (t == kO) {
+                // h1 = bf16( x + bf16(o_proj) )
+                const float h = __fadd_rn(res[r], round_bf16(mine));
+                st_word(p.w_h1 + par * W::H + r, f32_to_bf16_bits(h) | tag16(c, layer));
+            } else if (t == kGU) {
+                // act = bf16( bf16(silu(bf16 gate)) * bf16 up )   (HF LlamaMLP rounding)
+                const float g = round_bf16(mine);
+                const float u = round_bf16(mine_up);
+                const float silu = round_bf16(__fdividef(g, 1.f + __expf(-g)));
+                st_word(p.w_act + par * W::I + r, f32_to_bf16_bits(__fmul_rn(silu, u)) | tag16(c, layer));
+            } else if (t == kDown) {
+                // x' = bf16( h1 + bf16(down_proj) ), handed to the next layer
+                const uint32_t xb = f32_to_bf16_bits(__fadd_rn(res[r], round_bf16(mine)));
+                st_word(p.w_x + ((layer + 1) & 1) * W::H + r, xb | tag16(c, layer + 1));
+                if (p.layer_outputs) p.layer_outputs[(size_t)layer * W::H + r] = (uint16_t)xb;
+            } else {
+                const uint32_t lb = f32_to_bf16_bits(mine);
+                if (p.logits) p.logits[r] = (uint16_t)lb;
+                const uint32_t ord = (lb & 0x8000u) ? (~lb & 0xffffu) : (lb | 0x8000u);
+                best = max(best, (ord << 16) | (0xffffu - (uint32_t)(r - ra)));
+            }
+        }
+        PK_WSTAMP(c, 5);
+        issue_more<W, NW>(c, pol);
+    }
+    if (t == kLM) {
+        // greedy argmax: highest logit, ties toward the lowest index; one atomic per CTA
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) best = max(best, __shfl_xor_sync(kFullMask, best, off));
+        if (lane == 0) {
+            const uint32_t r = (uint32_t)ra + (0xffffu - (best & 0xffffu));
+            sh.lm_key[w] = best ? (((unsigned long long)(best >> 16) << 32) | (unsigned long long)(0xffffffffu - r)) : 0ull;
+        }
+        __syncthreads();
+        if (w == 0) {
+            unsigned long long k = lane < NW ? sh.lm_key[lane] : 0ull;
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+                const unsigned long long o = __shfl_xor_sync(kFullMask, k, off);
+                k = o > k ? o : k;
+            }
+            if (lane == 0 && k != 0ull && p.next_ids) atomicMax(p.argkey + (sh.epoch & 1u), k);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ activation staging
+// Residual stream in (embedding row, or H words [tag16 | bf16]), fp32 copy to `res`, and
+// bf16( bf16(x * rsqrt(mean x^2 + eps)) * w ) to `act`.  HF LlamaRMSNorm rounding.
+template <class W, int NW>
+__device__ __forceinline__ void stage_norm(FC<NW>& c, const uint32_t* src_words, uint32_t T, const uint16_t* next_weight,
+                                           bool from_embed, uint4* act, float* res) {
+    constexpr int NT = NW * 32;
+    constexpr int NP = W::H / 4;                    // packets of four values
+    constexpr int PPT = (NP + NT - 1) / NT;
+    const int tid = threadIdx.x;
+    FShared<NW>& sh = c.sh;
+    static_assert(PPT <= 2, "norm weights are carried in two registers pairs per thread");
+    // the norm weights were fetched during the previous phase (c.nwv): nothing here waits for DRAM
+    uint2 wv[PPT];
+#pragma unroll
+    for (int u = 0; u < PPT; ++u) wv[u] = c.nwv[u];
+    float x[PPT][4];
+    if (from_embed) {
+#pragma unroll
+        for (int u = 0; u < PPT; ++u) {
+            const int pk = tid + u * NT;
+            const uint2 e = pk < NP ? __ldg(reinterpret_cast<const uint2*>(c.p.embed + (size_t)sh.tok * W::H) + pk)
+                                    : make_uint2(0u, 0u);
+            x[u][0] = bf16_lo(e.x); x[u][1] = bf16_hi(e.x);
+            x[u][2] = bf16_lo(e.y); x[u][3] = bf16_hi(e.y);
+        }
+    } else {
+        uint4 pkt[PPT];
+        const uint32_t* ptr[PPT];
+#pragma unroll
+        for (int u = 0; u < PPT; ++u) ptr[u] = (tid + u * NT) < NP ? src_words + 4 * (tid + u * NT) : nullptr;
+        poll_packets<PPT>(c, ptr, T, pkt);
+#pragma unroll
+        for (int u = 0; u < PPT; ++u) {
+            x[u][0] = __uint_as_float(pkt[u].x << 16); x[u][1] = __uint_as_float(pkt[u].y << 16);
+            x[u][2] = __uint_as_float(pkt[u].z << 16); x[u][3] = __uint_as_float(pkt[u].w << 16);
+        }
+    }
+    PK_WSTAMP(c, 1);
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < PPT; ++u) {
+        const int pk = tid + u * NT;
+        if (pk < NP) {
+            *reinterpret_cast<float4*>(res + 4 * pk) = make_float4(x[u][0], x[u][1], x[u][2], x[u][3]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ss = fmaf(x[u][j], x[u][j], ss);
+        }
+    }
+    ss = warp_sum(ss);
+    if (c.lane == 0) sh.red[c.warp] = ss;
+    __syncthreads();
+    PK_WSTAMP(c, 2);
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) tot += sh.red[w];
+    const float s = rsqrtf(tot * (1.f / (float)W::H) + c.p.eps);
+#pragma unroll
+    for (int u = 0; u < PPT; ++u) {
+        const int pk = tid + u * NT;
+        if (pk < NP) {
+            const float n0 = round_bf16(__fmul_rn(x[u][0], s)), n1 = round_bf16(__fmul_rn(x[u][1], s));
+            const float n2 = round_bf16(__fmul_rn(x[u][2], s)), n3 = round_bf16(__fmul_rn(x[u][3], s));
+            uint2 o;
+            o.x = pack_bf16x2(__fmul_rn(n0, bf16_lo(wv[u].x)), __fmul_rn(n1, bf16_hi(wv[u].x)));
+            o.y = pack_bf16x2(__fmul_rn(n2, bf16_lo(wv[u].y)), __fmul_rn(n3, bf16_hi(wv[u].y)));
+            reinterpret_cast<uint2*>(act)[pk] = o;
+        }
+    }
+    // weights of the next norm phase: in flight while the phases in between run
+    if (next_weight) {
+#pragma unroll
+        for (int u = 0; u < PPT; ++u) {
+            const int pk = tid + u * NT;
+            if (pk < NP) c.nwv[u] = __ldg(reinterpret_cast<const uint2*>(next_weight) + pk);
+        }
+    }
+    __syncthreads();
+}
+
+// Copy N words [tag16 | bf16] into `act` (input of the down projection).
+template <int N, int NW>
+__device__ __forceinline__ void stage_copy(FC<NW>& c, const uint32_t* src_words, uint32_t T, uint4* act) {
+    constexpr int NT = NW * 32;
+    constexpr int NP = N / 4;
+    constexpr int PPT = (NP + NT - 1) / NT;
+    const int tid = threadIdx.x;
+    uint4 pkt[PPT];
+    const uint32_t* ptr[PPT];
+#pragma unroll
+    for (int u = 0; u < PPT; ++u) ptr[u] = (tid + u * NT) < NP ? src_words + 4 * (tid + u * NT) : nullptr;
+    poll_packets<PPT>(c, ptr, T, pkt);
+    PK_WSTAMP(c, 1);
+#pragma unroll
+    for (int u = 0; u < PPT; ++u) {
+        const int pk = tid + u * NT;
+        if (pk < NP) {
+            uint2 o;
+            o.x = (pkt[u].x & 0xffffu) | (pkt[u].y << 16);
+            o.y = (pkt[u].z & 0xffffu) | (pkt[u].w << 16);
+            reinterpret_cast<uint2*>(act)[pk] = o;
+        }
+    }
+    __syncthreads();
+}
+
+// Input of the O projection: pull the split-KV partials of every (query head, chunk), merge them with
+// log-sum-exp and write the bf16 attention output to `act`.
+template <class W, int NW>
+__device__ __forceinline__ void stage_attn(FC<NW>& c, int layer, uint4* act) {
+    constexpr int NT = NW * 32;
+    constexpr int G = W::G;
+    constexpr int PER_C = W::QH * 33;                       // 16-byte loads per chunk
+    constexpr int PU = (W::NC * PER_C + NT - 1) / NT;       // loads per thread at the most
+    const int tid = threadIdx.x;
+    const int nc = c.sh.nc;
+    const int total = nc * PER_C;
+    const uint32_t tag = tag32(c, layer);
+    const unsigned long long* base = c.p.w_part + (size_t)(layer & 1) * W::KVH * W::NC * G * 66;
+    float* S = c.attn;                                       // [chunk][hq][66]
+    // Gate: one warp waits for the "item published" word of every attention item before anybody touches the
+    // partials, so the lines the item CTAs are writing are not being read by the whole grid in the meantime.
+    // (The gate is only a hint: every partial word still validates itself below.)
+    if (c.warp == 0 && !(c.p.dbg & 4)) {
+        const int nitems = nc * W::KVH;
+        for (int i0 = 0; i0 < nitems; i0 += 32) {
+            const int i = i0 + c.lane;
+            if (i < nitems && !f_aborted(c)) {
+                const unsigned long long* g = c.p.w_gate + (size_t)(layer & 1) * W::KVH * W::NC + i;
+                unsigned spins = 0;
+                while ((uint32_t)(ld_flagged(g) >> 32) != tag) {
+                    if ((++spins & 255u) == 0 && f_give_up(c, spins)) break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (int u0 = 0; u0 < PU; u0 += 4) {
+        if (tid + u0 * NT >= total) break;
+        uint32_t bits[8];
+        const unsigned long long* ptr[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = tid + (u0 + u) * NT;
+            const int ch = i / PER_C, rem = i - ch * PER_C;
+            const int hq = rem / 33, pr = rem - hq * 33;
+            const int kvh = hq / G, g = hq - kvh * G;
+            ptr[u] = i < total ? base + ((size_t)((kvh * W::NC + ch) * G + g)) * 66 + 2 * pr : nullptr;
+        }
+        poll_flagged_pairs<4>(c, ptr, tag, bits);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = tid + (u0 + u) * NT;
+            if (i < total) {
+                const int hc = i / 33, pr = i - hc * 33;     // [chunk][hq] flattened: same order as the decode above
+                *reinterpret_cast<float2*>(S + hc * 66 + 2 * pr) =
+                    make_float2(__uint_as_float(bits[2 * u]), __uint_as_float(bits[2 * u + 1]));
+            }
+        }
+    }
+    PK_WSTAMP(c, 1);
+    __syncthreads();
+    PK_WSTAMP(c, 2);
+    uint16_t* act16 = reinterpret_cast<uint16_t*>(act);
+    for (int o = tid; o < W::AD; o += NT) {
+        const int hq = o / kD, d = o - hq * kD;
+        const float* src = S + hq * 66;
+        // all shared-memory loads first (one round of latency), then the arithmetic
+        float mv[W::NC], lv[W::NC], av[W::NC];
+#pragma unroll
+        for (int ch = 0; ch < W::NC; ++ch) {
+            const bool ok = ch < nc;
+            const float* sc = src + ch * W::QH * 66;
+            mv[ch] = ok ? sc[0] : -INFINITY;
+            lv[ch] = ok ? sc[1] : 0.f;
+            av[ch] = ok ? sc[2 + d] : 0.f;
+        }
+        float M = mv[0];       // chunk 0 always holds at least one position
+#pragma unroll
+        for (int ch = 1; ch < W::NC; ++ch) M = fmaxf(M, mv[ch]);
+        float den = 0.f, a = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < W::NC; ++ch) {
+            const float wgt = __expf(mv[ch] - M);      // exp(-inf) = 0 for empty / absent chunks
+            den = fmaf(lv[ch], wgt, den);
+            a = fmaf(av[ch], wgt, a);
+        }
+        act16[o] = (uint16_t)f32_to_bf16_bits(__fdividef(a, den));
+    }
+    __syncthreads();
+}
+
+// ------------------------------------------------------------------ attention item
+// One CTA = one (kv head, chunk) item over cache positions [start, end); its warps split the chunk into
+// runs of 16 positions.  Scores: lane = (position, half of the head dim); P.V: lane = two output dims.
+// All K and V loads of the first run are issued before the new token's q/k/v words are waited for.
+template <class W, int NW>
+__device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
+    constexpr int G = W::G;
+    constexpr int NT = NW * 32;
+    const FastParams& p = c.p;
+    FShared<NW>& sh = c.sh;
+    const int lane = c.lane, tid = threadIdx.x;
+    const int kvh = sh.item_kvh, chunk = sh.item_chunk;
+    const int seq = sh.seq;
+    const int start = chunk * sh.lc;
+    const int end = min(start + sh.lc, seq);
+    const int ppw = (((end - start + NW - 1) / NW) + 15) & ~15;
+    const int ws = min(start + c.warp * ppw, end);
+    const int we = min(ws + ppw, end);
+    const bool pre_ok = ppw <= kPre * 16;        // every run's offsets were resolved at kernel start
+    const uint16_t* kvr = reinterpret_cast<const uint16_t*>(layer < kKvPtrs ? sh.kv_ptr[layer] : __ldg(p.kv + layer));
+    const long long hs = (long long)kvh * p.head_stride;
+    const int pl = lane >> 1, half = lane & 1;
+
+    constexpr int kPartWords = (NW * G * 66 + 3) & ~3;
+    uint32_t* qkvb_s = reinterpret_cast<uint32_t*>(c.attn + kPartWords);       // [(G+2)*32] packed bf16: rotated q, k; v
+    float* prob_s = reinterpret_cast<float*>(qkvb_s + (G + 2) * 32) + c.warp * G * 16;
+
+    uint4 kq[4];
+    uint32_t vw[16];
+    auto fetch_run = [&](int r0) {
+        long long* offs = sh.kv_off[c.warp] + (((r0 - ws) >> 4) & (kPre - 1)) * 16;
+        if (!pre_ok) {
+            // long context: resolve this run's block-table entries now (lanes 0..15, one position each)
+            if (lane < 16) {
+                const int pp = r0 + lane;
+                long long off = -1;
+                if (pp < we) {
+                    const int blk = __ldg(p.block_table + pp / p.block_size);
+                    off = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride;
+                }
+                offs[lane] = off;
+            }
+            __syncwarp();
+        }
+        const int pp = r0 + pl;
+        const bool own_ok = pp < we && pp != seq - 1;
+        const long long e_own = own_ok ? offs[pl] + hs : 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            kq[i] = own_ok ? __ldcg(reinterpret_cast<const uint4*>(kvr + p.k_off + e_own + 32 * half) + i)
+                           : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int pj = r0 + j;
+            const bool ok = pj < we && pj != seq - 1;
+            vw[j] = ok ? __ldcg(reinterpret_cast<const uint32_t*>(kvr + p.v_off + offs[j] + hs) + lane) : 0u;
+        }
+        if (!pre_ok) __syncwarp();
+    };
+    if (c.prof) c.prof[10] = global_ns();
+    float m[G], l[G], acc[G][2];
+#pragma unroll
+    for (int hh = 0; hh < G; ++hh) {
+        m[hh] = -INFINITY;
+        l[hh] = 0.f;
+        acc[hh][0] = acc[hh][1] = 0.f;
+    }
+    // One loop over the warp's runs with a single site for the K/V loads; the first iteration (executed by
+    // every warp, also one without positions) contains the CTA-wide part: wait for the new token's q/k/v,
+    // rotate, append.  The K/V loads of the first run are therefore issued before that wait.
+    int r0 = ws;
+#pragma unroll 1
+    do {
+        if (r0 < we) fetch_run(r0);
+        if (r0 == ws) {
+            // rotated q of the G heads of this kv head, then rotated k and v of the new token: (G + 2) * 16 packets
+            {
+                const uint32_t* qkv = p.w_qkv + (layer & 1) * W::NQKV;
+                uint4 pkt[1];
+                const int which = tid >> 4, d4 = (tid & 15) * 4;
+                const int qrow = which < G ? (kvh * G + which) * kD : (which == G ? (W::QH + kvh) * kD : (W::QH + W::KVH + kvh) * kD);
+                const uint32_t* ptr[1] = {tid < (G + 2) * 16 ? qkv + qrow + d4 : nullptr};
+                poll_packets<1>(c, ptr, tag16(c, layer), pkt);
+                if (tid < (G + 2) * 16)
+                    *reinterpret_cast<uint2*>(qkvb_s + 2 * tid) =
+                        make_uint2((pkt[0].x & 0xffffu) | (pkt[0].y << 16), (pkt[0].z & 0xffffu) | (pkt[0].w << 16));
+            }
+            __syncthreads();
+            if (c.prof) c.prof[12] = global_ns();
+            // the item that holds position seq-1 appends the new token's K/V to the paged cache (slot -1: skip)
+            if (end == seq && c.warp == 0 && lane < 16 && sh.slot_off >= 0) {
+                uint16_t* kvw = const_cast<uint16_t*>(kvr);
+                const int l8 = lane & 7;
+                const long long e = sh.slot_off + hs + 8 * l8;
+                if (lane < 8) *reinterpret_cast<uint4*>(kvw + p.k_off + e) = *reinterpret_cast<const uint4*>(qkvb_s + G * 32 + 4 * l8);
+                else *reinterpret_cast<uint4*>(kvw + p.v_off + e) = *reinterpret_cast<const uint4*>(qkvb_s + (G + 1) * 32 + 4 * l8);
+            }
+        }
+        if (r0 < we) {
+            const int pp = r0 + pl;
+            const bool valid = pp < we;
+            uint32_t kwd[16];
+            if (pp == seq - 1) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint4 t4 = *reinterpret_cast<const uint4*>(qkvb_s + G * 32 + 16 * half + 4 * i);
+                    kwd[4 * i] = t4.x; kwd[4 * i + 1] = t4.y; kwd[4 * i + 2] = t4.z; kwd[4 * i + 3] = t4.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    kwd[4 * i] = kq[i].x; kwd[4 * i + 1] = kq[i].y; kwd[4 * i + 2] = kq[i].z; kwd[4 * i + 3] = kq[i].w;
+                }
+            }
+            float pr[G];
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) {
+                float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint4 q4 = *reinterpret_cast<const uint4*>(qkvb_s + hh * 32 + 16 * half + 4 * i);
+                    d0 = fma2_bf16(kwd[4 * i], q4.x, d0);
+                    d1 = fma2_bf16(kwd[4 * i + 1], q4.y, d1);
+                    d0 = fma2_bf16(kwd[4 * i + 2], q4.z, d0);
+                    d1 = fma2_bf16(kwd[4 * i + 3], q4.w, d1);
+                }
+                float dsum = d0 + d1;
+                dsum += __shfl_xor_sync(kFullMask, dsum, 1);
+                // bf16 matmul output, then the exact 1/8 scale (HF eager_attention_forward)
+                const float sc = valid ? round_bf16(dsum) * 0.125f : -INFINITY;
+                float mx = sc;
+#pragma unroll
+                for (int o = 2; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(kFullMask, mx, o));
+                const float mn = fmaxf(m[hh], mx);
+                const float alpha = (mn == -INFINITY) ? 1.f : __expf(m[hh] - mn);
+                pr[hh] = (sc == -INFINITY) ? 0.f : __expf(sc - mn);
+                float ps = pr[hh];
+#pragma unroll
+                for (int o = 2; o < 32; o <<= 1) ps += __shfl_xor_sync(kFullMask, ps, o);
+                l[hh] = l[hh] * alpha + ps;
+                m[hh] = mn;
+                acc[hh][0] *= alpha;
+                acc[hh][1] *= alpha;
+                if (half == 0) prob_s[hh * 16 + pl] = pr[hh];
+            }
+            __syncwarp();
+            const uint32_t vnew = qkvb_s[(G + 1) * 32 + lane];
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) {
+                float a0 = acc[hh][0], a1 = acc[hh][1];
+#pragma unroll
+                for (int j4 = 0; j4 < 4; ++j4) {
+                    const float4 p4 = *reinterpret_cast<const float4*>(prob_s + hh * 16 + 4 * j4);
+                    const float pj[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        const int j = 4 * j4 + jj;
+                        const uint32_t v = (r0 + j == seq - 1) ? vnew : vw[j];
+                        a0 = fmaf(pj[jj], bf16_lo(v), a0);
+                        a1 = fmaf(pj[jj], bf16_hi(v), a1);
+                    }
+                }
+                acc[hh][0] = a0;
+                acc[hh][1] = a1;
+            }
+            __syncwarp();
+        }
+        r0 += 16;
+    } while (r0 < we);
+    if (c.prof) c.prof[13] = global_ns();
+    // park the warp's partial: lanes hold two dims each
+    float* wpart = c.attn + c.warp * G * 66;
+#pragma unroll
+    for (int hh = 0; hh < G; ++hh) {
+        float* dst = wpart + hh * 66;
+        if (lane == 0) {
+            dst[0] = m[hh];
+            dst[1] = l[hh];
+        }
+        *reinterpret_cast<float2*>(dst + 2 + 2 * lane) = make_float2(acc[hh][0], acc[hh][1]);
+    }
+    __syncthreads();
+    if (c.prof) c.prof[14] = global_ns();
+    // combine the warps; thread (hh, d) publishes one accumulator word, d == 0 also m and l
+    unsigned long long* part =
+        p.w_part + ((size_t)(layer & 1) * W::KVH * W::NC + (size_t)(kvh * W::NC + chunk)) * G * 66;
+    const uint32_t tag = tag32(c, layer);
+    for (int t = tid; t < G * kD; t += NT) {
+        const int hh = t / kD, d = t % kD;
+        float M = -INFINITY;
+#pragma unroll 4
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, c.attn[(w * G + hh) * 66]);
+        float lt = 0.f, a = 0.f;
+#pragma unroll 4
+        for (int w = 0; w < NW; ++w) {
+            const float* src = c.attn + (w * G + hh) * 66;
+            const float f = (src[0] == -INFINITY) ? 0.f : __expf(src[0] - M);
+            lt = fmaf(src[1], f, lt);
+            a = fmaf(src[2 + d], f, a);
+        }
+        unsigned long long* dst = part + hh * 66;
+        if (d == 0) {
+            st_flagged(dst + 0, __float_as_uint(M), tag);
+            st_flagged(dst + 1, __float_as_uint(lt), tag);
+        }
+        st_flagged(dst + 2 + d, __float_as_uint(a), tag);
+    }
+    __syncthreads();     // c.attn is reused by the merge staging
+    // item index = chunk * KVH + kvh (the CTA index)
+    if (tid == 0) st_flagged(p.w_gate + (size_t)(layer & 1) * W::KVH * W::NC + chunk * W::KVH + kvh, 1u, tag);
+    if (c.prof) c.prof[15] = global_ns();
+}
+
+// L2 prefetch of this CTA's chunk (K and V rows of the positions resolved at kernel start).
+template <class W, int NW>
+__device__ __forceinline__ void attention_prefetch(FC<NW>& c, int layer) {
+    const FastParams& p = c.p;
+    FShared<NW>& sh = c.sh;
+    const unsigned char* kvr = reinterpret_cast<const unsigned char*>(layer < kKvPtrs ? sh.kv_ptr[layer] : __ldg(p.kv + layer));
+    const long long hs = (long long)sh.item_kvh * p.head_stride;
+    for (int t = (int)threadIdx.x; t < NW * kPre * 32; t += NW * 32) {
+        const long long off = sh.kv_off[t / (kPre * 32)][(t % (kPre * 32)) >> 1];
+        if (off >= 0) {
+            const long long e = off + hs;
+            const unsigned char* a = kvr + ((t & 1) ? p.v_off + e : p.k_off + e) * 2;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+        }
+    }
+}
+
+// ------------------------------------------------------------------ the kernel
+template <class W, int NW>
+__global__ void __launch_bounds__(NW * 32, 1) decode_fast_kernel(const FastParams p) {
+    constexpr int NT = NW * 32;
+    constexpr int G = W::G;
+    constexpr int ACT = W::H > W::I ? W::H : W::I;
+    constexpr int kAttnWords = (W::NC * W::QH * 66) > (((NW * G * 66 + 3) & ~3) + (G + 2) * kD + (G + 2) * 32 + NW * G * 16)
+                                   ? (W::NC * W::QH * 66)
+                                   : (((NW * G * 66 + 3) & ~3) + (G + 2) * kD + (G + 2) * 32 + NW * G * 16);
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    FShared<NW>& sh = *reinterpret_cast<FShared<NW>*>(smem_raw);
+    size_t off = (sizeof(FShared<NW>) + 127) & ~size_t(127);
+    uint4* act0 = reinterpret_cast<uint4*>(smem_raw + off);
+    off += ((size_t)ACT * 2 + 127) & ~size_t(127);
+    uint4* act1 = reinterpret_cast<uint4*>(smem_raw + off);
+    off += ((size_t)ACT * 2 + 127) & ~size_t(127);
+    float* res0 = reinterpret_cast<float*>(smem_raw + off);
+    off += ((size_t)W::H * 4 + 127) & ~size_t(127);
+    float* res1 = reinterpret_cast<float*>(smem_raw + off);
+    off += ((size_t)W::H * 4 + 127) & ~size_t(127);
+    float* attn = reinterpret_cast<float*>(smem_raw + off);
+    off += ((size_t)kAttnWords * 4 + 127) & ~size_t(127);
+    unsigned char* ring_base = smem_raw + off;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cta = blockIdx.x, ncta = gridDim.x;
+
+    if (tid == 0) {
+        sh.abort_flag = (p.ctrl[kCtrlStatus] != 0u) ? 1 : 0;     // an earlier failure on this workspace: fall through
+        sh.epoch = p.fctrl[kFctrlEpoch];
+        const int seq = min(max(p.seq_lens[0], 1), p.max_seq_len);
+        if (p.seq_lens[0] > p.max_seq_len) {
+            sh.abort_flag = 1;
+            atomicCAS(p.ctrl + kCtrlStatus, 0u, (unsigned)kErrMaxSeq);
+        }
+        sh.seq = seq;
+        sh.pos = (int)max(p.positions[0], 0LL);
+        const long long tok = p.ids_i64 ? reinterpret_cast<const long long*>(p.input_ids)[0]
+                                        : (long long)reinterpret_cast<const int*>(p.input_ids)[0];
+        sh.tok = tok < 0 ? 0 : (tok >= p.V ? p.V - 1 : tok);      // an out-of-range id must not become a wild read
+        const long long slot = p.slot_mapping[0];
+        sh.slot_off = slot < 0 ? -1 : (slot / p.block_size) * p.block_stride + (slot % p.block_size) * p.token_stride;
+        // split-KV: one run of 16 positions per warp while that needs at most W::NC chunks, longer chunks beyond
+        int nc = (seq + NW * 16 - 1) / (NW * 16);
+        nc = nc < 1 ? 1 : (nc > W::NC ? W::NC : nc);
+        const int lc = (((seq + nc - 1) / nc) + 15) & ~15;
+        sh.lc = lc;
+        sh.nc = (seq + lc - 1) / lc;
+        const bool has = cta < sh.nc * W::KVH;
+        sh.item_kvh = has ? cta % W::KVH : -1;
+        sh.item_chunk = has ? cta / W::KVH : 0;
+    }
+    if (tid < NW * kFE) {
+        mbar_init(&sh.full[tid / kFE][tid % kFE], 1);
+        sh.ent_off[tid / kFE][tid % kFE] = 0u;
+        sh.ent_foot[tid / kFE][tid % kFE] = 0u;
+    }
+    for (int l = tid; l < p.L && l < kKvPtrs; l += NT) sh.kv_ptr[l] = p.kv[l];
+    for (int i = tid; i < 4 * p.L; i += NT) {
+        const int l = i >> 2, m = i & 3;
+        sh.mat_ptr[l][m] = p.layers[l * 6 + (m == 0 ? 1 : (m == 1 ? 2 : (m == 2 ? 4 : 5)))];
+    }
+    for (int i = tid; i <= 2 * p.L; i += NT)
+        sh.norm_ptr[i] = i == 2 * p.L ? reinterpret_cast<unsigned long long>(p.final_norm) : p.layers[(i >> 1) * 6 + ((i & 1) ? 3 : 0)];
+    if (tid < kNumPhaseTypes * NW) {
+        const int t = tid / NW, w = tid % NW;
+        // units: QKV row pairs (d, d + 32), gate/up row pairs, single rows elsewhere
+        const int nrows = t == kQKV ? W::NQKV / 2 : (t == kGU ? W::I : (t == kLM ? (p.lm_head ? p.V : 0) : W::H));
+        int a = 0, b = 0;
+        warp_share<NW>(nrows, cta, ncta, w, a, b);
+        sh.row_a[t][w] = a;
+        sh.row_b[t][w] = b;
+    }
+    if (tid >= 64 && tid < 128) {
+        const int j = tid - 64;
+        const long long pos = max(p.positions[0], 0LL);
+        sh.cs[j] = p.cs_fp32 ? __ldg(reinterpret_cast<const float*>(p.cos_sin) + pos * kD + j)
+                             : __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(p.cos_sin) + pos * kD + j) << 16);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+
+    FC<NW> c{p, sh, {act0, act1}, {res0, res1}, attn, ring_base + (size_t)warp * p.ring_bytes, 0u, 0u, warp, lane, cta, ncta,
+             0u, 0u, 0u, 0u, 0, -1, 0, {make_uint2(0u, 0u), make_uint2(0u, 0u)}, nullptr
+#ifdef PK_FAST_WPROF
+             , nullptr
+#endif
+    };
+    c.T16 = ((sh.epoch % 511u) + 1u) << 23;
+    c.T32 = (sh.epoch + 1u) << 7;
+    const uint64_t pol = evict_first_policy();
+    // start the weight stream before anything else
+    cursor_next_phase(c);
+    issue_more<W, NW>(c, pol);
+
+    // block-table look-ups of this CTA's attention item do not depend on the layer: resolve them once
+    {
+        int ws = 0, we = 0;
+        if (sh.item_kvh >= 0) {
+            const int start = sh.item_chunk * sh.lc;
+            const int end = min(start + sh.lc, sh.seq);
+            const int ppw = (((end - start + NW - 1) / NW) + 15) & ~15;
+            ws = min(start + warp * ppw, end);
+            we = min(ws + ppw, end);
+        }
+        for (int j = lane; j < kPre * 16; j += 32) {
+            long long o = -1;
+            const int pp = ws + j;
+            if (pp < we) {
+                const int blk = p.block_table[pp / p.block_size];
+                o = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride;
+            }
+            sh.kv_off[warp][j] = o;
+        }
+    }
+    // reset the argmax cell the *next* launch will use
+    if (cta == 0 && tid == 0) p.argkey[(sh.epoch + 1u) & 1u] = 0ull;
+    // norm weights of the first norm phase (every later phase fetches the next one's ahead of time)
+    {
+        constexpr int NP = W::H / 4;
+        const uint2* nw0 = reinterpret_cast<const uint2*>(sh.norm_ptr[0]);
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            if (tid + u * NT < NP) c.nwv[u] = __ldg(nw0 + tid + u * NT);
+    }
+    __syncthreads();
+
+    // One loop over the global phase index (4 per layer, then the final norm + lm_head) with a single call
+    // site for every building block, so each exists once in the instruction stream.
+    const int nph = p.L * 4 + 1;
+#pragma unroll 1
+    for (int gp = 0; gp < nph; ++gp) {
+        const int layer = gp >> 2;
+        const bool last = gp == nph - 1;
+        const int t = last ? (int)kLM : (gp & 3);
+        if (last && !(p.lm_head || cta == 0)) break;
+        const int par = layer & 1;
+        unsigned long long* prof = nullptr;
+        if (p.profile && tid == 0 && !last) prof = p.profile + ((size_t)cta * p.L + layer) * kProfSlots;
+        c.prof = prof;
+        uint4* act = (t == kO || t == kDown) ? act1 : act0;
+        const float* res = (t == kGU || t == kDown) ? res1 : res0;
+#ifdef PK_FAST_WPROF
+        c.wprof = (p.profile && lane == 0 && layer == kWprofLayer && !last)
+                      ? p.profile + (size_t)ncta * p.L * kProfSlots + ((size_t)(cta * NW + warp) * 4 + t) * 8
+                      : nullptr;
+        PK_WSTAMP(c, 0);
+#endif
+        if (t == kQKV || t == kGU || last) {
+            if (t == kQKV) {
+                if (prof) prof[0] = global_ns();
+                if (sh.item_kvh >= 0) attention_prefetch<W, NW>(c, layer);
+            }
+            // RMSNorm: input norm (x -> res0), post-attention norm (h1 -> res1) or the final norm
+            const uint32_t* src = (t == kGU ? p.w_h1 : p.w_x) + par * W::H;
+            const int ni = 2 * layer + (t == kGU ? 1 : 0);          // index of this norm; the next one is fetched now
+            const uint16_t* next_w = ni < 2 * p.L ? reinterpret_cast<const uint16_t*>(sh.norm_ptr[ni + 1]) : nullptr;
+            stage_norm<W, NW>(c, src, tag16(c, layer), next_w, gp == 0, act0, t == kGU ? res1 : res0);
+        } else if (t == kO) {
+            if (sh.item_kvh >= 0) attention_item<W, NW>(c, layer);
+            if (prof) prof[3] = global_ns();
+            stage_attn<W, NW>(c, layer, act1);
+        } else {
+            stage_copy<W::I, NW>(c, p.w_act + par * W::I, tag16(c, layer), act1);
+        }
+        if (prof) prof[1 + 2 * t + (t >= kO ? 1 : 0)] = global_ns();     // slots 1, 4, 6, 8
+        PK_WSTAMP(c, 3);
+        if (last) {
+            if (cta == 0)
+                for (int i = tid; i < W::H / 2; i += NT)
+                    reinterpret_cast<uint32_t*>(p.out_hidden)[i] = reinterpret_cast<const uint32_t*>(act0)[i];
+            if (!p.lm_head) break;
+        }
+        gemv_phase<W, NW>(c, t, layer, act, res, pol);
+        // Nobody in this CTA polls the next hand-off before the CTA's own results are on their way: reads of a
+        // line that is still being written slow the writes down (measured: several microseconds per hand-off
+        // when the warps without rows in a phase started polling at once).
+        if (!(p.dbg & 1)) __syncthreads();
+        if (prof) prof[2 + 2 * t + (t >= kO ? 1 : 0)] = global_ns();     // slots 2, 5, 7, 9
+        PK_WSTAMP(c, 6);
+    }
+
+    // never leave while bulk copies into this CTA's shared memory are in flight (only after an abort)
+    for (uint32_t n = c.consumed; n < c.issued; ++n) {
+        const uint32_t slot = n % kFE;
+        unsigned spins = 0;
+        while (!mbar_probe(&sh.full[warp][slot], (n / kFE) & 1))
+            if (++spins >= p.spin_limit) break;
+    }
+    __syncthreads();
+    // The last CTA to finish publishes the greedy id, optionally advances the step inputs in place
+    // (device-driven generation), and opens the next launch's epoch.
+    if (tid == 0) {
+        __threadfence();
+        const unsigned prev = atomicAdd(p.fctrl + kFctrlDone, 1u);
+        if (prev == (unsigned)ncta - 1u) {
+            __threadfence();
+            const bool ok = *((volatile unsigned int*)(p.ctrl + kCtrlStatus)) == 0;
+            if (p.next_ids && p.lm_head && ok) {
+                const unsigned long long key = *((volatile unsigned long long*)(p.argkey + (sh.epoch & 1u)));
+                const long long id = (long long)(0xffffffffu - (uint32_t)key);
+                p.next_ids[0] = id;
+                if (p.advance) {
+                    if (p.ids_i64) reinterpret_cast<long long*>(const_cast<void*>(p.input_ids))[0] = id;
+                    else reinterpret_cast<int*>(const_cast<void*>(p.input_ids))[0] = (int)id;
+                    const long long np = p.positions[0] + 1;
+                    const_cast<long long*>(p.positions)[0] = np;
+                    const_cast<int*>(p.seq_lens)[0] = p.seq_lens[0] + 1;
+                    if (p.slot_mapping[0] >= 0 && np < (long long)p.max_seq_len) {
+                        const long long blk = p.block_table[(int)(np / p.block_size)];
+                        const_cast<long long*>(p.slot_mapping)[0] = blk * p.block_size + np % p.block_size;
+                    }
+                }
+            }
+            p.fctrl[kFctrlDone] = 0u;
+            p.fctrl[kFctrlEpoch] = sh.epoch + 1u;
+            __threadfence();
+        }
+    }
+}
+
+}  // namespace fast
+}  // namespace pk

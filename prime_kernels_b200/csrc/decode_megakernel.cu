@@ -10,9 +10,9 @@
 //  * Weight streaming is decoupled from the dependency chain.  Weights do not depend on
 //    activations, so a producer warp runs ahead of the math through the whole step and keeps
 //    ~190 KB of weights per SM in flight / staged in shared memory with bulk async copies
-//    (cp.async.bulk + mbarrier complete_tx, L2 evict-first).  Each of the 16 consumer warps owns a
+//    (cp.async.bulk + mbarrier complete_tx, L2 evict-first).  Each of the kNW (7) consumer warps owns a
 //    private single-producer/single-consumer byte ring; one producer lane serves each ring, and
-//    the 16 lanes advance in lock step so copy issue is 16-way parallel.  The row -> CTA -> warp
+//    the lanes advance in lock step so copy issue is kNW-way parallel.  The row -> CTA -> warp
 //    schedule is a pure function of the geometry, evaluated identically on both sides.
 //  * There is no grid barrier.  Activations cross CTAs through "flagged word" buffers in L2:
 //    every 64-bit word carries 32 bits of payload and a 32-bit tag (launch epoch, layer), written
@@ -32,6 +32,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -56,7 +57,7 @@ constexpr int kNormRegs = 10;              // norm weights held per thread: hidd
 constexpr int kDirectWords = 2048;         // direct-merge limit: partial words every CTA stages per layer
 constexpr int kAttnScratchWords = 3072;        // staged partials + merge weights; also >= kNW * 4 * 66 + staging
 constexpr int kMaxLayers = 120;
-constexpr unsigned kSpinLimit = 1u << 22;  // bounded waits: ~1-2 s of L2 polling
+constexpr unsigned kSpinLimit = 1u << 22;  // default bound of every device-side wait: ~1-2 s of L2 polling
 
 enum PhaseType { kQKV = 0, kO = 1, kGU = 2, kDown = 3, kLM = 4, kNumPhaseTypes = 5 };
 
@@ -112,6 +113,7 @@ struct DecodeParams {
     int max_seq_len;
     int ring_bytes;                     // per consumer warp
     int act_elems;                      // max(H, I)
+    unsigned spin_limit;                // bound of every device-side wait (polling rounds)
     float eps;
     PhaseDesc ph[kNumPhaseTypes];
 };
@@ -210,7 +212,7 @@ __device__ __forceinline__ uint32_t wait_flagged(Ctx& c, const unsigned long lon
                 c.sh.abort_flag = 1;
                 return 0;
             }
-            if (spins >= kSpinLimit) {
+            if (spins >= c.p.spin_limit) {
                 raise_abort(c, kErrBarrierTimeout);
                 return 0;
             }
@@ -249,7 +251,7 @@ __device__ __forceinline__ void wait_flagged_multi(Ctx& c, PtrFn ptr, uint32_t t
                 c.sh.abort_flag = 1;
                 return;
             }
-            if (spins >= kSpinLimit) {
+            if (spins >= c.p.spin_limit) {
                 raise_abort(c, kErrBarrierTimeout);
                 return;
             }
@@ -272,7 +274,7 @@ __device__ __forceinline__ bool wait_mbar(Ctx& c, uint64_t* bar, uint32_t parity
     while (!mbar_test(bar, parity)) {
         if ((++spins & 255u) == 0) {
             if (aborted(c)) return false;
-            if (spins >= kSpinLimit) {
+            if (spins >= c.p.spin_limit) {
                 raise_abort(c, kErrBarrierTimeout);
                 return false;
             }
@@ -391,7 +393,7 @@ __device__ void producer_loop(Ctx& c, unsigned char* ring_base) {
         // nothing to retire or issue: yield the issue slots to the consumer warp that shares this scheduler
         if (!__any_sync(kFullMask, progressed)) __nanosleep(kProducerIdleNs);
         if ((idle & 255u) == 255u) {
-            if (idle >= kSpinLimit) raise_abort(c, kErrBarrierTimeout);
+            if (idle >= c.p.spin_limit) raise_abort(c, kErrBarrierTimeout);
         }
         if (__any_sync(kFullMask, aborted(c))) break;
     }
@@ -401,7 +403,7 @@ __device__ void producer_loop(Ctx& c, unsigned char* ring_base) {
             const uint32_t slot = n % kE;
             unsigned spins = 0;
             while (!mbar_probe(&sh.full[w][slot], (n / kE) & 1)) {
-                if (++spins >= kSpinLimit) break;
+                if (++spins >= c.p.spin_limit) break;
             }
         }
     }
@@ -593,7 +595,7 @@ __device__ void gemv_phase(Ctx& c, const int T, int layer, uint32_t& consumed) {
             for (int b = 0; b < B; ++b) acc[i][b] = acc2[i][b] = 0.f;
         for (int seg = 0; seg < d.nseg; ++seg) {
             const uint32_t slot = consumed % kE;
-            if (!wait_mbar(c, &sh.full[w][slot], (consumed / kE) & 1)) return;
+            if (!__all_sync(kFullMask, wait_mbar(c, &sh.full[w][slot], (consumed / kE) & 1))) return;
             if (T == kGU && c.prof) c.prof[16] = global_ns();
             const uint4* ep = reinterpret_cast<const uint4*>(c.ring + sh.ent_off[w][slot]);
             // accumulator r <- staged row r; a gate/up entry stages nre gate rows, then nre up rows
@@ -1438,7 +1440,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
     const int cta = blockIdx.x, ncta = gridDim.x;
 
     if (tid == 0) {
-        sh.abort_flag = 0;
+        sh.abort_flag = (p.ctrl[kCtrlStatus] != 0u) ? 1 : 0;   // an earlier failure on this workspace: fall through
         sh.epoch = p.ctrl[kCtrlEpoch];
     }
     if (tid < kNW * kE) {
@@ -1457,12 +1459,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
     if (tid < B) {
         // padding rows (batch 5..7 run on the batch-8 kernel) mirror the last real request and write nothing
         const int src = min(tid, p.nb - 1);
-        const int seq = max(p.seq_lens[src], 1);
+        // a sequence length beyond the block table's capacity would index past its row: clamp and report
+        const int seq = min(max(p.seq_lens[src], 1), p.max_seq_len);
         sh.seq[tid] = seq;
         sh.pos[tid] = (int)max(p.positions[src], 0LL);
         sh.slot[tid] = tid < p.nb ? p.slot_mapping[src] : -1LL;
-        sh.tok[tid] = p.ids_i64 ? reinterpret_cast<const long long*>(p.input_ids)[src]
-                                : (long long)reinterpret_cast<const int*>(p.input_ids)[src];
+        const long long tok = p.ids_i64 ? reinterpret_cast<const long long*>(p.input_ids)[src]
+                                        : (long long)reinterpret_cast<const int*>(p.input_ids)[src];
+        sh.tok[tid] = tok < 0 ? 0 : (tok >= p.V ? p.V - 1 : tok);   // an out-of-range id must not become a wild read
         // Split-KV chunking: one CTA per (request, kv head, chunk) item.  The chunk length is the
         // shortest multiple of 16 positions, at least one 16-position run per warp, that keeps the
         // number of items within one round of the grid (and the chunks per request within kNCMax);
@@ -1472,7 +1476,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
         // and publishes the result (two hand-offs, but no redundant staging).  The mode is decided on
         // the longest request so it is CTA-uniform.
         int smax = 1;
-        for (int bb = 0; bb < p.nb; ++bb) smax = max(smax, max(p.seq_lens[bb], 1));
+        for (int bb = 0; bb < p.nb; ++bb) smax = max(smax, min(max(p.seq_lens[bb], 1), p.max_seq_len));
         const int nct = min(max(ncta / (B * p.KVH), 1), kNCMax);
         const int lc = max(16 * kNW, (((smax + nct - 1) / nct) + 15) & ~15);
         const int two = (B * p.QH * ((smax + lc - 1) / lc) * 66 > kDirectWords) ? 1 : 0;
@@ -1485,6 +1489,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
+    if (tid == 0) {
+        for (int bb = 0; bb < p.nb; ++bb)
+            if (p.seq_lens[bb] > p.max_seq_len) {
+                sh.abort_flag = 1;
+                atomicCAS(p.ctrl + kCtrlStatus, 0u, (unsigned)kErrMaxSeq);
+            }
+    }
     if (warp < kNW) {
         // The block-table look-ups of an attention item do not depend on the layer: resolve them once per
         // launch for this CTA's first item (the only one at moderate contexts), so that a layer's K/V loads
@@ -1559,7 +1570,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
         producer_loop(c, ring_base);
     } else {
         // reset the argmax cells the *next* launch will use
-        if (cta == 0 && tid < kMaxB && p.next_ids) p.argkey[(size_t)((sh.epoch + 1u) & 1u) * kMaxB + tid] = 0ull;
+        // (unconditionally: a launch without next_ids must not leave an older launch's keys behind)
+        if (cta == 0 && tid < kMaxB) p.argkey[(size_t)((sh.epoch + 1u) & 1u) * kMaxB + tid] = 0ull;
         uint32_t consumed = 0;
         // One loop over the global phase index (4 per layer, then the lm_head) with a single call site
         // for every building block, so each is instantiated once and the instruction footprint of a
@@ -1643,6 +1655,26 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
 }
 
 
+}  // namespace pk
+#include "decode_fast.cuh"
+namespace pk {
+
+// One-CTA helper for tests of the failure path: polls a flagged word that nothing writes with the same
+// bounded wait the decode kernels use; the wait runs out after `spin_limit` rounds and the status word
+// of the workspace receives kErrBarrierTimeout.  It cannot hang.
+__global__ void wait_probe_kernel(unsigned int* ctrl, const unsigned long long* never_written, unsigned spin_limit) {
+    unsigned spins = 0;
+    const uint32_t tag = 0xfffffff1u;       // no launch produces this tag
+    for (;;) {
+        const unsigned long long v = ld_flagged(never_written);
+        if ((uint32_t)(v >> 32) == tag) return;
+        if (++spins >= spin_limit) {
+            atomicCAS(ctrl + kCtrlStatus, 0u, (unsigned)kErrBarrierTimeout);
+            return;
+        }
+    }
+}
+
 // ------------------------------------------------------------------ host side
 struct ModelGeom {
     int H, I, L, QH, KVH, V, wfmt;
@@ -1650,10 +1682,41 @@ struct ModelGeom {
 };
 
 struct WsLayout {
-    size_t ctrl, argkey, x, qkv, attn, h1, act, part, total;
+    size_t ctrl, argkey, x, qkv, attn, h1, act, part, fast, total;
+};
+// Region of the batch-1 fast kernel (its own words; never shared with the generic kernel's buffers).
+struct FastLayout {
+    size_t fctrl, argkey, x, qkv, h1, act, part, gate, total;
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static int fast_nc(const ModelGeom& g) {
+    const int nc = fast::kNominalCtas / (g.KVH > 0 ? g.KVH : 1);
+    return nc < 6 ? nc : 6;
+}
+
+static FastLayout fast_layout(const ModelGeom& g) {
+    FastLayout l{};
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t at = off;
+        off += align_up(bytes, 256);
+        return at;
+    };
+    const size_t nqkv = (size_t)(g.QH + 2 * g.KVH) * kD;
+    const int G = g.QH / (g.KVH > 0 ? g.KVH : 1);
+    l.fctrl = take(256);
+    l.argkey = take(256);
+    l.x = take(2 * (size_t)g.H * 4);
+    l.qkv = take(2 * nqkv * 4);
+    l.h1 = take(2 * (size_t)g.H * 4);
+    l.act = take(2 * (size_t)g.I * 4);
+    l.part = take(2 * (size_t)g.KVH * fast_nc(g) * G * 66 * 8);
+    l.gate = take(2 * (size_t)g.KVH * fast_nc(g) * 8);
+    l.total = off;
+    return l;
+}
 
 static WsLayout ws_layout(const ModelGeom& g, int B) {
     WsLayout l{};
@@ -1675,6 +1738,8 @@ static WsLayout ws_layout(const ModelGeom& g, int B) {
     l.h1 = take((size_t)B * g.H);
     l.act = take((size_t)B * g.I);
     l.part = take((size_t)B * g.KVH * kNCMax * G * 66);
+    l.fast = off;
+    off += fast_layout(g).total;
     l.total = off;
     return l;
 }
@@ -1687,8 +1752,61 @@ static std::mutex g_mu;
 static unsigned long long* g_profile = nullptr;   // optional stage-timestamp buffer (debug aid)
 static size_t g_profile_bytes = 0;
 static std::unordered_map<int, DeviceInfo> g_devinfo;
-static std::unordered_map<const void*, size_t> g_ws_ready;      // workspace pointers already zeroed
-static std::unordered_map<const void*, int> g_kernel_smem;      // largest dynamic smem opted in per kernel
+struct WsState {
+    size_t bytes = 0;               // zeroed size
+    unsigned long long sig = 0;     // geometry the workspace was last used with
+    unsigned long long launches = 0;
+};
+static std::unordered_map<const void*, WsState> g_ws_ready;     // workspace pointers already zeroed
+// largest dynamic shared memory opted in, per (device, kernel): the attribute belongs to the device's context
+static std::unordered_map<unsigned long long, int> g_kernel_smem;
+static unsigned g_spin_limit = kSpinLimit;
+static int g_fast_dbg = 0;
+static int g_fast_warps = -1;        // batch-1 fast path: -1 = not decided yet (environment), 0 = off, 8 / 16 = warps per CTA
+
+static unsigned long long geom_sig(const ModelGeom& g) {
+    unsigned long long h = 1469598103934665603ull;
+    const int v[7] = {g.H, g.I, g.L, g.QH, g.KVH, g.V, g.wfmt};
+    for (int i = 0; i < 7; ++i) h = (h ^ (unsigned long long)(unsigned)v[i]) * 1099511628211ull;
+    return h | 1ull;
+}
+
+static unsigned long long smem_key(int dev, const void* fn) {
+    return ((unsigned long long)(unsigned)dev << 56) ^ (unsigned long long)reinterpret_cast<uintptr_t>(fn);
+}
+
+// Opt a kernel in to `smem` bytes of dynamic shared memory on the current device (once per device and size).
+static int ensure_smem(const void* fn, size_t smem) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    std::lock_guard<std::mutex> lk(g_mu);
+    int& cur = g_kernel_smem[smem_key(dev, fn)];
+    if ((int)smem > cur) {
+        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        cur = (int)smem;
+    }
+    return 0;
+}
+
+// Zero the workspace in stream order when it is new, when it was last used with another geometry (the
+// fast kernel's 16-bit tags only tell consecutive launches of one geometry apart) and every 2^24 launches
+// (so that the launch epoch inside the tags never wraps).
+static int ensure_workspace(void* ws, size_t ws_bytes, size_t need, const ModelGeom& g, cudaStream_t stream) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    WsState& st = g_ws_ready[ws];
+    const unsigned long long sig = geom_sig(g);
+    if (st.bytes < need || st.sig != sig || st.launches >= (1ull << 24)) {
+        cudaError_t e = cudaMemsetAsync(ws, 0, ws_bytes, stream);
+        if (e != cudaSuccess) return (int)e;
+        st.bytes = ws_bytes;
+        st.sig = sig;
+        st.launches = 0;
+    }
+    ++st.launches;
+    return 0;
+}
 
 static int device_info(DeviceInfo& out) {
     int dev = 0;
@@ -1714,8 +1832,10 @@ static KernelFn pick_kernel(int B, int G, int WF) {
 #define PK_CASE(b, g)                                            \
     if (B == b && G == g && WF == 0) return decode_step_kernel<b, g, 0>; \
     if (B == b && G == g && WF == 1) return decode_step_kernel<b, g, 1>;
+#ifndef PK_DECODE_FAST_ONLY      // development builds that only need the batch-1 fast kernel compile in seconds
     PK_CASE(1, 1) PK_CASE(2, 1) PK_CASE(3, 1) PK_CASE(4, 1) PK_CASE(8, 1)
     PK_CASE(1, 3) PK_CASE(2, 3) PK_CASE(3, 3) PK_CASE(4, 3) PK_CASE(8, 3)
+#endif
 #undef PK_CASE
     return nullptr;
 }
@@ -1803,6 +1923,114 @@ struct StepArgs {
     void* ws; size_t ws_bytes; int max_seq_len; int lm_head; int advance;
 };
 
+// ---- batch-1 fast path (decode_fast.cuh) --------------------------------------------------------
+constexpr int kFastNotEligible = -7777;
+
+static int fast_warps() {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_fast_warps < 0) {
+        const char* e = std::getenv("PK_DECODE_FAST");        // "0" = generic kernel only, "8" / "16" = warps per CTA
+        g_fast_warps = e ? std::atoi(e) : 16;
+        if (g_fast_warps != 0 && g_fast_warps != 8 && g_fast_warps != 16) g_fast_warps = 16;
+    }
+    return g_fast_warps;
+}
+
+template <class W, int NW>
+static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo& di, const WsLayout& lay) {
+    using namespace fast;
+    if (di.sm_count < kNominalCtas || di.sm_count < W::NC * W::KVH) return kFastNotEligible;
+    constexpr int G = W::G;
+    constexpr int ACT = W::H > W::I ? W::H : W::I;
+    constexpr size_t kItemWords = ((NW * G * 66 + 3) & ~3) + (G + 2) * kD + (G + 2) * 32 + NW * G * 16;
+    constexpr size_t kAttnWords = (size_t)(W::NC * W::QH * 66) > kItemWords ? (size_t)(W::NC * W::QH * 66) : kItemWords;
+    const size_t fixed = align_up(sizeof(FShared<NW>), 128) + 2 * align_up((size_t)ACT * 2, 128) +
+                         2 * align_up((size_t)W::H * 4, 128) + align_up(kAttnWords * 4, 128);
+    if ((size_t)di.smem_optin < fixed + (size_t)NW * 4096) return kFastNotEligible;
+    const int rw = (int)(((size_t)di.smem_optin - fixed) / NW / 128 * 128);
+    // the largest entry of any phase must fit the ring twice (one in use, one in flight)
+#define PK_ENT(T) (Ph<W, NW, T>::K * 2 * Ph<W, NW, T>::RPE * (Ph<W, NW, T>::PAIR ? 2 : 1))
+    const int ent[5] = {PK_ENT(kQKV), PK_ENT(kO), PK_ENT(kGU), PK_ENT(kDown), PK_ENT(kLM)};
+#undef PK_ENT
+    for (int t = 0; t < 5; ++t)
+        if (2 * ent[t] > rw) return kFastNotEligible;
+    const size_t smem = fixed + (size_t)NW * rw;
+    auto fn = decode_fast_kernel<W, NW>;
+    int rc = ensure_smem(reinterpret_cast<const void*>(fn), smem);
+    if (rc) return rc;
+    rc = ensure_workspace(a.ws, a.ws_bytes, lay.total, g, a.stream);
+    if (rc) return rc;
+
+    const FastLayout fl = fast_layout(g);
+    unsigned char* ws = static_cast<unsigned char*>(a.ws);
+    unsigned char* fw = ws + lay.fast;
+    FastParams p{};
+    p.layers = static_cast<const unsigned long long*>(a.layers);
+    p.kv = static_cast<const unsigned long long*>(a.kv);
+    p.embed = static_cast<const uint16_t*>(a.embed);
+    p.final_norm = static_cast<const uint16_t*>(a.final_norm);
+    p.input_ids = a.input_ids;
+    p.positions = static_cast<const long long*>(a.positions);
+    p.seq_lens = static_cast<const int*>(a.seq_lens);
+    p.block_table = static_cast<const int*>(a.block_table);
+    p.slot_mapping = static_cast<const long long*>(a.slot_mapping);
+    p.cos_sin = a.cos_sin;
+    p.out_hidden = static_cast<uint16_t*>(a.out_hidden);
+    p.logits = static_cast<uint16_t*>(a.logits);
+    p.next_ids = static_cast<long long*>(a.next_ids);
+    p.layer_outputs = static_cast<uint16_t*>(a.layer_outputs);
+    p.profile = (g_profile && g_profile_bytes >= (size_t)di.sm_count * g.L * kProfSlots * 8) ? g_profile : nullptr;
+    p.ctrl = reinterpret_cast<unsigned int*>(ws + lay.ctrl);
+    p.fctrl = reinterpret_cast<unsigned int*>(fw + fl.fctrl);
+    p.argkey = reinterpret_cast<unsigned long long*>(fw + fl.argkey);
+    p.w_x = reinterpret_cast<uint32_t*>(fw + fl.x);
+    p.w_qkv = reinterpret_cast<uint32_t*>(fw + fl.qkv);
+    p.w_h1 = reinterpret_cast<uint32_t*>(fw + fl.h1);
+    p.w_act = reinterpret_cast<uint32_t*>(fw + fl.act);
+    p.w_part = reinterpret_cast<unsigned long long*>(fw + fl.part);
+    p.w_gate = reinterpret_cast<unsigned long long*>(fw + fl.gate);
+    p.k_off = a.k_off;
+    p.v_off = a.v_off;
+    p.block_stride = a.block_stride;
+    p.token_stride = a.token_stride;
+    p.head_stride = a.head_stride;
+    p.block_size = a.block_size;
+    p.bt_stride = a.bt_stride;
+    p.ids_i64 = a.ids_i64 ? 1 : 0;
+    p.cs_fp32 = a.cs_fp32 ? 1 : 0;
+    p.L = g.L;
+    p.V = g.V;
+    p.lm_head = (a.lm_head && (a.logits || a.next_ids)) ? 1 : 0;
+    p.advance = (a.advance && p.lm_head && a.next_ids) ? 1 : 0;
+    p.max_seq_len = a.max_seq_len;
+    p.ring_bytes = rw;
+    p.spin_limit = g_spin_limit;
+    p.dbg = g_fast_dbg;
+    p.eps = g.eps;
+    void* args[] = {&p};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fn), dim3(di.sm_count), dim3(NW * 32), args,
+                                                smem, a.stream);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return e == cudaErrorCooperativeLaunchTooLarge ? (int)kErrResidency : (int)e;
+    }
+    return (int)cudaPeekAtLastError();
+}
+
+// Batch 1, bf16 weights, one of the model widths the fast kernel is instantiated for: returns the launch
+// status, or kFastNotEligible when the generic kernel has to take the step.
+static int fast_launch(const ModelGeom& g, const StepArgs& a, const DeviceInfo& di, const WsLayout& lay) {
+    const int nw = fast_warps();
+    if (nw == 0 || g.L > kMaxLayers) return kFastNotEligible;
+    using W135 = fast::Widths<576, 1536, 9, 3>;
+    using W360 = fast::Widths<960, 2560, 15, 5>;
+    const bool is135 = g.H == 576 && g.I == 1536 && g.QH == 9 && g.KVH == 3;
+    const bool is360 = g.H == 960 && g.I == 2560 && g.QH == 15 && g.KVH == 5;
+    if (is135) return nw == 8 ? fast_launch_t<W135, 8>(g, a, di, lay) : fast_launch_t<W135, 16>(g, a, di, lay);
+    if (is360) return nw == 8 ? fast_launch_t<W360, 8>(g, a, di, lay) : fast_launch_t<W360, 16>(g, a, di, lay);
+    return kFastNotEligible;
+}
+
 static int decode_launch(const ModelGeom& g, const StepArgs& a) {
     if (a.B < 1 || a.B > kMaxB) return kErrBatch;
     const int KB = a.B <= 4 ? a.B : kMaxB;      // kernel batch: exact up to 4, the batch-8 kernel (padded) beyond
@@ -1835,6 +2063,11 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
     if (di.major != 10) return kErrArch;
     if (!di.coop) return kErrCoop;
 
+    if (a.B == 1 && g.wfmt == 0 && (!a.embed_lookup || a.embed_lookup == a.embed)) {
+        rc = fast_launch(g, a, di, lay);
+        if (rc != kFastNotEligible) return rc;
+    }
+
     // shared memory: fixed part + per-warp rings
     const int act_elems = g.H > g.I ? g.H : g.I;
     const size_t fixed = align_up(sizeof(Shared), 128) + align_up((size_t)KB * act_elems * 2, 128) +
@@ -1854,22 +2087,10 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
     if (rc) return rc;
     const size_t smem = fixed + (size_t)kNW * rw;
 
-    {
-        std::lock_guard<std::mutex> lk(g_mu);
-        int& cur = g_kernel_smem[reinterpret_cast<const void*>(fn)];
-        if ((int)smem > cur) {
-            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-            cur = (int)smem;
-        }
-        auto it = g_ws_ready.find(a.ws);
-        if (it == g_ws_ready.end() || it->second < lay.total) {
-            // first use of this workspace: zero it in stream order (tags, counters, epoch start at 0)
-            cudaError_t e = cudaMemsetAsync(a.ws, 0, a.ws_bytes, a.stream);
-            if (e != cudaSuccess) return (int)e;
-            g_ws_ready[a.ws] = a.ws_bytes;
-        }
-    }
+    rc = ensure_smem(reinterpret_cast<const void*>(fn), smem);
+    if (rc) return rc;
+    rc = ensure_workspace(a.ws, a.ws_bytes, lay.total, g, a.stream);
+    if (rc) return rc;
 
     unsigned char* ws = static_cast<unsigned char*>(a.ws);
     p.layers = static_cast<const unsigned long long*>(a.layers);
@@ -1913,6 +2134,7 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
     p.ring_bytes = rw;
     p.profile = (g_profile && g_profile_bytes >= (size_t)ncta * g.L * kProfSlots * 8) ? g_profile : nullptr;
     p.act_elems = act_elems;
+    p.spin_limit = g_spin_limit;
     p.eps = g.eps;
 
     void* args[] = {&p};
@@ -1975,8 +2197,9 @@ static ModelGeom to_geom(const PkDecodeModel* m) {
 }
 
 extern "C" size_t pk_decode_workspace_bytes(const PkDecodeModel* m, int max_batch) {
-    if (!m || max_batch < 1 || m->kv_heads <= 0) return 0;
-    return ws_layout(to_geom(m), max_batch).total;
+    if (!m || max_batch < 1 || max_batch > kMaxB || m->kv_heads <= 0) return 0;
+    // batches 5..7 run on the batch-8 kernel (padded), so they need its workspace
+    return ws_layout(to_geom(m), max_batch <= 4 ? max_batch : kMaxB).total;
 }
 
 extern "C" int pk_decode_step(const PkDecodeModel* m, const PkDecodeArgs* a) {
@@ -1995,7 +2218,9 @@ extern "C" int pk_decode_workspace_init(void* workspace, size_t bytes, void* str
     cudaError_t e = cudaMemsetAsync(workspace, 0, bytes, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return (int)e;
     std::lock_guard<std::mutex> lk(g_mu);
-    g_ws_ready[workspace] = bytes;
+    WsState& st = g_ws_ready[workspace];
+    st = WsState{};
+    st.bytes = bytes;
     return 0;
 }
 
@@ -2026,6 +2251,34 @@ extern "C" int pk_decode_status(void* workspace, void* stream) {
 }
 
 extern "C" const char* pk_status_string(int status) { return status_string(status); }
+
+// Tuning / test knobs (process-wide).
+// Batch-1 bf16 steps of SmolLM2-135M / 360M widths run on the specialised kernel with `warps` (8 or 16)
+// warps per CTA; 0 sends every step to the generic kernel.  Default: environment PK_DECODE_FAST, else 16.
+extern "C" int pk_decode_set_fast_path(int warps) {
+    if (warps != 0 && warps != 8 && warps != 16) return kErrShape;
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_fast_warps = warps;
+    return 0;
+}
+extern "C" void pk_decode_set_debug(int flags) { g_fast_dbg = flags; }
+// Bound (polling rounds) of every device-side wait of later launches; 0 restores the default.
+extern "C" void pk_decode_set_spin_limit(unsigned rounds) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_spin_limit = rounds ? rounds : kSpinLimit;
+}
+// Failure-path probe: one CTA polls a word of `workspace` that nothing writes, with the decode kernels'
+// bounded wait; after `rounds` polls it gives up and the workspace status becomes 9110, which
+// pk_decode_status() then returns (and clears).  Never hangs; touches nothing else.
+extern "C" int pk_decode_wait_probe(void* workspace, size_t bytes, unsigned rounds, void* stream) {
+    if (!workspace) return kErrNull;
+    if (bytes < 512 || (reinterpret_cast<uintptr_t>(workspace) % 16) != 0) return kErrScratch;
+    if (rounds < 1 || rounds > (1u << 20)) return kErrShape;
+    unsigned int* ctrl = static_cast<unsigned int*>(workspace);
+    const unsigned long long* word = reinterpret_cast<const unsigned long long*>(static_cast<unsigned char*>(workspace) + 128);
+    wait_probe_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(ctrl, word, rounds);
+    return (int)cudaGetLastError();
+}
 
 // Debug aid: when set (device buffer of at least ctas * layers * 24 * 8 bytes), thread 0 of every CTA
 // stamps %globaltimer at each phase boundary of each layer: [cta][layer][12].  Pass null to disable.
@@ -2058,7 +2311,7 @@ extern "C" int mk_query(int* sm_count, int* coop, int* active_per_sm, int* major
     const int rc = device_info(di);
     if (rc) return rc;
     cudaFuncAttributes fa{};
-    cudaError_t e = cudaFuncGetAttributes(&fa, decode_step_kernel<4, 3, 0>);
+    cudaError_t e = cudaFuncGetAttributes(&fa, reinterpret_cast<const void*>(pick_kernel(4, 3, 0)));
     if (e != cudaSuccess) return (int)e;
     *sm_count = di.sm_count;
     *coop = di.coop;
@@ -2157,7 +2410,7 @@ extern "C" int pk_decode_step_static(const PkDecodeModel* m, const PkDecodeArgs*
             e = cudaGetSymbolAddress(&ptr, g_static_scratch);
             if (e != cudaSuccess) return (int)e;
             g_static_scratch_addr[dev] = ptr;
-            g_ws_ready[ptr] = kStaticScratchBytes;   // zero-initialised at module load: no first-use memset
+            g_ws_ready[ptr].bytes = kStaticScratchBytes;   // zero-initialised at module load
         } else {
             ptr = it->second;
         }
