@@ -9,10 +9,9 @@
 //    folds, and the whole kernel is a few thousand instructions, so a layer iteration stays inside the
 //    instruction cache (the generic kernel is ~200 KB of code per instantiation and refetches it from L2
 //    every layer);
-//  * every warp is a consumer and refills its own ring: right after it has used an entry it issues the
-//    bulk copies of the next entries that fit (the freed bytes are exactly what the next copy needs, so a
-//    separate producer warp would act at the same moment), which removes the producer warp, the "empty"
-//    barriers and their polling;
+//  * a producer warp feeds the per-warp weight rings (one lane per ring; issuing bulk copies can block for
+//    a while when the copy engine's queue is full at a phase boundary, which must not happen to a warp on
+//    the dependent chain: letting every consumer warp refill its own ring was measured 5 % slower);
 //  * bf16 activations travel as 32-bit words [tag:16 | bf16:16] and are polled with 16-byte loads: four
 //    values per load, each word validating itself (no reliance on 16-byte atomicity).  fp32 split-KV
 //    partials travel as 64-bit words [tag:32 | fp32] polled two per 16-byte load;
@@ -42,6 +41,15 @@ struct Widths {
     static_assert(QH_ % KVH_ == 0 && H_ % 32 == 0 && I_ % 32 == 0, "unsupported widths");
 };
 
+// Floats of the attention scratch: the larger of an item's working set (per-warp partials, staged q/k/v,
+// probabilities) and the merge staging (partials of every (chunk, query head) plus the merge weights).
+template <class W, int NW>
+__host__ __device__ constexpr int attn_words() {
+    constexpr int item = ((NW * W::G * 66 + 3) & ~3) + (W::G + 2) * kD + (W::G + 2) * 32 + NW * W::G * 16;
+    constexpr int merge = W::NC * W::QH * 66 + W::QH * W::NC;
+    return ((item > merge ? item : merge) + 3) & ~3;
+}
+
 struct FastParams {
     const unsigned long long* layers;   // device table [L][6]
     const unsigned long long* kv;       // device table [L]
@@ -66,7 +74,8 @@ struct FastParams {
     uint32_t* w_h1;                     // [2][H]
     uint32_t* w_act;                    // [2][I]
     unsigned long long* w_part;         // [2][KVH][NC][G][66]  words [tag32 | fp32]
-    unsigned long long* w_gate;         // [2][KVH * NC]        one word [tag32 | 1] per attention item, written after its partials
+    unsigned long long* w_gate;         // [2][KVH * NC][16]    one word [tag32 | 1] per attention item in a 128-byte line of its
+                                        //                      own (a polled line must receive one write), written after the partials
     long long k_off, v_off, block_stride, token_stride, head_stride;
     int block_size, bt_stride, ids_i64, cs_fp32;
     int L, V, lm_head, advance, max_seq_len, ring_bytes;
@@ -80,6 +89,7 @@ enum { kFctrlEpoch = 0, kFctrlDone = 1 };
 template <int NW>
 struct FShared {
     uint64_t full[NW][kFE];
+    uint64_t empty[NW][kFE];
     uint32_t ent_off[NW][kFE];
     uint32_t ent_foot[NW][kFE];
     int row_a[kNumPhaseTypes][NW];
@@ -131,10 +141,10 @@ struct FC {
     uint32_t T16;       // ((epoch % 511) + 1) << 23: the epoch part of a 16-bit tag, already in the high half
     uint32_t T32;       // (epoch + 1) << 7: the epoch part of a 32-bit tag
     int warp, lane, cta, ncta;
-    // ring state (warp-uniform)
-    uint32_t issued, consumed, head, used;
-    int i_layer, i_t, i_row;    // issue cursor; i_t == kNumPhaseTypes: nothing left
+    uint32_t consumed;          // ring entries this warp has used so far
     uint2 nwv[2];               // this thread's norm weights of the *next* norm phase (fetched one phase ahead)
+    uint32_t pre_off;           // ring offset of the upcoming phase's first entry, valid when pre_ok
+    bool pre_ok;                // that entry has landed (checked before the staging of the phase)
     unsigned long long* prof;
 #ifdef PK_FAST_WPROF
     unsigned long long* wprof;  // development builds: this warp's stamps of the current phase (lane 0, one layer)
@@ -147,6 +157,10 @@ constexpr int kWprofLayer = 5;
 #else
 #define PK_WSTAMP(c, i) do { } while (0)
 #endif
+
+// barrier of the NW consumer warps (the producer warp does not take part)
+template <int NW>
+__device__ __forceinline__ void csync() { asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory"); }
 
 template <int NW>
 __device__ __forceinline__ bool f_aborted(const FC<NW>& c) { return c.sh.abort_flag != 0; }
@@ -178,23 +192,27 @@ __device__ __forceinline__ uint32_t tag32(const FC<NW>& c, int layer) { return c
 // Wait for up to N packets (ptr[u] == nullptr: slot unused).  While nothing has arrived only the first
 // packet is polled (the CTAs that have no other work in a phase would otherwise multiply the polling
 // traffic in L2 by N); once it is there all remaining ones are fetched together.
-template <int N, int NW>
-__device__ __forceinline__ void poll_packets(FC<NW>& c, const uint32_t* const (&ptr)[N], uint32_t T, uint4 (&out)[N]) {
+// `mid` runs once, warp-converged, after the first round of loads has been issued and before it is looked
+// at: work that may block for a while (the ring refill: the copy engine's queue fills up when every warp
+// refills at a phase boundary) then overlaps the L2 round trip of the poll instead of preceding it.
+template <int N, int NW, typename Mid>
+__device__ __forceinline__ void poll_packets(FC<NW>& c, const uint32_t* const (&ptr)[N], uint32_t T, uint4 (&out)[N], Mid mid) {
     unsigned need = 0;
 #pragma unroll
     for (int u = 0; u < N; ++u) {
         out[u] = make_uint4(0u, 0u, 0u, 0u);
         if (ptr[u] != nullptr) need |= 1u << u;
     }
+    bool first_only = N > 1;
+    unsigned cur = first_only ? (need & (0u - need)) : need;
+    uint4 v[N];
+#pragma unroll
+    for (int u = 0; u < N; ++u)
+        if (cur & (1u << u)) v[u] = ld_packet(ptr[u]);
+    mid();
     if (f_aborted(c)) return;
     unsigned spins = 0;
-    bool first_only = N > 1;
     while (need) {
-        const unsigned cur = first_only ? (need & (0u - need)) : need;
-        uint4 v[N];
-#pragma unroll
-        for (int u = 0; u < N; ++u)
-            if (cur & (1u << u)) v[u] = ld_packet(ptr[u]);
 #pragma unroll
         for (int u = 0; u < N; ++u)
             if ((cur & (1u << u)) && packet_ok(v[u], T)) {
@@ -202,15 +220,24 @@ __device__ __forceinline__ void poll_packets(FC<NW>& c, const uint32_t* const (&
                 need &= ~(1u << u);
                 first_only = false;
             }
-        if (need && (c.p.dbg & 2)) __nanosleep(200);
-        if (need && (++spins & 255u) == 0 && f_give_up(c, spins)) return;
+        if (!need) break;
+        if (c.p.dbg & 2) __nanosleep(200);
+        if ((++spins & 255u) == 0 && f_give_up(c, spins)) return;
+        cur = first_only ? (need & (0u - need)) : need;
+#pragma unroll
+        for (int u = 0; u < N; ++u)
+            if (cur & (1u << u)) v[u] = ld_packet(ptr[u]);
     }
+}
+template <int N, int NW>
+__device__ __forceinline__ void poll_packets(FC<NW>& c, const uint32_t* const (&ptr)[N], uint32_t T, uint4 (&out)[N]) {
+    poll_packets<N>(c, ptr, T, out, [] {});
 }
 
 // Same for pairs of 64-bit flagged words [tag32 | fp32]; out[2u], out[2u+1] receive the payloads.
 template <int N, int NW>
 __device__ __forceinline__ void poll_flagged_pairs(FC<NW>& c, const unsigned long long* const (&ptr)[N], uint32_t tag,
-                                                   uint32_t (&out)[2 * N]) {
+                                                   uint32_t (&out)[2 * N], bool first_only = false) {
     unsigned need = 0;
 #pragma unroll
     for (int u = 0; u < N; ++u) {
@@ -219,7 +246,6 @@ __device__ __forceinline__ void poll_flagged_pairs(FC<NW>& c, const unsigned lon
     }
     if (f_aborted(c)) return;
     unsigned spins = 0;
-    bool first_only = N > 1;
     while (need) {
         const unsigned cur = first_only ? (need & (0u - need)) : need;
         unsigned long long a[N], b[N];
@@ -258,7 +284,7 @@ struct Ph<W, NW, kQKV> { static constexpr int K = W::H, WIDX = 1, PAIR = 1, RPE 
 template <class W, int NW>
 struct Ph<W, NW, kO> { static constexpr int K = W::AD, WIDX = 2, PAIR = 0, RPE = 2; };
 template <class W, int NW>
-struct Ph<W, NW, kGU> { static constexpr int K = W::H, WIDX = 4, PAIR = 1, RPE = (NW >= 12 ? 1 : 2); };
+struct Ph<W, NW, kGU> { static constexpr int K = W::H, WIDX = 4, PAIR = 1, RPE = (NW >= 12 ? 1 : 3); };
 template <class W, int NW>
 struct Ph<W, NW, kDown> { static constexpr int K = W::I, WIDX = 5, PAIR = 0, RPE = (W::I * 2 > 4096 ? 1 : 2); };
 template <class W, int NW>
@@ -284,76 +310,111 @@ __device__ __forceinline__ void warp_share(int nrows, int cta, int ncta, int war
     b = r0 + n * (warp + 1) / NW;
 }
 
-// Move the issue cursor to the next phase of this warp that owns rows (or to the end).
-template <int NW>
-__device__ __forceinline__ void cursor_next_phase(FC<NW>& c) {
-    for (;;) {
-        if (c.i_t == kLM) {
-            c.i_t = kNumPhaseTypes;
-            return;
+// Producer warp: lane w (< NW) feeds the ring of consumer warp w with that warp's entries in schedule
+// order (4 phases per layer, then the lm_head), in closed form from the row shares.  All lanes run the same
+// loop; every iteration a lane retires up to two consumed entries (non-blocking probes) and issues up to two
+// new ones if its ring has room.  Nothing here waits on a consumer, so one slow ring never stalls the others.
+template <class W, int NW>
+__device__ void producer_loop(const FastParams& p, FShared<NW>& sh, unsigned char* ring_base, int lane) {
+    const bool active = lane < NW;
+    const int w = active ? lane : 0;
+    const uint32_t RW = (uint32_t)p.ring_bytes;
+    unsigned char* ring = ring_base + (size_t)w * RW;
+    const uint64_t pol = evict_first_policy();
+    int layer = 0, t = -1, row = 0;        // cursor: next entry starts at unit `row` of phase t in `layer`
+    bool more = active;
+    auto next_phase = [&]() {
+        for (;;) {
+            if (t == kLM) { more = false; return; }
+            if (++t == 4) {
+                ++layer;
+                if (layer < p.L) t = 0;
+                else if (p.lm_head) t = kLM;
+                else { more = false; return; }
+            }
+            row = sh.row_a[t][w];
+            if (row < sh.row_b[t][w]) return;
         }
-        if (++c.i_t == 4) {
-            ++c.i_layer;
-            if (c.i_layer < c.p.L) {
-                c.i_t = 0;
-            } else if (c.p.lm_head) {
-                c.i_t = kLM;
-            } else {
-                c.i_t = kNumPhaseTypes;
-                return;
+    };
+    if (more) next_phase();
+    uint32_t issued = 0, tail = 0, head = 0, used = 0;
+    unsigned idle = 0;
+    for (;;) {
+        bool progressed = false;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            if (tail < issued) {
+                const uint32_t slot = tail % kFE;
+                if (mbar_probe(&sh.empty[w][slot], (tail / kFE) & 1)) {
+                    used -= sh.ent_foot[w][slot];
+                    ++tail;
+                    progressed = true;
+                }
             }
         }
-        c.i_row = c.sh.row_a[c.i_t][c.warp];
-        if (c.i_row < c.sh.row_b[c.i_t][c.warp]) return;
-    }
-}
-
-// Issue the bulk copies of as many upcoming entries as the ring has room for.  Warp-uniform; lane 0 issues.
-template <class W, int NW>
-__device__ __forceinline__ void issue_more(FC<NW>& c, uint64_t pol) {
-    const uint32_t RW = (uint32_t)c.p.ring_bytes;
-    while (c.i_t < kNumPhaseTypes) {
-        int rowbytes, rpe, widx;
-        phase_consts<W, NW>(c.i_t, rowbytes, rpe, widx);
-        const int nre = min(rpe, c.sh.row_b[c.i_t][c.warp] - c.i_row);
-        const uint32_t part = (uint32_t)(nre * rowbytes);
-        const bool pair = c.i_t == kGU || c.i_t == kQKV;
-        const uint32_t bytes = pair ? 2u * part : part;
-        const uint32_t gap = (c.head + bytes > RW) ? RW - c.head : 0u;
-        const uint32_t foot = bytes + gap;
-        if (c.issued - c.consumed >= (uint32_t)kFE || c.used + foot > RW) break;
-        const uint32_t off = gap ? 0u : c.head;
-        if (c.lane == 0) {
-            const uint32_t slot = c.issued % kFE;
-            c.sh.ent_off[c.warp][slot] = off;
-            c.sh.ent_foot[c.warp][slot] = foot;
-            // weight pointers come from the shared-memory copy of the table: no global load in front of the copy
-            const unsigned char* base = widx < 0 ? reinterpret_cast<const unsigned char*>(c.p.embed)
-                                                 : reinterpret_cast<const unsigned char*>(c.sh.mat_ptr[c.i_layer][c.i_t]);
-            // QKV units pair row d with row d + 32 of the same head; gate/up units pair row r with row I + r
-            const int row0 = c.i_t == kQKV ? ((c.i_row >> 5) << 6) + (c.i_row & 31) : c.i_row;
-            const size_t pair_off = (size_t)(c.i_t == kQKV ? 32 : W::I) * rowbytes;
-            const unsigned char* src = base + (size_t)row0 * rowbytes;
-            // the generic-proxy reads of the bytes being overwritten are ordered before the async-proxy writes
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_expect_tx(&c.sh.full[c.warp][slot], bytes);
-            bulk_g2s(c.ring + off, src, part, &c.sh.full[c.warp][slot], pol);
-            if (pair) bulk_g2s(c.ring + off + part, src + pair_off, part, &c.sh.full[c.warp][slot], pol);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            if (more) {
+                int rowbytes, rpe, widx;
+                phase_consts<W, NW>(t, rowbytes, rpe, widx);
+                const int nre = min(rpe, sh.row_b[t][w] - row);
+                const uint32_t part = (uint32_t)(nre * rowbytes);
+                const bool pair = t == kGU || t == kQKV;
+                const uint32_t bytes = pair ? 2u * part : part;
+                if (issued == tail) head = 0;      // empty ring: restart at its base, so any entry <= RW fits
+                const uint32_t gap = (head + bytes > RW) ? RW - head : 0u;
+                const uint32_t foot = bytes + gap;
+                if (issued - tail < (uint32_t)kFE && used + foot <= RW) {
+                    const uint32_t off = gap ? 0u : head;
+                    const uint32_t slot = issued % kFE;
+                    sh.ent_off[w][slot] = off;
+                    sh.ent_foot[w][slot] = foot;
+                    // weight pointers come from the shared-memory copy of the table: no global load in front of the copy
+                    const unsigned char* base = widx < 0 ? reinterpret_cast<const unsigned char*>(p.embed)
+                                                         : reinterpret_cast<const unsigned char*>(sh.mat_ptr[layer][t]);
+                    // QKV units pair row d with row d + 32 of the same head; gate/up units pair row r with row I + r
+                    const int row0 = t == kQKV ? ((row >> 5) << 6) + (row & 31) : row;
+                    const size_t pair_off = (size_t)(t == kQKV ? 32 : W::I) * rowbytes;
+                    const unsigned char* src = base + (size_t)row0 * rowbytes;
+                    mbar_expect_tx(&sh.full[w][slot], bytes);
+                    bulk_g2s(ring + off, src, part, &sh.full[w][slot], pol);
+                    if (pair) bulk_g2s(ring + off + part, src + pair_off, part, &sh.full[w][slot], pol);
+                    head = off + bytes;
+                    if (head >= RW) head = 0;
+                    used += foot;
+                    ++issued;
+                    row += rpe;
+                    if (row >= sh.row_b[t][w]) next_phase();
+                    progressed = true;
+                }
+            }
         }
-        c.head = off + bytes;
-        if (c.head >= RW) c.head = 0;
-        c.used += foot;
-        ++c.issued;
-        c.i_row += rpe;
-        if (c.i_row >= c.sh.row_b[c.i_t][c.warp]) cursor_next_phase(c);
+        const bool done = !more;                 // everything issued; outstanding copies are drained below
+        if (__all_sync(kFullMask, done)) break;
+        idle = (progressed || done) ? 0 : idle + 1;
+        // nothing to retire or issue: yield the issue slots to the consumer warp that shares this scheduler
+        if (!__any_sync(kFullMask, progressed)) __nanosleep(kProducerIdleNs);
+        if ((idle & 255u) == 255u && idle >= p.spin_limit) {
+            sh.abort_flag = 1;
+            atomicCAS(p.ctrl + kCtrlStatus, 0u, (unsigned)kErrBarrierTimeout);
+        }
+        if (__any_sync(kFullMask, sh.abort_flag != 0)) break;
     }
-    __syncwarp();
+    // Drain: never leave the CTA while bulk copies into its shared memory are still in flight.
+    if (active) {
+        for (uint32_t n = tail; n < issued; ++n) {
+            const uint32_t slot = n % kFE;
+            unsigned spins = 0;
+            while (!mbar_probe(&sh.full[w][slot], (n / kFE) & 1))
+                if (++spins >= p.spin_limit) break;
+        }
+    }
 }
 
 // ------------------------------------------------------------------ GEMV
 // NR staged rows of KC 16-byte chunks each times the activation vector, K split over the lanes.
 template <int KC, int NR>
-__device__ __forceinline__ void gemv_rows(const uint4* ep, const uint4* act, int lane, int nlive, float (&v)[4]) {
+__device__ __forceinline__ void gemv_rows(const uint4* ep, const uint4* act, int lane, int nlive, float (&v)[8]) {
     constexpr int IT = (KC + 31) / 32;
     float acc[NR], acc2[NR];
 #pragma unroll
@@ -378,7 +439,7 @@ __device__ __forceinline__ void gemv_rows(const uint4* ep, const uint4* act, int
 // (run-time t) so that the wait, the reduction and the ring refill exist once in the instruction stream;
 // only the dot products (compile-time K) and the epilogues are switched.
 template <class W, int NW>
-__device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, const uint4* act, const float* res, uint64_t pol) {
+__device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, const uint4* act, const float* res) {
     const FastParams& p = c.p;
     FShared<NW>& sh = c.sh;
     const int w = c.warp, lane = c.lane;
@@ -391,11 +452,15 @@ __device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, co
     for (int row = ra; row < rb; row += rpe) {
         const int nre = min(rpe, rb - row);
         const uint32_t slot = c.consumed % kFE;
-        // after an abort the staged bytes are undefined: leave the phase (warp-uniform)
-        if (!__all_sync(kFullMask, f_wait_mbar(c, &sh.full[w][slot], (c.consumed / kFE) & 1))) break;
+        uint32_t eoff = c.pre_off;
+        if (!(row == ra && c.pre_ok)) {
+            // after an abort the staged bytes are undefined: leave the phase (warp-uniform)
+            if (!__all_sync(kFullMask, f_wait_mbar(c, &sh.full[w][slot], (c.consumed / kFE) & 1))) break;
+            eoff = sh.ent_off[w][slot];
+        }
         if (row == ra) PK_WSTAMP(c, 4);
-        const uint4* ep = reinterpret_cast<const uint4*>(c.ring + sh.ent_off[w][slot]);
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint4* ep = reinterpret_cast<const uint4*>(c.ring + eoff);
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         switch (t) {
             case kQKV: gemv_rows<Ph<W, NW, kQKV>::K / 8, 2 * Ph<W, NW, kQKV>::RPE>(ep, act, lane, 2 * nre, v); break;
             case kO: gemv_rows<Ph<W, NW, kO>::K / 8, Ph<W, NW, kO>::RPE>(ep, act, lane, nre, v); break;
@@ -404,14 +469,14 @@ __device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, co
             default: gemv_rows<Ph<W, NW, kLM>::K / 8, Ph<W, NW, kLM>::RPE>(ep, act, lane, nre, v); break;
         }
         __syncwarp();
-        c.used -= sh.ent_foot[w][slot];
+        if (lane == 0) mbar_arrive(&sh.empty[w][slot]);      // every lane's loads of this entry have been consumed
         ++c.consumed;
-        // lane 8 j ends up with the total of staged row j (j < 4)
-        const float mine = transpose_reduce<4>(v, lane);
-        const int vj = lane >> 3;
+        // lane 4 j ends up with the total of staged row j (j < 8)
+        const float mine = transpose_reduce<8>(v, lane);
+        const int vj = lane >> 2;
         // pair entries stage nre first rows (gate / dim d), then nre second rows (up / dim d + 32)
-        const float mine_up = __shfl_sync(kFullMask, mine, ((vj + nre) << 3) & 31);
-        if ((lane & 7) == 0 && vj < nre) {
+        const float mine_up = __shfl_sync(kFullMask, mine, ((vj + nre) << 2) & 31);
+        if ((lane & 3) == 0 && vj < nre) {
             const int r = row + vj;
             if (t == kQKV) {
                 // unit r = (head, j): projection outputs of dims j and j + 32 rounded to bf16 (HF linear output),
@@ -450,7 +515,6 @@ __device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, co
             }
         }
         PK_WSTAMP(c, 5);
-        issue_more<W, NW>(c, pol);
     }
     if (t == kLM) {
         // greedy argmax: highest logit, ties toward the lowest index; one atomic per CTA
@@ -460,7 +524,7 @@ __device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, co
             const uint32_t r = (uint32_t)ra + (0xffffu - (best & 0xffffu));
             sh.lm_key[w] = best ? (((unsigned long long)(best >> 16) << 32) | (unsigned long long)(0xffffffffu - r)) : 0ull;
         }
-        __syncthreads();
+        csync<NW>();
         if (w == 0) {
             unsigned long long k = lane < NW ? sh.lm_key[lane] : 0ull;
 #pragma unroll
@@ -524,7 +588,7 @@ __device__ __forceinline__ void stage_norm(FC<NW>& c, const uint32_t* src_words,
     }
     ss = warp_sum(ss);
     if (c.lane == 0) sh.red[c.warp] = ss;
-    __syncthreads();
+    csync<NW>();
     PK_WSTAMP(c, 2);
     float tot = 0.f;
 #pragma unroll
@@ -550,11 +614,11 @@ __device__ __forceinline__ void stage_norm(FC<NW>& c, const uint32_t* src_words,
             if (pk < NP) c.nwv[u] = __ldg(reinterpret_cast<const uint2*>(next_weight) + pk);
         }
     }
-    __syncthreads();
+    csync<NW>();
 }
 
 // Copy N words [tag16 | bf16] into `act` (input of the down projection).
-template <int N, int NW>
+template <class W, int N, int NW>
 __device__ __forceinline__ void stage_copy(FC<NW>& c, const uint32_t* src_words, uint32_t T, uint4* act) {
     constexpr int NT = NW * 32;
     constexpr int NP = N / 4;
@@ -576,7 +640,7 @@ __device__ __forceinline__ void stage_copy(FC<NW>& c, const uint32_t* src_words,
             reinterpret_cast<uint2*>(act)[pk] = o;
         }
     }
-    __syncthreads();
+    csync<NW>();
 }
 
 // Input of the O projection: pull the split-KV partials of every (query head, chunk), merge them with
@@ -596,12 +660,12 @@ __device__ __forceinline__ void stage_attn(FC<NW>& c, int layer, uint4* act) {
     // Gate: one warp waits for the "item published" word of every attention item before anybody touches the
     // partials, so the lines the item CTAs are writing are not being read by the whole grid in the meantime.
     // (The gate is only a hint: every partial word still validates itself below.)
-    if (c.warp == 0 && !(c.p.dbg & 4)) {
+    if (c.warp == 0) {
         const int nitems = nc * W::KVH;
         for (int i0 = 0; i0 < nitems; i0 += 32) {
             const int i = i0 + c.lane;
             if (i < nitems && !f_aborted(c)) {
-                const unsigned long long* g = c.p.w_gate + (size_t)(layer & 1) * W::KVH * W::NC + i;
+                const unsigned long long* g = c.p.w_gate + ((size_t)(layer & 1) * W::KVH * W::NC + i) * 16;   // one 128-byte line per item
                 unsigned spins = 0;
                 while ((uint32_t)(ld_flagged(g) >> 32) != tag) {
                     if ((++spins & 255u) == 0 && f_give_up(c, spins)) break;
@@ -609,24 +673,24 @@ __device__ __forceinline__ void stage_attn(FC<NW>& c, int layer, uint4* act) {
             }
         }
     }
-    __syncthreads();
-#pragma unroll 1
-    for (int u0 = 0; u0 < PU; u0 += 4) {
-        if (tid + u0 * NT >= total) break;
-        uint32_t bits[8];
-        const unsigned long long* ptr[4];
+    csync<NW>();
+    // every pair this thread is responsible for is requested in the same round (the gate has told us the
+    // partials are on their way, so one L2 round trip normally brings them all)
+    {
+        uint32_t bits[2 * PU];
+        const unsigned long long* ptr[PU];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int i = tid + (u0 + u) * NT;
+        for (int u = 0; u < PU; ++u) {
+            const int i = tid + u * NT;
             const int ch = i / PER_C, rem = i - ch * PER_C;
             const int hq = rem / 33, pr = rem - hq * 33;
             const int kvh = hq / G, g = hq - kvh * G;
             ptr[u] = i < total ? base + ((size_t)((kvh * W::NC + ch) * G + g)) * 66 + 2 * pr : nullptr;
         }
-        poll_flagged_pairs<4>(c, ptr, tag, bits);
+        poll_flagged_pairs<PU>(c, ptr, tag, bits);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int i = tid + (u0 + u) * NT;
+        for (int u = 0; u < PU; ++u) {
+            const int i = tid + u * NT;
             if (i < total) {
                 const int hc = i / 33, pr = i - hc * 33;     // [chunk][hq] flattened: same order as the decode above
                 *reinterpret_cast<float2*>(S + hc * 66 + 2 * pr) =
@@ -635,35 +699,45 @@ __device__ __forceinline__ void stage_attn(FC<NW>& c, int layer, uint4* act) {
         }
     }
     PK_WSTAMP(c, 1);
-    __syncthreads();
+    csync<NW>();
     PK_WSTAMP(c, 2);
-    uint16_t* act16 = reinterpret_cast<uint16_t*>(act);
-    for (int o = tid; o < W::AD; o += NT) {
-        const int hq = o / kD, d = o - hq * kD;
-        const float* src = S + hq * 66;
-        // all shared-memory loads first (one round of latency), then the arithmetic
-        float mv[W::NC], lv[W::NC], av[W::NC];
+    // merge weights once per (query head, chunk): w = exp(m_c - M) / sum_c l_c exp(m_c - M)
+    float* wts = S + W::NC * W::QH * 66;                      // [QH][NC]
+    if (tid < W::QH) {
+        const float* src = S + tid * 66;
+        float mv[W::NC], lv[W::NC];
 #pragma unroll
         for (int ch = 0; ch < W::NC; ++ch) {
             const bool ok = ch < nc;
-            const float* sc = src + ch * W::QH * 66;
-            mv[ch] = ok ? sc[0] : -INFINITY;
-            lv[ch] = ok ? sc[1] : 0.f;
-            av[ch] = ok ? sc[2 + d] : 0.f;
+            mv[ch] = ok ? src[ch * W::QH * 66] : -INFINITY;
+            lv[ch] = ok ? src[ch * W::QH * 66 + 1] : 0.f;
         }
         float M = mv[0];       // chunk 0 always holds at least one position
 #pragma unroll
         for (int ch = 1; ch < W::NC; ++ch) M = fmaxf(M, mv[ch]);
-        float den = 0.f, a = 0.f;
+        float den = 0.f;
 #pragma unroll
         for (int ch = 0; ch < W::NC; ++ch) {
-            const float wgt = __expf(mv[ch] - M);      // exp(-inf) = 0 for empty / absent chunks
-            den = fmaf(lv[ch], wgt, den);
-            a = fmaf(av[ch], wgt, a);
+            mv[ch] = __expf(mv[ch] - M);                      // exp(-inf) = 0 for empty / absent chunks
+            den = fmaf(lv[ch], mv[ch], den);
         }
-        act16[o] = (uint16_t)f32_to_bf16_bits(__fdividef(a, den));
+        const float inv = 1.f / den;
+#pragma unroll
+        for (int ch = 0; ch < W::NC; ++ch) wts[tid * W::NC + ch] = mv[ch] * inv;
     }
-    __syncthreads();
+    csync<NW>();
+    uint16_t* act16 = reinterpret_cast<uint16_t*>(act);
+    for (int o = tid; o < W::AD; o += NT) {
+        const int hq = o / kD, d = o - hq * kD;
+        const float* src = S + hq * 66 + 2 + d;
+        const float* wq = wts + hq * W::NC;
+        float a = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < W::NC; ++ch)
+            if (ch < nc) a = fmaf(src[ch * W::QH * 66], wq[ch], a);
+        act16[o] = (uint16_t)f32_to_bf16_bits(a);
+    }
+    csync<NW>();
 }
 
 // ------------------------------------------------------------------ attention item
@@ -739,7 +813,7 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
     int r0 = ws;
 #pragma unroll 1
     do {
-        if (r0 < we) fetch_run(r0);
+        if (r0 != ws) fetch_run(r0);
         if (r0 == ws) {
             // rotated q of the G heads of this kv head, then rotated k and v of the new token: (G + 2) * 16 packets
             {
@@ -748,13 +822,14 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
                 const int which = tid >> 4, d4 = (tid & 15) * 4;
                 const int qrow = which < G ? (kvh * G + which) * kD : (which == G ? (W::QH + kvh) * kD : (W::QH + W::KVH + kvh) * kD);
                 const uint32_t* ptr[1] = {tid < (G + 2) * 16 ? qkv + qrow + d4 : nullptr};
-                poll_packets<1>(c, ptr, tag16(c, layer), pkt);
+                // the K/V loads of the first run go out while the first poll is in flight
+                poll_packets<1>(c, ptr, tag16(c, layer), pkt, [&] { if (ws < we) fetch_run(ws); });
                 if (tid < (G + 2) * 16)
                     *reinterpret_cast<uint2*>(qkvb_s + 2 * tid) =
                         make_uint2((pkt[0].x & 0xffffu) | (pkt[0].y << 16), (pkt[0].z & 0xffffu) | (pkt[0].w << 16));
             }
-            __syncthreads();
-            if (c.prof) c.prof[12] = global_ns();
+            csync<NW>();
+            if (c.prof) c.prof[11] = global_ns();
             // the item that holds position seq-1 appends the new token's K/V to the paged cache (slot -1: skip)
             if (end == seq && c.warp == 0 && lane < 16 && sh.slot_off >= 0) {
                 uint16_t* kvw = const_cast<uint16_t*>(kvr);
@@ -765,6 +840,7 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
             }
         }
         if (r0 < we) {
+            if (c.prof && r0 == ws) c.prof[16] = global_ns();
             const int pp = r0 + pl;
             const bool valid = pp < we;
             uint32_t kwd[16];
@@ -780,7 +856,9 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
                     kwd[4 * i] = kq[i].x; kwd[4 * i + 1] = kq[i].y; kwd[4 * i + 2] = kq[i].z; kwd[4 * i + 3] = kq[i].w;
                 }
             }
-            float pr[G];
+            // The G heads are processed side by side in every step (shuffles keep their program order, so
+            // a head-by-head loop would run the three dependent chains one after the other).
+            float sc[G], mx[G], pr[G];
 #pragma unroll
             for (int hh = 0; hh < G; ++hh) {
                 float d0 = 0.f, d1 = 0.f;
@@ -792,26 +870,40 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
                     d0 = fma2_bf16(kwd[4 * i + 2], q4.z, d0);
                     d1 = fma2_bf16(kwd[4 * i + 3], q4.w, d1);
                 }
-                float dsum = d0 + d1;
-                dsum += __shfl_xor_sync(kFullMask, dsum, 1);
+                sc[hh] = d0 + d1;
+            }
+            if (c.prof && r0 == ws) c.prof[17] = global_ns();
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) sc[hh] += __shfl_xor_sync(kFullMask, sc[hh], 1);
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) {
                 // bf16 matmul output, then the exact 1/8 scale (HF eager_attention_forward)
-                const float sc = valid ? round_bf16(dsum) * 0.125f : -INFINITY;
-                float mx = sc;
+                sc[hh] = valid ? round_bf16(sc[hh]) * 0.125f : -INFINITY;
+                mx[hh] = sc[hh];
+            }
+            // warp maximum with one redux per head: floats compare like these integer keys
 #pragma unroll
-                for (int o = 2; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(kFullMask, mx, o));
-                const float mn = fmaxf(m[hh], mx);
+            for (int hh = 0; hh < G; ++hh) {
+                int key = __float_as_int(mx[hh]);
+                key ^= (key >> 31) & 0x7fffffff;
+                key = __reduce_max_sync(kFullMask, key);
+                mx[hh] = __int_as_float(key ^ ((key >> 31) & 0x7fffffff));
+            }
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) {
+                const float mn = fmaxf(m[hh], mx[hh]);
                 const float alpha = (mn == -INFINITY) ? 1.f : __expf(m[hh] - mn);
-                pr[hh] = (sc == -INFINITY) ? 0.f : __expf(sc - mn);
-                float ps = pr[hh];
-#pragma unroll
-                for (int o = 2; o < 32; o <<= 1) ps += __shfl_xor_sync(kFullMask, ps, o);
-                l[hh] = l[hh] * alpha + ps;
+                pr[hh] = (sc[hh] == -INFINITY) ? 0.f : __expf(sc[hh] - mn);
                 m[hh] = mn;
+                // per-lane share of the denominator (one lane of every position pair); summed over the warp after
+                // the last run -- the rescale factor is warp-uniform, so the order does not matter
+                l[hh] = l[hh] * alpha + (half == 0 ? pr[hh] : 0.f);
                 acc[hh][0] *= alpha;
                 acc[hh][1] *= alpha;
                 if (half == 0) prob_s[hh * 16 + pl] = pr[hh];
             }
             __syncwarp();
+            if (c.prof && r0 == ws) c.prof[18] = global_ns();
             const uint32_t vnew = qkvb_s[(G + 1) * 32 + lane];
 #pragma unroll
             for (int hh = 0; hh < G; ++hh) {
@@ -835,7 +927,11 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
         }
         r0 += 16;
     } while (r0 < we);
-    if (c.prof) c.prof[13] = global_ns();
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) l[hh] += __shfl_xor_sync(kFullMask, l[hh], off);
+    if (c.prof) c.prof[12] = global_ns();
     // park the warp's partial: lanes hold two dims each
     float* wpart = c.attn + c.warp * G * 66;
 #pragma unroll
@@ -847,8 +943,8 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
         }
         *reinterpret_cast<float2*>(dst + 2 + 2 * lane) = make_float2(acc[hh][0], acc[hh][1]);
     }
-    __syncthreads();
-    if (c.prof) c.prof[14] = global_ns();
+    csync<NW>();
+    if (c.prof) c.prof[13] = global_ns();
     // combine the warps; thread (hh, d) publishes one accumulator word, d == 0 also m and l
     unsigned long long* part =
         p.w_part + ((size_t)(layer & 1) * W::KVH * W::NC + (size_t)(kvh * W::NC + chunk)) * G * 66;
@@ -856,10 +952,10 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
     for (int t = tid; t < G * kD; t += NT) {
         const int hh = t / kD, d = t % kD;
         float M = -INFINITY;
-#pragma unroll 4
+#pragma unroll 8
         for (int w = 0; w < NW; ++w) M = fmaxf(M, c.attn[(w * G + hh) * 66]);
         float lt = 0.f, a = 0.f;
-#pragma unroll 4
+#pragma unroll 8
         for (int w = 0; w < NW; ++w) {
             const float* src = c.attn + (w * G + hh) * 66;
             const float f = (src[0] == -INFINITY) ? 0.f : __expf(src[0] - M);
@@ -873,10 +969,10 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
         }
         st_flagged(dst + 2 + d, __float_as_uint(a), tag);
     }
-    __syncthreads();     // c.attn is reused by the merge staging
+    csync<NW>();     // c.attn is reused by the merge staging
     // item index = chunk * KVH + kvh (the CTA index)
-    if (tid == 0) st_flagged(p.w_gate + (size_t)(layer & 1) * W::KVH * W::NC + chunk * W::KVH + kvh, 1u, tag);
-    if (c.prof) c.prof[15] = global_ns();
+    if (tid == 0) st_flagged(p.w_gate + ((size_t)(layer & 1) * W::KVH * W::NC + chunk * W::KVH + kvh) * 16, 1u, tag);
+    if (c.prof) c.prof[14] = global_ns();
 }
 
 // L2 prefetch of this CTA's chunk (K and V rows of the positions resolved at kernel start).
@@ -898,13 +994,12 @@ __device__ __forceinline__ void attention_prefetch(FC<NW>& c, int layer) {
 
 // ------------------------------------------------------------------ the kernel
 template <class W, int NW>
-__global__ void __launch_bounds__(NW * 32, 1) decode_fast_kernel(const FastParams p) {
-    constexpr int NT = NW * 32;
+__global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const FastParams p) {
+    constexpr int NT = (NW + 1) * 32;      // NW consumer warps + the producer warp
+    constexpr int NTC = NW * 32;           // consumer threads
     constexpr int G = W::G;
     constexpr int ACT = W::H > W::I ? W::H : W::I;
-    constexpr int kAttnWords = (W::NC * W::QH * 66) > (((NW * G * 66 + 3) & ~3) + (G + 2) * kD + (G + 2) * 32 + NW * G * 16)
-                                   ? (W::NC * W::QH * 66)
-                                   : (((NW * G * 66 + 3) & ~3) + (G + 2) * kD + (G + 2) * 32 + NW * G * 16);
+    constexpr int kAttnWords = attn_words<W, NW>();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     FShared<NW>& sh = *reinterpret_cast<FShared<NW>*>(smem_raw);
     size_t off = (sizeof(FShared<NW>) + 127) & ~size_t(127);
@@ -950,6 +1045,7 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_fast_kernel(const FastParam
     }
     if (tid < NW * kFE) {
         mbar_init(&sh.full[tid / kFE][tid % kFE], 1);
+        mbar_init(&sh.empty[tid / kFE][tid % kFE], 1);
         sh.ent_off[tid / kFE][tid % kFE] = 0u;
         sh.ent_foot[tid / kFE][tid % kFE] = 0u;
     }
@@ -979,17 +1075,16 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_fast_kernel(const FastParam
     __syncthreads();
 
     FC<NW> c{p, sh, {act0, act1}, {res0, res1}, attn, ring_base + (size_t)warp * p.ring_bytes, 0u, 0u, warp, lane, cta, ncta,
-             0u, 0u, 0u, 0u, 0, -1, 0, {make_uint2(0u, 0u), make_uint2(0u, 0u)}, nullptr
+             0u, {make_uint2(0u, 0u), make_uint2(0u, 0u)}, 0u, false, nullptr
 #ifdef PK_FAST_WPROF
              , nullptr
 #endif
     };
     c.T16 = ((sh.epoch % 511u) + 1u) << 23;
     c.T32 = (sh.epoch + 1u) << 7;
-    const uint64_t pol = evict_first_policy();
-    // start the weight stream before anything else
-    cursor_next_phase(c);
-    issue_more<W, NW>(c, pol);
+    if (warp == NW) {
+        producer_loop<W, NW>(p, sh, ring_base, lane);
+    } else {
 
     // block-table look-ups of this CTA's attention item do not depend on the layer: resolve them once
     {
@@ -1019,9 +1114,9 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_fast_kernel(const FastParam
         const uint2* nw0 = reinterpret_cast<const uint2*>(sh.norm_ptr[0]);
 #pragma unroll
         for (int u = 0; u < 2; ++u)
-            if (tid + u * NT < NP) c.nwv[u] = __ldg(nw0 + tid + u * NT);
+            if (tid + u * NTC < NP) c.nwv[u] = __ldg(nw0 + tid + u * NTC);
     }
-    __syncthreads();
+    csync<NW>();
 
     // One loop over the global phase index (4 per layer, then the final norm + lm_head) with a single call
     // site for every building block, so each exists once in the instruction stream.
@@ -1038,6 +1133,14 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_fast_kernel(const FastParam
         c.prof = prof;
         uint4* act = (t == kO || t == kDown) ? act1 : act0;
         const float* res = (t == kGU || t == kDown) ? res1 : res0;
+        // The weights of this phase normally landed long ago: confirm it now, before the activations are waited
+        // for, so that the first dot product can start right behind the staging barrier.
+        c.pre_ok = false;
+        if (sh.row_a[t][warp] < sh.row_b[t][warp] && !(last && !p.lm_head)) {
+            const uint32_t slot = c.consumed % kFE;
+            c.pre_ok = __all_sync(kFullMask, f_wait_mbar(c, &sh.full[warp][slot], (c.consumed / kFE) & 1));
+            c.pre_off = sh.ent_off[warp][slot];
+        }
 #ifdef PK_FAST_WPROF
         c.wprof = (p.profile && lane == 0 && layer == kWprofLayer && !last)
                       ? p.profile + (size_t)ncta * p.L * kProfSlots + ((size_t)(cta * NW + warp) * 4 + t) * 8
@@ -1059,32 +1162,26 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_fast_kernel(const FastParam
             if (prof) prof[3] = global_ns();
             stage_attn<W, NW>(c, layer, act1);
         } else {
-            stage_copy<W::I, NW>(c, p.w_act + par * W::I, tag16(c, layer), act1);
+            stage_copy<W, W::I, NW>(c, p.w_act + par * W::I, tag16(c, layer), act1);
         }
         if (prof) prof[1 + 2 * t + (t >= kO ? 1 : 0)] = global_ns();     // slots 1, 4, 6, 8
         PK_WSTAMP(c, 3);
         if (last) {
             if (cta == 0)
-                for (int i = tid; i < W::H / 2; i += NT)
+                for (int i = tid; i < W::H / 2; i += NTC)
                     reinterpret_cast<uint32_t*>(p.out_hidden)[i] = reinterpret_cast<const uint32_t*>(act0)[i];
             if (!p.lm_head) break;
         }
-        gemv_phase<W, NW>(c, t, layer, act, res, pol);
+        gemv_phase<W, NW>(c, t, layer, act, res);
         // Nobody in this CTA polls the next hand-off before the CTA's own results are on their way: reads of a
         // line that is still being written slow the writes down (measured: several microseconds per hand-off
         // when the warps without rows in a phase started polling at once).
-        if (!(p.dbg & 1)) __syncthreads();
+        if (!(p.dbg & 1)) csync<NW>();
         if (prof) prof[2 + 2 * t + (t >= kO ? 1 : 0)] = global_ns();     // slots 2, 5, 7, 9
         PK_WSTAMP(c, 6);
     }
 
-    // never leave while bulk copies into this CTA's shared memory are in flight (only after an abort)
-    for (uint32_t n = c.consumed; n < c.issued; ++n) {
-        const uint32_t slot = n % kFE;
-        unsigned spins = 0;
-        while (!mbar_probe(&sh.full[warp][slot], (n / kFE) & 1))
-            if (++spins >= p.spin_limit) break;
-    }
+    }   // consumer warps
     __syncthreads();
     // The last CTA to finish publishes the greedy id, optionally advances the step inputs in place
     // (device-driven generation), and opens the next launch's epoch.

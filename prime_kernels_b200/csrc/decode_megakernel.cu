@@ -1713,7 +1713,7 @@ static FastLayout fast_layout(const ModelGeom& g) {
     l.h1 = take(2 * (size_t)g.H * 4);
     l.act = take(2 * (size_t)g.I * 4);
     l.part = take(2 * (size_t)g.KVH * fast_nc(g) * G * 66 * 8);
-    l.gate = take(2 * (size_t)g.KVH * fast_nc(g) * 8);
+    l.gate = take(2 * (size_t)g.KVH * fast_nc(g) * 128);
     l.total = off;
     return l;
 }
@@ -1762,7 +1762,7 @@ static std::unordered_map<const void*, WsState> g_ws_ready;     // workspace poi
 static std::unordered_map<unsigned long long, int> g_kernel_smem;
 static unsigned g_spin_limit = kSpinLimit;
 static int g_fast_dbg = 0;
-static int g_fast_warps = -1;        // batch-1 fast path: -1 = not decided yet (environment), 0 = off, 8 / 16 = warps per CTA
+static int g_fast_warps = -1;        // batch-1 fast path: -1 = not decided yet (environment), 0 = off, 7 / 8 = consumer warps per CTA
 
 static unsigned long long geom_sig(const ModelGeom& g) {
     unsigned long long h = 1469598103934665603ull;
@@ -1929,9 +1929,9 @@ constexpr int kFastNotEligible = -7777;
 static int fast_warps() {
     std::lock_guard<std::mutex> lk(g_mu);
     if (g_fast_warps < 0) {
-        const char* e = std::getenv("PK_DECODE_FAST");        // "0" = generic kernel only, "8" / "16" = warps per CTA
-        g_fast_warps = e ? std::atoi(e) : 16;
-        if (g_fast_warps != 0 && g_fast_warps != 8 && g_fast_warps != 16) g_fast_warps = 16;
+        const char* e = std::getenv("PK_DECODE_FAST");        // "0" = generic kernel only, "7" / "8" = consumer warps per CTA
+        g_fast_warps = e ? std::atoi(e) : 8;
+        if (g_fast_warps != 0 && g_fast_warps != 7 && g_fast_warps != 8) g_fast_warps = 8;
     }
     return g_fast_warps;
 }
@@ -1940,20 +1940,18 @@ template <class W, int NW>
 static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo& di, const WsLayout& lay) {
     using namespace fast;
     if (di.sm_count < kNominalCtas || di.sm_count < W::NC * W::KVH) return kFastNotEligible;
-    constexpr int G = W::G;
     constexpr int ACT = W::H > W::I ? W::H : W::I;
-    constexpr size_t kItemWords = ((NW * G * 66 + 3) & ~3) + (G + 2) * kD + (G + 2) * 32 + NW * G * 16;
-    constexpr size_t kAttnWords = (size_t)(W::NC * W::QH * 66) > kItemWords ? (size_t)(W::NC * W::QH * 66) : kItemWords;
+    constexpr size_t kAttnWords = (size_t)attn_words<W, NW>();
     const size_t fixed = align_up(sizeof(FShared<NW>), 128) + 2 * align_up((size_t)ACT * 2, 128) +
                          2 * align_up((size_t)W::H * 4, 128) + align_up(kAttnWords * 4, 128);
     if ((size_t)di.smem_optin < fixed + (size_t)NW * 4096) return kFastNotEligible;
     const int rw = (int)(((size_t)di.smem_optin - fixed) / NW / 128 * 128);
-    // the largest entry of any phase must fit the ring twice (one in use, one in flight)
+    // every entry must fit the ring (an empty ring restarts at its base)
 #define PK_ENT(T) (Ph<W, NW, T>::K * 2 * Ph<W, NW, T>::RPE * (Ph<W, NW, T>::PAIR ? 2 : 1))
     const int ent[5] = {PK_ENT(kQKV), PK_ENT(kO), PK_ENT(kGU), PK_ENT(kDown), PK_ENT(kLM)};
 #undef PK_ENT
     for (int t = 0; t < 5; ++t)
-        if (2 * ent[t] > rw) return kFastNotEligible;
+        if (ent[t] > rw) return kFastNotEligible;
     const size_t smem = fixed + (size_t)NW * rw;
     auto fn = decode_fast_kernel<W, NW>;
     int rc = ensure_smem(reinterpret_cast<const void*>(fn), smem);
@@ -2008,7 +2006,7 @@ static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo
     p.dbg = g_fast_dbg;
     p.eps = g.eps;
     void* args[] = {&p};
-    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fn), dim3(di.sm_count), dim3(NW * 32), args,
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fn), dim3(di.sm_count), dim3((NW + 1) * 32), args,
                                                 smem, a.stream);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
@@ -2026,8 +2024,8 @@ static int fast_launch(const ModelGeom& g, const StepArgs& a, const DeviceInfo& 
     using W360 = fast::Widths<960, 2560, 15, 5>;
     const bool is135 = g.H == 576 && g.I == 1536 && g.QH == 9 && g.KVH == 3;
     const bool is360 = g.H == 960 && g.I == 2560 && g.QH == 15 && g.KVH == 5;
-    if (is135) return nw == 8 ? fast_launch_t<W135, 8>(g, a, di, lay) : fast_launch_t<W135, 16>(g, a, di, lay);
-    if (is360) return nw == 8 ? fast_launch_t<W360, 8>(g, a, di, lay) : fast_launch_t<W360, 16>(g, a, di, lay);
+    if (is135) return nw == 8 ? fast_launch_t<W135, 8>(g, a, di, lay) : fast_launch_t<W135, 7>(g, a, di, lay);
+    if (is360) return nw == 8 ? fast_launch_t<W360, 8>(g, a, di, lay) : fast_launch_t<W360, 7>(g, a, di, lay);
     return kFastNotEligible;
 }
 
@@ -2253,10 +2251,10 @@ extern "C" int pk_decode_status(void* workspace, void* stream) {
 extern "C" const char* pk_status_string(int status) { return status_string(status); }
 
 // Tuning / test knobs (process-wide).
-// Batch-1 bf16 steps of SmolLM2-135M / 360M widths run on the specialised kernel with `warps` (8 or 16)
-// warps per CTA; 0 sends every step to the generic kernel.  Default: environment PK_DECODE_FAST, else 16.
+// Batch-1 bf16 steps of SmolLM2-135M / 360M widths run on the specialised kernel with `warps` (7 or 8)
+// consumer warps per CTA; 0 sends every step to the generic kernel.  Default: environment PK_DECODE_FAST, else 8.
 extern "C" int pk_decode_set_fast_path(int warps) {
-    if (warps != 0 && warps != 8 && warps != 16) return kErrShape;
+    if (warps != 0 && warps != 7 && warps != 8) return kErrShape;
     std::lock_guard<std::mutex> lk(g_mu);
     g_fast_warps = warps;
     return 0;

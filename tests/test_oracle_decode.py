@@ -59,25 +59,54 @@ def test_restatement_against_committed_135m_golden_first_steps():
         cur = torch.tensor([int(z["ids"][s])])
 
 
-def test_summation_order_noise_floor_on_the_headline_configuration():
-    """Two CPU implementations with identical rounding points and identical KV caches (HuggingFace eager and
-    the restatement, which differ only in fp32 summation order) on SmolLM2-360M with a 512-token context:
-    their bf16 logits differ by 3-5e-2 over the vocabulary while the greedy ids agree.  This is the floor any
-    independent implementation (the CUDA kernel included) sits on at this configuration; the per-step 2e-2
-    target is only reachable on the shallower 135M / short-context configuration."""
+def test_noise_floor_on_the_headline_configuration_in_both_probability_modes():
+    """HuggingFace eager against the CPU restatement on SmolLM2-360M with HuggingFace's own 511-token prefill
+    cache, two decode steps, in both softmax-probability modes.
+
+    ``probs="bf16"`` has the same rounding points as HuggingFace (layer 0 comes out bit-identical, 0 of 960
+    elements differ) and still ends 0.035-0.041 away at the logits: the first bf16 flips caused by fp32 summation
+    order appear in layer 1 (65 of 960 elements) and this random-init 32-layer stack amplifies them.
+    ``probs="fp32"`` (what the split-KV kernel computes) adds a real rounding-point difference -- 668 of 960
+    layer-0 outputs differ by one bf16 ulp -- and ends 0.039-0.046 away.  Either way the per-step 2e-2 target is
+    out of reach for an independent implementation at this depth; rounding the probabilities to bf16 does not
+    close the gap.  Greedy ids agree in both modes."""
     from prime_kernels_b200.decode import SMOLLM2_360M as geom
 
     w = harness.make_weights(geom, 0)
     prompt = torch.randint(0, geom.vocab, (1, 512), generator=torch.Generator().manual_seed(1234))
     ref = decode_hf.run(geom, w, prompt, 2)
     cs = harness.make_cos_sin_cache(geom, 640)
-    keys = [[ref["prefill_k"][l][0].clone()] for l in range(geom.layers)]
-    vals = [[ref["prefill_v"][l][0].clone()] for l in range(geom.layers)]
-    cur = prompt[:, -1]
-    worst = 0.0
-    for s in range(2):
-        _, logits, _ = R.decode_step(geom, w, cur, torch.tensor([511 + s]), keys, vals, cs)
-        worst = max(worst, (logits - ref["logits"][s]).abs().max().item())
-        assert (logits.argmax(-1) == ref["ids"][s]).all()
-        cur = ref["ids"][s]
-    assert 2e-2 < worst <= 1.25e-1
+    worst = {}
+    for mode in ("fp32", "bf16"):
+        keys = [[ref["prefill_k"][l][0].clone()] for l in range(geom.layers)]
+        vals = [[ref["prefill_v"][l][0].clone()] for l in range(geom.layers)]
+        cur = prompt[:, -1]
+        worst[mode] = 0.0
+        for s in range(2):
+            _, logits, _ = R.decode_step(geom, w, cur, torch.tensor([511 + s]), keys, vals, cs, probs=mode)
+            worst[mode] = max(worst[mode], (logits - ref["logits"][s]).abs().max().item())
+            assert (logits.argmax(-1) == ref["ids"][s]).all()
+            cur = ref["ids"][s]
+    assert 2e-2 < worst["fp32"] <= 7e-2
+    assert 2e-2 < worst["bf16"] <= 7e-2
+
+
+def test_bf16_probabilities_reproduce_hf_layer_zero_exactly():
+    """With the probabilities rounded to bf16 where HuggingFace rounds them, the first layer of the restatement
+    equals HuggingFace eager bit for bit (small geometry, several requests): the rounding points of the whole
+    layer are the ones HuggingFace uses."""
+    geom = Geometry("tiny1", 192, 512, 1, 3, 1, vocab=512)
+    w = harness.make_weights(geom, 3, norm_weights="random")
+    prompt = torch.randint(0, 512, (3, 40), generator=torch.Generator().manual_seed(5))
+    model = decode_hf.build_model(geom, w)
+    with torch.no_grad():
+        pre = model(input_ids=prompt[:, :-1], use_cache=True)
+        pk, pv = decode_hf._cache_layers(pre.past_key_values)
+        pk, pv = [k.clone() for k in pk], [v.clone() for v in pv]
+        res = model(input_ids=prompt[:, -1:], past_key_values=pre.past_key_values, use_cache=True,
+                    output_hidden_states=True)
+    cs = harness.make_cos_sin_cache(geom, 64)
+    keys = [[pk[0][b].clone() for b in range(3)]]
+    vals = [[pv[0][b].clone() for b in range(3)]]
+    hid, _, _ = R.decode_step(geom, w, prompt[:, -1], torch.tensor([39, 39, 39]), keys, vals, cs, probs="bf16")
+    assert torch.equal(hid.float(), res.hidden_states[-1][:, -1].float())
