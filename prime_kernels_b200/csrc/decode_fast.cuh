@@ -41,13 +41,10 @@ struct Widths {
     static_assert(QH_ % KVH_ == 0 && H_ % 32 == 0 && I_ % 32 == 0, "unsupported widths");
 };
 
-// Floats of the attention scratch: the larger of an item's working set (per-warp partials, staged q/k/v,
-// probabilities) and the merge staging (partials of every (chunk, query head) plus the merge weights).
+// Floats of the attention scratch: an item's working set (per-warp partials, staged q/k/v, probabilities).
 template <class W, int NW>
 __host__ __device__ constexpr int attn_words() {
-    constexpr int item = ((NW * W::G * 66 + 3) & ~3) + (W::G + 2) * kD + (W::G + 2) * 32 + NW * W::G * 16;
-    constexpr int merge = W::NC * W::QH * 66 + W::QH * W::NC;
-    return ((item > merge ? item : merge) + 3) & ~3;
+    return (((NW * W::G * 66 + 3) & ~3) + (W::G + 2) * kD + (W::G + 2) * 32 + NW * W::G * 16 + 3) & ~3;
 }
 
 struct FastParams {
@@ -74,8 +71,7 @@ struct FastParams {
     uint32_t* w_h1;                     // [2][H]
     uint32_t* w_act;                    // [2][I]
     unsigned long long* w_part;         // [2][KVH][NC][G][66]  words [tag32 | fp32]
-    unsigned long long* w_gate;         // [2][KVH * NC][16]    one word [tag32 | 1] per attention item in a 128-byte line of its
-                                        //                      own (a polled line must receive one write), written after the partials
+    uint32_t* w_attn;                   // [2][QH * 64]         merged attention output, words [tag16 | bf16]
     long long k_off, v_off, block_stride, token_stride, head_stride;
     int block_size, bt_stride, ids_i64, cs_fp32;
     int L, V, lm_head, advance, max_seq_len, ring_bytes;
@@ -643,101 +639,88 @@ __device__ __forceinline__ void stage_copy(FC<NW>& c, const uint32_t* src_words,
     csync<NW>();
 }
 
-// Input of the O projection: pull the split-KV partials of every (query head, chunk), merge them with
-// log-sum-exp and write the bf16 attention output to `act`.
+// One warp merges the split-KV partials of one query head with log-sum-exp and publishes that head's bf16
+// attention output (64 words [tag16 | bf16]).  Only QH warps of the grid poll the partials, so the lines the
+// attention items are writing are not read by the whole grid; everybody else waits for the 64-word results,
+// which are written once (pulling all partials into every CTA cost 6 MB of L2 traffic per layer and ~1 us).
+// Lane = two output dims; lane c also owns the (m, l) statistics of chunk c.
 template <class W, int NW>
-__device__ __forceinline__ void stage_attn(FC<NW>& c, int layer, uint4* act) {
-    constexpr int NT = NW * 32;
+__device__ __forceinline__ void merge_head(FC<NW>& c, int layer, int hq) {
     constexpr int G = W::G;
-    constexpr int PER_C = W::QH * 33;                       // 16-byte loads per chunk
-    constexpr int PU = (W::NC * PER_C + NT - 1) / NT;       // loads per thread at the most
-    const int tid = threadIdx.x;
-    const int nc = c.sh.nc;
-    const int total = nc * PER_C;
-    const uint32_t tag = tag32(c, layer);
-    const unsigned long long* base = c.p.w_part + (size_t)(layer & 1) * W::KVH * W::NC * G * 66;
-    float* S = c.attn;                                       // [chunk][hq][66]
-    // Gate: one warp waits for the "item published" word of every attention item before anybody touches the
-    // partials, so the lines the item CTAs are writing are not being read by the whole grid in the meantime.
-    // (The gate is only a hint: every partial word still validates itself below.)
-    if (c.warp == 0) {
-        const int nitems = nc * W::KVH;
-        for (int i0 = 0; i0 < nitems; i0 += 32) {
-            const int i = i0 + c.lane;
-            if (i < nitems && !f_aborted(c)) {
-                const unsigned long long* g = c.p.w_gate + ((size_t)(layer & 1) * W::KVH * W::NC + i) * 16;   // one 128-byte line per item
-                unsigned spins = 0;
-                while ((uint32_t)(ld_flagged(g) >> 32) != tag) {
-                    if ((++spins & 255u) == 0 && f_give_up(c, spins)) break;
-                }
+    static_assert(W::NC <= 32, "one lane per chunk");
+    const int lane = c.lane, nc = c.sh.nc;
+    const int kvh = hq / G, g = hq - kvh * G;
+    const unsigned long long* part =
+        c.p.w_part + ((size_t)(layer & 1) * W::KVH * W::NC + (size_t)kvh * W::NC) * G * 66 + g * 66;
+    constexpr size_t cstride = (size_t)G * 66;
+    const unsigned long long* ptr[1 + W::NC];
+    ptr[0] = lane < nc ? part + lane * cstride : nullptr;                       // words 0, 1: m and l of chunk `lane`
+#pragma unroll
+    for (int ch = 0; ch < W::NC; ++ch) ptr[1 + ch] = ch < nc ? part + ch * cstride + 2 + 2 * lane : nullptr;
+    uint32_t bits[2 * (1 + W::NC)];
+    poll_flagged_pairs<1 + W::NC>(c, ptr, tag32(c, layer), bits);
+    const float mc = lane < nc ? __uint_as_float(bits[0]) : -INFINITY;
+    const float lc = lane < nc ? __uint_as_float(bits[1]) : 0.f;
+    const float M = warp_max(mc);                          // chunk 0 always holds at least one position
+    const float wc = __expf(mc - M);                       // exp(-inf) = 0 for empty / absent chunks
+    const float den = warp_sum(lc * wc);
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < W::NC; ++ch) {
+        const float wgt = __shfl_sync(kFullMask, wc, ch);
+        if (ch < nc) {
+            a0 = fmaf(wgt, __uint_as_float(bits[2 + 2 * ch]), a0);
+            a1 = fmaf(wgt, __uint_as_float(bits[3 + 2 * ch]), a1);
+        }
+    }
+    const float inv = 1.f / den;
+    const uint32_t T = tag16(c, layer);
+    uint32_t* dst = c.p.w_attn + (layer & 1) * W::AD + hq * kD + 2 * lane;
+    // two self-validating words in one 8-byte store: a head's 64 words are two stores of 16 lanes' worth each
+    const uint32_t w0 = f32_to_bf16_bits(a0 * inv) | T, w1 = f32_to_bf16_bits(a1 * inv) | T;
+    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(w0), "r"(w1) : "memory");
+}
+
+// K (this lane's position and half of the head dim) and V (all 16 positions, this lane's two dims) of one
+// run of 16 cache positions starting at r0, into registers.  The position seq-1 (the new token) is never
+// read from the cache.  ws / we: this warp's share of its CTA's chunk.
+template <int NW>
+__device__ __forceinline__ void fetch_kv_run(FC<NW>& c, int layer, int r0, int ws, int we, bool pre_ok, uint4 (&kq)[4],
+                                             uint32_t (&vw)[16]) {
+    const FastParams& p = c.p;
+    FShared<NW>& sh = c.sh;
+    const int lane = c.lane, pl = lane >> 1, half = lane & 1;
+    const int seq = sh.seq;
+    const uint16_t* kvr = reinterpret_cast<const uint16_t*>(layer < kKvPtrs ? sh.kv_ptr[layer] : __ldg(p.kv + layer));
+    const long long hs = (long long)sh.item_kvh * p.head_stride;
+    long long* offs = sh.kv_off[c.warp] + (((r0 - ws) >> 4) & (kPre - 1)) * 16;
+    if (!pre_ok) {
+        // long context: resolve this run's block-table entries now (lanes 0..15, one position each)
+        if (lane < 16) {
+            const int pp = r0 + lane;
+            long long off = -1;
+            if (pp < we) {
+                const int blk = __ldg(p.block_table + pp / p.block_size);
+                off = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride;
             }
+            offs[lane] = off;
         }
+        __syncwarp();
     }
-    csync<NW>();
-    // every pair this thread is responsible for is requested in the same round (the gate has told us the
-    // partials are on their way, so one L2 round trip normally brings them all)
-    {
-        uint32_t bits[2 * PU];
-        const unsigned long long* ptr[PU];
+    const int pp = r0 + pl;
+    const bool own_ok = pp < we && pp != seq - 1;
+    const long long e_own = own_ok ? offs[pl] + hs : 0;
 #pragma unroll
-        for (int u = 0; u < PU; ++u) {
-            const int i = tid + u * NT;
-            const int ch = i / PER_C, rem = i - ch * PER_C;
-            const int hq = rem / 33, pr = rem - hq * 33;
-            const int kvh = hq / G, g = hq - kvh * G;
-            ptr[u] = i < total ? base + ((size_t)((kvh * W::NC + ch) * G + g)) * 66 + 2 * pr : nullptr;
-        }
-        poll_flagged_pairs<PU>(c, ptr, tag, bits);
+    for (int i = 0; i < 4; ++i)
+        kq[i] = own_ok ? __ldcg(reinterpret_cast<const uint4*>(kvr + p.k_off + e_own + 32 * half) + i)
+                       : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-        for (int u = 0; u < PU; ++u) {
-            const int i = tid + u * NT;
-            if (i < total) {
-                const int hc = i / 33, pr = i - hc * 33;     // [chunk][hq] flattened: same order as the decode above
-                *reinterpret_cast<float2*>(S + hc * 66 + 2 * pr) =
-                    make_float2(__uint_as_float(bits[2 * u]), __uint_as_float(bits[2 * u + 1]));
-            }
-        }
+    for (int j = 0; j < 16; ++j) {
+        const int pj = r0 + j;
+        const bool ok = pj < we && pj != seq - 1;
+        vw[j] = ok ? __ldcg(reinterpret_cast<const uint32_t*>(kvr + p.v_off + offs[j] + hs) + lane) : 0u;
     }
-    PK_WSTAMP(c, 1);
-    csync<NW>();
-    PK_WSTAMP(c, 2);
-    // merge weights once per (query head, chunk): w = exp(m_c - M) / sum_c l_c exp(m_c - M)
-    float* wts = S + W::NC * W::QH * 66;                      // [QH][NC]
-    if (tid < W::QH) {
-        const float* src = S + tid * 66;
-        float mv[W::NC], lv[W::NC];
-#pragma unroll
-        for (int ch = 0; ch < W::NC; ++ch) {
-            const bool ok = ch < nc;
-            mv[ch] = ok ? src[ch * W::QH * 66] : -INFINITY;
-            lv[ch] = ok ? src[ch * W::QH * 66 + 1] : 0.f;
-        }
-        float M = mv[0];       // chunk 0 always holds at least one position
-#pragma unroll
-        for (int ch = 1; ch < W::NC; ++ch) M = fmaxf(M, mv[ch]);
-        float den = 0.f;
-#pragma unroll
-        for (int ch = 0; ch < W::NC; ++ch) {
-            mv[ch] = __expf(mv[ch] - M);                      // exp(-inf) = 0 for empty / absent chunks
-            den = fmaf(lv[ch], mv[ch], den);
-        }
-        const float inv = 1.f / den;
-#pragma unroll
-        for (int ch = 0; ch < W::NC; ++ch) wts[tid * W::NC + ch] = mv[ch] * inv;
-    }
-    csync<NW>();
-    uint16_t* act16 = reinterpret_cast<uint16_t*>(act);
-    for (int o = tid; o < W::AD; o += NT) {
-        const int hq = o / kD, d = o - hq * kD;
-        const float* src = S + hq * 66 + 2 + d;
-        const float* wq = wts + hq * W::NC;
-        float a = 0.f;
-#pragma unroll
-        for (int ch = 0; ch < W::NC; ++ch)
-            if (ch < nc) a = fmaf(src[ch * W::QH * 66], wq[ch], a);
-        act16[o] = (uint16_t)f32_to_bf16_bits(a);
-    }
-    csync<NW>();
+    if (!pre_ok) __syncwarp();
 }
 
 // ------------------------------------------------------------------ attention item
@@ -745,7 +728,8 @@ __device__ __forceinline__ void stage_attn(FC<NW>& c, int layer, uint4* act) {
 // runs of 16 positions.  Scores: lane = (position, half of the head dim); P.V: lane = two output dims.
 // All K and V loads of the first run are issued before the new token's q/k/v words are waited for.
 template <class W, int NW>
-__device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
+__device__ __forceinline__ void attention_item(FC<NW>& c, int layer, const int ws, const int we, const bool pre_ok,
+                                               uint4 (&kq)[4], uint32_t (&vw)[16]) {
     constexpr int G = W::G;
     constexpr int NT = NW * 32;
     const FastParams& p = c.p;
@@ -753,12 +737,7 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
     const int lane = c.lane, tid = threadIdx.x;
     const int kvh = sh.item_kvh, chunk = sh.item_chunk;
     const int seq = sh.seq;
-    const int start = chunk * sh.lc;
-    const int end = min(start + sh.lc, seq);
-    const int ppw = (((end - start + NW - 1) / NW) + 15) & ~15;
-    const int ws = min(start + c.warp * ppw, end);
-    const int we = min(ws + ppw, end);
-    const bool pre_ok = ppw <= kPre * 16;        // every run's offsets were resolved at kernel start
+    const int end = min((chunk + 1) * sh.lc, seq);
     const uint16_t* kvr = reinterpret_cast<const uint16_t*>(layer < kKvPtrs ? sh.kv_ptr[layer] : __ldg(p.kv + layer));
     const long long hs = (long long)kvh * p.head_stride;
     const int pl = lane >> 1, half = lane & 1;
@@ -767,38 +746,6 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
     uint32_t* qkvb_s = reinterpret_cast<uint32_t*>(c.attn + kPartWords);       // [(G+2)*32] packed bf16: rotated q, k; v
     float* prob_s = reinterpret_cast<float*>(qkvb_s + (G + 2) * 32) + c.warp * G * 16;
 
-    uint4 kq[4];
-    uint32_t vw[16];
-    auto fetch_run = [&](int r0) {
-        long long* offs = sh.kv_off[c.warp] + (((r0 - ws) >> 4) & (kPre - 1)) * 16;
-        if (!pre_ok) {
-            // long context: resolve this run's block-table entries now (lanes 0..15, one position each)
-            if (lane < 16) {
-                const int pp = r0 + lane;
-                long long off = -1;
-                if (pp < we) {
-                    const int blk = __ldg(p.block_table + pp / p.block_size);
-                    off = (long long)blk * p.block_stride + (long long)(pp % p.block_size) * p.token_stride;
-                }
-                offs[lane] = off;
-            }
-            __syncwarp();
-        }
-        const int pp = r0 + pl;
-        const bool own_ok = pp < we && pp != seq - 1;
-        const long long e_own = own_ok ? offs[pl] + hs : 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-            kq[i] = own_ok ? __ldcg(reinterpret_cast<const uint4*>(kvr + p.k_off + e_own + 32 * half) + i)
-                           : make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int pj = r0 + j;
-            const bool ok = pj < we && pj != seq - 1;
-            vw[j] = ok ? __ldcg(reinterpret_cast<const uint32_t*>(kvr + p.v_off + offs[j] + hs) + lane) : 0u;
-        }
-        if (!pre_ok) __syncwarp();
-    };
     if (c.prof) c.prof[10] = global_ns();
     float m[G], l[G], acc[G][2];
 #pragma unroll
@@ -813,7 +760,7 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
     int r0 = ws;
 #pragma unroll 1
     do {
-        if (r0 != ws) fetch_run(r0);
+        if (r0 != ws) fetch_kv_run<NW>(c, layer, r0, ws, we, pre_ok, kq, vw);   // the first run was fetched at the top of the layer
         if (r0 == ws) {
             // rotated q of the G heads of this kv head, then rotated k and v of the new token: (G + 2) * 16 packets
             {
@@ -822,8 +769,7 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
                 const int which = tid >> 4, d4 = (tid & 15) * 4;
                 const int qrow = which < G ? (kvh * G + which) * kD : (which == G ? (W::QH + kvh) * kD : (W::QH + W::KVH + kvh) * kD);
                 const uint32_t* ptr[1] = {tid < (G + 2) * 16 ? qkv + qrow + d4 : nullptr};
-                // the K/V loads of the first run go out while the first poll is in flight
-                poll_packets<1>(c, ptr, tag16(c, layer), pkt, [&] { if (ws < we) fetch_run(ws); });
+                poll_packets<1>(c, ptr, tag16(c, layer), pkt);
                 if (tid < (G + 2) * 16)
                     *reinterpret_cast<uint2*>(qkvb_s + 2 * tid) =
                         make_uint2((pkt[0].x & 0xffffu) | (pkt[0].y << 16), (pkt[0].z & 0xffffu) | (pkt[0].w << 16));
@@ -970,8 +916,6 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer) {
         st_flagged(dst + 2 + d, __float_as_uint(a), tag);
     }
     csync<NW>();     // c.attn is reused by the merge staging
-    // item index = chunk * KVH + kvh (the CTA index)
-    if (tid == 0) st_flagged(p.w_gate + ((size_t)(layer & 1) * W::KVH * W::NC + chunk * W::KVH + kvh) * 16, 1u, tag);
     if (c.prof) c.prof[14] = global_ns();
 }
 
@@ -1106,6 +1050,23 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const Fas
             sh.kv_off[warp][j] = o;
         }
     }
+    // this warp's share of the CTA's attention item (layer-invariant) and the registers its first run lives in
+    int item_ws = 0, item_we = 0;
+    bool item_pre_ok = true;
+    if (sh.item_kvh >= 0) {
+        const int start = sh.item_chunk * sh.lc;
+        const int end = min(start + sh.lc, sh.seq);
+        const int ppw = (((end - start + NW - 1) / NW) + 15) & ~15;
+        item_ws = min(start + warp * ppw, end);
+        item_we = min(item_ws + ppw, end);
+        item_pre_ok = ppw <= kPre * 16;      // every run's offsets were resolved above
+    }
+    uint4 kq[4];
+    uint32_t vw[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) kq[i] = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) vw[j] = 0u;
     // reset the argmax cell the *next* launch will use
     if (cta == 0 && tid == 0) p.argkey[(sh.epoch + 1u) & 1u] = 0ull;
     // norm weights of the first norm phase (every later phase fetches the next one's ahead of time)
@@ -1150,7 +1111,10 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const Fas
         if (t == kQKV || t == kGU || last) {
             if (t == kQKV) {
                 if (prof) prof[0] = global_ns();
-                if (sh.item_kvh >= 0) attention_prefetch<W, NW>(c, layer);
+                // K/V of the first run of this warp's share go into registers now: they have the whole norm + QKV
+                // phase to arrive, and no burst of loads sits in front of the q poll of the attention item
+                // (20 loads per thread issued right before that poll delayed its answer by ~0.7 us)
+                if (sh.item_kvh >= 0 && item_ws < item_we) fetch_kv_run<NW>(c, layer, item_ws, item_ws, item_we, item_pre_ok, kq, vw);
             }
             // RMSNorm: input norm (x -> res0), post-attention norm (h1 -> res1) or the final norm
             const uint32_t* src = (t == kGU ? p.w_h1 : p.w_x) + par * W::H;
@@ -1158,9 +1122,11 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const Fas
             const uint16_t* next_w = ni < 2 * p.L ? reinterpret_cast<const uint16_t*>(sh.norm_ptr[ni + 1]) : nullptr;
             stage_norm<W, NW>(c, src, tag16(c, layer), next_w, gp == 0, act0, t == kGU ? res1 : res0);
         } else if (t == kO) {
-            if (sh.item_kvh >= 0) attention_item<W, NW>(c, layer);
+            if (sh.item_kvh >= 0) attention_item<W, NW>(c, layer, item_ws, item_we, item_pre_ok, kq, vw);
             if (prof) prof[3] = global_ns();
-            stage_attn<W, NW>(c, layer, act1);
+            // the last QH CTAs (never attention items) merge one query head each; everybody stages the result
+            if (cta >= ncta - W::QH && warp == 0) merge_head<W, NW>(c, layer, ncta - 1 - cta);
+            stage_copy<W, W::AD, NW>(c, p.w_attn + par * W::AD, tag16(c, layer), act1);
         } else {
             stage_copy<W, W::I, NW>(c, p.w_act + par * W::I, tag16(c, layer), act1);
         }

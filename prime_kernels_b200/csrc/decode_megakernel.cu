@@ -1713,7 +1713,7 @@ static FastLayout fast_layout(const ModelGeom& g) {
     l.h1 = take(2 * (size_t)g.H * 4);
     l.act = take(2 * (size_t)g.I * 4);
     l.part = take(2 * (size_t)g.KVH * fast_nc(g) * G * 66 * 8);
-    l.gate = take(2 * (size_t)g.KVH * fast_nc(g) * 128);
+    l.gate = take(2 * (size_t)g.QH * kD * 4);       // merged attention output words
     l.total = off;
     return l;
 }
@@ -1939,7 +1939,8 @@ static int fast_warps() {
 template <class W, int NW>
 static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo& di, const WsLayout& lay) {
     using namespace fast;
-    if (di.sm_count < kNominalCtas || di.sm_count < W::NC * W::KVH) return kFastNotEligible;
+    // the attention items take the first NC * KVH CTAs, the head merges the last QH
+    if (di.sm_count < kNominalCtas || di.sm_count < W::NC * W::KVH + W::QH) return kFastNotEligible;
     constexpr int ACT = W::H > W::I ? W::H : W::I;
     constexpr size_t kAttnWords = (size_t)attn_words<W, NW>();
     const size_t fixed = align_up(sizeof(FShared<NW>), 128) + 2 * align_up((size_t)ACT * 2, 128) +
@@ -1986,7 +1987,7 @@ static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo
     p.w_h1 = reinterpret_cast<uint32_t*>(fw + fl.h1);
     p.w_act = reinterpret_cast<uint32_t*>(fw + fl.act);
     p.w_part = reinterpret_cast<unsigned long long*>(fw + fl.part);
-    p.w_gate = reinterpret_cast<unsigned long long*>(fw + fl.gate);
+    p.w_attn = reinterpret_cast<uint32_t*>(fw + fl.gate);
     p.k_off = a.k_off;
     p.v_off = a.v_off;
     p.block_stride = a.block_stride;
