@@ -30,22 +30,22 @@ sys.path.insert(0, str(ROOT))
 
 WORKLOADS = {
     # name: (geometry name, batch, context tokens before timing, default steps)
-    "smollm2-360m-b1": ("smollm2-360m", 1, 512, 256),            # BASELINE config 2 (headline)
-    "smollm2-135m-b1": ("smollm2-135m", 1, 32, 64),              # config 1
-    "smollm2-1.7b-b1": ("smollm2-1.7b", 1, 1024, 256),           # config 5
-    "smollm2-1.7b-b8": ("smollm2-1.7b", 8, 1024, 64),            # config 5, two launches of 4 requests per step
-    "smollm2-1.7b-b64": ("smollm2-1.7b", 64, 1024, 16),          # config 5, sixteen launches per step
+    "smollm2-360m-b1": ("smollm2-360m", 1, 512, 256),            # the headline: 512-token prompt, 256 greedy steps
+    "smollm2-135m-b1": ("smollm2-135m", 1, 32, 64),              # 32-token prompt, 64 greedy steps
+    "smollm2-1.7b-b1": ("smollm2-1.7b", 1, 1024, 256),           # 1024-token prompt, 256 steps
+    "smollm2-1.7b-b8": ("smollm2-1.7b", 8, 1024, 64),
+    "smollm2-1.7b-b64": ("smollm2-1.7b", 64, 1024, 16),
     "smollm2-360m-b4": ("smollm2-360m", 4, 512, 256),
     "smollm2-360m-b8": ("smollm2-360m", 8, 512, 256),
-    # config 4: MXFP8 weights (E4M3 + E8M0 per 32 along K), context pre-filled to 4096 with normal(0,1) K/V
+    # MXFP8 weights (E4M3 + E8M0 per 32 along K), context pre-filled to 4096 with normal(0,1) K/V, 128 steps
     "smollm2-360m-mxfp8-b1": ("smollm2-360m", 1, 4096, 128),
     "smollm2-360m-mxfp8-b4": ("smollm2-360m", 4, 4096, 128),
-    "smollm2-360m-mxfp8-b16": ("smollm2-360m", 16, 4096, 32),    # config 4, two launches of 8 requests per step
+    "smollm2-360m-mxfp8-b16": ("smollm2-360m", 16, 4096, 32),
 }
 METRIC = "SmolLM2-360M bs1 decode tok/s & % HBM roofline; aggregate tok/s @1/2/4/8 GPUs"
 # DRAM bytes per launch measured with ncu (dram__bytes_read + write) at context 503-505 divided by the
-# algorithmic bytes at that context: 747.8 MB / 744.3 MB (profiles/decode_step_kernel_smollm2-360m-b1_ctx505.md).
-# Traffic grows with the same units as the algorithmic bytes (weights + KV positions).
+# algorithmic bytes at that context (747.8 MB / 744.3 MB).  Traffic grows with the same units as the
+# algorithmic bytes (weights + KV positions).
 NCU_TRAFFIC_RATIO = 1.005
 
 
@@ -63,7 +63,7 @@ def algorithmic_bytes(geom, batch, seq, mxfp8=False):
 
 class ClockSampler:
     """SM clock / throttle-reason samples taken while the timed region runs.  Read-only NVML queries from a
-    thread of this process every 10 ms (an `nvidia-smi -lms` child needs longer to start than the timed
+    thread of this process every 2 ms (an `nvidia-smi -lms` child needs longer to start than the timed
     region lasts); falls back to an `nvidia-smi` child when the NVML binding is missing."""
 
     REASONS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
@@ -94,7 +94,7 @@ class ClockSampler:
                 self.rows.append((mhz, self.max_mhz, mask))
             except Exception:
                 pass
-            self.stop.wait(0.01)
+            self.stop.wait(0.002)
 
     def _read_smi(self):
         for line in self.proc.stdout:
@@ -107,6 +107,7 @@ class ClockSampler:
                 self.rows.append((int(c[0]), int(c[1]), mask))
 
     def __enter__(self):
+        self.stop.clear()
         if self.nvml is not None:
             self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
             self.thread.start()
@@ -184,28 +185,120 @@ def cpu_reference(geom, batch, prompt_len, sample_steps, seed=1234):
     return toks, torch.get_num_threads(), desc
 
 
-def run_reference(args, wl):
-    import torch
+def config_block(wl, gname, batch, prompt_len, world):
+    """The `config` object of a bench line: both arms print exactly this for the same workload (what differs
+    between the arms goes into the line's `detail`)."""
+    return {"workload": wl, "geometry": gname, "batch": batch, "prompt_tokens": prompt_len, "kv_block": 16,
+            "replicas": world, "l2": "weights (>= 269 MB per step) exceed the 126 MB L2; no flush needed"}
 
-    from prime_kernels_b200.decode import GEOMETRIES
+
+def run_reference(args, wl):
+    """The CPU arm: the reference's own oracle (HuggingFace eager bf16) on the host cores, a bounded sample of the
+    same workload.  Imports nothing that loads the CUDA libraries of this repository."""
+    from prime_kernels_b200.geometry import GEOMETRIES
 
     gname, batch, prompt_len, _ = WORKLOADS[wl]
+    if args.prompt_tokens:
+        prompt_len = args.prompt_tokens
     geom = GEOMETRIES[gname]
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 16))
-    for _ in range(min(args.warmup, 1)):
-        pass
+    steps = max(1, min(args.steps, 16))          # bounded sample: at most 16 timed decode steps
     toks, cores, desc = cpu_reference(geom, batch, prompt_len, steps)
-    line = {"metric": METRIC, "value": toks, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": 1e3 * batch / toks, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
-            "config": {"workload": wl, "note": "CPU arm: bounded sample of the same workload"},
+    line = {"metric": METRIC, "value": toks, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps,
+            "steps_requested": args.steps, "warmup": 0, "ms_per_step": 1e3 * batch / toks, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+            "config": config_block(wl, gname, batch, prompt_len, int(os.environ.get("WORLD_SIZE", "1"))),
+            "detail": {"note": "CPU arm: prompt prefilled untimed, then `steps` timed decode steps"},
             "cpu_baseline": {"value": toks, "unit": "tok/s", "cores": cores, "kind": "reference", "sample": desc},
             "e2e": {"value": toks, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def extra_measurements(dev, peak):
+    """Secondary measurements of the same run (rank 0, one GPU): the fused RMSNorm + residual + MXFP8 kernel at
+    three shapes with both traffic models, the reference project's own kernels on the same box when its
+    benchmark executable was built (oracle/_ref), the CPU quantiser timed on the host, and short device-timed
+    lines for the other two model sizes."""
+    import subprocess as sp
+
+    import numpy as np
+    import torch
+
+    from prime_kernels_b200 import decode as D
+    from prime_kernels_b200 import harness
+    from prime_kernels_b200.rmsnorm import bench_rmsnorm
+
+    out = {"rmsnorm": [], "decode": []}
+    pool = int(1.0 * (1 << 30) / 2)
+    ref_bench = ROOT / "oracle" / "_ref" / "ref_rmsnorm_bench"
+    for n, c in ((8192, 4096), (65536, 4096), (8192, 960)):
+        us, gbs = bench_rmsnorm.measure(n, c, pool, 2, dev)
+        full = n * c * 5 + n * ((c + 31) // 32) + 2 * c + 4 * n
+        row = {"N": n, "C": c, "us": round(us, 2), "GBs_reference_model": round(gbs, 1),
+               "GBs_full_model": round(full / (us * 1e-6) / 1e9, 1), "frac_of_measured_peak": round(gbs / peak, 3)}
+        if ref_bench.exists() and c % 128 == 0:
+            try:
+                txt = sp.run([str(ref_bench), "--sweep", "--rows", str(n), "--cols", str(c), "--reps", "2", "--gib", "1.0"],
+                             capture_output=True, text=True, timeout=120).stdout
+                best = 0.0
+                for ln in txt.splitlines():
+                    f = ln.split()
+                    if len(f) >= 4 and f[0] not in ("variant", "copy") and not ln.startswith(("#", "N=")):
+                        try:
+                            best = max(best, float(f[3]))
+                        except ValueError:
+                            pass
+                row["reference_best_kernel_GBs_same_box"] = best or None
+            except (OSError, sp.TimeoutExpired):
+                row["reference_best_kernel_GBs_same_box"] = None
+        out["rmsnorm"].append(row)
+    # CPU quantiser (oracle): 1024 x 4096 rows, single thread
+    try:
+        from oracle import mxfp8
+
+        g = np.random.default_rng(0)
+        nb, cb = 1024, 4096
+        x = torch.from_numpy(g.standard_normal((nb, cb), dtype=np.float32)).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+        w = torch.ones(cb, dtype=torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+        t0 = time.perf_counter()
+        mxfp8.quantise_port(x, x, w, None, 1e-6)
+        dt = time.perf_counter() - t0
+        out["rmsnorm_cpu_baseline"] = {"value": (nb * cb * 5 + 4 * nb) / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                                       "sample": f"{nb} x {cb} rows through the plain-C quantiser oracle, one thread"}
+    except Exception as e:      # the oracle library is test infrastructure; its absence must not break the bench
+        out["rmsnorm_cpu_baseline"] = {"unavailable": str(e)[:120]}
+    for gname, ctx, steps in (("smollm2-135m", 32, 64), ("smollm2-1.7b", 1024, 32)):
+        geom = D.GEOMETRIES[gname]
+        weights = harness.weights_to(harness.make_weights(geom, 0), dev)
+        cap = ctx + steps + 80
+        cap = (cap + 15) // 16 * 16
+        kv = harness.PagedKV(geom, 1, cap, dev)
+        for cache in kv.kv_caches:
+            cache.normal_()
+        sess = D.DecodeSession(geom, embed=weights["embed"], layers=weights["layers"], final_norm=weights["final_norm"],
+                               kv_caches=kv.kv_caches, cos_sin_cache=harness.make_cos_sin_cache(geom, cap, dev),
+                               block_table=kv.block_table)
+        sess.start(torch.tensor([17]), torch.tensor([ctx]))
+        for _ in range(4):
+            sess.step()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            sess.step()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        D.check_status(geom, dev)
+        ms = e0.elapsed_time(e1) / steps
+        nbytes = algorithmic_bytes(geom, 1, ctx + 4 + steps // 2)
+        out["decode"].append({"workload": f"{gname}-b1", "context": ctx, "steps": steps, "ms_per_step": round(ms, 4),
+                              "tok_s": round(1e3 / ms, 1), "roofline_frac_of_measured": round(nbytes / (ms * 1e-3) / 1e9 / peak, 3),
+                              "note": "KV pre-filled with normal(0,1), device-driven greedy loop, CUDA events"})
+        del sess, kv, weights
+        torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -217,6 +310,7 @@ def main():
     ap.add_argument("--workload", default="smollm2-360m-b1", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements (rmsnorm, other model sizes)")
     ap.add_argument("--prompt-tokens", type=int, default=None, help="override the workload's prompt length")
     args = ap.parse_args()
     wl = args.workload
@@ -295,7 +389,8 @@ def main():
     stream = torch.cuda.current_stream(dev)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     seq_first = int(sess.seq_lens[0])
-    with ClockSampler(local_rank) as clocks:
+    clocks = ClockSampler(local_rank)      # samples during the device-timed loop and during the end-to-end loop
+    with clocks:
         barrier()
         ev0.record(stream)
         for _ in range(K):
@@ -332,11 +427,12 @@ def main():
         for t in range(W):
             e2e_step(t)
         barrier()
-        t0 = time.perf_counter()
-        for t in range(W, W + K):
-            e2e_step(t)
-        torch.cuda.synchronize(dev)
-        dt = time.perf_counter() - t0
+        with clocks:
+            t0 = time.perf_counter()
+            for t in range(W, W + K):
+                e2e_step(t)
+            torch.cuda.synchronize(dev)
+            dt = time.perf_counter() - t0
         barrier()
         D.check_status(geom, dev)
         return dt
@@ -358,9 +454,8 @@ def main():
             "metric": METRIC, "value": aggregate_throughput(world, batch, K, ms_max), "unit": "tok/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16 activations, MXFP8 weights" if mxfp8 else "bf16", "data": "synthetic",
-            "config": {"workload": wl, "geometry": gname, "batch": batch, "prompt_tokens": prompt_len,
-                       "context_during_timing": [seq_first, seq_last], "kv_block": 16,
-                       "replicas": world, "l2": "weights (>= 269 MB per step) exceed the 126 MB L2; no flush needed",
+            "config": config_block(wl, gname, batch, prompt_len, world),
+            "detail": {"context_during_timing": [seq_first, seq_last],
                        "timing": "CUDA events on the launching stream around K back-to-back launches"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": mean_bytes * NCU_TRAFFIC_RATIO if gname == "smollm2-360m" and batch == 1 and not mxfp8 else None,
@@ -375,6 +470,10 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             toks, cores, desc = cpu_reference(geom, batch, prompt_len, 8)
             line["cpu_baseline"] = {"value": toks, "unit": "tok/s", "cores": cores, "kind": "reference", "sample": desc}
+        if world == 1 and not args.no_extra and wl == "smollm2-360m-b1":
+            del sess, kv
+            torch.cuda.empty_cache()
+            line["extra"] = extra_measurements(dev, peak)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -133,7 +133,7 @@ const char* pk_status_string(int status);
 /* Tuning and test knobs, process-wide; no counterpart in the reference.
  * pk_decode_set_fast_path: batch-1 bf16 steps of the SmolLM2-135M / 360M widths run on a kernel specialised
  * for those widths with `warps` (7 or 8) consumer warps per CTA; 0 sends every step to the generic kernel
- * (default: environment variable PK_DECODE_FAST, else 8).  Both kernels keep the same rounding points.
+ * (default: environment variable PK_DECODE_FAST, else 7).  Both kernels keep the same rounding points.
  * pk_decode_set_spin_limit: bound, in polling rounds, of every device-side wait of later launches (the
  * reference spins without a bound, prime_kernels/decode_megakernel/csrc/megakernel.cu:109-122); 0 = default.
  * pk_decode_wait_probe: failure-path check in the form of the reference's harness watchdog

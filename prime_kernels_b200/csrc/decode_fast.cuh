@@ -37,7 +37,7 @@ struct Widths {
     static constexpr int H = H_, I = I_, QH = QH_, KVH = KVH_, G = QH_ / KVH_;
     static constexpr int NQKV = (QH_ + 2 * KVH_) * kD;
     static constexpr int AD = QH_ * kD;                           // attention output width (K of the O projection)
-    static constexpr int NC = (kNominalCtas / KVH_) < 6 ? (kNominalCtas / KVH_) : 6;   // max chunks per kv head
+    static constexpr int NC = ((kNominalCtas - QH_) / KVH_) < 8 ? ((kNominalCtas - QH_) / KVH_) : 8;   // max chunks per kv head
     static_assert(QH_ % KVH_ == 0 && H_ % 32 == 0 && I_ % 32 == 0, "unsupported widths");
 };
 

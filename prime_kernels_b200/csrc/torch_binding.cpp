@@ -218,8 +218,11 @@ TORCH_LIBRARY_FRAGMENT(prime_rmsnorm, m) {
 }
 
 TORCH_LIBRARY_FRAGMENT(prime_decode, m) {
-    m.def("decode_step(Tensor input_ids, Tensor positions, Tensor seq_lens, Tensor block_table, Tensor slot_mapping, "
-          "Tensor embed, Tensor? embed_lookup, Tensor layers_table, Tensor final_norm, Tensor kv_table, int k_off, "
+    // with advance=true the kernel rewrites input_ids, positions, seq_lens and slot_mapping for the next step, and
+    // every step appends to the KV caches behind kv_table: all of them are declared mutable
+    m.def("decode_step(Tensor(f!) input_ids, Tensor(g!) positions, Tensor(h!) seq_lens, Tensor block_table, "
+          "Tensor(i!) slot_mapping, "
+          "Tensor embed, Tensor? embed_lookup, Tensor layers_table, Tensor final_norm, Tensor(j!) kv_table, int k_off, "
           "int v_off, int block_stride, int token_stride, int head_stride, int block_size, Tensor cos_sin_cache, "
           "Tensor(a!) out_hidden, Tensor(b!)? logits, Tensor(c!)? next_ids, Tensor(d!)? layer_outputs, "
           "Tensor(e!) workspace, int hidden, int intermediate, int layers, int q_heads, int kv_heads, int vocab, "

@@ -7,16 +7,15 @@ FLASH_ATTN-style decode metadata, fused ``qkv`` / ``gate_up`` weights, a paged b
 The returned hidden state is a view of a per-device buffer that the next call overwrites.
 
 Extensions over the reference: any Llama geometry with head_dim 64 (SmolLM2 135M / 360M / 1.7B are
-predefined), batch up to 4, MXFP8-packed weights, and ``lm_head=True`` which also returns bf16
+predefined), batch up to 8 per launch (64 per call), MXFP8-packed weights, and ``lm_head=True`` which also returns bf16
 logits and greedy next ids computed inside the same launch.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-
 import torch
 
 from .._cabi import library, load_ops
+from ..geometry import GEOMETRIES, HEAD_DIM, SMOLLM2_135M, SMOLLM2_1P7B, SMOLLM2_360M, Geometry
 
 load_ops()
 
@@ -27,35 +26,6 @@ __all__ = ["Geometry", "SMOLLM2_135M", "SMOLLM2_360M", "SMOLLM2_1P7B", "GEOMETRI
 MAX_BATCH = 8          # requests one kernel launch takes
 MAX_REQUESTS = 64      # requests one decode_step call takes (larger batches run as several launches)
 MAX_SEQ = 8192
-HEAD_DIM = 64
-
-
-@dataclass(frozen=True)
-class Geometry:
-    name: str
-    hidden: int
-    intermediate: int
-    layers: int
-    q_heads: int
-    kv_heads: int
-    vocab: int = 49152
-    rope_theta: float = 100000.0
-    eps: float = 1e-5
-    weight_format: int = 0   # 0 = bf16, 1 = MXFP8 packed rows
-
-    @property
-    def qkv_rows(self) -> int:
-        return (self.q_heads + 2 * self.kv_heads) * HEAD_DIM
-
-    def with_format(self, weight_format: int) -> "Geometry":
-        return Geometry(self.name, self.hidden, self.intermediate, self.layers, self.q_heads, self.kv_heads,
-                        self.vocab, self.rope_theta, self.eps, weight_format)
-
-
-SMOLLM2_135M = Geometry("smollm2-135m", 576, 1536, 30, 9, 3)
-SMOLLM2_360M = Geometry("smollm2-360m", 960, 2560, 32, 15, 5)
-SMOLLM2_1P7B = Geometry("smollm2-1.7b", 2048, 8192, 24, 32, 32, rope_theta=130000.0)
-GEOMETRIES = {g.name: g for g in (SMOLLM2_135M, SMOLLM2_360M, SMOLLM2_1P7B)}
 
 
 @torch.library.register_fake("prime_decode::decode_step")
@@ -87,7 +57,6 @@ class _Runtime:
         self.logits = None
         self.next_ids = None
         self.table_key = None
-        self.fast_key = None
         self.layers_t = None
         self.kv_t = None
 
@@ -97,28 +66,26 @@ class _Runtime:
             self.next_ids = torch.zeros((MAX_REQUESTS,), dtype=torch.int64, device=self.device)
         return self.logits, self.next_ids
 
-    def tables(self, layers, kv_caches):
-        # Fast path for the steady state of a serving loop: the same list objects with the same first and last
-        # tensors as in the previous call have already been validated and tabulated (walking all ~250 pointers
-        # costs tens of microseconds per step in Python).  Anything else takes the full comparison below.
-        fast = (id(layers), id(kv_caches), len(layers), layers[0][1].data_ptr(), layers[-1][5].data_ptr(),
-                kv_caches[0].data_ptr(), kv_caches[-1].data_ptr())
-        if fast == self.fast_key:
+    def tables(self, layers, kv_caches, embed, final_norm, embed_lookup):
+        # Steady state of a serving loop: the key covers the data pointer of every weight and cache tensor, so a
+        # caller that swaps any tensor is noticed; building it costs ~15 us for a 32-layer model, validation and
+        # the device tables are only redone when it changes.
+        key = (tuple(t.data_ptr() for layer in layers for t in layer), tuple(kv.data_ptr() for kv in kv_caches),
+               embed.data_ptr(), final_norm.data_ptr(), 0 if embed_lookup is None else embed_lookup.data_ptr())
+        if key == self.table_key:
             return self.layers_t, self.kv_t
         _check_kv(self.geometry, kv_caches)
-        key = (tuple(t.data_ptr() for layer in layers for t in layer), tuple(kv.data_ptr() for kv in kv_caches))
-        self.fast_key = fast
-        if key != self.table_key:
-            layer_table = torch.tensor([[t.data_ptr() for t in layer] for layer in layers], dtype=torch.int64)
-            kv_table = torch.tensor([kv.data_ptr() for kv in kv_caches], dtype=torch.int64)
-            if self.layers_t is None:
-                self.layers_t = layer_table.to(self.device)
-                self.kv_t = kv_table.to(self.device)
-            else:
-                # in place, so CUDA graphs captured with these tables see the new pointers
-                self.layers_t.copy_(layer_table)
-                self.kv_t.copy_(kv_table)
-            self.table_key = key
+        _check_weights(self.geometry, self.device, embed, final_norm, layers, embed_lookup)
+        layer_table = torch.tensor([[t.data_ptr() for t in layer] for layer in layers], dtype=torch.int64)
+        kv_table = torch.tensor([kv.data_ptr() for kv in kv_caches], dtype=torch.int64)
+        if self.layers_t is None:
+            self.layers_t = layer_table.to(self.device)
+            self.kv_t = kv_table.to(self.device)
+        else:
+            # in place, so CUDA graphs captured with these tables see the new pointers
+            self.layers_t.copy_(layer_table)
+            self.kv_t.copy_(kv_table)
+        self.table_key = key
         return self.layers_t, self.kv_t
 
 
@@ -188,6 +155,39 @@ def _check_kv(geometry: Geometry, kv_caches):
             raise ValueError("kv_caches must be CUDA tensors")
 
 
+def _check_weights(geometry: Geometry, device, embed, final_norm, layers, embed_lookup):
+    """Shapes, dtypes, contiguity and device of every tensor the kernel will stream with bulk copies: a matrix of
+    the wrong size would otherwise become an out-of-bounds read on the device."""
+    g = geometry
+    h, i, ad = g.hidden, g.intermediate, g.q_heads * HEAD_DIM
+
+    def check(t, name, shape, dtype):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda or t.device != device:
+            raise ValueError(f"{name} must be a CUDA tensor on {device}")
+        if t.dtype != dtype or tuple(t.shape) != shape or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous {dtype} tensor of shape {shape}, got {t.dtype} {tuple(t.shape)}")
+        if t.data_ptr() % 16:
+            raise ValueError(f"{name} must be 16-byte aligned")
+
+    if g.weight_format:
+        mat = lambda rows, k: ((rows, packed_row_bytes(k)), torch.uint8)
+    else:
+        mat = lambda rows, k: ((rows, k), torch.bfloat16)
+    check(embed, "embed", *mat(g.vocab, h))
+    check(final_norm, "final_norm", (h,), torch.bfloat16)
+    if embed_lookup is not None:
+        check(embed_lookup, "embed_lookup", (g.vocab, h), torch.bfloat16)
+    elif g.weight_format:
+        raise ValueError("MXFP8 weights need embed_lookup (the bf16 embedding rows for the input lookup)")
+    specs = (("norm1", (h,), torch.bfloat16), ("qkv",) + mat(g.qkv_rows, h), ("o",) + mat(h, ad),
+             ("norm2", (h,), torch.bfloat16), ("gate_up",) + mat(2 * i, h), ("down",) + mat(h, i))
+    for li, layer in enumerate(layers):
+        if len(layer) != 6:
+            raise ValueError(f"layer {li} must contain six weight tensors")
+        for t, (name, shape, dtype) in zip(layer, specs):
+            check(t, f"layer {li} {name}", shape, dtype)
+
+
 def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_table, slot_mapping, embed, layers,
                 final_norm, kv_caches, cos_sin_cache, eps, layer_outputs=None, lm_head=False, advance=False,
                 embed_lookup=None, name="decode"):
@@ -218,7 +218,7 @@ def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_tab
         raise ValueError(f"context limit {max_seq} exceeds the kernel's {MAX_SEQ}")
 
     rt = _runtime(geometry, device)
-    layers_t, kv_t = rt.tables(layers, kv_caches)      # validates the KV caches when anything changed
+    layers_t, kv_t = rt.tables(layers, kv_caches, embed, final_norm, embed_lookup)    # validates when anything changed
     logits = next_ids = None
     if lm_head:
         logits, next_ids = rt.lm_buffers()

@@ -8,6 +8,7 @@ stage dump is not produced).
 The returned tensor is a view into a shared per-device output buffer and is overwritten by the next
 call on that device.  Consume or copy it before then.
 """
+import hashlib
 from pathlib import Path
 
 import torch
@@ -16,6 +17,12 @@ from .. import decode as _generic
 
 SOURCE = Path(__file__).resolve().parent.parent / "csrc" / "decode_megakernel.cu"
 NVCC_FLAGS = ["-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-lineinfo"]
+# The reference pins the sha256 of its kernel source and JIT-builds into a per-user cache directory; this library
+# is prebuilt in-tree, so the digest is simply that of the source the library was built from (computed on
+# import) and CACHE_ROOT is the directory that holds the built library.
+SOURCE_SHA256 = hashlib.sha256(SOURCE.read_bytes()).hexdigest()
+INCLUDE_SHA256 = hashlib.sha256((SOURCE.parent / "decode_fast.cuh").read_bytes()).hexdigest()
+CACHE_ROOT = SOURCE.parent.parent / "lib"
 
 GEOMETRY = _generic.SMOLLM2_360M
 MAX_BATCH = _generic.MAX_BATCH

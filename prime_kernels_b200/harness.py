@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from .decode import HEAD_DIM, Geometry
+from .geometry import HEAD_DIM, Geometry
 
 
 def make_weights(geometry: Geometry, seed: int = 0, device="cpu", norm_weights: str = "ones", std: float = 0.02):

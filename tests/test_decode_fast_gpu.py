@@ -31,7 +31,7 @@ def _set_path(warps):
 @pytest.fixture(autouse=True)
 def _restore_default_path():
     yield
-    _set_path(8)
+    _set_path(7)
 
 
 def _step(D, geom, wd, kv, csd, cur, pos, lm_head=True, layer_outputs=None):
@@ -42,11 +42,11 @@ def _step(D, geom, wd, kv, csd, cur, pos, lm_head=True, layer_outputs=None):
                          layer_outputs=layer_outputs, lm_head=lm_head)
 
 
-@pytest.mark.parametrize("warps", [8, 7])
+@pytest.mark.parametrize("warps", [7, 8])
 @pytest.mark.parametrize("which,ctx,shuffle,block_size", [
     ("360m", 0, False, 16),        # the new token is the whole context
     ("360m", 5, False, 16),
-    ("360m", 127, True, 16),       # chunk boundary of the 8-warp kernel (128 positions with the new token)
+    ("360m", 111, True, 16),       # chunk boundary of the 7-warp kernel (112 positions with the new token)
     ("360m", 600, True, 16),       # the benchmark's context range: several chunks per kv head
     ("360m", 150, True, 8),        # a 16-position run straddles cache blocks
     ("360m", 3300, True, 16),      # beyond the pre-resolved runs: block table read per run, longer chunks
@@ -100,7 +100,7 @@ def test_fast_and_generic_kernels_agree(cuda_device):
     csd = harness.make_cos_sin_cache(geom, 512, cuda_device)
     gen = torch.Generator().manual_seed(3)
     outs = []
-    for warps in (8, 0):
+    for warps in (7, 0):
         _set_path(warps)
         kv = harness.PagedKV(geom, 1, 512, cuda_device, shuffle=True, seed=1)
         g2 = torch.Generator().manual_seed(5)
@@ -119,7 +119,7 @@ def test_fast_and_generic_kernels_agree(cuda_device):
         assert torch.equal(n1, n0)
 
 
-@pytest.mark.parametrize("warps", [8, 0])
+@pytest.mark.parametrize("warps", [7, 0])
 def test_alternating_lm_head_does_not_reuse_old_argmax(cuda_device, warps):
     """lm_head steps alternating with hidden-only steps on one workspace: the greedy id of every lm_head step is
     that step's own argmax (an argmax cell left over from two launches earlier must never win)."""
@@ -150,7 +150,7 @@ def test_alternating_lm_head_does_not_reuse_old_argmax(cuda_device, warps):
                 assert int(nxt[0]) == int(rl.argmax(-1)[0])
 
 
-@pytest.mark.parametrize("warps", [8, 7])
+@pytest.mark.parametrize("warps", [7, 8])
 def test_fast_device_driven_generation_matches_stepwise(cuda_device, warps):
     from prime_kernels_b200 import decode as D
 
@@ -181,7 +181,7 @@ def test_fast_device_driven_generation_matches_stepwise(cuda_device, warps):
         assert torch.equal(ca, cb)
 
 
-@pytest.mark.parametrize("warps", [8, 0])
+@pytest.mark.parametrize("warps", [7, 0])
 def test_padded_row_and_sequence_overflow(cuda_device, warps):
     """slot -1 writes nothing into the cache; a sequence length beyond the block table's capacity is reported
     (status 9102) instead of indexing past the table, and the workspace is usable again afterwards."""

@@ -4,9 +4,11 @@ oracles: the HuggingFace-eager golden run (committed fixture) and the rounding-p
 Tolerances.  The target is max-abs 2e-2 on bf16 logits and token-exact greedy ids.  Two independent
 implementations that round to bf16 at the same places still differ in fp32 summation order, and in
 this random-init model a single one-ulp bf16 flip early in the stack grows to a few 1e-2 at the
-logits, so the per-step check is: logits within 2e-2 on most steps (LOGIT_TOL), never worse than
-LOGIT_HARD, and greedy ids exact wherever the oracle's top-2 margin exceeds 2 * LOGIT_HARD (the
-committed golden run has a minimum margin of 0.19, so that is every step).
+logits (tests/test_oracle_decode.py measures that floor between two CPU implementations).  The bounds
+asserted here sit within 1.5 x of what the kernel measures on a B200: SmolLM2-135M, 64 steps: median
+0.018, max 0.023, 86 % of the steps within 2e-2; SmolLM2-360M, 256 steps at context 512-767: median
+0.027, max 0.039 (HuggingFace against the CPU restatement: 0.039-0.046).  Greedy ids must be exact
+wherever the oracle's top-2 margin exceeds twice the bound.
 """
 from pathlib import Path
 
@@ -20,8 +22,8 @@ from prime_kernels_b200 import harness
 pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).parent / "golden" / "decode_135m_b1.npz"
 LOGIT_TOL = 2e-2       # north-star tolerance (bf16 logits, max-abs)
-LOGIT_HARD = 1.25e-1   # hard bound on any step
-MIN_FRACTION_WITHIN_TOL = 0.5
+LOGIT_HARD = 3.5e-2    # SmolLM2-135M: bound on any step (measured max 0.023)
+MIN_FRACTION_WITHIN_TOL = 0.6   # SmolLM2-135M: share of steps within LOGIT_TOL (measured 0.86)
 # SmolLM2-360M, 512-token context: two CPU implementations (HuggingFace eager and the restatement) differ by
 # 0.039-0.046 in the logits whichever way the softmax probabilities are rounded (tests/test_oracle_decode.py);
 # the bound for the kernel is 1.5 x that measured floor.
@@ -47,7 +49,7 @@ def _step(D, geom, wd, kv, csd, cur, pos, lm_head=True, layer_outputs=None):
     ("gqa3-b1-ctx1000", (192, 512, 2, 3, 1, 1024), 1, 1000, True),
     ("gqa3-b6-padded", (192, 512, 2, 3, 1, 1024), 6, 50, True),
     ("mha-b8", (128, 256, 2, 2, 2, 512), 8, 30, False),
-    ("gqa3-b16-two-launches", (192, 512, 2, 3, 1, 1024), 16, 40, True),       # BASELINE config 4's batch 16
+    ("gqa3-b16-two-launches", (192, 512, 2, 3, 1, 1024), 16, 40, True),       # batch 16
     ("gqa3-b19-ragged-groups", (192, 512, 2, 3, 1, 1024), 19, 33, False),     # 8 + 8 + 3 requests
 ])
 def test_small_geometries_against_restatement(cuda_device, name, dims, B, ctx, shuffle):
@@ -111,7 +113,7 @@ def test_padded_row_skips_the_cache_write(cuda_device):
 
 @pytest.mark.skipif(not GOLDEN.exists(), reason="golden fixture missing")
 def test_smollm2_135m_against_hf_golden(cuda_device):
-    """BASELINE config 1: 32-token prompt, 64 greedy steps, KV capacity 2048."""
+    """SmolLM2-135M, 32-token seeded prompt, 64 greedy steps, KV capacity 2048, against the committed HuggingFace-eager run."""
     from prime_kernels_b200 import decode as D
     from prime_kernels_b200 import decode_megakernel as MK
 
@@ -370,7 +372,7 @@ def test_router_drives_the_real_kernel(cuda_device):
 
 
 def test_smollm2_360m_headline_against_hf_golden(cuda_device):
-    """BASELINE config 2 (the headline): 512-token prompt, 256 greedy steps.  The prompt goes through the
+    """The headline configuration (SmolLM2-360M, 512-token seeded prompt, 256 greedy steps).  The prompt goes through the
     kernel token by token (which builds the KV cache), then every decode step is fed the oracle's previous id
     and its logits are compared with the HuggingFace-eager golden run."""
     from prime_kernels_b200 import decode as D
@@ -400,15 +402,15 @@ def test_smollm2_360m_headline_against_hf_golden(cuda_device):
     dl, dt = np.array(dl), np.array(dt)
     print(f"360M teacher-forced: sampled logits max-abs median {np.median(dl):.4f} max {dl.max():.4f}, top-8 max {dt.max():.4f}, "
           f"within {LOGIT_TOL}: {(dl <= LOGIT_TOL).mean():.2f}; ids differing {wrong}")
-    # At this depth and context two CPU implementations that differ only in summation order already disagree
-    # by 4-5e-2 (tests/test_oracle_decode.py, noise-floor test), so the per-step 2e-2 target cannot be held;
-    # the kernel has to stay on that floor: every step within the hard bound, the median within 5e-2.
-    assert max(dl.max(), dt.max()) <= LOGIT_HARD
-    assert np.median(dl) <= 5e-2
+    # At this depth and context HuggingFace eager and the CPU restatement already disagree by 0.035-0.046
+    # whichever way the softmax probabilities are rounded (tests/test_oracle_decode.py), so the per-step 2e-2
+    # target cannot be held; the kernel has to stay on that floor.
+    assert max(dl.max(), dt.max()) <= 6e-2            # measured 0.039
+    assert np.median(dl) <= 4.1e-2                    # measured 0.027
     # greedy ids are exact wherever the oracle's top-2 margin exceeds twice the observed logit error
-    # (the golden run contains exact top-2 ties, which no independent implementation can be held to)
+    # (the golden run contains one exact top-2 tie, which no independent implementation can be held to)
     assert all(margin <= 2 * max(dl.max(), dt.max()) for _, margin in wrong)
-    assert len(wrong) <= 8
+    assert len(wrong) <= 1
 
 
 def test_smollm2_360m_from_hf_prefill_cache(cuda_device):
@@ -644,7 +646,7 @@ def test_host_driven_step_matches_device_driven_generation(cuda_device, graph):
 
 def test_wide_geometry_falls_back_to_smaller_launch_groups(cuda_device):
     """A geometry whose 8-request activation staging does not fit shared memory (SmolLM2-1.7B's widths, two layers):
-    the step runs as launches of 4 requests and still matches the restatement (BASELINE config 5's batch 8)."""
+    the step runs as launches of 4 requests and still matches the restatement (SmolLM2-1.7B widths, batch 8)."""
     from prime_kernels_b200 import decode as D
 
     geom = D.Geometry("wide", 2048, 8192, 2, 32, 32, 2048, rope_theta=130000.0)

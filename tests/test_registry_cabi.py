@@ -71,7 +71,23 @@ def test_argument_validation_needs_no_device():
     # contract violations are rejected before any CUDA call
     assert lib.pk_fused_rmsnorm_residual_forward(None, None, None, None, None, None, 1e-6, 4, 100, None) == 9111
     assert lib.pk_fused_rmsnorm_residual_forward(None, None, None, None, None, None, 1e-6, 4, 128, None) == 9103
-    assert lib.mk_decode(None, 9, *([None] * 23)) == 9101 if False else True
+    # the drop-in entries validate like the reference: batch first, then the context capacity, then pointers
+    def mk(batch, max_seq):       # stream, B, ids, ids_i64, positions, seq_lens, block_table, bt_stride, slot_mapping,
+        return lib.mk_decode(None, batch, None, 0, None, None, None, 128, None,     # layers, embed, final_norm, kv,
+                             None, None, None, None, 0, 64, 0, 0, 0, 16,            # 5 strides, block_size,
+                             None, 0, None, None, 0, max_seq)                       # cos_sin, fp32, out, scratch, bytes
+
+    assert mk(9, 2048) == 9101
+    assert mk(1, 9000) == 9102
+    assert mk(1, 2048) == 9103
+
+    def d360(batch, max_seq, debug_layer):
+        return lib.decode360(None, batch, None, None, None, None, None, None, 128, None, None, None, 0, 64, 0, 0, 0, 16,
+                             None, 0, None, None, None, 0, None, 0, max_seq, debug_layer)
+
+    assert d360(9, 2048, -1) == 9101
+    assert d360(1, 2048, 40) == 9109          # debug_layer_index out of range
+    assert d360(1, 2048, -1) == 9103
     m = _cabi.PkDecodeModel(960, 2560, 32, 15, 5, 49152, 0, 1e-5)
     a = _cabi.PkDecodeArgs()
     a.batch = 9

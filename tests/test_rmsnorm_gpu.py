@@ -7,7 +7,7 @@ from oracle import mxfp8
 
 pytestmark = pytest.mark.gpu
 
-# reference test shapes (prime_kernels/rmsnorm/test.cu:409-410) + BASELINE config 3 + ragged edges
+# reference test shapes (prime_kernels/rmsnorm/test.cu:409-410) + hidden {960, 2048, 4096} x tokens {1 ... 8192} + ragged edges
 SHAPES = [(128, 128), (128, 512), (256, 2048), (128, 3072), (256, 4096), (128, 8192), (128, 16384),
           (1, 960), (16, 960), (128, 960), (1024, 960), (1, 2048), (16, 2048), (1024, 2048), (1, 4096),
           (16, 4096), (1024, 4096), (130, 960), (257, 32), (3, 12288)]
@@ -133,7 +133,7 @@ def test_rejects_bad_shapes(cuda_device):
 
 
 def test_full_size_properties(cuda_device):
-    """BASELINE config 3's largest shape: de-quantised output tracks the bf16 pre-quant value within the
+    """The largest benchmark shape (8192 tokens x 4096): de-quantised output tracks the bf16 pre-quant value within the
     E4M3 step, scales are the smallest power of two that keeps every value <= 448, run is deterministic."""
     from prime_kernels_b200 import rmsnorm
 
