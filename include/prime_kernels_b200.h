@@ -37,6 +37,11 @@ int pk_fused_rmsnorm_residual_forward_ex(void* vals, void* scales, float* rrms, 
                                          const void* residual, const void* weight, float epsilon, int N, int C,
                                          int mode, void* stream);
 
+/* Which kernel pk_fused_rmsnorm_residual_forward would launch for these pointers and this shape, without launching:
+ * 2 = pipelined bulk-copy kernel (needs 16-byte aligned vals / branch / residual), 1 = lane-owns-group kernel
+ * (32-byte aligned pointers), 0 = register kernel; a negative value is minus the status the entry would return.
+ * Replaces the shape-only dispatch rule of prime_kernels/rmsnorm/rmsnorm.cu:15-31.  Host only. */
+int pk_rmsnorm_dispatch(const void* vals, const void* branch, const void* residual, const void* weight, int N, int C);
 /* Size in bytes of the blocked scale buffer: ceil(N/128) * ceil(C/128) * 512
  * (scale_numel in prime_kernels/rmsnorm/csrc/torch_interface.cpp:18-20, extended to ragged shapes). */
 long long pk_rmsnorm_scale_bytes(int N, int C);

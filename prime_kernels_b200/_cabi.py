@@ -40,6 +40,7 @@ SYMBOLS = {
     "pk_fused_rmsnorm_residual_forward": (ci, [vp, vp, vp, vp, vp, vp, cf, ci, ci, vp]),
     "pk_fused_rmsnorm_residual_forward_ex": (ci, [vp, vp, vp, vp, vp, vp, vp, cf, ci, ci, ci, vp]),
     "pk_rmsnorm_scale_bytes": (ll, [ci, ci]),
+    "pk_rmsnorm_dispatch": (ci, [vp, vp, vp, vp, ci, ci]),
     "pk_rmsnorm_wait_timeouts": (ll, []),
     "pk_apply_rotary": (ci, [vp, vp, vp, vp, ll, ci, ci, ci, ci, ci, ci, vp]),
     "pk_rmsnorm_forward": (ci, [vp, vp, vp, vp, vp, ll, ci, cf, vp]),

@@ -408,6 +408,10 @@ static int launch_pipe_mp(const RmsParams& p, cudaStream_t stream) {
 // every CTA several tiles.  The templates also cover C = 1024, 2048 and 4096, where the other kernel is as fast.
 static bool pipe_eligible(const RmsParams& p) {
     if (p.mode != 0 || p.res_out != nullptr || (p.n % 128) != 0) return false;
+    // bulk copies in both directions (global -> shared for branch / residual, shared -> global for vals) need
+    // 16-byte aligned global addresses; the C entries only guarantee 8 bytes for vals
+    auto a16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    if (!a16(p.vals) || !a16(p.branch) || !a16(p.residual)) return false;
     if (p.c == 8192) return p.n >= 8192;
     if (p.c == 16384) return p.n >= 2048;
     return false;
@@ -673,6 +677,26 @@ extern "C" int pk_fused_rmsnorm_residual_forward(void* vals, void* scales, float
     p.nkt = (C + 127) / 128;
     p.mode = 0;
     return launch_rmsnorm(p, static_cast<cudaStream_t>(stream));
+}
+
+// Host-side view of the dispatcher for the reference-semantics entry (no launch, no device needed): 2 = pipelined
+// bulk-copy kernel, 1 = lane-owns-group kernel, 0 = register kernel, negative = the status the entry would return.
+// Lets callers and tests see that pointers that are not 16-byte aligned never reach the bulk-copy kernel.
+extern "C" int pk_rmsnorm_dispatch(const void* vals, const void* branch, const void* residual, const void* weight,
+                                   int N, int C) {
+    using namespace pk;
+    if (N <= 0 || C <= 0 || (C % 32) != 0) return -kErrShape;
+    if ((reinterpret_cast<uintptr_t>(vals) % 8) || (reinterpret_cast<uintptr_t>(branch) % 16) ||
+        (reinterpret_cast<uintptr_t>(residual) % 16) || (reinterpret_cast<uintptr_t>(weight) % 16))
+        return -kErrAlign;
+    RmsParams p{};
+    p.vals = static_cast<uint8_t*>(const_cast<void*>(vals));
+    p.branch = static_cast<const uint4*>(branch);
+    p.residual = static_cast<const uint4*>(residual);
+    p.weight = static_cast<const uint4*>(weight);
+    p.n = N;
+    p.c = C;
+    return pipe_eligible(p) ? 2 : (group_eligible(p) ? 1 : 0);
 }
 
 // Extended entry: mode 0 = residual added after the norm (reference semantics), mode 1 = residual

@@ -139,3 +139,30 @@ def test_decode_contract_errors_are_valueerrors():
     with pytest.raises(ValueError, match="expected 30 layers"):
         a.decode_step(input_ids=ids, positions=ids, seq_lens=ids, block_table=ids, slot_mapping=ids, embed=None,
                       layers=[], final_norm=None, kv_caches=[], cos_sin_cache=None, eps=1e-5)
+
+
+def test_rmsnorm_dispatch_keeps_misaligned_pointers_off_the_bulk_copy_kernel():
+    """The pipelined kernel moves data with bulk copies, which need 16-byte aligned global addresses; the C entry
+    accepts `vals` at 8-byte alignment, so such a pointer must be routed to another kernel (host-side check)."""
+    lib = _cabi.library()
+    base = 1 << 20
+    assert lib.pk_rmsnorm_dispatch(base, base, base, base, 8192, 8192) == 2
+    assert lib.pk_rmsnorm_dispatch(base, base, base, base, 2048, 16384) == 2
+    assert lib.pk_rmsnorm_dispatch(base + 8, base, base, base, 8192, 8192) == 0      # vals only 8-byte aligned
+    assert lib.pk_rmsnorm_dispatch(base + 16, base, base, base, 8192, 8192) == 2     # 16 is enough for the pipe
+    assert lib.pk_rmsnorm_dispatch(base, base + 16, base, base, 8192, 4096) == 0     # group kernel wants 32
+    assert lib.pk_rmsnorm_dispatch(base, base, base, base, 8192, 4096) == 1
+    assert lib.pk_rmsnorm_dispatch(base + 4, base, base, base, 8192, 8192) == -9107
+    assert lib.pk_rmsnorm_dispatch(base, base, base, base, 128, 100) == -9111
+
+
+def test_workspace_bytes_covers_every_batch_up_to_the_declared_maximum():
+    """A caller that sizes the workspace for max_batch must be able to run every batch up to it: batches 5..7 run
+    on the batch-8 kernel, so they report its size; more than 8 requests per launch is refused (0)."""
+    lib = _cabi.library()
+    m = _cabi.PkDecodeModel(960, 2560, 32, 15, 5, 49152, 0, 1e-5)
+    sizes = [lib.pk_decode_workspace_bytes(ctypes.byref(m), b) for b in range(1, 10)]
+    assert all(sizes[i] <= sizes[i + 1] for i in range(7))
+    assert sizes[4] == sizes[5] == sizes[6] == sizes[7] > sizes[3]
+    assert sizes[8] == 0
+    assert lib.pk_decode_workspace_bytes(ctypes.byref(m), 0) == 0

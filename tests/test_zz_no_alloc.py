@@ -98,6 +98,54 @@ def test_static_scratch_entry_matches_regular_entry(cuda_device):
         del keep_a, keep_b
 
 
+def test_static_scratch_entry_on_the_batch1_kernel_with_alternating_lm_head(cuda_device):
+    """SmolLM2-360M widths at batch 1 (the specialised batch-1 kernel) through both entry points, with steps that
+    ask for the greedy id alternating with hidden-only steps: the built-in scratch keeps the previous call's
+    contents, so an argmax cell left over from an earlier call must never leak into a later id."""
+    from prime_kernels_b200 import _cabi
+    from prime_kernels_b200 import decode as D
+
+    lib = _cabi.library()
+    dev = cuda_device
+    geom = D.Geometry("noalloc-360w", 960, 2560, 2, 15, 5, 2048)
+    model = _cabi.PkDecodeModel(geom.hidden, geom.intermediate, geom.layers, geom.q_heads, geom.kv_heads,
+                                geom.vocab, 0, geom.eps)
+    wd = harness.weights_to(harness.make_weights(geom, 7, norm_weights="random"), dev)
+    csd = harness.make_cos_sin_cache(geom, 128, dev)
+
+    def fresh():
+        kv = harness.PagedKV(geom, 1, 128, dev)
+        layer_t = torch.tensor([[t.data_ptr() for t in layer] for layer in wd["layers"]], dtype=torch.int64, device=dev)
+        kv_t = torch.tensor([c.data_ptr() for c in kv.kv_caches], dtype=torch.int64, device=dev)
+        out = (torch.zeros(1, geom.hidden, dtype=torch.bfloat16, device=dev),
+               torch.zeros(1, geom.vocab, dtype=torch.bfloat16, device=dev),
+               torch.zeros(1, dtype=torch.int64, device=dev))
+        return kv, (layer_t, kv_t), out
+
+    kv_a, tab_a, out_a = fresh()
+    kv_b, tab_b, out_b = fresh()
+    workspace = torch.zeros(D.workspace_bytes(geom, 1), dtype=torch.uint8, device=dev)
+    assert workspace.numel() <= lib.pk_decode_static_scratch_bytes()
+    gen = torch.Generator().manual_seed(2)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    for step, lm in enumerate([1, 0, 1, 0, 0, 1, 1]):
+        ids = torch.randint(0, geom.vocab, (1,), generator=gen).to(dev)
+        pos = torch.full((1,), step, dtype=torch.int64, device=dev)
+        a, keep_a = _args(_cabi, geom, dev, wd, kv_a, csd, ids, pos, *out_a, tab_a, workspace)
+        b, keep_b = _args(_cabi, geom, dev, wd, kv_b, csd, ids, pos, *out_b, tab_b, None)
+        a.lm_head = b.lm_head = lm
+        assert lib.pk_decode_step(ctypes.byref(model), ctypes.byref(a)) == 0
+        assert lib.pk_decode_step_static(ctypes.byref(model), ctypes.byref(b)) == 0
+        assert lib.pk_decode_status(workspace.data_ptr(), stream) == 0
+        assert lib.pk_decode_static_status(stream) == 0
+        torch.cuda.synchronize(dev)
+        assert torch.equal(out_a[0], out_b[0])                 # same kernel, same inputs: same hidden state
+        if lm:
+            assert torch.equal(out_a[1], out_b[1]) and torch.equal(out_a[2], out_b[2])
+            assert int(out_b[2][0]) == int(out_b[1][0].float().argmax())    # this step's own argmax
+        del keep_a, keep_b
+
+
 def test_static_scratch_refuses_oversized_requests(cuda_device):
     from prime_kernels_b200 import _cabi
 
