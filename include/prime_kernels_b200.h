@@ -101,10 +101,19 @@ typedef struct PkDecodeArgs {
     void* workspace; size_t workspace_bytes; int max_seq_len; int lm_head; int advance;
 } PkDecodeArgs;
 
-/* Generic form of mk_workspace_bytes / decode360_workspace_bytes. */
+/* Generic form of mk_workspace_bytes / decode360_workspace_bytes; max_batch 1..64 (a workspace sized for more than 8
+ * requests serves the tensor-core kernel and must not be shared with launches of up to 8 requests). */
 size_t pk_decode_workspace_bytes(const PkDecodeModel* model, int max_batch);
-/* Generic form of mk_decode / decode360 (one cooperative launch on args->stream). */
+/* Generic form of mk_decode / decode360 (one cooperative launch on args->stream).  1..8 requests run on the CUDA-core
+ * kernels (batch 1 of the SmolLM2-135M / 360M widths on a kernel specialised for them), 9..64 requests on the
+ * tensor-core kernel: projections as tcgen05 GEMMs with the weight tile as the 128-row operand, batch padded to
+ * 16 / 32 / 64, accumulators in tensor memory, every weight streamed once per step. */
 int pk_decode_step(const PkDecodeModel* model, const PkDecodeArgs* args);
+/* Same step on the tensor-core kernel whatever the batch (1..64): for models whose rows are too wide for the CUDA-core
+ * kernel at the wanted batch (SmolLM2-1.7B above 4 requests).  No counterpart in the reference (its decode kernels
+ * have no tensor-core path beyond wmma at batch 2, prime_kernels/decode_megakernel_360m/csrc/block360.cu:312-364).
+ * Workspace: pk_decode_workspace_bytes(model, 64) bytes, used by this kernel only. */
+int pk_decode_step_tc(const PkDecodeModel* model, const PkDecodeArgs* args);
 /* Zero a workspace in stream order (also done implicitly the first time a pointer is seen). */
 int pk_decode_workspace_init(void* workspace, size_t bytes, void* stream);
 void pk_decode_workspace_forget(void* workspace);

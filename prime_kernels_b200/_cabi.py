@@ -49,6 +49,7 @@ SYMBOLS = {
     "pk_pack_weights_mxfp8": (ci, [vp, vp, ll, ci, vp]),
     "pk_decode_workspace_bytes": (sz, [ctypes.POINTER(PkDecodeModel), ci]),
     "pk_decode_step": (ci, [ctypes.POINTER(PkDecodeModel), ctypes.POINTER(PkDecodeArgs)]),
+    "pk_decode_step_tc": (ci, [ctypes.POINTER(PkDecodeModel), ctypes.POINTER(PkDecodeArgs)]),
     "pk_decode_step_static": (ci, [ctypes.POINTER(PkDecodeModel), ctypes.POINTER(PkDecodeArgs)]),
     "pk_decode_static_scratch_bytes": (sz, []),
     "pk_decode_static_status": (ci, [vp]),

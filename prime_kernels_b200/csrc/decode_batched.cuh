@@ -1,0 +1,870 @@
+// Batched decode step (9..64 requests) with the projections on the 5th-generation tensor cores
+// (included by decode_megakernel.cu).
+//
+// At these batch sizes every projection is a real GEMM, C[rows, B] = W[rows, K] . X[B, K]^T.  It is mapped
+// "swap-AB": the A operand is a tile of 128 weight rows (so a weight byte is streamed exactly once per step,
+// like in the GEMV kernels), the B operand is the activation matrix with the batch padded to N = 16 / 32 / 64,
+// and the fp32 accumulator tile (128 lanes x N columns) lives in tensor memory:
+//
+//   * operands are staged in shared memory in the K-major 128-byte-swizzle layout tcgen05.mma reads (rows of
+//     64 bf16, eight-row groups of 1024 bytes, 16-byte chunks XOR-swizzled by the row).  bf16 weights and
+//     activations arrive with 16-byte cp.async copies placed chunk by chunk; MXFP8 weights (E4M3 + one E8M0 per
+//     32 along K) are de-quantised to bf16 in registers on their way in, which is exact;
+//   * one elected thread issues tcgen05.mma (kind::f16, cta_group::1, M = 128, K = 16 per instruction) and
+//     commits to an mbarrier; four warps read the accumulator back with tcgen05.ld (thread = weight row) and
+//     run the epilogue;
+//   * a phase has too few 128-row tiles to occupy 148 SMs, so K is split over work items as well; partial
+//     tiles are added into an fp32 matrix in L2 with red.global.add and the rounding / residual / SwiGLU /
+//     norm epilogues run after the grid barrier that ends the phase (the lm_head is not split: its epilogue
+//     rounds the logits and takes the argmax directly);
+//   * attention runs as split-KV items (request, kv head, chunk) on the CUDA cores like in the small-batch
+//     kernels, followed by a log-sum-exp merge.
+//
+// One persistent cooperative launch per step; phases are separated by a counter-based grid barrier whose
+// wait is bounded (status 9110 instead of a hang).  Rounding points are those of the small-batch kernels
+// (HuggingFace eager); fp32 partial sums meet in a different order, which is within the parity tolerance.
+//
+// Behaviour of the reference's tensor-core code that was used as a map (nothing copied): descriptor fields
+// and roles in prime_kernels/flash_moe/csrc/kernels/tcgen05_prelude.cuh:38-96,136-157,213-258 and
+// fused_moe_bf16_kernel.cu:105-229; its waits are unbounded (tcgen05_prelude.cuh:404-414), these are not.
+#pragma once
+
+namespace pk {
+namespace batched {
+
+constexpr int kThreadsB = 256;        // warps 0-3: operand staging + epilogue; warp 4: MMA issue; all: SIMT phases
+constexpr int kStages = 4;            // 64-wide K blocks staged per work item pass
+constexpr int kNcB = 16;              // max split-KV chunks per (request, kv head)
+constexpr int kMaxReq = 64;
+constexpr int kAStage = 128 * 128;    // bytes of one A stage (128 rows x 64 bf16)
+constexpr int kKvStages = 4;          // attention: runs of 16 positions in flight per warp
+constexpr int kRunBytes = 16 * 256;   // K and V rows of one run
+// the GEMM operand stages and the attention rings share the front of the dynamic shared memory
+__host__ __device__ constexpr int staging_bytes(int np) {
+    return kStages * kAStage + kStages * np * 128 > (kThreadsB / 32) * kKvStages * kRunBytes
+               ? kStages * kAStage + kStages * np * 128
+               : (kThreadsB / 32) * kKvStages * kRunBytes;
+}
+
+struct GemmDesc {
+    int rows;            // weight rows (output features)
+    int K;               // reduction length
+    int blocks;          // 64-wide K blocks per work item
+    int widx;            // index in the per-layer pointer table, -1: embedding matrix
+    int rowbytes;        // bytes per stored weight row
+};
+
+struct BParams {
+    const unsigned long long* layers;   // device table [L][6]
+    const unsigned long long* kv;       // device table [L]
+    const unsigned char* embed;         // lm_head matrix (bf16 rows or packed MXFP8 rows)
+    const uint16_t* embed_bf16;         // bf16 embedding rows for the input lookup
+    const uint16_t* final_norm;
+    const void* input_ids;
+    const long long* positions;
+    const int* seq_lens;
+    const int* block_table;
+    const long long* slot_mapping;
+    const void* cos_sin;
+    uint16_t* out_hidden;
+    uint16_t* logits;
+    long long* next_ids;
+    uint16_t* layer_outputs;
+    unsigned long long* profile;        // optional [ctas][L][kProfSlots] globaltimer stamps (thread 0, after every phase)
+    unsigned dbg;                       // development switches
+    unsigned int* ctrl;                 // control words shared with the other kernels (status)
+    unsigned int* bctrl;                // this kernel's words: [0] barrier counter, [1] completion counter
+    unsigned long long* argkey;         // [kMaxReq]
+    float* c_qkv;                       // [NP][NQKV]   fp32 sums of the split-K partial tiles
+    float* c_o;                         // [NP][H]
+    float* c_gu;                        // [NP][2I]
+    float* c_down;                      // [NP][H]
+    uint16_t* x;                        // [NP][H]   residual stream (bf16)
+    uint16_t* h1;                       // [NP][H]
+    uint16_t* xn;                       // [NP][H]   normed input of the QKV / gate-up / lm_head GEMMs
+    uint16_t* attn;                     // [NP][AD]
+    uint16_t* act;                      // [NP][I]
+    float* part;                        // [B][KVH][kNcB][G][66]
+    long long k_off, v_off, block_stride, token_stride, head_stride;
+    int block_size, bt_stride, ids_i64, cs_fp32;
+    int H, I, L, QH, KVH, V, G, nb, wfmt, lm_head, advance, max_seq_len;
+    unsigned spin_limit;
+    float eps;
+    GemmDesc gd[kNumPhaseTypes];
+};
+
+struct BShared {
+    uint64_t full[kStages];
+    uint64_t accum;
+    uint64_t kvbar[kThreadsB / 32][kKvStages];
+    uint32_t tmem_base;
+    volatile int abort_flag;
+    uint32_t bar_gen;
+    int seq[kMaxReq], pos[kMaxReq], nc[kMaxReq];
+    long long tok[kMaxReq], slot_off[kMaxReq];
+    int lc, ncmax;
+    float red[8];
+    unsigned long long lm_key[4][kMaxReq];
+};
+
+// ------------------------------------------------------------------ small helpers
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const uint32_t n = valid ? 16u : 0u;      // src-size 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
+}
+// global -> shared bulk copy without a cache hint, completion counted in bytes on an mbarrier; never multicast
+__device__ __forceinline__ void bulk_g2s_plain(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+
+// K-major, 128-byte swizzle: start address, stride between eight-row groups = 1024 bytes, descriptor version 1
+__device__ __forceinline__ uint64_t smem_desc_sw128(const void* p) {
+    const uint64_t addr = smem_u32(p);
+    return ((addr >> 4) & 0x3fffull) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16: D = f32, A = B = bf16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    const uint32_t acc = accumulate ? 1u : 0u;
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+template <int NP>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&v)[NP]);
+template <>
+__device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, float (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]),
+          "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld<32>(uint32_t taddr, float (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+        "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]),
+          "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15]), "=f"(v[16]),
+          "=f"(v[17]), "=f"(v[18]), "=f"(v[19]), "=f"(v[20]), "=f"(v[21]), "=f"(v[22]), "=f"(v[23]), "=f"(v[24]),
+          "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld<64>(uint32_t taddr, float (&v)[64]) {
+    float a[32], b[32];
+    tmem_ld<32>(taddr, a);
+    tmem_ld<32>(taddr + 32u, b);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        v[i] = a[i];
+        v[32 + i] = b[i];
+    }
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+struct BC {
+    const BParams& p;
+    BShared& sh;
+    unsigned char* stage_a;     // kStages x 16 KB, 1024-byte aligned
+    unsigned char* stage_b;     // kStages x NP x 128 bytes
+    float* scratch;             // attention scratch (floats)
+    int tid, warp, lane, cta, ncta;
+    uint32_t uses;              // passes done so far (parity of the accumulator barrier)
+    uint32_t suse[kStages];     // uses of every stage barrier so far (a pass may use fewer than kStages stages)
+    unsigned char* kvring;      // attention: kThreadsB/32 rings of kKvStages runs (over the GEMM stages)
+    uint32_t kvi, kvc;          // runs this warp has issued / consumed so far (stage and parity of the ring)
+};
+
+__device__ __forceinline__ bool b_aborted(const BC& c) { return c.sh.abort_flag != 0; }
+__device__ __forceinline__ void b_raise(BC& c, int code) {
+    c.sh.abort_flag = 1;
+    atomicCAS(c.p.ctrl + kCtrlStatus, 0u, (unsigned)code);
+}
+__device__ __forceinline__ bool b_wait_mbar(BC& c, uint64_t* bar, uint32_t parity) {
+    if (mbar_probe(bar, parity)) return true;
+    unsigned spins = 0;
+    while (!mbar_test(bar, parity)) {
+        if ((++spins & 255u) == 0) {
+            if (b_aborted(c)) return false;
+            if (spins >= c.p.spin_limit) {
+                b_raise(c, kErrBarrierTimeout);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// Grid barrier: every CTA adds one to a counter and waits until it reaches generation * grid size.  Global
+// writes made before the barrier are visible to every CTA after it.  The wait is bounded; after a failure all
+// later barriers fall through at once (the status word is checked first).
+__device__ __forceinline__ void grid_barrier(BC& c) {
+    __syncthreads();
+    if (c.tid == 0) {
+        const uint32_t target = (++c.sh.bar_gen) * (uint32_t)c.ncta;
+        __threadfence();
+        atomicAdd(c.p.bctrl, 1u);
+        unsigned spins = 0;
+        while (!b_aborted(c)) {
+            uint32_t v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(c.p.bctrl) : "memory");
+            if (v >= target) break;
+            if ((++spins & 255u) == 0) {
+                if (*((volatile unsigned int*)(c.p.ctrl + kCtrlStatus)) != 0) c.sh.abort_flag = 1;
+                else if (spins >= c.p.spin_limit) b_raise(c, kErrBarrierTimeout);
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// ------------------------------------------------------------------ tensor-core GEMM phase
+// Stage one 64-wide K block: A = 128 weight rows starting at row r0 (rows >= nrows are zero), B = the NP
+// activation rows (requests >= nb are zero).  Threads 0..127.
+template <int NP, int WF>
+__device__ __forceinline__ void stage_block(BC& c, int st, const unsigned char* wbase, int rowbytes, int K, int r0, int nrows,
+                                            int kblk, const uint16_t* xmat, int xstride) {
+    unsigned char* sa = c.stage_a + st * kAStage;
+    unsigned char* sb = c.stage_b + st * NP * 128;
+    const int t = c.tid;
+    if (WF == 0) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int idx = t + u * 128;              // 128 rows x 8 chunks of 16 bytes
+            const int row = idx >> 3, ch = idx & 7;
+            const bool ok = r0 + row < nrows;
+            const unsigned char* src = wbase + (size_t)(ok ? r0 + row : 0) * rowbytes + (size_t)kblk * 128 + ch * 16;
+            cp_async16(sa + (row >> 3) * 1024 + (row & 7) * 128 + ((ch ^ (row & 7)) << 4), src, ok);
+        }
+    } else {
+        // packed rows [K e4m3][K/32 e8m0][pad]: 64 values = four 16-byte pieces per row; thread = (row, piece)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int idx = t + u * 128;              // 128 rows x 4 pieces
+            const int row = idx >> 2, pc = idx & 3;
+            uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
+            if (r0 + row < nrows) {
+                const unsigned char* rp = wbase + (size_t)(r0 + row) * rowbytes;
+                const uint4 q = ld_stream_16(rp + (size_t)kblk * 64 + pc * 16);
+                const unsigned char sbyte = __ldg(rp + K + kblk * 2 + (pc >> 1));
+                const float scale = __uint_as_float(sbyte ? ((uint32_t)sbyte << 23) : 0x00400000u);
+                float f[4];
+                e4m3x4_to_f32(q.x, f);
+                lo.x = pack_bf16x2(f[0] * scale, f[1] * scale); lo.y = pack_bf16x2(f[2] * scale, f[3] * scale);
+                e4m3x4_to_f32(q.y, f);
+                lo.z = pack_bf16x2(f[0] * scale, f[1] * scale); lo.w = pack_bf16x2(f[2] * scale, f[3] * scale);
+                e4m3x4_to_f32(q.z, f);
+                hi.x = pack_bf16x2(f[0] * scale, f[1] * scale); hi.y = pack_bf16x2(f[2] * scale, f[3] * scale);
+                e4m3x4_to_f32(q.w, f);
+                hi.z = pack_bf16x2(f[0] * scale, f[1] * scale); hi.w = pack_bf16x2(f[2] * scale, f[3] * scale);
+            }
+            unsigned char* rowp = sa + (row >> 3) * 1024 + (row & 7) * 128;
+            *reinterpret_cast<uint4*>(rowp + (((2 * pc) ^ (row & 7)) << 4)) = lo;
+            *reinterpret_cast<uint4*>(rowp + (((2 * pc + 1) ^ (row & 7)) << 4)) = hi;
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < (NP * 8 + 127) / 128; ++u) {
+        const int idx = t + u * 128;
+        if (idx < NP * 8) {
+            const int row = idx >> 3, ch = idx & 7;
+            const bool ok = row < c.p.nb;
+            const uint16_t* src = xmat + (size_t)(ok ? row : 0) * xstride + kblk * 64 + ch * 8;
+            cp_async16(sb + (row >> 3) * 1024 + (row & 7) * 128 + ((ch ^ (row & 7)) << 4), src, ok);
+        }
+    }
+    cp_async_commit();
+}
+
+// All work items of one GEMM phase that belong to this CTA.  `mode` 0: partial tiles are added into cmat
+// ([NP][rows] fp32); mode 1 (lm_head, K not split): bf16 logits and the per-request argmax.
+template <int NP, int WF>
+__device__ void gemm_phase(BC& c, const GemmDesc& gd, const unsigned char* wbase, const uint16_t* xmat, float* cmat, int mode) {
+    const BParams& p = c.p;
+    BShared& sh = c.sh;
+    const int rtiles = (gd.rows + 127) / 128;
+    const int nk64 = gd.K / 64;
+    const int slices = mode == 1 ? 1 : (nk64 + gd.blocks - 1) / gd.blocks;
+    const int items = rtiles * slices;
+    if (mode == 1 && c.tid < 4 * kMaxReq) (&sh.lm_key[0][0])[c.tid] = 0ull;
+    for (int item = c.cta; item < items; item += c.ncta) {
+        const int rt = item / slices, sl = item - rt * slices;
+        const int r0 = rt * 128;
+        const int kb0 = mode == 1 ? 0 : sl * gd.blocks;
+        const int kb1 = mode == 1 ? nk64 : min(kb0 + gd.blocks, nk64);
+        // passes of up to kStages blocks; the accumulator stays in tensor memory across the passes of an item
+        for (int kb = kb0; kb < kb1; kb += kStages) {
+            const int nst = min(kStages, kb1 - kb);
+            const uint32_t parity = c.uses & 1u;
+            uint32_t spar[kStages];
+#pragma unroll
+            for (int s = 0; s < kStages; ++s) {
+                spar[s] = c.suse[s] & 1u;
+                if (s < nst) ++c.suse[s];
+            }
+            if (c.warp < 4) {
+                for (int s = 0; s < nst; ++s) stage_block<NP, WF>(c, s, wbase, gd.rowbytes, gd.K, r0, gd.rows, kb + s, xmat, gd.K);
+                // as each block's copies complete: make them visible to the tensor core's (async-proxy) reads, signal
+                for (int s = 0; s < nst; ++s) {
+                    switch (nst - 1 - s) {
+                        case 3: cp_async_wait<3>(); break;
+                        case 2: cp_async_wait<2>(); break;
+                        case 1: cp_async_wait<1>(); break;
+                        default: cp_async_wait<0>(); break;
+                    }
+                    fence_async_smem();
+                    mbar_arrive(&sh.full[s]);
+                }
+            } else if (c.warp == 4 && c.lane == 0) {
+                const uint32_t idesc = idesc_bf16(128, NP);
+                for (int s = 0; s < nst; ++s) {
+                    if (!b_wait_mbar(c, &sh.full[s], spar[s])) break;
+                    tc_fence_after();
+                    const uint64_t da = smem_desc_sw128(c.stage_a + s * kAStage);
+                    const uint64_t db = smem_desc_sw128(c.stage_b + s * NP * 128);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)      // 16 bf16 = 32 bytes per instruction: start address + 2 (16-byte units)
+                        mma_bf16(sh.tmem_base, da + 2 * k, db + 2 * k, idesc, (kb + s > kb0) || k > 0);
+                }
+                mma_commit(&sh.accum);               // arrives when every MMA issued so far has completed
+            }
+            // everybody waits for the MMAs of this pass before the stages are overwritten / the accumulator is read
+            b_wait_mbar(c, &sh.accum, parity);
+            ++c.uses;
+            __syncthreads();
+        }
+        // ---- epilogue: thread = weight row (tensor-memory lane), NP accumulator columns
+        if (c.warp < 4) {
+            tc_fence_after();
+            float v[NP];
+            tmem_ld<NP>(sh.tmem_base + ((uint32_t)(c.warp * 32) << 16), v);
+            tmem_ld_wait();
+            const int row = r0 + c.tid;
+            if (mode == 0) {
+                if (row < gd.rows) {
+#pragma unroll
+                    for (int j = 0; j < NP; ++j)
+                        if (j < p.nb) atomicAdd(cmat + (size_t)j * gd.rows + row, v[j]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < NP; ++j) {
+                    if (j < p.nb) {
+                        const uint32_t lb = f32_to_bf16_bits(v[j]);
+                        unsigned long long key = 0ull;
+                        if (row < gd.rows) {
+                            if (p.logits) p.logits[(size_t)j * gd.rows + row] = (uint16_t)lb;
+                            const uint32_t ord = (lb & 0x8000u) ? (~lb & 0xffffu) : (lb | 0x8000u);
+                            key = ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - (uint32_t)row);
+                        }
+#pragma unroll
+                        for (int off = 16; off >= 1; off >>= 1) {
+                            const unsigned long long o = __shfl_xor_sync(kFullMask, key, off);
+                            key = o > key ? o : key;
+                        }
+                        if (c.lane == 0 && key > sh.lm_key[c.warp][j]) sh.lm_key[c.warp][j] = key;
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+        __syncthreads();        // the accumulator may be overwritten by the next item
+    }
+    if (mode == 1 && p.next_ids) {
+        __syncthreads();
+        if (c.tid < p.nb) {
+            unsigned long long k = sh.lm_key[0][c.tid];
+#pragma unroll
+            for (int w = 1; w < 4; ++w) k = sh.lm_key[w][c.tid] > k ? sh.lm_key[w][c.tid] : k;
+            if (k) atomicMax(p.argkey + c.tid, k);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ SIMT phases between the GEMMs
+// Residual add + RMSNorm of whole rows: request b is handled by one CTA.
+//   which 0: x = embedding row (layer 0)            -> xn = norm(x, w)
+//   which 1: x = bf16(h1 + bf16(c_down))            -> xn = norm(x, w)   (also layer_outputs, final hidden)
+//   which 2: h1 = bf16(x + bf16(c_o))               -> xn = norm(h1, w)
+__device__ void norm_phase(BC& c, int which, int layer, const uint16_t* weight, bool write_hidden) {
+    const BParams& p = c.p;
+    BShared& sh = c.sh;
+    const int H = p.H;
+    for (int b = c.cta; b < p.nb; b += c.ncta) {
+        float ss = 0.f;
+        float* row = c.scratch;               // H floats
+        for (int i = c.tid; i < H; i += kThreadsB) {
+            float v;
+            if (which == 0) {
+                v = __uint_as_float((uint32_t)__ldg(p.embed_bf16 + (size_t)sh.tok[b] * H + i) << 16);
+                p.x[(size_t)b * H + i] = (uint16_t)(__float_as_uint(v) >> 16);
+            } else if (which == 1) {
+                float* cd = p.c_down + (size_t)b * H + i;
+                const float h = __uint_as_float((uint32_t)__ldcg(p.h1 + (size_t)b * H + i) << 16);
+                v = round_bf16(__fadd_rn(h, round_bf16(__ldcg(cd))));
+                *cd = 0.f;
+                const uint16_t bits = (uint16_t)(__float_as_uint(v) >> 16);
+                p.x[(size_t)b * H + i] = bits;
+                if (p.layer_outputs) p.layer_outputs[((size_t)(layer - 1) * p.nb + b) * H + i] = bits;
+            } else {
+                float* co = p.c_o + (size_t)b * H + i;
+                const float xv = __uint_as_float((uint32_t)__ldcg(p.x + (size_t)b * H + i) << 16);
+                v = round_bf16(__fadd_rn(xv, round_bf16(__ldcg(co))));
+                *co = 0.f;
+                p.h1[(size_t)b * H + i] = (uint16_t)(__float_as_uint(v) >> 16);
+            }
+            row[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        if (c.lane == 0) sh.red[c.warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kThreadsB / 32; ++w) tot += sh.red[w];
+        const float s = rsqrtf(tot * (1.f / (float)H) + p.eps);
+        for (int i = c.tid; i < H; i += kThreadsB) {
+            const float n = round_bf16(__fmul_rn(row[i], s));
+            const uint16_t o = (uint16_t)f32_to_bf16_bits(__fmul_rn(n, __uint_as_float((uint32_t)__ldg(weight + i) << 16)));
+            p.xn[(size_t)b * H + i] = o;
+            if (write_hidden) p.out_hidden[(size_t)b * H + i] = o;
+        }
+        __syncthreads();
+    }
+}
+
+// act = bf16( bf16(silu(bf16 gate)) * bf16 up ) over [nb][I]; clears the gate/up sums
+__device__ void swiglu_phase(BC& c) {
+    const BParams& p = c.p;
+    const long long total = (long long)p.nb * p.I;
+    for (long long e = (long long)c.cta * kThreadsB + c.tid; e < total; e += (long long)c.ncta * kThreadsB) {
+        const int b = (int)(e / p.I), j = (int)(e - (long long)b * p.I);
+        float* gp = p.c_gu + (size_t)b * 2 * p.I + j;
+        const float g = round_bf16(__ldcg(gp)), u = round_bf16(__ldcg(gp + p.I));
+        gp[0] = 0.f;
+        gp[p.I] = 0.f;
+        const float silu = round_bf16(__fdividef(g, 1.f + __expf(-g)));
+        p.act[(size_t)b * p.I + j] = (uint16_t)f32_to_bf16_bits(__fmul_rn(silu, u));
+    }
+}
+
+// Split-KV attention item: one WARP, (request b, kv head, chunk), no CTA-wide synchronisation.  The K and V rows
+// of a run of 16 positions are brought into the warp's shared-memory ring by bulk copies (one 4 KB copy per run
+// where a block's K and V rows are adjacent, else one 128-byte copy per row) that complete on the run's
+// mbarrier; kKvStages runs are in flight per warp, so eight warps keep about 100 KB per SM outstanding, which is
+// what the HBM latency-bandwidth product asks for.  Scores: lane = (position, half of the head dim), 16-byte
+// chunks read in an order rotated by the position so that the 256-byte row stride does not collide on banks;
+// P.V: lane = two output dims.  The prologue rounds this head group's q / k / v sums to bf16, rotates q and k
+// (lane j owns dims j and j + 32, HF rounding) and appends the new token, whose row is patched into the staged
+// run instead of being read back.
+template <int G>
+__device__ void attention_item_b(BC& c, int layer, int b, int kvh, int chunk) {
+    const BParams& p = c.p;
+    BShared& sh = c.sh;
+    const int lane = c.lane;
+    const int seq = sh.seq[b], pos = sh.pos[b];
+    const int ws = chunk * sh.lc;
+    const int we = min(ws + sh.lc, seq);
+    const int wcopy = (we == seq) ? seq - 1 : we;      // position seq-1 is this step's token: never read from the cache
+    const int nruns = (we - ws + 15) >> 4;
+    const uint16_t* kvr = reinterpret_cast<const uint16_t*>(__ldg(p.kv + layer));
+    const long long hs = (long long)kvh * p.head_stride;
+    const int pl = lane >> 1, half = lane & 1;
+    const int nqkv = (p.QH + 2 * p.KVH) * kD;
+    // per-warp shared memory: packed bf16 q (G heads, rotated), k (rotated), v; probabilities of a run
+    uint32_t* qkvb_s = reinterpret_cast<uint32_t*>(c.scratch) + c.warp * ((G + 2) * 32 + G * 16);
+    float* prob_s = reinterpret_cast<float*>(qkvb_s + (G + 2) * 32);
+    unsigned char* ring = c.kvring + (size_t)c.warp * (kKvStages * kRunBytes);
+    uint64_t* bars = sh.kvbar[c.warp];
+
+    // a window of 32 block-table entries, one per lane, refreshed as the runs move along
+    const int* bt = p.block_table + (size_t)b * p.bt_stride;
+    const int bs = p.block_size;
+    int bt_base = ws / bs;
+    int btc = __ldg(bt + min(bt_base + lane, p.bt_stride - 1));
+    const bool packed = p.token_stride == 2 * kD && p.v_off == p.k_off + kD;
+    auto issue = [&](int r0) {
+        const int st = (int)(c.kvi & (kKvStages - 1));
+        const int n = max(0, min(16, wcopy - r0));
+        if ((r0 + 15) / bs >= bt_base + 32) {
+            bt_base = r0 / bs;
+            btc = __ldg(bt + min(bt_base + lane, p.bt_stride - 1));
+        }
+        const int j = lane & 15, pj = r0 + j;
+        const int blk = __shfl_sync(kFullMask, btc, (pj / bs - bt_base) & 31);
+        if (lane == 0) mbar_expect_tx(&bars[st], (uint32_t)n * 256u);      // n == 0: the phase completes at once
+        __syncwarp();
+        unsigned char* dst = ring + st * kRunBytes + j * 256;
+        const long long e = (long long)blk * p.block_stride + (long long)(pj % bs) * p.token_stride + hs;
+        if (packed) {
+            // one copy per piece of a block: lane j starts a piece when position j is the first of the run or of a block
+            if (lane < 16 && j < n && (j == 0 || pj % bs == 0))
+                bulk_g2s_plain(dst, kvr + p.k_off + e, (uint32_t)min(bs - pj % bs, n - j) * 256u, &bars[st]);
+        } else if (j < n) {
+            const bool isv = lane >= 16;
+            bulk_g2s_plain(dst + (isv ? 128 : 0), kvr + (isv ? p.v_off : p.k_off) + e, 128u, &bars[st]);
+        }
+        ++c.kvi;
+    };
+    fence_async_smem();      // the previous item's generic writes to the ring (patched rows) before new bulk copies
+    for (int k = 0; k < min(nruns, kKvStages); ++k) issue(ws + 16 * k);      // in flight during the prologue
+
+    // ---- prologue: q (G heads), k, v of the new token; lane j owns dims j and j + 32
+    {
+        float cs, sn;
+        if (p.cs_fp32) {
+            cs = __ldg(reinterpret_cast<const float*>(p.cos_sin) + (size_t)pos * kD + lane);
+            sn = __ldg(reinterpret_cast<const float*>(p.cos_sin) + (size_t)pos * kD + 32 + lane);
+        } else {
+            cs = __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(p.cos_sin) + (size_t)pos * kD + lane) << 16);
+            sn = __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(p.cos_sin) + (size_t)pos * kD + 32 + lane) << 16);
+        }
+        uint16_t* q16 = reinterpret_cast<uint16_t*>(qkvb_s);
+#pragma unroll
+        for (int which = 0; which < G + 2; ++which) {
+            const int row = which < G ? (kvh * G + which) * kD : (which == G ? (p.QH + kvh) * kD : (p.QH + p.KVH + kvh) * kD);
+            const float* src = p.c_qkv + (size_t)b * nqkv + row;
+            float x0 = round_bf16(__ldcg(src + lane)), x1 = round_bf16(__ldcg(src + 32 + lane));   // projection output dtype
+            if (which <= G) {
+                const float y0 = rope_elem(x0, x1, cs, sn, true);
+                x1 = rope_elem(x1, x0, cs, sn, false);
+                x0 = y0;
+            }
+            q16[which * kD + lane] = (uint16_t)f32_to_bf16_bits(x0);
+            q16[which * kD + 32 + lane] = (uint16_t)f32_to_bf16_bits(x1);
+        }
+    }
+    __syncwarp();
+    if (we == seq && lane < 16 && sh.slot_off[b] >= 0) {      // this chunk holds position seq-1: append K/V
+        uint16_t* kvw = const_cast<uint16_t*>(kvr);
+        const int l8 = lane & 7;
+        const long long e = sh.slot_off[b] + hs + 8 * l8;
+        if (lane < 8) *reinterpret_cast<uint4*>(kvw + p.k_off + e) = *reinterpret_cast<const uint4*>(qkvb_s + G * 32 + 4 * l8);
+        else *reinterpret_cast<uint4*>(kvw + p.v_off + e) = *reinterpret_cast<const uint4*>(qkvb_s + (G + 1) * 32 + 4 * l8);
+    }
+
+    float m[G], l[G], acc[G][2];
+#pragma unroll
+    for (int hh = 0; hh < G; ++hh) {
+        m[hh] = -INFINITY;
+        l[hh] = 0.f;
+        acc[hh][0] = acc[hh][1] = 0.f;
+    }
+    bool alive = true;
+#pragma unroll 1
+    for (int k = 0; k < nruns; ++k) {
+        const int r0 = ws + 16 * k;
+        const int st = (int)(c.kvc & (kKvStages - 1));
+        // after a failed wait the remaining runs are still waited for (each wait bounded), nothing is computed
+        alive = b_wait_mbar(c, &bars[st], (c.kvc / kKvStages) & 1u) && alive;
+        unsigned char* data = ring + st * kRunBytes;
+        if (alive && !(p.dbg & 8u)) {
+        if (we == seq && seq - 1 >= r0 && seq - 1 < r0 + 16) {      // the new token's row, from the prologue
+            uint32_t* rowp = reinterpret_cast<uint32_t*>(data + (seq - 1 - r0) * 256);
+            rowp[lane] = qkvb_s[G * 32 + lane];
+            rowp[32 + lane] = qkvb_s[(G + 1) * 32 + lane];
+            __syncwarp();
+        }
+        const int pp = r0 + pl;
+        const bool valid = pp < we;
+        float d0[G], d1[G];
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) d0[hh] = d1[hh] = 0.f;
+        const unsigned char* krow = data + pl * 256 + half * 64;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int ii = (i + pl) & 3;
+            const uint4 k4 = *reinterpret_cast<const uint4*>(krow + ii * 16);
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) {
+                const uint4 q4 = *reinterpret_cast<const uint4*>(qkvb_s + hh * 32 + 16 * half + 4 * ii);
+                d0[hh] = fma2_bf16(k4.x, q4.x, d0[hh]);
+                d1[hh] = fma2_bf16(k4.y, q4.y, d1[hh]);
+                d0[hh] = fma2_bf16(k4.z, q4.z, d0[hh]);
+                d1[hh] = fma2_bf16(k4.w, q4.w, d1[hh]);
+            }
+        }
+        float sc[G], mx[G], pr[G];
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) {
+            sc[hh] = d0[hh] + d1[hh];
+            sc[hh] += __shfl_xor_sync(kFullMask, sc[hh], 1);
+        }
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) {
+            sc[hh] = valid ? round_bf16(sc[hh]) * 0.125f : -INFINITY;    // bf16 matmul output, exact 1/8 scale
+            int key = __float_as_int(sc[hh]);
+            key ^= (key >> 31) & 0x7fffffff;
+            key = __reduce_max_sync(kFullMask, key);
+            mx[hh] = __int_as_float(key ^ ((key >> 31) & 0x7fffffff));
+        }
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) {
+            const float mn = fmaxf(m[hh], mx[hh]);
+            const float alpha = (mn == -INFINITY) ? 1.f : __expf(m[hh] - mn);
+            pr[hh] = (sc[hh] == -INFINITY) ? 0.f : __expf(sc[hh] - mn);
+            m[hh] = mn;
+            l[hh] = l[hh] * alpha + (half == 0 ? pr[hh] : 0.f);
+            acc[hh][0] *= alpha;
+            acc[hh][1] *= alpha;
+            if (half == 0) prob_s[hh * 16 + pl] = pr[hh];
+        }
+        __syncwarp();
+        const int jn = we - r0;               // positions of this run that exist (the rest of the stage is stale)
+        float a0[G], a1[G];
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) {
+            a0[hh] = acc[hh][0];
+            a1[hh] = acc[hh][1];
+        }
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+            uint32_t v[4];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const int j = 4 * j4 + jj;
+                v[jj] = *reinterpret_cast<const uint32_t*>(data + j * 256 + 128 + lane * 4);
+                if (j >= jn) v[jj] = 0u;
+            }
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) {
+                const float4 p4 = *reinterpret_cast<const float4*>(prob_s + hh * 16 + 4 * j4);
+                a0[hh] = fmaf(p4.x, bf16_lo(v[0]), a0[hh]); a1[hh] = fmaf(p4.x, bf16_hi(v[0]), a1[hh]);
+                a0[hh] = fmaf(p4.y, bf16_lo(v[1]), a0[hh]); a1[hh] = fmaf(p4.y, bf16_hi(v[1]), a1[hh]);
+                a0[hh] = fmaf(p4.z, bf16_lo(v[2]), a0[hh]); a1[hh] = fmaf(p4.z, bf16_hi(v[2]), a1[hh]);
+                a0[hh] = fmaf(p4.w, bf16_lo(v[3]), a0[hh]); a1[hh] = fmaf(p4.w, bf16_hi(v[3]), a1[hh]);
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) {
+            acc[hh][0] = a0[hh];
+            acc[hh][1] = a1[hh];
+        }
+        }
+        __syncwarp();                          // every lane is done with the stage before it is refilled
+        ++c.kvc;
+        if (k + kKvStages < nruns) issue(ws + 16 * (k + kKvStages));
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) l[hh] += __shfl_xor_sync(kFullMask, l[hh], off);
+    float* part = p.part + ((size_t)(b * p.KVH + kvh) * kNcB + chunk) * G * 66;
+#pragma unroll
+    for (int hh = 0; hh < G; ++hh) {
+        float* dst = part + hh * 66;
+        if (lane == 0) {
+            dst[0] = m[hh];
+            dst[1] = l[hh];
+        }
+        *reinterpret_cast<float2*>(dst + 2 + 2 * lane) = make_float2(acc[hh][0], acc[hh][1]);
+    }
+    __syncwarp();
+}
+
+// log-sum-exp merge of the chunk partials: one warp per (request, query head); bf16 output into attn[b][hq*64 + d]
+__device__ void merge_phase(BC& c) {
+    const BParams& p = c.p;
+    BShared& sh = c.sh;
+    const int G = p.G, lane = c.lane;
+    const int gw = c.cta * (kThreadsB / 32) + c.warp, nw = c.ncta * (kThreadsB / 32);
+    for (int t = gw; t < p.nb * p.QH; t += nw) {
+        const int b = t / p.QH, hq = t - b * p.QH;
+        const int kvh = hq / G, g = hq - kvh * G;
+        const int nc = sh.nc[b];
+        const float* part = p.part + ((size_t)(b * p.KVH + kvh) * kNcB * G + g) * 66;
+        const size_t cs = (size_t)G * 66;
+        const float mc = lane < nc ? __ldcg(part + lane * cs) : -INFINITY;
+        const float lc = lane < nc ? __ldcg(part + lane * cs + 1) : 0.f;
+        const float M = warp_max(mc);
+        const float wc = __expf(mc - M);
+        const float den = warp_sum(lc * wc);
+        float a0 = 0.f, a1 = 0.f;
+        for (int ch = 0; ch < nc; ++ch) {
+            const float wgt = __shfl_sync(kFullMask, wc, ch);
+            const float2 a = __ldcg(reinterpret_cast<const float2*>(part + ch * cs + 2) + lane);
+            a0 = fmaf(wgt, a.x, a0);
+            a1 = fmaf(wgt, a.y, a1);
+        }
+        const float inv = 1.f / den;
+        reinterpret_cast<uint32_t*>(p.attn + (size_t)b * p.QH * kD + hq * kD)[lane] = pack_bf16x2(a0 * inv, a1 * inv);
+    }
+    // the q / k / v sums have been consumed by every attention item: clear them for the next layer
+    const long long total = (long long)p.nb * (p.QH + 2 * p.KVH) * kD;
+    for (long long e = (long long)c.cta * kThreadsB + c.tid; e < total; e += (long long)c.ncta * kThreadsB) p.c_qkv[e] = 0.f;
+}
+
+// ------------------------------------------------------------------ the kernel
+template <int NP, int G, int WF>
+__global__ void __launch_bounds__(kThreadsB, 1) decode_batched_kernel(const BParams p) {
+    extern __shared__ __align__(128) unsigned char smem_dyn[];
+    // layout: A stages (1024-byte aligned: the swizzle pattern repeats every 1024 bytes), B stages, shared struct,
+    // scratch floats; the launcher asks for 1024 bytes more than the sum so the base can be rounded up
+    unsigned char* smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+    unsigned char* stage_a = smem_raw;
+    unsigned char* stage_b = stage_a + kStages * kAStage;
+    BShared& sh = *reinterpret_cast<BShared*>(stage_a + staging_bytes(NP));
+    float* scratch = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(&sh) + ((sizeof(BShared) + 127) & ~size_t(127)));
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    BC c{p, sh, stage_a, stage_b, scratch, tid, warp, lane, (int)blockIdx.x, (int)gridDim.x, 0u, {0u, 0u, 0u, 0u}, stage_a, 0u, 0u};
+
+    if (tid == 0) {
+        sh.abort_flag = (p.ctrl[kCtrlStatus] != 0u) ? 1 : 0;
+        sh.bar_gen = 0;
+        for (int s = 0; s < kStages; ++s) mbar_init(&sh.full[s], 128);
+        mbar_init(&sh.accum, 1);
+        for (int w = 0; w < kThreadsB / 32; ++w)
+            for (int s = 0; s < kKvStages; ++s) mbar_init(&sh.kvbar[w][s], 1);
+        int smax = 1;
+        for (int b = 0; b < p.nb; ++b) {
+            if (p.seq_lens[b] > p.max_seq_len) {
+                sh.abort_flag = 1;
+                atomicCAS(p.ctrl + kCtrlStatus, 0u, (unsigned)kErrMaxSeq);
+            }
+            smax = max(smax, min(max(p.seq_lens[b], 1), p.max_seq_len));
+        }
+        // chunks per (request, kv head): enough warp-level items for about two rounds of the grid's warps, at most
+        // kNcB, at least 64 positions each
+        const int units = p.nb * p.KVH, nwarps = (int)gridDim.x * (kThreadsB / 32);
+        int nc = (2 * nwarps + units - 1) / units;
+        nc = nc < 1 ? 1 : (nc > kNcB ? kNcB : nc);
+        const int lc = max(64, (((smax + nc - 1) / nc) + 15) & ~15);
+        sh.lc = lc;
+        sh.ncmax = (smax + lc - 1) / lc;
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+    if (tid < p.nb) {
+        const int seq = min(max(p.seq_lens[tid], 1), p.max_seq_len);
+        sh.seq[tid] = seq;
+        sh.pos[tid] = (int)max(p.positions[tid], 0LL);
+        sh.nc[tid] = (seq + sh.lc - 1) / sh.lc;
+        const long long tok = p.ids_i64 ? reinterpret_cast<const long long*>(p.input_ids)[tid]
+                                        : (long long)reinterpret_cast<const int*>(p.input_ids)[tid];
+        sh.tok[tid] = tok < 0 ? 0 : (tok >= p.V ? p.V - 1 : tok);
+        const long long slot = p.slot_mapping[tid];
+        sh.slot_off[tid] = slot < 0 ? -1 : (slot / p.block_size) * p.block_stride + (slot % p.block_size) * p.token_stride;
+    }
+    if (warp == 4) {
+        // tensor memory for one accumulator tile: 128 lanes x NP fp32 columns (allocation unit: power of two >= 32)
+        const uint32_t ncols = NP < 32 ? 32u : (uint32_t)NP;
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)), "r"(ncols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (c.cta == 0 && tid < p.nb) p.argkey[tid] = 0ull;
+
+    auto wptr = [&](int layer, int widx) { return reinterpret_cast<const unsigned char*>(__ldg(p.layers + layer * 6 + widx)); };
+    // stamps: slot 2k = the CTA's own work of phase k done, slot 2k+1 = the grid barrier behind it passed
+    int slot = 0;
+    unsigned long long* prof = nullptr;
+    auto stamp = [&]() {
+        if (prof && slot < kProfSlots) prof[slot] = global_ns();
+        ++slot;
+    };
+    auto sync_phase = [&]() {
+        stamp();
+        grid_barrier(c);
+        stamp();
+    };
+    for (int layer = 0; layer < p.L; ++layer) {
+        prof = (p.profile && tid == 0) ? p.profile + ((size_t)c.cta * p.L + layer) * kProfSlots : nullptr;
+        slot = 0;
+        stamp();
+        norm_phase(c, layer == 0 ? 0 : 1, layer, reinterpret_cast<const uint16_t*>(wptr(layer, 0)), false);
+        sync_phase();
+        gemm_phase<NP, WF>(c, p.gd[kQKV], wptr(layer, 1), p.xn, p.c_qkv, 0);
+        sync_phase();
+        {
+            // attention items (chunk, request, kv head), chunk-major, dealt to the warps of the grid
+            const int nslots = sh.ncmax * p.nb * p.KVH;
+            const int nwarps = c.ncta * (kThreadsB / 32);
+            for (int s = c.warp * c.ncta + c.cta; s < nslots; s += nwarps) {
+                const int kvh = s % p.KVH, rest = s / p.KVH;
+                const int b = rest % p.nb, chunk = rest / p.nb;
+                if (chunk >= sh.nc[b]) continue;
+                attention_item_b<G>(c, layer, b, kvh, chunk);
+            }
+        }
+        sync_phase();
+        merge_phase(c);
+        sync_phase();
+        gemm_phase<NP, WF>(c, p.gd[kO], wptr(layer, 2), p.attn, p.c_o, 0);
+        sync_phase();
+        norm_phase(c, 2, layer, reinterpret_cast<const uint16_t*>(wptr(layer, 3)), false);
+        sync_phase();
+        gemm_phase<NP, WF>(c, p.gd[kGU], wptr(layer, 4), p.xn, p.c_gu, 0);
+        sync_phase();
+        swiglu_phase(c);
+        sync_phase();
+        gemm_phase<NP, WF>(c, p.gd[kDown], wptr(layer, 5), p.act, p.c_down, 0);
+        sync_phase();
+    }
+    norm_phase(c, 1, p.L, p.final_norm, true);
+    if (p.lm_head) {
+        grid_barrier(c);
+        gemm_phase<NP, WF>(c, p.gd[kLM], p.embed, p.xn, nullptr, 1);
+    }
+
+    __syncthreads();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        const uint32_t ncols = NP < 32 ? 32u : (uint32_t)NP;
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(sh.tmem_base), "r"(ncols) : "memory");
+    }
+    // the last CTA to finish publishes the greedy ids, optionally advances the step inputs, resets the counters
+    if (tid == 0) {
+        __threadfence();
+        const unsigned prev = atomicAdd(p.bctrl + 1, 1u);
+        if (prev == (unsigned)c.ncta - 1u) {
+            __threadfence();
+            const bool ok = *((volatile unsigned int*)(p.ctrl + kCtrlStatus)) == 0;
+            if (p.next_ids && p.lm_head && ok) {
+                for (int b = 0; b < p.nb; ++b) {
+                    const unsigned long long key = *((volatile unsigned long long*)(p.argkey + b));
+                    const long long id = (long long)(0xffffffffu - (uint32_t)key);
+                    p.next_ids[b] = id;
+                    if (p.advance) {
+                        if (p.ids_i64) reinterpret_cast<long long*>(const_cast<void*>(p.input_ids))[b] = id;
+                        else reinterpret_cast<int*>(const_cast<void*>(p.input_ids))[b] = (int)id;
+                        const long long np = p.positions[b] + 1;
+                        const_cast<long long*>(p.positions)[b] = np;
+                        const_cast<int*>(p.seq_lens)[b] = p.seq_lens[b] + 1;
+                        if (p.slot_mapping[b] >= 0 && np < (long long)p.max_seq_len) {
+                            const long long blk = p.block_table[(size_t)b * p.bt_stride + (int)(np / p.block_size)];
+                            const_cast<long long*>(p.slot_mapping)[b] = blk * p.block_size + np % p.block_size;
+                        }
+                    }
+                }
+            }
+            p.bctrl[0] = 0u;
+            p.bctrl[1] = 0u;
+            __threadfence();
+        }
+    }
+}
+
+}  // namespace batched
+}  // namespace pk

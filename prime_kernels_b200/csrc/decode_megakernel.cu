@@ -1657,6 +1657,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const DecodePa
 
 }  // namespace pk
 #include "decode_fast.cuh"
+#include "decode_batched.cuh"
 namespace pk {
 
 // One-CTA helper for tests of the failure path: polls a flagged word that nothing writes with the same
@@ -1683,6 +1684,10 @@ struct ModelGeom {
 
 struct WsLayout {
     size_t ctrl, argkey, x, qkv, attn, h1, act, part, fast, total;
+};
+// Region of the tensor-core batched kernel (9..64 requests).
+struct BatchedLayout {
+    size_t bctrl, argkey, c_qkv, c_o, c_gu, c_down, x, h1, xn, attn, act, part, total;
 };
 // Region of the batch-1 fast kernel (its own words; never shared with the generic kernel's buffers).
 struct FastLayout {
@@ -1718,6 +1723,35 @@ static FastLayout fast_layout(const ModelGeom& g) {
     return l;
 }
 
+static int batched_np(int B) { return B <= 16 ? 16 : (B <= 32 ? 32 : 64); }
+
+static BatchedLayout batched_layout(const ModelGeom& g, int B) {
+    BatchedLayout l{};
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t at = off;
+        off += align_up(bytes, 256);
+        return at;
+    };
+    const size_t NP = (size_t)batched_np(B);
+    const size_t nqkv = (size_t)(g.QH + 2 * g.KVH) * kD;
+    const int G = g.QH / (g.KVH > 0 ? g.KVH : 1);
+    l.bctrl = take(256);
+    l.argkey = take(8 * batched::kMaxReq);
+    l.c_qkv = take(NP * nqkv * 4);
+    l.c_o = take(NP * g.H * 4);
+    l.c_gu = take(NP * 2 * g.I * 4);
+    l.c_down = take(NP * g.H * 4);
+    l.x = take(NP * g.H * 2);
+    l.h1 = take(NP * g.H * 2);
+    l.xn = take(NP * g.H * 2);
+    l.attn = take(NP * g.QH * kD * 2);
+    l.act = take(NP * g.I * 2);
+    l.part = take((size_t)B * g.KVH * batched::kNcB * G * 66 * 4);
+    l.total = off;
+    return l;
+}
+
 static WsLayout ws_layout(const ModelGeom& g, int B) {
     WsLayout l{};
     size_t off = 0;
@@ -1743,6 +1777,9 @@ static WsLayout ws_layout(const ModelGeom& g, int B) {
     l.total = off;
     return l;
 }
+
+// Workspace of a launch of 9..64 requests (tensor-core kernel): control words, then its own region.
+static size_t batched_ws_bytes(const ModelGeom& g, int B) { return 256 + batched_layout(g, B).total; }
 
 struct DeviceInfo {
     bool valid = false;
@@ -1921,6 +1958,7 @@ struct StepArgs {
     const void* cos_sin; int cs_fp32;
     void* out_hidden; void* logits; void* next_ids; void* layer_outputs;
     void* ws; size_t ws_bytes; int max_seq_len; int lm_head; int advance;
+    int force_tc = 0;     // run the tensor-core kernel whatever the batch
 };
 
 // ---- batch-1 fast path (decode_fast.cuh) --------------------------------------------------------
@@ -1979,6 +2017,7 @@ static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo
     p.next_ids = static_cast<long long*>(a.next_ids);
     p.layer_outputs = static_cast<uint16_t*>(a.layer_outputs);
     p.profile = (g_profile && g_profile_bytes >= (size_t)di.sm_count * g.L * kProfSlots * 8) ? g_profile : nullptr;
+    p.dbg = (unsigned)g_fast_dbg;
     p.ctrl = reinterpret_cast<unsigned int*>(ws + lay.ctrl);
     p.fctrl = reinterpret_cast<unsigned int*>(fw + fl.fctrl);
     p.argkey = reinterpret_cast<unsigned long long*>(fw + fl.argkey);
@@ -2030,8 +2069,136 @@ static int fast_launch(const ModelGeom& g, const StepArgs& a, const DeviceInfo& 
     return kFastNotEligible;
 }
 
+// ---- tensor-core batched path (decode_batched.cuh): 9..64 requests in one launch -------------------
+template <int NP, int G, int WF>
+static int batched_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo& di) {
+    using namespace batched;
+    const size_t need = batched_ws_bytes(g, a.B);
+    if (a.ws_bytes < need) return kErrScratch;
+    constexpr int NW = kThreadsB / 32;
+    const size_t item_words = (size_t)NW * ((G + 2) * 32 + G * 16);      // per-warp q/k/v + probabilities
+    const size_t scratch_words = item_words > (size_t)g.H ? item_words : (size_t)g.H;
+    const size_t smem = 1024 + (size_t)staging_bytes(NP) + align_up(sizeof(BShared), 128) +
+                        align_up(scratch_words * 4, 128);
+    if (smem > (size_t)di.smem_optin) return kErrResidency;
+    auto fn = decode_batched_kernel<NP, G, WF>;
+    int rc = ensure_smem(reinterpret_cast<const void*>(fn), smem);
+    if (rc) return rc;
+    rc = ensure_workspace(a.ws, a.ws_bytes, need, g, a.stream);
+    if (rc) return rc;
+    const BatchedLayout bl = batched_layout(g, a.B);
+    unsigned char* ws = static_cast<unsigned char*>(a.ws);
+    unsigned char* bw = ws + 256;
+    BParams p{};
+    p.layers = static_cast<const unsigned long long*>(a.layers);
+    p.kv = static_cast<const unsigned long long*>(a.kv);
+    p.embed = static_cast<const unsigned char*>(a.embed);
+    p.embed_bf16 = static_cast<const uint16_t*>(a.embed_lookup ? a.embed_lookup : a.embed);
+    p.final_norm = static_cast<const uint16_t*>(a.final_norm);
+    p.input_ids = a.input_ids;
+    p.positions = static_cast<const long long*>(a.positions);
+    p.seq_lens = static_cast<const int*>(a.seq_lens);
+    p.block_table = static_cast<const int*>(a.block_table);
+    p.slot_mapping = static_cast<const long long*>(a.slot_mapping);
+    p.cos_sin = a.cos_sin;
+    p.out_hidden = static_cast<uint16_t*>(a.out_hidden);
+    p.logits = static_cast<uint16_t*>(a.logits);
+    p.next_ids = static_cast<long long*>(a.next_ids);
+    p.layer_outputs = static_cast<uint16_t*>(a.layer_outputs);
+    p.profile = (g_profile && g_profile_bytes >= (size_t)di.sm_count * g.L * kProfSlots * 8) ? g_profile : nullptr;
+    p.dbg = (unsigned)g_fast_dbg;
+    p.ctrl = reinterpret_cast<unsigned int*>(ws);
+    p.bctrl = reinterpret_cast<unsigned int*>(bw + bl.bctrl);
+    p.argkey = reinterpret_cast<unsigned long long*>(bw + bl.argkey);
+    p.c_qkv = reinterpret_cast<float*>(bw + bl.c_qkv);
+    p.c_o = reinterpret_cast<float*>(bw + bl.c_o);
+    p.c_gu = reinterpret_cast<float*>(bw + bl.c_gu);
+    p.c_down = reinterpret_cast<float*>(bw + bl.c_down);
+    p.x = reinterpret_cast<uint16_t*>(bw + bl.x);
+    p.h1 = reinterpret_cast<uint16_t*>(bw + bl.h1);
+    p.xn = reinterpret_cast<uint16_t*>(bw + bl.xn);
+    p.attn = reinterpret_cast<uint16_t*>(bw + bl.attn);
+    p.act = reinterpret_cast<uint16_t*>(bw + bl.act);
+    p.part = reinterpret_cast<float*>(bw + bl.part);
+    p.k_off = a.k_off;
+    p.v_off = a.v_off;
+    p.block_stride = a.block_stride;
+    p.token_stride = a.token_stride;
+    p.head_stride = a.head_stride;
+    p.block_size = a.block_size;
+    p.bt_stride = a.bt_stride;
+    p.ids_i64 = a.ids_i64 ? 1 : 0;
+    p.cs_fp32 = a.cs_fp32 ? 1 : 0;
+    p.H = g.H; p.I = g.I; p.L = g.L; p.QH = g.QH; p.KVH = g.KVH; p.V = g.V; p.G = G;
+    p.nb = a.B;
+    p.wfmt = g.wfmt;
+    p.lm_head = (a.lm_head && (a.logits || a.next_ids)) ? 1 : 0;
+    p.advance = (a.advance && p.lm_head && a.next_ids) ? 1 : 0;
+    p.max_seq_len = a.max_seq_len;
+    p.spin_limit = g_spin_limit;
+    p.eps = g.eps;
+    // GEMM phases: rows, K, K blocks (of 64) per work item chosen so that a phase has about one item per CTA
+    const int nqkv = (g.QH + 2 * g.KVH) * kD;
+    const int rows[5] = {nqkv, g.H, 2 * g.I, g.H, g.V};
+    const int Ks[5] = {g.H, g.QH * kD, g.H, g.I, g.H};
+    const int widx[5] = {1, 2, 4, 5, -1};
+    for (int t = 0; t < 5; ++t) {
+        GemmDesc& d = p.gd[t];
+        d.rows = rows[t];
+        d.K = Ks[t];
+        d.widx = widx[t];
+        d.rowbytes = g.wfmt ? (int)align_up((size_t)Ks[t] + Ks[t] / 32, 16) : Ks[t] * 2;
+        const int rtiles = (rows[t] + 127) / 128, nk64 = Ks[t] / 64;
+        int blocks = (rtiles * nk64 + di.sm_count - 1) / di.sm_count;
+        d.blocks = blocks < 1 ? 1 : (blocks > nk64 ? nk64 : blocks);
+    }
+    void* args[] = {&p};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fn), dim3(di.sm_count), dim3(kThreadsB), args,
+                                                smem, a.stream);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return e == cudaErrorCooperativeLaunchTooLarge ? (int)kErrResidency : (int)e;
+    }
+    return (int)cudaPeekAtLastError();
+}
+
+static int batched_launch(const ModelGeom& g, const StepArgs& a, const DeviceInfo& di) {
+    const int G = g.QH / g.KVH;
+    if ((G != 1 && G != 3) || g.H % 64 || g.I % 64 || (g.QH * kD) % 64 || g.H > 4096) return kErrShape;
+    const int NP = batched_np(a.B);
+#define PK_BCASE(np, gg)                                                                      \
+    if (NP == np && G == gg) return g.wfmt ? batched_launch_t<np, gg, 1>(g, a, di) : batched_launch_t<np, gg, 0>(g, a, di);
+    PK_BCASE(16, 1) PK_BCASE(32, 1) PK_BCASE(64, 1) PK_BCASE(16, 3) PK_BCASE(32, 3) PK_BCASE(64, 3)
+#undef PK_BCASE
+    return kErrShape;
+}
+
 static int decode_launch(const ModelGeom& g, const StepArgs& a) {
-    if (a.B < 1 || a.B > kMaxB) return kErrBatch;
+    if (a.B < 1 || a.B > batched::kMaxReq) return kErrBatch;
+    if (a.B > kMaxB || a.force_tc) {
+        // 9..64 requests: the tensor-core kernel (same argument checks as below)
+        if (a.max_seq_len < 1 || a.max_seq_len > kMaxSeq) return kErrMaxSeq;
+        if (!a.input_ids || !a.positions || !a.seq_lens || !a.block_table || !a.slot_mapping || !a.layers || !a.embed ||
+            !a.final_norm || !a.kv || !a.cos_sin || !a.out_hidden || !a.ws)
+            return kErrNull;
+        if (g.H <= 0 || g.I <= 0 || g.L < 1 || g.L > kMaxLayers || g.QH <= 0 || g.KVH <= 0 || g.QH % g.KVH || g.V <= 0 ||
+            (g.wfmt != 0 && g.wfmt != 1))
+            return kErrShape;
+        if (a.block_size <= 0 || a.bt_stride < 1 || (long long)a.bt_stride * a.block_size < a.max_seq_len) return kErrBlock;
+        if (a.k_off % 8 || a.v_off % 8 || a.block_stride % 8 || a.token_stride % 8 || a.head_stride % 8 || a.k_off < 0 ||
+            a.v_off < 0 || a.block_stride < 0 || a.token_stride < 0 || a.head_stride < 0)
+            return kErrAlign;
+        auto mis = [](const void* q) { return q && (reinterpret_cast<uintptr_t>(q) % 16) != 0; };
+        if (mis(a.layers) || mis(a.embed) || mis(a.final_norm) || mis(a.ws) || mis(a.out_hidden) || mis(a.kv) ||
+            mis(a.embed_lookup) || mis(a.layer_outputs) || mis(a.logits))
+            return kErrAlign;
+        DeviceInfo dib;
+        int rcb = device_info(dib);
+        if (rcb) return rcb;
+        if (dib.major != 10) return kErrArch;
+        if (!dib.coop) return kErrCoop;
+        return batched_launch(g, a, dib);
+    }
     const int KB = a.B <= 4 ? a.B : kMaxB;      // kernel batch: exact up to 4, the batch-8 kernel (padded) beyond
     if (a.max_seq_len < 1 || a.max_seq_len > kMaxSeq) return kErrMaxSeq;
     if (!a.input_ids || !a.positions || !a.seq_lens || !a.block_table || !a.slot_mapping || !a.layers || !a.embed ||
@@ -2149,7 +2316,7 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
 static const char* status_string(int status) {
     switch (status) {
         case kOk: return "ok";
-        case kErrBatch: return "batch_must_be_1_to_8";
+        case kErrBatch: return "batch_must_be_1_to_64";
         case kErrMaxSeq: return "max_seq_len_must_be_1_to_8192";
         case kErrNull: return "null_device_pointer";
         case kErrCoop: return "cooperative_launch_unsupported";
@@ -2196,9 +2363,14 @@ static ModelGeom to_geom(const PkDecodeModel* m) {
 }
 
 extern "C" size_t pk_decode_workspace_bytes(const PkDecodeModel* m, int max_batch) {
-    if (!m || max_batch < 1 || max_batch > kMaxB || m->kv_heads <= 0) return 0;
-    // batches 5..7 run on the batch-8 kernel (padded), so they need its workspace
-    return ws_layout(to_geom(m), max_batch <= 4 ? max_batch : kMaxB).total;
+    if (!m || max_batch < 1 || max_batch > batched::kMaxReq || m->kv_heads <= 0) return 0;
+    // batches 5..7 run on the batch-8 kernel (padded), so they need its workspace; a workspace for more than 8
+    // requests per launch (tensor-core kernel) also serves every smaller launch
+    const ModelGeom g = to_geom(m);
+    const size_t small = ws_layout(g, max_batch <= 4 ? max_batch : kMaxB).total;
+    if (max_batch <= kMaxB) return small;
+    const size_t big = batched_ws_bytes(g, max_batch);
+    return big > small ? big : small;
 }
 
 extern "C" int pk_decode_step(const PkDecodeModel* m, const PkDecodeArgs* a) {
@@ -2208,6 +2380,21 @@ extern "C" int pk_decode_step(const PkDecodeModel* m, const PkDecodeArgs* a) {
                a->kv_layers, a->k_off, a->v_off, a->block_stride, a->token_stride, a->head_stride, a->block_size,
                a->cos_sin, a->cs_fp32, a->out_hidden, a->logits, a->next_ids, a->layer_outputs, a->workspace,
                a->workspace_bytes, a->max_seq_len, a->lm_head, a->advance};
+    return decode_launch(to_geom(m), s);
+}
+
+// Same step on the tensor-core kernel whatever the batch (pk_decode_step picks it from 9 requests on).  For
+// models whose rows are too wide for the CUDA-core kernel at the wanted batch (SmolLM2-1.7B above 4 requests).
+// The workspace must have pk_decode_workspace_bytes(model, 64) bytes and must not be shared with launches of the
+// other kernels.
+extern "C" int pk_decode_step_tc(const PkDecodeModel* m, const PkDecodeArgs* a) {
+    if (!m || !a) return kErrNull;
+    StepArgs s{static_cast<cudaStream_t>(a->stream), a->batch, a->input_ids, a->ids_i64, a->positions, a->seq_lens,
+               a->block_table, a->bt_stride, a->slot_mapping, a->layers, a->embed, a->embed_lookup, a->final_norm,
+               a->kv_layers, a->k_off, a->v_off, a->block_stride, a->token_stride, a->head_stride, a->block_size,
+               a->cos_sin, a->cs_fp32, a->out_hidden, a->logits, a->next_ids, a->layer_outputs, a->workspace,
+               a->workspace_bytes, a->max_seq_len, a->lm_head, a->advance};
+    s.force_tc = 1;
     return decode_launch(to_geom(m), s);
 }
 
@@ -2335,6 +2522,7 @@ extern "C" int mk_decode(void* stream, int B, const void* input_ids, int ids_i64
                          long long k_off, long long v_off, long long block_stride, long long token_stride,
                          long long head_stride, int block_size, const void* cos_sin, int cs_fp32, void* out_hidden,
                          void* scratch, size_t scratch_bytes, int max_seq_len) {
+    if (B < 1 || B > kMaxB) return kErrBatch;      // the drop-in entry takes one launch of the CUDA-core kernels
     StepArgs s{static_cast<cudaStream_t>(stream), B, input_ids, ids_i64, positions, seq_lens, block_table, bt_stride,
                slot_mapping, layers, embed, nullptr, final_norm, kv_layers, k_off, v_off, block_stride, token_stride,
                head_stride, block_size, cos_sin, cs_fp32, out_hidden, nullptr, nullptr, nullptr, scratch, scratch_bytes,
@@ -2358,6 +2546,7 @@ extern "C" int decode360(void* stream, int B, const void* input_ids, const void*
     (void)debug;
     (void)debug_bytes;
     if (debug_layer_index < -1 || debug_layer_index >= kGeom360.L) return kErrBlock;
+    if (B < 1 || B > kMaxB) return kErrBatch;      // the drop-in entry takes one launch of the CUDA-core kernels
     StepArgs s{static_cast<cudaStream_t>(stream), B, input_ids, 0, positions, seq_lens, block_table, bt_stride,
                slot_mapping, layers, embed, nullptr, final_norm, kv, k_off, v_off, block_stride, token_stride,
                head_stride, block_size, cos_sin, cs_fp32, out_hidden, nullptr, nullptr, layer_outputs, scratch,

@@ -23,8 +23,8 @@ __all__ = ["Geometry", "SMOLLM2_135M", "SMOLLM2_360M", "SMOLLM2_1P7B", "GEOMETRI
            "HEAD_DIM", "decode_step", "check_status", "DecodeSession", "HostStep", "workspace_bytes", "pack_matrix_mxfp8", "pack_weights_mxfp8",
            "unpack_matrix_mxfp8", "packed_row_bytes"]
 
-MAX_BATCH = 8          # requests one kernel launch takes
-MAX_REQUESTS = 64      # requests one decode_step call takes (larger batches run as several launches)
+MAX_BATCH = 8          # requests one launch of the CUDA-core kernels takes
+MAX_REQUESTS = 64      # requests one decode_step call takes: 9..64 run as one launch of the tensor-core kernel
 MAX_SEQ = 8192
 
 
@@ -32,7 +32,8 @@ MAX_SEQ = 8192
 def _decode_step_fake(input_ids, positions, seq_lens, block_table, slot_mapping, embed, embed_lookup, layers_table,
                       final_norm, kv_table, k_off, v_off, block_stride, token_stride, head_stride, block_size,
                       cos_sin_cache, out_hidden, logits, next_ids, layer_outputs, workspace, hidden, intermediate,
-                      layers, q_heads, kv_heads, vocab, weight_format, eps, max_seq_len, lm_head, advance):
+                      layers, q_heads, kv_heads, vocab, weight_format, eps, max_seq_len, lm_head, advance,
+                      tensor_cores=False):
     return 0
 
 
@@ -54,11 +55,17 @@ class _Runtime:
         self.scratch = torch.zeros(workspace_bytes(geometry, MAX_BATCH), dtype=torch.uint8, device=device)
         self.out = torch.empty((MAX_REQUESTS, geometry.hidden), dtype=torch.bfloat16, device=device)
         self.group = MAX_BATCH          # requests per launch; lowered when the geometry does not fit at that batch
+        self.scratch_tc = None          # workspace of the tensor-core kernel (9..64 requests), allocated on first use
         self.logits = None
         self.next_ids = None
         self.table_key = None
         self.layers_t = None
         self.kv_t = None
+
+    def tc_scratch(self):
+        if self.scratch_tc is None:
+            self.scratch_tc = torch.zeros(workspace_bytes(self.geometry, MAX_REQUESTS), dtype=torch.uint8, device=self.device)
+        return self.scratch_tc
 
     def lm_buffers(self):
         if self.logits is None:
@@ -190,11 +197,12 @@ def _check_weights(geometry: Geometry, device, embed, final_norm, layers, embed_
 
 def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_table, slot_mapping, embed, layers,
                 final_norm, kv_caches, cos_sin_cache, eps, layer_outputs=None, lm_head=False, advance=False,
-                embed_lookup=None, name="decode"):
+                embed_lookup=None, name="decode", tensor_cores=True):
     """One decode step for ``geometry``.  Returns the final-normed hidden ``[B, hidden]`` (a view of a
     shared buffer), or ``(hidden, logits, next_ids)`` when ``lm_head`` is true.  Up to ``MAX_BATCH`` requests run in
-    one launch; up to ``MAX_REQUESTS`` are accepted and run as consecutive launches (micro-batches), each of which
-    streams the weights again."""
+    one launch of the CUDA-core kernels; 9 to ``MAX_REQUESTS`` requests run in one launch of the tensor-core kernel
+    (``tensor_cores=False`` runs them as consecutive launches of the CUDA-core kernel instead, each of which streams
+    the weights again)."""
     batch = input_ids.shape[0]
     if not 1 <= batch <= MAX_REQUESTS:
         raise ValueError(f"batch must be 1..{MAX_REQUESTS}, got {batch}")
@@ -223,20 +231,34 @@ def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_tab
     if lm_head:
         logits, next_ids = rt.lm_buffers()
 
-    def launch(g0, g1, lo):
+    def launch(g0, g1, lo, scratch=None):
         whole = g0 == 0 and g1 == batch                 # the common case: no slicing on the hot path
         cut = (lambda t: t) if whole else (lambda t: t[g0:g1])
         return torch.ops.prime_decode.decode_step(
             cut(input_ids), cut(positions), cut(seq_lens), cut(block_table), cut(slot_mapping), embed, embed_lookup,
             layers_t, final_norm, kv_t, 0, kv0.shape[3] // 2, kv0.stride(0), kv0.stride(2), kv0.stride(1), block_size,
             cos_sin_cache, rt.out if whole else rt.out[g0:g1], (logits if whole else logits[g0:g1]) if lm_head else None,
-            (next_ids if whole else next_ids[g0:g1]) if lm_head else None, lo, rt.scratch, geometry.hidden,
+            (next_ids if whole else next_ids[g0:g1]) if lm_head else None, lo, rt.scratch if scratch is None else scratch,
+            geometry.hidden,
             geometry.intermediate, geometry.layers, geometry.q_heads, geometry.kv_heads, geometry.vocab,
-            geometry.weight_format, float(eps), max_seq, bool(lm_head), bool(advance))
+            geometry.weight_format, float(eps), max_seq, bool(lm_head), bool(advance), scratch is not None)
 
-    # A launch takes up to rt.group requests (MAX_BATCH, fewer when the geometry's activation staging does not fit
-    # shared memory at that batch: status 9111 / 9105 lowers the group once and for all).  Larger batches run as
-    # consecutive launches over slices of the request arrays: every launch streams the weights again.
+    # 9..64 requests: one launch of the tensor-core kernel (projections as tcgen05 GEMMs, weights streamed once);
+    # also smaller batches that the CUDA-core kernel cannot take in one launch for this geometry (rt.group)
+    def tensor_core_launch():
+        rc = launch(0, batch, layer_outputs, rt.tc_scratch())
+        if rc != 0:
+            raise RuntimeError(f"{name} failed: {status_string(rc)}")
+        if lm_head:
+            return rt.out[:batch], logits[:batch], next_ids[:batch]
+        return rt.out[:batch]
+
+    if tensor_cores and (batch > MAX_BATCH or batch > rt.group):
+        return tensor_core_launch()
+    # A launch of the CUDA-core kernels takes up to rt.group requests (MAX_BATCH, fewer when the geometry's activation
+    # staging does not fit shared memory at that batch: status 9111 / 9105 lowers the group once and for all).
+    # With tensor_cores=False larger batches run as consecutive launches over slices of the request arrays, each of
+    # which streams the weights again.
     g0 = 0
     while g0 < batch:
         g1 = min(batch, g0 + rt.group)
@@ -246,6 +268,8 @@ def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_tab
         rc = launch(g0, g1, lo)
         if rc in (9111, 9105) and g1 - g0 > 1 and rt.group > 1:
             rt.group = max(1, (g1 - g0) // 2)
+            if tensor_cores and g0 == 0 and batch > rt.group:
+                return tensor_core_launch()
             continue
         if rc != 0:
             raise RuntimeError(f"{name} failed: {status_string(rc)}")
@@ -264,7 +288,10 @@ def check_status(geometry: Geometry, device) -> None:
     if rt is None:
         return
     with torch.cuda.device(device):
-        rc = library().pk_decode_status(rt.scratch.data_ptr(), torch.cuda.current_stream(device).cuda_stream)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        rc = library().pk_decode_status(rt.scratch.data_ptr(), stream)
+        if rc == 0 and rt.scratch_tc is not None:
+            rc = library().pk_decode_status(rt.scratch_tc.data_ptr(), stream)
     if rc != 0:
         raise RuntimeError(f"decode failed on the device: {status_string(rc)}")
 

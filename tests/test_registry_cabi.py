@@ -55,7 +55,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_status_strings_and_sizes_without_a_device():
     lib = _cabi.library()
-    assert lib.pk_status_string(9101).decode() == "batch_must_be_1_to_8"
+    assert lib.pk_status_string(9101).decode() == "batch_must_be_1_to_64"
     assert lib.mk_status_string(9110).decode() == "device_wait_timed_out"
     assert lib.decode360_status_string(9106).decode() == "kernel_requires_sm100"
     assert lib.pk_rmsnorm_scale_bytes(1, 960) == 8 * 512
@@ -90,7 +90,7 @@ def test_argument_validation_needs_no_device():
     assert d360(1, 2048, -1) == 9103
     m = _cabi.PkDecodeModel(960, 2560, 32, 15, 5, 49152, 0, 1e-5)
     a = _cabi.PkDecodeArgs()
-    a.batch = 9
+    a.batch = 65
     assert lib.pk_decode_step(ctypes.byref(m), ctypes.byref(a)) == 9101
     a.batch = 1
     a.max_seq_len = 9000
@@ -158,11 +158,12 @@ def test_rmsnorm_dispatch_keeps_misaligned_pointers_off_the_bulk_copy_kernel():
 
 def test_workspace_bytes_covers_every_batch_up_to_the_declared_maximum():
     """A caller that sizes the workspace for max_batch must be able to run every batch up to it: batches 5..7 run
-    on the batch-8 kernel, so they report its size; more than 8 requests per launch is refused (0)."""
+    on the batch-8 kernel, so they report its size; 9..64 requests (tensor-core kernel) never need less than a
+    smaller batch does; more than 64 requests per launch is refused (0)."""
     lib = _cabi.library()
     m = _cabi.PkDecodeModel(960, 2560, 32, 15, 5, 49152, 0, 1e-5)
-    sizes = [lib.pk_decode_workspace_bytes(ctypes.byref(m), b) for b in range(1, 10)]
-    assert all(sizes[i] <= sizes[i + 1] for i in range(7))
+    sizes = [lib.pk_decode_workspace_bytes(ctypes.byref(m), b) for b in range(1, 66)]
+    assert all(sizes[i] <= sizes[i + 1] for i in range(63))
     assert sizes[4] == sizes[5] == sizes[6] == sizes[7] > sizes[3]
-    assert sizes[8] == 0
+    assert sizes[63] > 0 and sizes[64] == 0
     assert lib.pk_decode_workspace_bytes(ctypes.byref(m), 0) == 0
