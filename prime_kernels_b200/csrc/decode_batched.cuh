@@ -33,7 +33,9 @@ namespace pk {
 namespace batched {
 
 constexpr int kThreadsB = 256;        // warps 0-3: operand staging + epilogue; warp 4: MMA issue; all: SIMT phases
-constexpr int kStages = 4;            // 64-wide K blocks staged per work item pass
+constexpr int kStages = 8;            // ring of staged 64-wide K blocks (A tile 16 KB + B tile NP x 128 bytes each)
+constexpr int kDepth = 4;             // cp.async groups (K blocks) a producer thread keeps in flight
+constexpr int kConv = 4;              // MXFP8 weights: de-quantised bf16 A slots (the raw bytes use a ring of kStages)
 constexpr int kNcB = 16;              // max split-KV chunks per (request, kv head)
 constexpr int kMaxReq = 64;
 constexpr int kAStage = 128 * 128;    // bytes of one A stage (128 rows x 64 bf16)
@@ -49,7 +51,6 @@ __host__ __device__ constexpr int staging_bytes(int np) {
 struct GemmDesc {
     int rows;            // weight rows (output features)
     int K;               // reduction length
-    int blocks;          // 64-wide K blocks per work item
     int widx;            // index in the per-layer pointer table, -1: embedding matrix
     int rowbytes;        // bytes per stored weight row
 };
@@ -94,7 +95,8 @@ struct BParams {
 };
 
 struct BShared {
-    uint64_t full[kStages];
+    uint64_t full[kStages];      // 128 producer threads arrive
+    uint64_t empty[kStages];     // tcgen05.commit arrives when the MMAs that read the stage have completed
     uint64_t accum;
     uint64_t kvbar[kThreadsB / 32][kKvStages];
     uint32_t tmem_base;
@@ -184,11 +186,11 @@ struct BC {
     const BParams& p;
     BShared& sh;
     unsigned char* stage_a;     // kStages x 16 KB, 1024-byte aligned
-    unsigned char* stage_b;     // kStages x NP x 128 bytes
+    unsigned char* stage_b;     // kStages x NP x 128 bytes (MXFP8 weights: followed by the raw ring, kStages x 8 KB)
     float* scratch;             // attention scratch (floats)
     int tid, warp, lane, cta, ncta;
-    uint32_t uses;              // passes done so far (parity of the accumulator barrier)
-    uint32_t suse[kStages];     // uses of every stage barrier so far (a pass may use fewer than kStages stages)
+    uint32_t uses;              // accumulator tiles finished so far (parity of the accumulator barrier)
+    uint32_t prod, cons;        // K blocks this thread has produced / consumed so far (stage and parity of the ring)
     unsigned char* kvring;      // attention: kThreadsB/32 rings of kKvStages runs (over the GEMM stages)
     uint32_t kvi, kvc;          // runs this warp has issued / consumed so far (stage and parity of the ring)
 };
@@ -237,50 +239,33 @@ __device__ __forceinline__ void grid_barrier(BC& c) {
 }
 
 // ------------------------------------------------------------------ tensor-core GEMM phase
-// Stage one 64-wide K block: A = 128 weight rows starting at row r0 (rows >= nrows are zero), B = the NP
-// activation rows (requests >= nb are zero).  Threads 0..127.
-template <int NP, int WF>
-__device__ __forceinline__ void stage_block(BC& c, int st, const unsigned char* wbase, int rowbytes, int K, int r0, int nrows,
-                                            int kblk, const uint16_t* xmat, int xstride) {
-    unsigned char* sa = c.stage_a + st * kAStage;
+// A phase is the flat sequence of (128-row tile, 64-wide K block) units of its weight matrix; CTA c owns the
+// contiguous range [c U / n, (c+1) U / n), so every CTA streams the same number of weight bytes (+-1 block) and
+// touches at most two or three row tiles.  Warps 0-3 produce (stage the operands of one K block per ring slot),
+// lane 0 of warp 4 issues the MMAs and releases each slot with tcgen05.commit, warps 4-7 read a finished
+// accumulator tile back (thread = weight row) and add it into the fp32 sums; the ring keeps the loads of the
+// next tile going while a tile's epilogue runs.
+__device__ __forceinline__ unsigned char* a_slot(BC& c, int st) { return c.stage_a + st * kAStage; }
+
+// bf16 weights: 16-byte cp.async copies placed chunk by chunk in the swizzled layout.  Threads 0..127.
+template <int NP>
+__device__ __forceinline__ void stage_a_bf16(BC& c, int st, const unsigned char* wbase, int rowbytes, int r0, int nrows, int kblk) {
+    unsigned char* sa = a_slot(c, st);
+    const int t = c.tid;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int idx = t + u * 128;              // 128 rows x 8 chunks of 16 bytes
+        const int row = idx >> 3, ch = idx & 7;
+        const bool ok = r0 + row < nrows;
+        const unsigned char* src = wbase + (size_t)(ok ? r0 + row : 0) * rowbytes + (size_t)kblk * 128 + ch * 16;
+        cp_async16(sa + (row >> 3) * 1024 + (row & 7) * 128 + ((ch ^ (row & 7)) << 4), src, ok);
+    }
+}
+// activations of one K block: NP rows x 128 bytes (requests >= nb are zero).  Threads 0..127.
+template <int NP>
+__device__ __forceinline__ void stage_b(BC& c, int st, const uint16_t* xmat, int xstride, int kblk) {
     unsigned char* sb = c.stage_b + st * NP * 128;
     const int t = c.tid;
-    if (WF == 0) {
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int idx = t + u * 128;              // 128 rows x 8 chunks of 16 bytes
-            const int row = idx >> 3, ch = idx & 7;
-            const bool ok = r0 + row < nrows;
-            const unsigned char* src = wbase + (size_t)(ok ? r0 + row : 0) * rowbytes + (size_t)kblk * 128 + ch * 16;
-            cp_async16(sa + (row >> 3) * 1024 + (row & 7) * 128 + ((ch ^ (row & 7)) << 4), src, ok);
-        }
-    } else {
-        // packed rows [K e4m3][K/32 e8m0][pad]: 64 values = four 16-byte pieces per row; thread = (row, piece)
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int idx = t + u * 128;              // 128 rows x 4 pieces
-            const int row = idx >> 2, pc = idx & 3;
-            uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
-            if (r0 + row < nrows) {
-                const unsigned char* rp = wbase + (size_t)(r0 + row) * rowbytes;
-                const uint4 q = ld_stream_16(rp + (size_t)kblk * 64 + pc * 16);
-                const unsigned char sbyte = __ldg(rp + K + kblk * 2 + (pc >> 1));
-                const float scale = __uint_as_float(sbyte ? ((uint32_t)sbyte << 23) : 0x00400000u);
-                float f[4];
-                e4m3x4_to_f32(q.x, f);
-                lo.x = pack_bf16x2(f[0] * scale, f[1] * scale); lo.y = pack_bf16x2(f[2] * scale, f[3] * scale);
-                e4m3x4_to_f32(q.y, f);
-                lo.z = pack_bf16x2(f[0] * scale, f[1] * scale); lo.w = pack_bf16x2(f[2] * scale, f[3] * scale);
-                e4m3x4_to_f32(q.z, f);
-                hi.x = pack_bf16x2(f[0] * scale, f[1] * scale); hi.y = pack_bf16x2(f[2] * scale, f[3] * scale);
-                e4m3x4_to_f32(q.w, f);
-                hi.z = pack_bf16x2(f[0] * scale, f[1] * scale); hi.w = pack_bf16x2(f[2] * scale, f[3] * scale);
-            }
-            unsigned char* rowp = sa + (row >> 3) * 1024 + (row & 7) * 128;
-            *reinterpret_cast<uint4*>(rowp + (((2 * pc) ^ (row & 7)) << 4)) = lo;
-            *reinterpret_cast<uint4*>(rowp + (((2 * pc + 1) ^ (row & 7)) << 4)) = hi;
-        }
-    }
 #pragma unroll
     for (int u = 0; u < (NP * 8 + 127) / 128; ++u) {
         const int idx = t + u * 128;
@@ -291,75 +276,182 @@ __device__ __forceinline__ void stage_block(BC& c, int st, const unsigned char* 
             cp_async16(sb + (row >> 3) * 1024 + (row & 7) * 128 + ((ch ^ (row & 7)) << 4), src, ok);
         }
     }
-    cp_async_commit();
+}
+// MXFP8 weights (rows [K e4m3][K/32 e8m0][pad]): a K block of a row is four 16-byte pieces.  Thread t owns pieces
+// (row, pc) = ((t + 128 u) >> 2, (t + 128 u) & 3), u = 0..3: it copies them raw into the raw ring with cp.async
+// (piece idx at byte 16 idx of the slot), keeps their E8M0 bytes in a register, and later de-quantises its own
+// pieces (exact) into the swizzled bf16 tile - no other thread reads the raw ring.
+__device__ __forceinline__ uint32_t copy_raw(BC& c, unsigned char* raw_slot, const unsigned char* wbase, int rowbytes, int K, int r0,
+                                             int nrows, int kblk) {
+    uint32_t scales = 0u;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int idx = c.tid + u * 128;
+        const int row = idx >> 2, pc = idx & 3;
+        const bool ok = r0 + row < nrows;
+        const unsigned char* rp = wbase + (size_t)(ok ? r0 + row : 0) * rowbytes;
+        cp_async16(raw_slot + idx * 16, rp + (size_t)kblk * 64 + pc * 16, ok);
+        if (ok) scales |= (uint32_t)__ldg(rp + K + kblk * 2 + (pc >> 1)) << (8 * u);
+    }
+    return scales;
+}
+__device__ __forceinline__ void store_dequant(BC& c, unsigned char* sa, const unsigned char* raw_slot, uint32_t scales) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int idx = c.tid + u * 128;
+        const int row = idx >> 2, pc = idx & 3;
+        const uint32_t sbyte = (scales >> (8 * u)) & 0xffu;
+        const float scale = __uint_as_float(sbyte ? (sbyte << 23) : 0x00400000u);
+        const uint4 q = *reinterpret_cast<const uint4*>(raw_slot + idx * 16);
+        uint4 lo, hi;
+        float f[4];
+        e4m3x4_to_f32(q.x, f);
+        lo.x = pack_bf16x2(f[0] * scale, f[1] * scale); lo.y = pack_bf16x2(f[2] * scale, f[3] * scale);
+        e4m3x4_to_f32(q.y, f);
+        lo.z = pack_bf16x2(f[0] * scale, f[1] * scale); lo.w = pack_bf16x2(f[2] * scale, f[3] * scale);
+        e4m3x4_to_f32(q.z, f);
+        hi.x = pack_bf16x2(f[0] * scale, f[1] * scale); hi.y = pack_bf16x2(f[2] * scale, f[3] * scale);
+        e4m3x4_to_f32(q.w, f);
+        hi.z = pack_bf16x2(f[0] * scale, f[1] * scale); hi.w = pack_bf16x2(f[2] * scale, f[3] * scale);
+        unsigned char* rowp = sa + (row >> 3) * 1024 + (row & 7) * 128;
+        *reinterpret_cast<uint4*>(rowp + (((2 * pc) ^ (row & 7)) << 4)) = lo;
+        *reinterpret_cast<uint4*>(rowp + (((2 * pc + 1) ^ (row & 7)) << 4)) = hi;
+    }
 }
 
-// All work items of one GEMM phase that belong to this CTA.  `mode` 0: partial tiles are added into cmat
-// ([NP][rows] fp32); mode 1 (lm_head, K not split): bf16 logits and the per-request argmax.
+// producers, bf16 weights: up to kDepth cp.async groups in flight per thread; a slot is published (proxy fence +
+// arrive) when its group has landed
+template <int NP>
+__device__ void gemm_produce_bf16(BC& c, const GemmDesc& gd, const unsigned char* wbase, const uint16_t* xmat, int g0, int g1, int nk64) {
+    BShared& sh = c.sh;
+    int inflight = 0;
+    for (int g = g0; g < g1; ++g) {
+        const int rt = g / nk64, kb = g - rt * nk64;
+        const int st = (int)(c.prod % kStages);
+        if (!b_wait_mbar(c, &sh.empty[st], ((c.prod / kStages) & 1u) ^ 1u)) break;
+        stage_a_bf16<NP>(c, st, wbase, gd.rowbytes, rt * 128, gd.rows, kb);
+        stage_b<NP>(c, st, xmat, gd.K, kb);
+        cp_async_commit();
+        ++c.prod;
+        if (++inflight == kDepth) {
+            cp_async_wait<kDepth - 1>();
+            fence_async_smem();
+            mbar_arrive(&sh.full[(c.prod - kDepth) % kStages]);
+            --inflight;
+        }
+    }
+    while (inflight > 0) {
+        switch (inflight - 1) {
+            case 3: cp_async_wait<3>(); break;
+            case 2: cp_async_wait<2>(); break;
+            case 1: cp_async_wait<1>(); break;
+            default: cp_async_wait<0>(); break;
+        }
+        fence_async_smem();
+        mbar_arrive(&sh.full[(c.prod - inflight) % kStages]);
+        --inflight;
+    }
+}
+// producers, MXFP8 weights: raw pieces and activations of the next kDepth K blocks are in flight (cp.async into the
+// raw ring / the B ring, kStages slots each) while the current block is de-quantised into one of the kConv bf16
+// A slots.  B slot of block n + kDepth is rewritten after the MMAs of block n - kConv have completed (the
+// empty-wait of block n), and kDepth + kConv <= kStages.
+template <int NP>
+__device__ void gemm_produce_mxfp8(BC& c, const GemmDesc& gd, const unsigned char* wbase, const uint16_t* xmat, int g0, int g1, int nk64) {
+    BShared& sh = c.sh;
+    static_assert(kDepth == 4 && kDepth + kConv <= kStages, "ring arithmetic");
+    unsigned char* raw = c.stage_b + kStages * NP * 128;
+    uint32_t sc0 = 0u, sc1 = 0u, sc2 = 0u, sc3 = 0u;
+    auto issue = [&](int g, int ahead) -> uint32_t {
+        const int slot = (int)((c.prod + (uint32_t)ahead) % kStages);
+        const uint32_t scales = copy_raw(c, raw + slot * (kAStage / 2), wbase, gd.rowbytes, gd.K, (g / nk64) * 128, gd.rows, g % nk64);
+        stage_b<NP>(c, slot, xmat, gd.K, g % nk64);
+        cp_async_commit();
+        return scales;
+    };
+    if (g0 < g1) sc0 = issue(g0, 0);
+    if (g0 + 1 < g1) sc1 = issue(g0 + 1, 1);
+    if (g0 + 2 < g1) sc2 = issue(g0 + 2, 2);
+    if (g0 + 3 < g1) sc3 = issue(g0 + 3, 3);
+#pragma unroll 1
+    for (int g = g0; g < g1; ++g) {
+        switch (min(kDepth - 1, g1 - 1 - g)) {      // groups issued after block g's
+            case 3: cp_async_wait<3>(); break;
+            case 2: cp_async_wait<2>(); break;
+            case 1: cp_async_wait<1>(); break;
+            default: cp_async_wait<0>(); break;
+        }
+        const int cs = (int)(c.prod % kConv);
+        if (!b_wait_mbar(c, &sh.empty[cs], ((c.prod / kConv) & 1u) ^ 1u)) break;
+        store_dequant(c, a_slot(c, cs), raw + (c.prod % kStages) * (kAStage / 2), sc0);
+        fence_async_smem();
+        mbar_arrive(&sh.full[cs]);
+        ++c.prod;
+        sc0 = sc1;
+        sc1 = sc2;
+        sc2 = sc3;
+        if (g + kDepth < g1) sc3 = issue(g + kDepth, kDepth - 1);
+    }
+    cp_async_wait<0>();
+}
+
+// `mode` 0: partial tiles are added into cmat ([NP][rows] fp32); mode 1 (lm_head, whole row tiles per CTA): bf16
+// logits and the per-request argmax.
 template <int NP, int WF>
 __device__ void gemm_phase(BC& c, const GemmDesc& gd, const unsigned char* wbase, const uint16_t* xmat, float* cmat, int mode) {
     const BParams& p = c.p;
     BShared& sh = c.sh;
     const int rtiles = (gd.rows + 127) / 128;
     const int nk64 = gd.K / 64;
-    const int slices = mode == 1 ? 1 : (nk64 + gd.blocks - 1) / gd.blocks;
-    const int items = rtiles * slices;
+    int g0, g1;
+    if (mode == 1) {
+        g0 = (int)((long long)c.cta * rtiles / c.ncta) * nk64;
+        g1 = (int)((long long)(c.cta + 1) * rtiles / c.ncta) * nk64;
+    } else {
+        const long long units = (long long)rtiles * nk64;
+        g0 = (int)(units * c.cta / c.ncta);
+        g1 = (int)(units * (c.cta + 1) / c.ncta);
+    }
     if (mode == 1 && c.tid < 4 * kMaxReq) (&sh.lm_key[0][0])[c.tid] = 0ull;
-    for (int item = c.cta; item < items; item += c.ncta) {
-        const int rt = item / slices, sl = item - rt * slices;
-        const int r0 = rt * 128;
-        const int kb0 = mode == 1 ? 0 : sl * gd.blocks;
-        const int kb1 = mode == 1 ? nk64 : min(kb0 + gd.blocks, nk64);
-        // passes of up to kStages blocks; the accumulator stays in tensor memory across the passes of an item
-        for (int kb = kb0; kb < kb1; kb += kStages) {
-            const int nst = min(kStages, kb1 - kb);
-            const uint32_t parity = c.uses & 1u;
-            uint32_t spar[kStages];
-#pragma unroll
-            for (int s = 0; s < kStages; ++s) {
-                spar[s] = c.suse[s] & 1u;
-                if (s < nst) ++c.suse[s];
-            }
-            if (c.warp < 4) {
-                for (int s = 0; s < nst; ++s) stage_block<NP, WF>(c, s, wbase, gd.rowbytes, gd.K, r0, gd.rows, kb + s, xmat, gd.K);
-                // as each block's copies complete: make them visible to the tensor core's (async-proxy) reads, signal
-                for (int s = 0; s < nst; ++s) {
-                    switch (nst - 1 - s) {
-                        case 3: cp_async_wait<3>(); break;
-                        case 2: cp_async_wait<2>(); break;
-                        case 1: cp_async_wait<1>(); break;
-                        default: cp_async_wait<0>(); break;
-                    }
-                    fence_async_smem();
-                    mbar_arrive(&sh.full[s]);
-                }
-            } else if (c.warp == 4 && c.lane == 0) {
-                const uint32_t idesc = idesc_bf16(128, NP);
-                for (int s = 0; s < nst; ++s) {
-                    if (!b_wait_mbar(c, &sh.full[s], spar[s])) break;
+    if (mode == 1) __syncthreads();
+    if (c.warp < 4) {
+        if (WF == 0) gemm_produce_bf16<NP>(c, gd, wbase, xmat, g0, g1, nk64);
+        else gemm_produce_mxfp8<NP>(c, gd, wbase, xmat, g0, g1, nk64);
+    } else {
+        const uint32_t idesc = idesc_bf16(128, NP);
+        const int q4 = c.warp - 4;                 // this warp's quarter of the tensor-memory lanes
+        int g = g0;
+        while (g < g1) {
+            const int rt = g / nk64;
+            const int gend = min(g1, (rt + 1) * nk64);
+            if (c.warp == 4 && c.lane == 0) {
+                for (int q = g; q < gend; ++q) {
+                    constexpr int kARing = WF ? kConv : kStages;
+                    const int st = (int)(c.cons % kARing);
+                    if (!b_wait_mbar(c, &sh.full[st], (c.cons / kARing) & 1u)) break;
                     tc_fence_after();
-                    const uint64_t da = smem_desc_sw128(c.stage_a + s * kAStage);
-                    const uint64_t db = smem_desc_sw128(c.stage_b + s * NP * 128);
+                    const uint64_t da = smem_desc_sw128(a_slot(c, st));
+                    const uint64_t db = smem_desc_sw128(c.stage_b + (c.cons % kStages) * NP * 128);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)      // 16 bf16 = 32 bytes per instruction: start address + 2 (16-byte units)
-                        mma_bf16(sh.tmem_base, da + 2 * k, db + 2 * k, idesc, (kb + s > kb0) || k > 0);
+                        mma_bf16(sh.tmem_base, da + 2 * k, db + 2 * k, idesc, q > g || k > 0);
+                    mma_commit(&sh.empty[st]);       // the slot is free when these MMAs have read it
+                    ++c.cons;
                 }
                 mma_commit(&sh.accum);               // arrives when every MMA issued so far has completed
             }
-            // everybody waits for the MMAs of this pass before the stages are overwritten / the accumulator is read
-            b_wait_mbar(c, &sh.accum, parity);
+            __syncwarp();
+            b_wait_mbar(c, &sh.accum, c.uses & 1u);
             ++c.uses;
-            __syncthreads();
-        }
-        // ---- epilogue: thread = weight row (tensor-memory lane), NP accumulator columns
-        if (c.warp < 4) {
             tc_fence_after();
             float v[NP];
-            tmem_ld<NP>(sh.tmem_base + ((uint32_t)(c.warp * 32) << 16), v);
+            tmem_ld<NP>(sh.tmem_base + ((uint32_t)(q4 * 32) << 16), v);
             tmem_ld_wait();
-            const int row = r0 + c.tid;
+            tc_fence_before();
+            asm volatile("bar.sync 2, 128;" ::: "memory");      // all four quarters are read: the next tile may start
+            const int row = rt * 128 + q4 * 32 + c.lane;
             if (mode == 0) {
-                if (row < gd.rows) {
+                if (row < gd.rows && !b_aborted(c)) {
 #pragma unroll
                     for (int j = 0; j < NP; ++j)
                         if (j < p.nb) atomicAdd(cmat + (size_t)j * gd.rows + row, v[j]);
@@ -380,13 +472,12 @@ __device__ void gemm_phase(BC& c, const GemmDesc& gd, const unsigned char* wbase
                             const unsigned long long o = __shfl_xor_sync(kFullMask, key, off);
                             key = o > key ? o : key;
                         }
-                        if (c.lane == 0 && key > sh.lm_key[c.warp][j]) sh.lm_key[c.warp][j] = key;
+                        if (c.lane == 0 && key > sh.lm_key[q4][j]) sh.lm_key[q4][j] = key;
                     }
                 }
             }
-            tc_fence_before();
+            g = gend;
         }
-        __syncthreads();        // the accumulator may be overwritten by the next item
     }
     if (mode == 1 && p.next_ids) {
         __syncthreads();
@@ -720,17 +811,20 @@ __global__ void __launch_bounds__(kThreadsB, 1) decode_batched_kernel(const BPar
     // scratch floats; the launcher asks for 1024 bytes more than the sum so the base can be rounded up
     unsigned char* smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
     unsigned char* stage_a = smem_raw;
-    unsigned char* stage_b = stage_a + kStages * kAStage;
+    unsigned char* stage_b = stage_a + (WF ? kConv : kStages) * kAStage;      // MXFP8: bf16 A slots, B ring, raw ring
     BShared& sh = *reinterpret_cast<BShared*>(stage_a + staging_bytes(NP));
     float* scratch = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(&sh) + ((sizeof(BShared) + 127) & ~size_t(127)));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    BC c{p, sh, stage_a, stage_b, scratch, tid, warp, lane, (int)blockIdx.x, (int)gridDim.x, 0u, {0u, 0u, 0u, 0u}, stage_a, 0u, 0u};
+    BC c{p, sh, stage_a, stage_b, scratch, tid, warp, lane, (int)blockIdx.x, (int)gridDim.x, 0u, 0u, 0u, stage_a, 0u, 0u};
 
     if (tid == 0) {
         sh.abort_flag = (p.ctrl[kCtrlStatus] != 0u) ? 1 : 0;
         sh.bar_gen = 0;
-        for (int s = 0; s < kStages; ++s) mbar_init(&sh.full[s], 128);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&sh.full[s], 128);
+            mbar_init(&sh.empty[s], 1);
+        }
         mbar_init(&sh.accum, 1);
         for (int w = 0; w < kThreadsB / 32; ++w)
             for (int s = 0; s < kKvStages; ++s) mbar_init(&sh.kvbar[w][s], 1);
@@ -742,12 +836,21 @@ __global__ void __launch_bounds__(kThreadsB, 1) decode_batched_kernel(const BPar
             }
             smax = max(smax, min(max(p.seq_lens[b], 1), p.max_seq_len));
         }
-        // chunks per (request, kv head): enough warp-level items for about two rounds of the grid's warps, at most
-        // kNcB, at least 64 positions each
+        // chunks per (request, kv head): the split that minimises rounds x (runs per item + a prologue's worth),
+        // counted for the longest request; at most kNcB chunks, at least 64 positions each
         const int units = p.nb * p.KVH, nwarps = (int)gridDim.x * (kThreadsB / 32);
-        int nc = (2 * nwarps + units - 1) / units;
-        nc = nc < 1 ? 1 : (nc > kNcB ? kNcB : nc);
-        const int lc = max(64, (((smax + nc - 1) / nc) + 15) & ~15);
+        int lc = 64;
+        long long best = -1;
+        for (int nc = 1; nc <= kNcB; ++nc) {
+            const int l = max(64, (((smax + nc - 1) / nc) + 15) & ~15);
+            const int ncr = (smax + l - 1) / l;
+            const long long rounds = ((long long)units * ncr + nwarps - 1) / nwarps;
+            const long long cost = rounds * (l / 16 + 3);
+            if (best < 0 || cost < best) {
+                best = cost;
+                lc = l;
+            }
+        }
         sh.lc = lc;
         sh.ncmax = (smax + lc - 1) / lc;
     }

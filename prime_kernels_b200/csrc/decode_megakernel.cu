@@ -2137,7 +2137,7 @@ static int batched_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceI
     p.max_seq_len = a.max_seq_len;
     p.spin_limit = g_spin_limit;
     p.eps = g.eps;
-    // GEMM phases: rows, K, K blocks (of 64) per work item chosen so that a phase has about one item per CTA
+    // GEMM phases: rows, K and row pitch of each weight matrix
     const int nqkv = (g.QH + 2 * g.KVH) * kD;
     const int rows[5] = {nqkv, g.H, 2 * g.I, g.H, g.V};
     const int Ks[5] = {g.H, g.QH * kD, g.H, g.I, g.H};
@@ -2148,9 +2148,6 @@ static int batched_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceI
         d.K = Ks[t];
         d.widx = widx[t];
         d.rowbytes = g.wfmt ? (int)align_up((size_t)Ks[t] + Ks[t] / 32, 16) : Ks[t] * 2;
-        const int rtiles = (rows[t] + 127) / 128, nk64 = Ks[t] / 64;
-        int blocks = (rtiles * nk64 + di.sm_count - 1) / di.sm_count;
-        d.blocks = blocks < 1 ? 1 : (blocks > nk64 ? nk64 : blocks);
     }
     void* args[] = {&p};
     cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fn), dim3(di.sm_count), dim3(kThreadsB), args,
