@@ -498,32 +498,53 @@ __device__ void gemm_phase(BC& c, const GemmDesc& gd, const unsigned char* wbase
 __device__ void norm_phase(BC& c, int which, int layer, const uint16_t* weight, bool write_hidden) {
     const BParams& p = c.p;
     BShared& sh = c.sh;
-    const int H = p.H;
+    const int H = p.H, H8 = H >> 3;           // a thread handles 8 consecutive elements at a time
     for (int b = c.cta; b < p.nb; b += c.ncta) {
         float ss = 0.f;
         float* row = c.scratch;               // H floats
-        for (int i = c.tid; i < H; i += kThreadsB) {
-            float v;
+        for (int i8 = c.tid; i8 < H8; i8 += kThreadsB) {
+            const size_t off = (size_t)b * H + 8 * i8;
+            float v[8];
+            uint4 bits;
             if (which == 0) {
-                v = __uint_as_float((uint32_t)__ldg(p.embed_bf16 + (size_t)sh.tok[b] * H + i) << 16);
-                p.x[(size_t)b * H + i] = (uint16_t)(__float_as_uint(v) >> 16);
-            } else if (which == 1) {
-                float* cd = p.c_down + (size_t)b * H + i;
-                const float h = __uint_as_float((uint32_t)__ldcg(p.h1 + (size_t)b * H + i) << 16);
-                v = round_bf16(__fadd_rn(h, round_bf16(__ldcg(cd))));
-                *cd = 0.f;
-                const uint16_t bits = (uint16_t)(__float_as_uint(v) >> 16);
-                p.x[(size_t)b * H + i] = bits;
-                if (p.layer_outputs) p.layer_outputs[((size_t)(layer - 1) * p.nb + b) * H + i] = bits;
+                bits = __ldg(reinterpret_cast<const uint4*>(p.embed_bf16 + (size_t)sh.tok[b] * H + 8 * i8));
+                const uint32_t w[4] = {bits.x, bits.y, bits.z, bits.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    v[2 * k] = bf16_lo(w[k]);
+                    v[2 * k + 1] = bf16_hi(w[k]);
+                }
+                *reinterpret_cast<uint4*>(p.x + off) = bits;
             } else {
-                float* co = p.c_o + (size_t)b * H + i;
-                const float xv = __uint_as_float((uint32_t)__ldcg(p.x + (size_t)b * H + i) << 16);
-                v = round_bf16(__fadd_rn(xv, round_bf16(__ldcg(co))));
-                *co = 0.f;
-                p.h1[(size_t)b * H + i] = (uint16_t)(__float_as_uint(v) >> 16);
+                // which 1: x = bf16(h1 + bf16(c_down));  which 2: h1 = bf16(x + bf16(c_o))
+                float* sums = (which == 1 ? p.c_down : p.c_o) + off;
+                const uint4 rb = __ldcg(reinterpret_cast<const uint4*>((which == 1 ? p.h1 : p.x) + off));
+                const float4 s0 = __ldcg(reinterpret_cast<const float4*>(sums));
+                const float4 s1 = __ldcg(reinterpret_cast<const float4*>(sums) + 1);
+                const uint32_t w[4] = {rb.x, rb.y, rb.z, rb.w};
+                const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    v[2 * k] = round_bf16(__fadd_rn(bf16_lo(w[k]), round_bf16(sv[2 * k])));
+                    v[2 * k + 1] = round_bf16(__fadd_rn(bf16_hi(w[k]), round_bf16(sv[2 * k + 1])));
+                    o[k] = (__float_as_uint(v[2 * k]) >> 16) | (__float_as_uint(v[2 * k + 1]) & 0xffff0000u);
+                }
+                bits = make_uint4(o[0], o[1], o[2], o[3]);
+                reinterpret_cast<float4*>(sums)[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+                reinterpret_cast<float4*>(sums)[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (which == 1) {
+                    *reinterpret_cast<uint4*>(p.x + off) = bits;
+                    if (p.layer_outputs) *reinterpret_cast<uint4*>(p.layer_outputs + ((size_t)(layer - 1) * p.nb + b) * H + 8 * i8) = bits;
+                } else {
+                    *reinterpret_cast<uint4*>(p.h1 + off) = bits;
+                }
             }
-            row[i] = v;
-            ss = fmaf(v, v, ss);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                row[8 * i8 + k] = v[k];
+                ss = fmaf(v[k], v[k], ss);
+            }
         }
         ss = warp_sum(ss);
         if (c.lane == 0) sh.red[c.warp] = ss;
@@ -532,28 +553,59 @@ __device__ void norm_phase(BC& c, int which, int layer, const uint16_t* weight, 
 #pragma unroll
         for (int w = 0; w < kThreadsB / 32; ++w) tot += sh.red[w];
         const float s = rsqrtf(tot * (1.f / (float)H) + p.eps);
-        for (int i = c.tid; i < H; i += kThreadsB) {
-            const float n = round_bf16(__fmul_rn(row[i], s));
-            const uint16_t o = (uint16_t)f32_to_bf16_bits(__fmul_rn(n, __uint_as_float((uint32_t)__ldg(weight + i) << 16)));
-            p.xn[(size_t)b * H + i] = o;
-            if (write_hidden) p.out_hidden[(size_t)b * H + i] = o;
+        for (int i8 = c.tid; i8 < H8; i8 += kThreadsB) {
+            const uint4 wb = __ldg(reinterpret_cast<const uint4*>(weight) + i8);
+            const uint32_t w[4] = {wb.x, wb.y, wb.z, wb.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float n0 = round_bf16(__fmul_rn(row[8 * i8 + 2 * k], s));
+                const float n1 = round_bf16(__fmul_rn(row[8 * i8 + 2 * k + 1], s));
+                o[k] = pack_bf16x2(__fmul_rn(n0, bf16_lo(w[k])), __fmul_rn(n1, bf16_hi(w[k])));
+            }
+            const uint4 ob = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(p.xn + (size_t)b * H + 8 * i8) = ob;
+            if (write_hidden) *reinterpret_cast<uint4*>(p.out_hidden + (size_t)b * H + 8 * i8) = ob;
         }
         __syncthreads();
     }
 }
 
-// act = bf16( bf16(silu(bf16 gate)) * bf16 up ) over [nb][I]; clears the gate/up sums
+// act = bf16( bf16(silu(bf16 gate)) * bf16 up ) over [nb][I]; clears the gate/up sums.  Four elements per thread
+// and step, two steps' loads in flight.
 __device__ void swiglu_phase(BC& c) {
     const BParams& p = c.p;
-    const long long total = (long long)p.nb * p.I;
-    for (long long e = (long long)c.cta * kThreadsB + c.tid; e < total; e += (long long)c.ncta * kThreadsB) {
-        const int b = (int)(e / p.I), j = (int)(e - (long long)b * p.I);
-        float* gp = p.c_gu + (size_t)b * 2 * p.I + j;
-        const float g = round_bf16(__ldcg(gp)), u = round_bf16(__ldcg(gp + p.I));
-        gp[0] = 0.f;
-        gp[p.I] = 0.f;
-        const float silu = round_bf16(__fdividef(g, 1.f + __expf(-g)));
-        p.act[(size_t)b * p.I + j] = (uint16_t)f32_to_bf16_bits(__fmul_rn(silu, u));
+    const int I4 = p.I >> 2;
+    const int total = p.nb * I4;
+    const int stride = c.ncta * kThreadsB;
+    auto fetch = [&](int e, float4& g, float4& u) {
+        const int b = e / I4, j4 = e - b * I4;
+        const float4* gp = reinterpret_cast<const float4*>(p.c_gu + (size_t)b * 2 * p.I) + j4;
+        g = __ldcg(gp);
+        u = __ldcg(gp + I4);
+    };
+    auto finish = [&](int e, const float4& g, const float4& u) {
+        const int b = e / I4, j4 = e - b * I4;
+        float4* gp = reinterpret_cast<float4*>(p.c_gu + (size_t)b * 2 * p.I) + j4;
+        gp[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+        gp[I4] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {u.x, u.y, u.z, u.w};
+        float a[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float gr = round_bf16(gv[k]);
+            const float silu = round_bf16(__fdividef(gr, 1.f + __expf(-gr)));
+            a[k] = __fmul_rn(silu, round_bf16(uv[k]));
+        }
+        *reinterpret_cast<uint2*>(p.act + (size_t)b * p.I + 4 * j4) = make_uint2(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]));
+    };
+    for (int e = c.cta * kThreadsB + c.tid; e < total; e += 2 * stride) {
+        float4 g0, u0, g1 = make_float4(0.f, 0.f, 0.f, 0.f), u1 = g1;
+        fetch(e, g0, u0);
+        const bool two = e + stride < total;
+        if (two) fetch(e + stride, g1, u1);
+        finish(e, g0, u0);
+        if (two) finish(e + stride, g1, u1);
     }
 }
 
@@ -593,7 +645,7 @@ __device__ void attention_item_b(BC& c, int layer, int b, int kvh, int chunk) {
     int btc = __ldg(bt + min(bt_base + lane, p.bt_stride - 1));
     const bool packed = p.token_stride == 2 * kD && p.v_off == p.k_off + kD;
     auto issue = [&](int r0) {
-        const int st = (int)(c.kvi & (kKvStages - 1));
+        const int st = (int)(c.kvi % kKvStages);
         const int n = max(0, min(16, wcopy - r0));
         if ((r0 + 15) / bs >= bt_base + 32) {
             bt_base = r0 / bs;
@@ -663,7 +715,7 @@ __device__ void attention_item_b(BC& c, int layer, int b, int kvh, int chunk) {
 #pragma unroll 1
     for (int k = 0; k < nruns; ++k) {
         const int r0 = ws + 16 * k;
-        const int st = (int)(c.kvc & (kKvStages - 1));
+        const int st = (int)(c.kvc % kKvStages);
         // after a failed wait the remaining runs are still waited for (each wait bounded), nothing is computed
         alive = b_wait_mbar(c, &bars[st], (c.kvc / kKvStages) & 1u) && alive;
         unsigned char* data = ring + st * kRunBytes;
