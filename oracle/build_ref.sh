@@ -6,9 +6,11 @@
 #                           without a GPU)
 #   libref_rmsnorm_gpu.so   the reference's own GPU kernels behind a C entry point (GPU parity tests)
 #   ref_rmsnorm_bench       the reference's own benchmark executable (same-box timing of its kernels)
-#   libref_megakernel135.so, libref_megakernel360.so
+#   libref_megakernel135.so, libref_megakernel360.so, libref_megakernel360f.so
 #                           the reference's own SmolLM2-135M / 360M decode megakernels (their sm_89-only device check
-#                           shimmed, see ref_megakernel_wrapper.cu): second decode oracle and same-box baseline
+#                           shimmed, see ref_megakernel_wrapper.cu): second decode oracle and same-box baseline.
+#                           360f is the fast 360M line (decode_megakernel_360m_lossless, entry decode360_lossless),
+#                           run with a NULL encoded gate-up table, i.e. on the plain bf16 weights
 # The reference's cmake project is not run: its sources are handed to nvcc directly.
 #   usage: oracle/build_ref.sh [/path/to/reference/checkout]
 set -euo pipefail
@@ -50,4 +52,12 @@ if [ -f "$mk360" ]; then
   nvcc -O3 -std=c++17 -w -gencode arch=compute_100a,code=sm_100a -shared -Xcompiler -fPIC \
     -DREF_MEGAKERNEL_CU="\"$mk360\"" -o "$here/_ref/libref_megakernel360.so" "$here/ref_megakernel_wrapper.cu"
   echo "built $here/_ref/libref_megakernel360.so"
+fi
+mk360f="$ref/prime_kernels/decode_megakernel_360m_lossless/csrc/block360.cu"
+if [ -f "$mk360f" ]; then
+  fresh "$here/_ref/libref_megakernel360f.so" "$mk360f" "$ref/prime_kernels/decode_megakernel_360m_lossless/csrc/block360_kernel.inc" \
+        "$ref/prime_kernels/lossless_bf16/csrc/encoded_gu.h" "$here/ref_megakernel_wrapper.cu" || \
+  nvcc -O3 -std=c++17 -w -gencode arch=compute_100a,code=sm_100a -shared -Xcompiler -fPIC \
+    -DREF_MEGAKERNEL_CU="\"$mk360f\"" -o "$here/_ref/libref_megakernel360f.so" "$here/ref_megakernel_wrapper.cu"
+  echo "built $here/_ref/libref_megakernel360f.so"
 fi
