@@ -567,6 +567,52 @@ def test_against_the_reference_projects_own_360m_kernel(cuda_device):
     D.check_status(geom, cuda_device)
 
 
+def test_against_the_reference_projects_fast_360m_kernel(cuda_device):
+    """The reference's fast SmolLM2-360M line (decode_megakernel_360m_lossless, run on the plain bf16 weights) against
+    this library at batch 1, context 520: final hidden states, the residual stream after the first layer and the K/V
+    rows both kernels append."""
+    from oracle import ref_megakernel as REF
+    from prime_kernels_b200 import decode as D
+    from prime_kernels_b200 import decode_megakernel_360m as MK360
+
+    if not REF.available_360m_fast():
+        pytest.skip("reference fast 360M megakernel not built (oracle/build_ref.sh)")
+    geom = D.SMOLLM2_360M
+    wd = harness.weights_to(harness.make_weights(geom, 0, norm_weights="random"), cuda_device)
+    csd = harness.make_cos_sin_cache(geom, 640, cuda_device)
+    B, ctxs = 1, [520]
+    g = torch.Generator().manual_seed(21)
+    kvs = [harness.PagedKV(geom, B, 640, cuda_device, shuffle=True, seed=5) for _ in range(2)]
+    for l in range(geom.layers):
+        fill = (torch.randn(kvs[0].kv_caches[l].shape, generator=g) * 0.5).to(torch.bfloat16).to(cuda_device)
+        kvs[0].kv_caches[l].copy_(fill)
+        kvs[1].kv_caches[l].copy_(fill)
+    ids = torch.randint(0, geom.vocab, (B,), generator=g).to(cuda_device)
+    pos = torch.tensor(ctxs, dtype=torch.int64, device=cuda_device)
+    seq = (pos + 1).to(torch.int32)
+    outs, streams = [], []
+    for kv, step in zip(kvs, (REF.decode_step_360m_fast, MK360.decode_step)):
+        lo = torch.zeros((geom.layers, B, geom.hidden), dtype=torch.bfloat16, device=cuda_device)
+        outs.append(step(input_ids=ids, positions=pos, seq_lens=seq, block_table=kv.block_table,
+                         slot_mapping=kv.slots(pos), embed=wd["embed"], layers=wd["layers"], final_norm=wd["final_norm"],
+                         kv_caches=kv.kv_caches, cos_sin_cache=csd, eps=1e-5, layer_outputs=lo).float().clone())
+        streams.append(lo.float())
+    torch.cuda.synchronize()
+    per_layer = (streams[0] - streams[1]).abs().amax(dim=(1, 2))
+    rel0 = per_layer[0].item() / max(streams[0][0].abs().max().item(), 1.0)
+    diff = (outs[0] - outs[1]).abs().max().item()
+    scale = outs[0].abs().max().item()
+    a = kvs[0].gather(0, 0, ctxs[0] + 1)[:, -1].float()
+    c = kvs[1].gather(0, 0, ctxs[0] + 1)[:, -1].float()
+    kdiff0 = (a - c).abs().max().item() / max(a.abs().max().item(), 1.0)
+    print(f"reference fast 360M kernel vs this library: hidden max-abs {diff:.4f} (scale {scale:.2f}), residual stream after "
+          f"layer 0 (relative) {rel0:.4f}, last {per_layer[-1].item():.4f}, appended K/V layer 0 (relative) {kdiff0:.4f}")
+    assert rel0 <= 2 ** -6
+    assert diff <= 2 ** -4 * max(scale, 1.0)
+    assert kdiff0 <= 2 ** -6
+    D.check_status(geom, cuda_device)
+
+
 def test_same_box_timing_against_the_reference_kernels(cuda_device):
     """Step time of the reference project's own kernels (24-CTA sm_89 designs, compiled for this GPU) and of this
     library on the same box and the same inputs: SmolLM2-135M batch 1 at context 64 and SmolLM2-360M batch 1 at
@@ -578,8 +624,12 @@ def test_same_box_timing_against_the_reference_kernels(cuda_device):
 
     if not (REF.available() and REF.available_360m()):
         pytest.skip("reference megakernels not built (oracle/build_ref.sh)")
-    for geom, ctx, ref_step, my_step in [(D.SMOLLM2_135M, 64, REF.decode_step, MK.decode_step),
-                                         (D.SMOLLM2_360M, 520, REF.decode_step_360m, MK360.decode_step)]:
+    cases = [(D.SMOLLM2_135M, 64, REF.decode_step, MK.decode_step, "decode_megakernel"),
+             (D.SMOLLM2_360M, 520, REF.decode_step_360m, MK360.decode_step, "decode_megakernel_360m (strict parity)")]
+    if REF.available_360m_fast():
+        cases.append((D.SMOLLM2_360M, 520, REF.decode_step_360m_fast, MK360.decode_step,
+                      "decode_megakernel_360m_lossless (fast line, no encoded gate-up table)"))
+    for geom, ctx, ref_step, my_step, label in cases:
         wd = harness.weights_to(harness.make_weights(geom, 0), cuda_device)
         csd = harness.make_cos_sin_cache(geom, 640, cuda_device)
         kv = harness.PagedKV(geom, 1, 640, cuda_device)
@@ -603,7 +653,7 @@ def test_same_box_timing_against_the_reference_kernels(cuda_device):
             e1.record()
             torch.cuda.synchronize()
             times.append(e0.elapsed_time(e1) / 40 * 1e3)
-        print(f"{geom.name} B=1 ctx {ctx}: reference kernel {times[0]:.0f} us/step, this library {times[1]:.0f} us/step "
+        print(f"{geom.name} B=1 ctx {ctx}: reference {label} {times[0]:.0f} us/step, this library {times[1]:.0f} us/step "
               f"({times[0] / times[1]:.1f}x)")
         assert times[1] < times[0]
     D.check_status(D.SMOLLM2_360M, cuda_device)

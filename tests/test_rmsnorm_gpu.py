@@ -10,7 +10,8 @@ pytestmark = pytest.mark.gpu
 # reference test shapes (prime_kernels/rmsnorm/test.cu:409-410) + hidden {960, 2048, 4096} x tokens {1 ... 8192} + ragged edges
 SHAPES = [(128, 128), (128, 512), (256, 2048), (128, 3072), (256, 4096), (128, 8192), (128, 16384),
           (1, 960), (16, 960), (128, 960), (1024, 960), (1, 2048), (16, 2048), (1024, 2048), (1, 4096),
-          (16, 4096), (1024, 4096), (130, 960), (257, 32), (3, 12288)]
+          (16, 4096), (1024, 4096), (130, 960), (257, 32), (3, 12288),
+          (8192, 960), (128, 2048), (8192, 2048), (128, 4096), (8192, 4096)]
 
 
 # large shapes: (8192, 8192) and (2048, 16384) take the pipelined (shared-memory ring) kernel, the others the
