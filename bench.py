@@ -43,10 +43,12 @@ WORKLOADS = {
     "smollm2-360m-mxfp8-b16": ("smollm2-360m", 16, 4096, 32),
 }
 METRIC = "SmolLM2-360M bs1 decode tok/s & % HBM roofline; aggregate tok/s @1/2/4/8 GPUs"
-# DRAM bytes per launch measured with ncu (dram__bytes_read + write) at context 503-505 divided by the
-# algorithmic bytes at that context (747.8 MB / 744.3 MB).  Traffic grows with the same units as the
-# algorithmic bytes (weights + KV positions).
-NCU_TRAFFIC_RATIO = 1.005
+# DRAM bytes per launch measured with ncu (dram__bytes_read + write) divided by the algorithmic bytes of the
+# captured launch: decode_fast_kernel, SmolLM2-360M batch 1 at context 503-505: 747.7 MB / 744.3 MB;
+# decode_batched_kernel, SmolLM2-360M MXFP8 batch 16 at context 1027: 1051.7 MB / 1046.6 MB.  Traffic grows with
+# the same units as the algorithmic bytes (weights + KV positions), so other contexts are scaled by them.
+NCU_TRAFFIC_RATIO = {("smollm2-360m", 1, False): (1.005, "ncu capture of decode_fast_kernel at context 503-505"),
+                     ("smollm2-360m", 16, True): (1.005, "ncu capture of decode_batched_kernel at context 1027")}
 
 
 def algorithmic_bytes(geom, batch, seq, mxfp8=False):
@@ -450,6 +452,7 @@ def main():
         mean_bytes = statistics.mean(algorithmic_bytes(geom, batch, s, mxfp8) for s in (seq_first, seq_last))
         step_ms = ms_max / K
         achieved = mean_bytes / (step_ms * 1e-3) / 1e9
+        ratio = NCU_TRAFFIC_RATIO.get((gname, batch, bool(mxfp8)))
         line = {
             "metric": METRIC, "value": aggregate_throughput(world, batch, K, ms_max), "unit": "tok/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
@@ -458,8 +461,8 @@ def main():
             "detail": {"context_during_timing": [seq_first, seq_last],
                        "timing": "CUDA events on the launching stream around K back-to-back launches"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": mean_bytes * NCU_TRAFFIC_RATIO if gname == "smollm2-360m" and batch == 1 and not mxfp8 else None,
-                         "traffic_source": "ncu capture at context 503-505 scaled by algorithmic bytes",
+                         "traffic": mean_bytes * ratio[0] if ratio else None,
+                         "traffic_source": ratio[1] + ", scaled by algorithmic bytes" if ratio else None,
                          "peak_source": peak_src, "frac_of_8TBs_nominal": achieved / 8000.0,
                          "algorithmic_bytes_per_step": mean_bytes},
             "e2e": {"value": None if args.no_e2e else aggregate_throughput(world, batch, K, e2e_ms_max), "unit": "tok/s",
