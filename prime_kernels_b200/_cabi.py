@@ -50,6 +50,8 @@ SYMBOLS = {
     "pk_decode_workspace_bytes": (sz, [ctypes.POINTER(PkDecodeModel), ci]),
     "pk_decode_step": (ci, [ctypes.POINTER(PkDecodeModel), ctypes.POINTER(PkDecodeArgs)]),
     "pk_decode_step_tc": (ci, [ctypes.POINTER(PkDecodeModel), ctypes.POINTER(PkDecodeArgs)]),
+    "pk_decode_step_cc": (ci, [ctypes.POINTER(PkDecodeModel), ctypes.POINTER(PkDecodeArgs)]),
+    "pk_decode_set_tc_min_batch": (None, [ci]),
     "pk_decode_step_static": (ci, [ctypes.POINTER(PkDecodeModel), ctypes.POINTER(PkDecodeArgs)]),
     "pk_decode_static_scratch_bytes": (sz, []),
     "pk_decode_static_status": (ci, [vp]),

@@ -1778,8 +1778,15 @@ static WsLayout ws_layout(const ModelGeom& g, int B) {
     return l;
 }
 
-// Workspace of a launch of 9..64 requests (tensor-core kernel): control words, then its own region.
-static size_t batched_ws_bytes(const ModelGeom& g, int B) { return 256 + batched_layout(g, B).total; }
+// The tensor-core kernel's region lies behind the CUDA-core kernels' region (batch 8), so one workspace serves every
+// kernel and a caller may alternate batch sizes on it; the control words at the front are shared.
+static size_t tc_offset(const ModelGeom& g) { return align_up(ws_layout(g, kMaxB).total, 256); }
+static size_t batched_ws_bytes(const ModelGeom& g, int B) { return tc_offset(g) + batched_layout(g, B).total; }
+static bool batched_eligible(const ModelGeom& g) {
+    if (g.KVH <= 0 || g.QH % g.KVH) return false;
+    const int G = g.QH / g.KVH;
+    return (G == 1 || G == 3) && g.H % 64 == 0 && g.I % 64 == 0 && (g.QH * kD) % 64 == 0 && g.H <= 4096;
+}
 
 struct DeviceInfo {
     bool valid = false;
@@ -1799,6 +1806,7 @@ static std::unordered_map<const void*, WsState> g_ws_ready;     // workspace poi
 static std::unordered_map<unsigned long long, int> g_kernel_smem;
 static unsigned g_spin_limit = kSpinLimit;
 static int g_fast_dbg = 0;
+static int g_tc_min_batch = 4;       // pk_decode_step hands launches of this many requests or more to the tensor-core kernel
 static int g_fast_warps = -1;        // batch-1 fast path: -1 = not decided yet (environment), 0 = off, 7 / 8 = consumer warps per CTA
 
 static unsigned long long geom_sig(const ModelGeom& g) {
@@ -1958,7 +1966,7 @@ struct StepArgs {
     const void* cos_sin; int cs_fp32;
     void* out_hidden; void* logits; void* next_ids; void* layer_outputs;
     void* ws; size_t ws_bytes; int max_seq_len; int lm_head; int advance;
-    int force_tc = 0;     // run the tensor-core kernel whatever the batch
+    int path = 0;         // 0: chosen by batch size, 1: tensor-core kernel, 2: CUDA-core kernels
 };
 
 // ---- batch-1 fast path (decode_fast.cuh) --------------------------------------------------------
@@ -2088,7 +2096,7 @@ static int batched_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceI
     if (rc) return rc;
     const BatchedLayout bl = batched_layout(g, a.B);
     unsigned char* ws = static_cast<unsigned char*>(a.ws);
-    unsigned char* bw = ws + 256;
+    unsigned char* bw = ws + tc_offset(g);
     BParams p{};
     p.layers = static_cast<const unsigned long long*>(a.layers);
     p.kv = static_cast<const unsigned long long*>(a.kv);
@@ -2172,8 +2180,12 @@ static int batched_launch(const ModelGeom& g, const StepArgs& a, const DeviceInf
 
 static int decode_launch(const ModelGeom& g, const StepArgs& a) {
     if (a.B < 1 || a.B > batched::kMaxReq) return kErrBatch;
-    if (a.B > kMaxB || a.force_tc) {
-        // 9..64 requests: the tensor-core kernel (same argument checks as below)
+    if (a.path == 2 && a.B > kMaxB) return kErrBatch;
+    const bool tc = a.path == 1 || a.B > kMaxB ||
+                    (a.path == 0 && a.B >= g_tc_min_batch && batched_eligible(g) && a.ws_bytes >= batched_ws_bytes(g, a.B));
+    if (tc) {
+        // the tensor-core kernel: always from 9 requests on, from g_tc_min_batch on when the geometry and the
+        // workspace allow it (same argument checks as below)
         if (a.max_seq_len < 1 || a.max_seq_len > kMaxSeq) return kErrMaxSeq;
         if (!a.input_ids || !a.positions || !a.seq_lens || !a.block_table || !a.slot_mapping || !a.layers || !a.embed ||
             !a.final_norm || !a.kv || !a.cos_sin || !a.out_hidden || !a.ws)
@@ -2361,13 +2373,11 @@ static ModelGeom to_geom(const PkDecodeModel* m) {
 
 extern "C" size_t pk_decode_workspace_bytes(const PkDecodeModel* m, int max_batch) {
     if (!m || max_batch < 1 || max_batch > batched::kMaxReq || m->kv_heads <= 0) return 0;
-    // batches 5..7 run on the batch-8 kernel (padded), so they need its workspace; a workspace for more than 8
-    // requests per launch (tensor-core kernel) also serves every smaller launch
+    // up to 3 requests only the CUDA-core kernels run; from 4 on the workspace also holds the tensor-core kernel's
+    // region (behind the CUDA-core kernels' batch-8 region, which batches 5..7 need anyway)
     const ModelGeom g = to_geom(m);
-    const size_t small = ws_layout(g, max_batch <= 4 ? max_batch : kMaxB).total;
-    if (max_batch <= kMaxB) return small;
-    const size_t big = batched_ws_bytes(g, max_batch);
-    return big > small ? big : small;
+    if (max_batch < 4) return ws_layout(g, max_batch).total;
+    return batched_ws_bytes(g, max_batch);
 }
 
 extern "C" int pk_decode_step(const PkDecodeModel* m, const PkDecodeArgs* a) {
@@ -2380,10 +2390,9 @@ extern "C" int pk_decode_step(const PkDecodeModel* m, const PkDecodeArgs* a) {
     return decode_launch(to_geom(m), s);
 }
 
-// Same step on the tensor-core kernel whatever the batch (pk_decode_step picks it from 9 requests on).  For
-// models whose rows are too wide for the CUDA-core kernel at the wanted batch (SmolLM2-1.7B above 4 requests).
-// The workspace must have pk_decode_workspace_bytes(model, 64) bytes and must not be shared with launches of the
-// other kernels.
+// Same step on the tensor-core kernel whatever the batch (pk_decode_step picks it from
+// pk_decode_set_tc_min_batch requests on, default 4, and always above 8).  The workspace must have
+// pk_decode_workspace_bytes(model, n) bytes for some n >= max(4, batch).
 extern "C" int pk_decode_step_tc(const PkDecodeModel* m, const PkDecodeArgs* a) {
     if (!m || !a) return kErrNull;
     StepArgs s{static_cast<cudaStream_t>(a->stream), a->batch, a->input_ids, a->ids_i64, a->positions, a->seq_lens,
@@ -2391,9 +2400,24 @@ extern "C" int pk_decode_step_tc(const PkDecodeModel* m, const PkDecodeArgs* a) 
                a->kv_layers, a->k_off, a->v_off, a->block_stride, a->token_stride, a->head_stride, a->block_size,
                a->cos_sin, a->cs_fp32, a->out_hidden, a->logits, a->next_ids, a->layer_outputs, a->workspace,
                a->workspace_bytes, a->max_seq_len, a->lm_head, a->advance};
-    s.force_tc = 1;
+    s.path = 1;
     return decode_launch(to_geom(m), s);
 }
+
+// Same step on the CUDA-core kernels only (1..8 requests), whatever pk_decode_set_tc_min_batch says.
+extern "C" int pk_decode_step_cc(const PkDecodeModel* m, const PkDecodeArgs* a) {
+    if (!m || !a) return kErrNull;
+    StepArgs s{static_cast<cudaStream_t>(a->stream), a->batch, a->input_ids, a->ids_i64, a->positions, a->seq_lens,
+               a->block_table, a->bt_stride, a->slot_mapping, a->layers, a->embed, a->embed_lookup, a->final_norm,
+               a->kv_layers, a->k_off, a->v_off, a->block_stride, a->token_stride, a->head_stride, a->block_size,
+               a->cos_sin, a->cs_fp32, a->out_hidden, a->logits, a->next_ids, a->layer_outputs, a->workspace,
+               a->workspace_bytes, a->max_seq_len, a->lm_head, a->advance};
+    s.path = 2;
+    return decode_launch(to_geom(m), s);
+}
+
+// Smallest batch pk_decode_step / mk_decode hand to the tensor-core kernel (default 4; 9 = only above 8 requests).
+extern "C" void pk_decode_set_tc_min_batch(int n) { g_tc_min_batch = n < 1 ? 1 : (n > kMaxB + 1 ? kMaxB + 1 : n); }
 
 // Zero a workspace in stream order and mark it ready (also done implicitly on first use).
 extern "C" int pk_decode_workspace_init(void* workspace, size_t bytes, void* stream) {
@@ -2510,7 +2534,7 @@ extern "C" int mk_query(int* sm_count, int* coop, int* active_per_sm, int* major
 extern "C" size_t mk_workspace_bytes(int B, int max_seq_len) {
     (void)B;
     (void)max_seq_len;
-    return ws_layout(kGeom135, kMaxB).total;
+    return batched_ws_bytes(kGeom135, kMaxB);      // batches 4..8 run on the tensor-core kernel when the scratch has this size
 }
 
 extern "C" int mk_decode(void* stream, int B, const void* input_ids, int ids_i64, const void* positions,
@@ -2519,7 +2543,7 @@ extern "C" int mk_decode(void* stream, int B, const void* input_ids, int ids_i64
                          long long k_off, long long v_off, long long block_stride, long long token_stride,
                          long long head_stride, int block_size, const void* cos_sin, int cs_fp32, void* out_hidden,
                          void* scratch, size_t scratch_bytes, int max_seq_len) {
-    if (B < 1 || B > kMaxB) return kErrBatch;      // the drop-in entry takes one launch of the CUDA-core kernels
+    if (B < 1 || B > kMaxB) return kErrBatch;      // the reference's entry takes 1..8 requests
     StepArgs s{static_cast<cudaStream_t>(stream), B, input_ids, ids_i64, positions, seq_lens, block_table, bt_stride,
                slot_mapping, layers, embed, nullptr, final_norm, kv_layers, k_off, v_off, block_stride, token_stride,
                head_stride, block_size, cos_sin, cs_fp32, out_hidden, nullptr, nullptr, nullptr, scratch, scratch_bytes,
@@ -2543,7 +2567,7 @@ extern "C" int decode360(void* stream, int B, const void* input_ids, const void*
     (void)debug;
     (void)debug_bytes;
     if (debug_layer_index < -1 || debug_layer_index >= kGeom360.L) return kErrBlock;
-    if (B < 1 || B > kMaxB) return kErrBatch;      // the drop-in entry takes one launch of the CUDA-core kernels
+    if (B < 1 || B > kMaxB) return kErrBatch;      // the reference's entry takes 1..8 requests
     StepArgs s{static_cast<cudaStream_t>(stream), B, input_ids, 0, positions, seq_lens, block_table, bt_stride,
                slot_mapping, layers, embed, nullptr, final_norm, kv, k_off, v_off, block_stride, token_stride,
                head_stride, block_size, cos_sin, cs_fp32, out_hidden, nullptr, nullptr, layer_outputs, scratch,
@@ -2609,6 +2633,7 @@ extern "C" int pk_decode_step_static(const PkDecodeModel* m, const PkDecodeArgs*
                a->slot_mapping, a->layers, a->embed, a->embed_lookup, a->final_norm, a->kv_layers, a->k_off, a->v_off,
                a->block_stride, a->token_stride, a->head_stride, a->block_size, a->cos_sin, a->cs_fp32, a->out_hidden,
                a->logits, a->next_ids, a->layer_outputs, ptr, kStaticScratchBytes, a->max_seq_len, a->lm_head, a->advance};
+    s.path = 2;      // the static scratch holds the CUDA-core kernels' workspace only
     return decode_launch(g, s);
 }
 

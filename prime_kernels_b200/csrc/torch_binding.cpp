@@ -89,7 +89,7 @@ int64_t decode_step(const torch::Tensor& input_ids, const torch::Tensor& positio
                     std::optional<torch::Tensor> layer_outputs, torch::Tensor workspace, int64_t hidden,
                     int64_t intermediate, int64_t layers, int64_t q_heads, int64_t kv_heads, int64_t vocab,
                     int64_t weight_format, double eps, int64_t max_seq_len, bool lm_head, bool advance,
-                    bool tensor_cores) {
+                    int64_t path) {
     at::cuda::OptionalCUDAGuard guard{device_of(input_ids)};
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
     PkDecodeModel m{(int)hidden, (int)intermediate, (int)layers, (int)q_heads, (int)kv_heads, (int)vocab,
@@ -126,7 +126,8 @@ int64_t decode_step(const torch::Tensor& input_ids, const torch::Tensor& positio
     a.max_seq_len = (int)max_seq_len;
     a.lm_head = lm_head;
     a.advance = advance;
-    return tensor_cores ? pk_decode_step_tc(&m, &a) : pk_decode_step(&m, &a);
+    // path 0: chosen by batch size, 1: tensor-core kernel, 2: CUDA-core kernels
+    return path == 1 ? pk_decode_step_tc(&m, &a) : (path == 2 ? pk_decode_step_cc(&m, &a) : pk_decode_step(&m, &a));
 }
 
 void check_bf16_cuda(const torch::Tensor& t, const char* name) {
@@ -227,6 +228,6 @@ TORCH_LIBRARY_FRAGMENT(prime_decode, m) {
           "int v_off, int block_stride, int token_stride, int head_stride, int block_size, Tensor cos_sin_cache, "
           "Tensor(a!) out_hidden, Tensor(b!)? logits, Tensor(c!)? next_ids, Tensor(d!)? layer_outputs, "
           "Tensor(e!) workspace, int hidden, int intermediate, int layers, int q_heads, int kv_heads, int vocab, "
-          "int weight_format, float eps, int max_seq_len, bool lm_head, bool advance, bool tensor_cores=False) -> int");
+          "int weight_format, float eps, int max_seq_len, bool lm_head, bool advance, int path=0) -> int");
     m.impl("decode_step", torch::kCUDA, &decode_step);
 }

@@ -24,7 +24,7 @@ __all__ = ["Geometry", "SMOLLM2_135M", "SMOLLM2_360M", "SMOLLM2_1P7B", "GEOMETRI
            "unpack_matrix_mxfp8", "packed_row_bytes"]
 
 MAX_BATCH = 8          # requests one launch of the CUDA-core kernels takes
-MAX_REQUESTS = 64      # requests one decode_step call takes: 9..64 run as one launch of the tensor-core kernel
+MAX_REQUESTS = 64      # requests one decode_step call takes: larger batches run as one launch of the tensor-core kernel
 MAX_SEQ = 8192
 
 
@@ -33,8 +33,19 @@ def _decode_step_fake(input_ids, positions, seq_lens, block_table, slot_mapping,
                       final_norm, kv_table, k_off, v_off, block_stride, token_stride, head_stride, block_size,
                       cos_sin_cache, out_hidden, logits, next_ids, layer_outputs, workspace, hidden, intermediate,
                       layers, q_heads, kv_heads, vocab, weight_format, eps, max_seq_len, lm_head, advance,
-                      tensor_cores=False):
+                      path=0):
     return 0
+
+
+_tc_min_batch = 4      # batches from here on run on the tensor-core kernel (measured faster from 4 requests)
+
+
+def set_tensor_core_min_batch(n: int) -> None:
+    """Smallest batch ``decode_step`` (and the C entries pk_decode_step / mk_decode) hand to the tensor-core kernel;
+    ``MAX_BATCH + 1`` keeps batches up to 8 on the CUDA-core kernels."""
+    global _tc_min_batch
+    _tc_min_batch = max(1, min(int(n), MAX_BATCH + 1))
+    library().pk_decode_set_tc_min_batch(_tc_min_batch)
 
 
 def workspace_bytes(geometry: Geometry, max_batch: int = MAX_BATCH) -> int:
@@ -52,20 +63,15 @@ class _Runtime:
     def __init__(self, geometry: Geometry, device: torch.device):
         self.geometry = geometry
         self.device = device
-        self.scratch = torch.zeros(workspace_bytes(geometry, MAX_BATCH), dtype=torch.uint8, device=device)
+        # one workspace for all kernels: the tensor-core kernel's region lies behind the CUDA-core kernels' region
+        self.scratch = torch.zeros(workspace_bytes(geometry, MAX_REQUESTS), dtype=torch.uint8, device=device)
         self.out = torch.empty((MAX_REQUESTS, geometry.hidden), dtype=torch.bfloat16, device=device)
         self.group = MAX_BATCH          # requests per launch; lowered when the geometry does not fit at that batch
-        self.scratch_tc = None          # workspace of the tensor-core kernel (9..64 requests), allocated on first use
         self.logits = None
         self.next_ids = None
         self.table_key = None
         self.layers_t = None
         self.kv_t = None
-
-    def tc_scratch(self):
-        if self.scratch_tc is None:
-            self.scratch_tc = torch.zeros(workspace_bytes(self.geometry, MAX_REQUESTS), dtype=torch.uint8, device=self.device)
-        return self.scratch_tc
 
     def lm_buffers(self):
         if self.logits is None:
@@ -200,9 +206,10 @@ def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_tab
                 embed_lookup=None, name="decode", tensor_cores=True):
     """One decode step for ``geometry``.  Returns the final-normed hidden ``[B, hidden]`` (a view of a
     shared buffer), or ``(hidden, logits, next_ids)`` when ``lm_head`` is true.  Up to ``MAX_BATCH`` requests run in
-    one launch of the CUDA-core kernels; 9 to ``MAX_REQUESTS`` requests run in one launch of the tensor-core kernel
-    (``tensor_cores=False`` runs them as consecutive launches of the CUDA-core kernel instead, each of which streams
-    the weights again)."""
+    one launch of the CUDA-core kernels; batches of 4 (``set_tensor_core_min_batch``) to ``MAX_REQUESTS`` requests run
+    in one launch of the tensor-core kernel (``tensor_cores=False`` runs them on the CUDA-core kernels instead, above 8
+    requests as consecutive launches each of which streams the weights again; ``"force"`` takes the tensor-core kernel
+    at any batch)."""
     batch = input_ids.shape[0]
     if not 1 <= batch <= MAX_REQUESTS:
         raise ValueError(f"batch must be 1..{MAX_REQUESTS}, got {batch}")
@@ -231,29 +238,29 @@ def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_tab
     if lm_head:
         logits, next_ids = rt.lm_buffers()
 
-    def launch(g0, g1, lo, scratch=None):
+    def launch(g0, g1, lo, path=2):
         whole = g0 == 0 and g1 == batch                 # the common case: no slicing on the hot path
         cut = (lambda t: t) if whole else (lambda t: t[g0:g1])
         return torch.ops.prime_decode.decode_step(
             cut(input_ids), cut(positions), cut(seq_lens), cut(block_table), cut(slot_mapping), embed, embed_lookup,
             layers_t, final_norm, kv_t, 0, kv0.shape[3] // 2, kv0.stride(0), kv0.stride(2), kv0.stride(1), block_size,
             cos_sin_cache, rt.out if whole else rt.out[g0:g1], (logits if whole else logits[g0:g1]) if lm_head else None,
-            (next_ids if whole else next_ids[g0:g1]) if lm_head else None, lo, rt.scratch if scratch is None else scratch,
-            geometry.hidden,
+            (next_ids if whole else next_ids[g0:g1]) if lm_head else None, lo, rt.scratch, geometry.hidden,
             geometry.intermediate, geometry.layers, geometry.q_heads, geometry.kv_heads, geometry.vocab,
-            geometry.weight_format, float(eps), max_seq, bool(lm_head), bool(advance), scratch is not None)
+            geometry.weight_format, float(eps), max_seq, bool(lm_head), bool(advance), path)
 
-    # 9..64 requests: one launch of the tensor-core kernel (projections as tcgen05 GEMMs, weights streamed once);
-    # also smaller batches that the CUDA-core kernel cannot take in one launch for this geometry (rt.group)
+    # one launch of the tensor-core kernel (projections as tcgen05 GEMMs, weights streamed once): batches of
+    # _tc_min_batch requests or more, and smaller ones that the CUDA-core kernel cannot take in one launch for this
+    # geometry (rt.group)
     def tensor_core_launch():
-        rc = launch(0, batch, layer_outputs, rt.tc_scratch())
+        rc = launch(0, batch, layer_outputs, 1)
         if rc != 0:
             raise RuntimeError(f"{name} failed: {status_string(rc)}")
         if lm_head:
             return rt.out[:batch], logits[:batch], next_ids[:batch]
         return rt.out[:batch]
 
-    if tensor_cores and (batch > MAX_BATCH or batch > rt.group):
+    if tensor_cores == "force" or (tensor_cores and (batch >= _tc_min_batch or batch > MAX_BATCH or batch > rt.group)):
         return tensor_core_launch()
     # A launch of the CUDA-core kernels takes up to rt.group requests (MAX_BATCH, fewer when the geometry's activation
     # staging does not fit shared memory at that batch: status 9111 / 9105 lowers the group once and for all).
@@ -290,8 +297,6 @@ def check_status(geometry: Geometry, device) -> None:
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream(device).cuda_stream
         rc = library().pk_decode_status(rt.scratch.data_ptr(), stream)
-        if rc == 0 and rt.scratch_tc is not None:
-            rc = library().pk_decode_status(rt.scratch_tc.data_ptr(), stream)
     if rc != 0:
         raise RuntimeError(f"decode failed on the device: {status_string(rc)}")
 

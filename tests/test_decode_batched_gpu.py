@@ -23,6 +23,8 @@ def _oracle_weights(D, w, wq, geom):
 
 
 @pytest.mark.parametrize("name,dims,B,ctxs,mxfp8,block_size", [
+    ("gqa3-b4", (192, 512, 2, 3, 1, 1024), 4, [5, 17, 1, 40], False, 16),                             # default routing from 4 requests
+    ("mha-b7-mxfp8", (128, 256, 2, 2, 2, 512), 7, [3, 90, 31, 16, 15, 64, 200], True, 16),
     ("gqa3-b9", (192, 512, 2, 3, 1, 1024), 9, [5, 17, 1, 40, 33, 64, 2, 100, 7], False, 16),          # N padded to 16
     ("gqa3-b16", (192, 512, 3, 6, 2, 2048), 16, [37] * 16, False, 16),
     ("mha-b33", (128, 256, 2, 2, 2, 512), 33, [3 + 4 * i for i in range(33)], False, 16),             # N padded to 64, ragged
@@ -93,7 +95,7 @@ def test_batched_kernel_agrees_with_micro_batched_launches(cuda_device):
     csd = harness.make_cos_sin_cache(geom, 256, cuda_device)
     B, ctx = 20, 90
     outs = []
-    for tc in (True, False):
+    for tc in ("force", False):
         kv = harness.PagedKV(geom, B, 256, cuda_device, shuffle=True, seed=1)
         g2 = torch.Generator().manual_seed(5)
         for cache in kv.kv_caches:

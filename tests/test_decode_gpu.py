@@ -30,6 +30,17 @@ MIN_FRACTION_WITHIN_TOL = 0.6   # SmolLM2-135M: share of steps within LOGIT_TOL 
 LOGIT_360M = 7e-2
 
 
+@pytest.fixture(autouse=True)
+def _cuda_core_kernels_up_to_8_requests(cuda_device):
+    """This module tests the CUDA-core kernels (1..8 requests per launch); by default batches of 4 or more go to the
+    tensor-core kernel, which tests/test_decode_batched_gpu.py and tests/test_decode_real_configs_gpu.py cover."""
+    from prime_kernels_b200 import decode as D
+
+    D.set_tensor_core_min_batch(D.MAX_BATCH + 1)
+    yield
+    D.set_tensor_core_min_batch(4)
+
+
 def _step(D, geom, wd, kv, csd, cur, pos, lm_head=True, layer_outputs=None):
     dev = kv.device
     out = D.decode_step(geom, input_ids=cur.to(dev), positions=pos.to(dev),
