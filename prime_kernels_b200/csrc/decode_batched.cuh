@@ -72,7 +72,6 @@ struct BParams {
     long long* next_ids;
     uint16_t* layer_outputs;
     unsigned long long* profile;        // optional [ctas][L][kProfSlots] globaltimer stamps (thread 0, after every phase)
-    unsigned dbg;                       // development switches
     unsigned int* ctrl;                 // control words shared with the other kernels (status)
     unsigned int* bctrl;                // this kernel's words: [0] barrier counter, [1] completion counter
     unsigned long long* argkey;         // [kMaxReq]
@@ -719,7 +718,7 @@ __device__ void attention_item_b(BC& c, int layer, int b, int kvh, int chunk) {
         // after a failed wait the remaining runs are still waited for (each wait bounded), nothing is computed
         alive = b_wait_mbar(c, &bars[st], (c.kvc / kKvStages) & 1u) && alive;
         unsigned char* data = ring + st * kRunBytes;
-        if (alive && !(p.dbg & 8u)) {
+        if (alive) {
         if (we == seq && seq - 1 >= r0 && seq - 1 < r0 + 16) {      // the new token's row, from the prologue
             uint32_t* rowp = reinterpret_cast<uint32_t*>(data + (seq - 1 - r0) * 256);
             rowp[lane] = qkvb_s[G * 32 + lane];

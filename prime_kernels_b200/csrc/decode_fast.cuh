@@ -76,7 +76,6 @@ struct FastParams {
     int block_size, bt_stride, ids_i64, cs_fp32;
     int L, V, lm_head, advance, max_seq_len, ring_bytes;
     unsigned spin_limit;
-    int dbg;                            // development switches (bit 0: CTA barrier after every GEMV phase; bit 1: poll back-off)
     float eps;
 };
 
@@ -142,17 +141,7 @@ struct FC {
     uint32_t pre_off;           // ring offset of the upcoming phase's first entry, valid when pre_ok
     bool pre_ok;                // that entry has landed (checked before the staging of the phase)
     unsigned long long* prof;
-#ifdef PK_FAST_WPROF
-    unsigned long long* wprof;  // development builds: this warp's stamps of the current phase (lane 0, one layer)
-#endif
 };
-
-#ifdef PK_FAST_WPROF
-constexpr int kWprofLayer = 5;
-#define PK_WSTAMP(c, i) do { if ((c).wprof) (c).wprof[i] = global_ns(); } while (0)
-#else
-#define PK_WSTAMP(c, i) do { } while (0)
-#endif
 
 // barrier of the NW consumer warps (the producer warp does not take part)
 template <int NW>
@@ -217,7 +206,6 @@ __device__ __forceinline__ void poll_packets(FC<NW>& c, const uint32_t* const (&
                 first_only = false;
             }
         if (!need) break;
-        if (c.p.dbg & 2) __nanosleep(200);
         if ((++spins & 255u) == 0 && f_give_up(c, spins)) return;
         cur = first_only ? (need & (0u - need)) : need;
 #pragma unroll
@@ -454,7 +442,6 @@ __device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, co
             if (!__all_sync(kFullMask, f_wait_mbar(c, &sh.full[w][slot], (c.consumed / kFE) & 1))) break;
             eoff = sh.ent_off[w][slot];
         }
-        if (row == ra) PK_WSTAMP(c, 4);
         const uint4* ep = reinterpret_cast<const uint4*>(c.ring + eoff);
         float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         switch (t) {
@@ -510,7 +497,6 @@ __device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, co
                 best = max(best, (ord << 16) | (0xffffu - (uint32_t)(r - ra)));
             }
         }
-        PK_WSTAMP(c, 5);
     }
     if (t == kLM) {
         // greedy argmax: highest logit, ties toward the lowest index; one atomic per CTA
@@ -571,7 +557,6 @@ __device__ __forceinline__ void stage_norm(FC<NW>& c, const uint32_t* src_words,
             x[u][2] = __uint_as_float(pkt[u].z << 16); x[u][3] = __uint_as_float(pkt[u].w << 16);
         }
     }
-    PK_WSTAMP(c, 1);
     float ss = 0.f;
 #pragma unroll
     for (int u = 0; u < PPT; ++u) {
@@ -585,7 +570,6 @@ __device__ __forceinline__ void stage_norm(FC<NW>& c, const uint32_t* src_words,
     ss = warp_sum(ss);
     if (c.lane == 0) sh.red[c.warp] = ss;
     csync<NW>();
-    PK_WSTAMP(c, 2);
     float tot = 0.f;
 #pragma unroll
     for (int w = 0; w < NW; ++w) tot += sh.red[w];
@@ -625,7 +609,6 @@ __device__ __forceinline__ void stage_copy(FC<NW>& c, const uint32_t* src_words,
 #pragma unroll
     for (int u = 0; u < PPT; ++u) ptr[u] = (tid + u * NT) < NP ? src_words + 4 * (tid + u * NT) : nullptr;
     poll_packets<PPT>(c, ptr, T, pkt);
-    PK_WSTAMP(c, 1);
 #pragma unroll
     for (int u = 0; u < PPT; ++u) {
         const int pk = tid + u * NT;
@@ -919,23 +902,6 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer, const int w
     if (c.prof) c.prof[14] = global_ns();
 }
 
-// L2 prefetch of this CTA's chunk (K and V rows of the positions resolved at kernel start).
-template <class W, int NW>
-__device__ __forceinline__ void attention_prefetch(FC<NW>& c, int layer) {
-    const FastParams& p = c.p;
-    FShared<NW>& sh = c.sh;
-    const unsigned char* kvr = reinterpret_cast<const unsigned char*>(layer < kKvPtrs ? sh.kv_ptr[layer] : __ldg(p.kv + layer));
-    const long long hs = (long long)sh.item_kvh * p.head_stride;
-    for (int t = (int)threadIdx.x; t < NW * kPre * 32; t += NW * 32) {
-        const long long off = sh.kv_off[t / (kPre * 32)][(t % (kPre * 32)) >> 1];
-        if (off >= 0) {
-            const long long e = off + hs;
-            const unsigned char* a = kvr + ((t & 1) ? p.v_off + e : p.k_off + e) * 2;
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
-        }
-    }
-}
-
 // ------------------------------------------------------------------ the kernel
 template <class W, int NW>
 __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const FastParams p) {
@@ -1019,11 +985,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const Fas
     __syncthreads();
 
     FC<NW> c{p, sh, {act0, act1}, {res0, res1}, attn, ring_base + (size_t)warp * p.ring_bytes, 0u, 0u, warp, lane, cta, ncta,
-             0u, {make_uint2(0u, 0u), make_uint2(0u, 0u)}, 0u, false, nullptr
-#ifdef PK_FAST_WPROF
-             , nullptr
-#endif
-    };
+             0u, {make_uint2(0u, 0u), make_uint2(0u, 0u)}, 0u, false, nullptr};
     c.T16 = ((sh.epoch % 511u) + 1u) << 23;
     c.T32 = (sh.epoch + 1u) << 7;
     if (warp == NW) {
@@ -1102,12 +1064,6 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const Fas
             c.pre_ok = __all_sync(kFullMask, f_wait_mbar(c, &sh.full[warp][slot], (c.consumed / kFE) & 1));
             c.pre_off = sh.ent_off[warp][slot];
         }
-#ifdef PK_FAST_WPROF
-        c.wprof = (p.profile && lane == 0 && layer == kWprofLayer && !last)
-                      ? p.profile + (size_t)ncta * p.L * kProfSlots + ((size_t)(cta * NW + warp) * 4 + t) * 8
-                      : nullptr;
-        PK_WSTAMP(c, 0);
-#endif
         if (t == kQKV || t == kGU || last) {
             if (t == kQKV) {
                 if (prof) prof[0] = global_ns();
@@ -1131,7 +1087,6 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const Fas
             stage_copy<W, W::I, NW>(c, p.w_act + par * W::I, tag16(c, layer), act1);
         }
         if (prof) prof[1 + 2 * t + (t >= kO ? 1 : 0)] = global_ns();     // slots 1, 4, 6, 8
-        PK_WSTAMP(c, 3);
         if (last) {
             if (cta == 0)
                 for (int i = tid; i < W::H / 2; i += NTC)
@@ -1142,9 +1097,8 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const Fas
         // Nobody in this CTA polls the next hand-off before the CTA's own results are on their way: reads of a
         // line that is still being written slow the writes down (measured: several microseconds per hand-off
         // when the warps without rows in a phase started polling at once).
-        if (!(p.dbg & 1)) csync<NW>();
+        csync<NW>();
         if (prof) prof[2 + 2 * t + (t >= kO ? 1 : 0)] = global_ns();     // slots 2, 5, 7, 9
-        PK_WSTAMP(c, 6);
     }
 
     }   // consumer warps

@@ -1805,7 +1805,6 @@ static std::unordered_map<const void*, WsState> g_ws_ready;     // workspace poi
 // largest dynamic shared memory opted in, per (device, kernel): the attribute belongs to the device's context
 static std::unordered_map<unsigned long long, int> g_kernel_smem;
 static unsigned g_spin_limit = kSpinLimit;
-static int g_fast_dbg = 0;
 static int g_tc_min_batch = 4;       // pk_decode_step hands launches of this many requests or more to the tensor-core kernel
 static int g_fast_warps = -1;        // batch-1 fast path: -1 = not decided yet (environment), 0 = off, 7 / 8 = consumer warps per CTA
 
@@ -2025,7 +2024,6 @@ static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo
     p.next_ids = static_cast<long long*>(a.next_ids);
     p.layer_outputs = static_cast<uint16_t*>(a.layer_outputs);
     p.profile = (g_profile && g_profile_bytes >= (size_t)di.sm_count * g.L * kProfSlots * 8) ? g_profile : nullptr;
-    p.dbg = (unsigned)g_fast_dbg;
     p.ctrl = reinterpret_cast<unsigned int*>(ws + lay.ctrl);
     p.fctrl = reinterpret_cast<unsigned int*>(fw + fl.fctrl);
     p.argkey = reinterpret_cast<unsigned long long*>(fw + fl.argkey);
@@ -2051,7 +2049,6 @@ static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo
     p.max_seq_len = a.max_seq_len;
     p.ring_bytes = rw;
     p.spin_limit = g_spin_limit;
-    p.dbg = g_fast_dbg;
     p.eps = g.eps;
     void* args[] = {&p};
     cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fn), dim3(di.sm_count), dim3((NW + 1) * 32), args,
@@ -2114,7 +2111,6 @@ static int batched_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceI
     p.next_ids = static_cast<long long*>(a.next_ids);
     p.layer_outputs = static_cast<uint16_t*>(a.layer_outputs);
     p.profile = (g_profile && g_profile_bytes >= (size_t)di.sm_count * g.L * kProfSlots * 8) ? g_profile : nullptr;
-    p.dbg = (unsigned)g_fast_dbg;
     p.ctrl = reinterpret_cast<unsigned int*>(ws);
     p.bctrl = reinterpret_cast<unsigned int*>(bw + bl.bctrl);
     p.argkey = reinterpret_cast<unsigned long long*>(bw + bl.argkey);
@@ -2469,7 +2465,6 @@ extern "C" int pk_decode_set_fast_path(int warps) {
     g_fast_warps = warps;
     return 0;
 }
-extern "C" void pk_decode_set_debug(int flags) { g_fast_dbg = flags; }
 // Bound (polling rounds) of every device-side wait of later launches; 0 restores the default.
 extern "C" void pk_decode_set_spin_limit(unsigned rounds) {
     std::lock_guard<std::mutex> lk(g_mu);
