@@ -272,18 +272,28 @@ def extra_measurements(dev, peak):
                                        "sample": f"{nb} x {cb} rows through the plain-C quantiser oracle, one thread"}
     except Exception as e:      # the oracle library is test infrastructure; its absence must not break the bench
         out["rmsnorm_cpu_baseline"] = {"unavailable": str(e)[:120]}
-    for gname, ctx, steps in (("smollm2-135m", 32, 64), ("smollm2-1.7b", 1024, 32)):
+    # (geometry, batch, context, timed steps, MXFP8 weights): the other two model sizes at batch 1 and the two batched
+    # configurations (tensor-core kernel), short device-timed lines
+    host_weights = {}
+    for gname, batch, ctx, steps, mx in (("smollm2-135m", 1, 32, 64, False), ("smollm2-360m", 16, 4096, 16, True),
+                                         ("smollm2-1.7b", 1, 1024, 32, False), ("smollm2-1.7b", 64, 1024, 8, False)):
         geom = D.GEOMETRIES[gname]
-        weights = harness.weights_to(harness.make_weights(geom, 0), dev)
+        if gname not in host_weights:
+            host_weights.clear()                     # one model's host copy at a time
+            host_weights[gname] = harness.make_weights(geom, 0)
+        weights = harness.weights_to(host_weights[gname], dev)
+        if mx:
+            geom = geom.with_format(1)
+            weights = D.pack_weights_mxfp8(weights)
         cap = ctx + steps + 80
         cap = (cap + 15) // 16 * 16
-        kv = harness.PagedKV(geom, 1, cap, dev)
+        kv = harness.PagedKV(geom, batch, cap, dev)
         for cache in kv.kv_caches:
             cache.normal_()
         sess = D.DecodeSession(geom, embed=weights["embed"], layers=weights["layers"], final_norm=weights["final_norm"],
                                kv_caches=kv.kv_caches, cos_sin_cache=harness.make_cos_sin_cache(geom, cap, dev),
-                               block_table=kv.block_table)
-        sess.start(torch.tensor([17]), torch.tensor([ctx]))
+                               block_table=kv.block_table, embed_lookup=weights.get("embed_lookup"))
+        sess.start(torch.full((batch,), 17), torch.full((batch,), ctx))
         for _ in range(4):
             sess.step()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -294,9 +304,10 @@ def extra_measurements(dev, peak):
         torch.cuda.synchronize(dev)
         D.check_status(geom, dev)
         ms = e0.elapsed_time(e1) / steps
-        nbytes = algorithmic_bytes(geom, 1, ctx + 4 + steps // 2)
-        out["decode"].append({"workload": f"{gname}-b1", "context": ctx, "steps": steps, "ms_per_step": round(ms, 4),
-                              "tok_s": round(1e3 / ms, 1), "roofline_frac_of_measured": round(nbytes / (ms * 1e-3) / 1e9 / peak, 3),
+        nbytes = algorithmic_bytes(geom, batch, ctx + 4 + steps // 2, mxfp8=mx)
+        out["decode"].append({"workload": f"{gname}{'-mxfp8' if mx else ''}-b{batch}", "context": ctx, "steps": steps,
+                              "ms_per_step": round(ms, 4), "tok_s": round(batch * 1e3 / ms, 1),
+                              "roofline_frac_of_measured": round(nbytes / (ms * 1e-3) / 1e9 / peak, 3),
                               "note": "KV pre-filled with normal(0,1), device-driven greedy loop, CUDA events"})
         del sess, kv, weights
         torch.cuda.empty_cache()
