@@ -64,6 +64,19 @@ int pk_rmsnorm_forward(const void* x, const void* residual, const void* weight, 
  * out = bf16(bf16(silu(gate)) * up); gate/up row strides in elements. */
 int pk_swiglu_forward(const void* gate, const void* up, void* out, long long rows, int cols, long long gate_stride,
                       long long up_stride, void* stream);
+/* Backward passes of the three ops above (bf16; same rounding points as the reference's Triton backward kernels:
+ * prime_kernels/triton_rope/__init__.py:85-123, triton_swiglu/swiglu.py:62-97, triton_rmsnorm/rmsnorm.py:107-193
+ * and :300-392).  pk_rmsnorm_backward: `x` is the normed input (the returned sum for the residual variant), `grad_sum`
+ * the gradient arriving through that sum (NULL for plain rmsnorm), `dx` the gradient of x (of branch and of residual),
+ * `dw` bf16 [H], `dw_partials` fp32 scratch [pk_rmsnorm_backward_parts(rows)][H]; H % 8 == 0, H <= 8192; the weight
+ * gradient is summed in a fixed order (deterministic). */
+int pk_apply_rotary_backward(const void* g, void* gx, const void* cos, const void* sin, long long batch, int heads, int seq,
+                             int D, int rot, int head_major, int cos_batch, void* stream);
+int pk_swiglu_backward(const void* grad, const void* gate, const void* up, void* d_gate, void* d_up, long long rows, int cols,
+                       long long gate_stride, long long up_stride, void* stream);
+int pk_rmsnorm_backward_parts(long long rows);
+int pk_rmsnorm_backward(const void* grad_out, const void* grad_sum, const void* x, const void* weight, void* dx, void* dw,
+                        void* dw_partials, long long rows, int H, float eps, void* stream);
 
 /* MXFP8 weight packing for the decode GEMVs.  No counterpart in the reference (its kernels take
  * pre-quantised weights, prime_kernels/flash_moe/__init__.py:165-170).  Quantises bf16 [rows, K] along K

@@ -45,6 +45,10 @@ SYMBOLS = {
     "pk_apply_rotary": (ci, [vp, vp, vp, vp, ll, ci, ci, ci, ci, ci, ci, vp]),
     "pk_rmsnorm_forward": (ci, [vp, vp, vp, vp, vp, ll, ci, cf, vp]),
     "pk_swiglu_forward": (ci, [vp, vp, vp, ll, ci, ll, ll, vp]),
+    "pk_apply_rotary_backward": (ci, [vp, vp, vp, vp, ll, ci, ci, ci, ci, ci, ci, vp]),
+    "pk_swiglu_backward": (ci, [vp, vp, vp, vp, vp, ll, ci, ll, ll, vp]),
+    "pk_rmsnorm_backward_parts": (ci, [ll]),
+    "pk_rmsnorm_backward": (ci, [vp, vp, vp, vp, vp, vp, vp, ll, ci, ctypes.c_float, vp]),
     "pk_mxfp8_packed_row_bytes": (ll, [ci]),
     "pk_pack_weights_mxfp8": (ci, [vp, vp, ll, ci, vp]),
     "pk_decode_workspace_bytes": (sz, [ctypes.POINTER(PkDecodeModel), ci]),

@@ -198,6 +198,66 @@ torch::Tensor swiglu_fwd(const torch::Tensor& gate, const torch::Tensor& up) {
     return out;
 }
 
+std::tuple<torch::Tensor, torch::Tensor> apply_rotary_bwd(const torch::Tensor& gq, const torch::Tensor& gk,
+                                                          const torch::Tensor& cos, const torch::Tensor& sin,
+                                                          int64_t unsqueeze_dim) {
+    check_bf16_cuda(gq, "grad_q"); check_bf16_cuda(gk, "grad_k"); check_bf16_cuda(cos, "cos"); check_bf16_cuda(sin, "sin");
+    TORCH_CHECK(gq.dim() == 4 && gk.dim() == 4 && cos.dim() == 3 && sin.sizes() == cos.sizes(), "expected 4-D grads and 3-D cos, sin");
+    TORCH_CHECK(unsqueeze_dim == 1 || unsqueeze_dim == 2, "unsqueeze_dim must be 1 or 2");
+    TORCH_CHECK(gq.is_contiguous() && gk.is_contiguous() && cos.is_contiguous() && sin.is_contiguous(), "inputs must be contiguous");
+    at::cuda::OptionalCUDAGuard guard{device_of(gq)};
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    const bool hm = unsqueeze_dim == 1;
+    const int64_t B = gq.size(0), S = hm ? gq.size(2) : gq.size(1), D = gq.size(3), rot = cos.size(2);
+    TORCH_CHECK(cos.size(1) == S && (cos.size(0) == 1 || cos.size(0) == B), "cos must be [1 or B, S, rot]");
+    torch::Tensor dq = torch::empty_like(gq), dk = torch::empty_like(gk);
+    int rc = pk_apply_rotary_backward(gq.const_data_ptr(), dq.data_ptr(), cos.const_data_ptr(), sin.const_data_ptr(), B,
+                                      (int)(hm ? gq.size(1) : gq.size(2)), (int)S, (int)D, (int)rot, hm, (int)cos.size(0), stream);
+    TORCH_CHECK(rc == 0, "apply_rotary backward failed: ", pk_status_string(rc));
+    rc = pk_apply_rotary_backward(gk.const_data_ptr(), dk.data_ptr(), cos.const_data_ptr(), sin.const_data_ptr(), B,
+                                  (int)(hm ? gk.size(1) : gk.size(2)), (int)S, (int)D, (int)rot, hm, (int)cos.size(0), stream);
+    TORCH_CHECK(rc == 0, "apply_rotary backward failed: ", pk_status_string(rc));
+    return {dq, dk};
+}
+
+// grad_sum is optional (plain rmsnorm, or nothing flowed back through the returned sum)
+std::tuple<torch::Tensor, torch::Tensor> rmsnorm_bwd(const torch::Tensor& grad_out, const std::optional<torch::Tensor>& grad_sum,
+                                                     const torch::Tensor& x, const torch::Tensor& weight, double eps) {
+    check_bf16_cuda(grad_out, "grad_out"); check_bf16_cuda(x, "x"); check_bf16_cuda(weight, "weight");
+    TORCH_CHECK(grad_out.is_contiguous() && x.is_contiguous() && grad_out.sizes() == x.sizes(), "grad_out and x must be contiguous and match");
+    TORCH_CHECK(weight.dim() == 1 && weight.size(0) == x.size(-1), "weight must be [H]");
+    if (grad_sum.has_value()) {
+        check_bf16_cuda(*grad_sum, "grad_sum");
+        TORCH_CHECK(grad_sum->is_contiguous() && grad_sum->sizes() == x.sizes(), "grad_sum must be contiguous and match x");
+    }
+    at::cuda::OptionalCUDAGuard guard{device_of(x)};
+    const int64_t H = x.size(-1), rows = x.numel() / H;
+    torch::Tensor dx = torch::empty_like(x), dw = torch::empty_like(weight);
+    torch::Tensor parts = torch::empty({pk_rmsnorm_backward_parts(rows), H}, x.options().dtype(torch::kFloat32));
+    const int rc = pk_rmsnorm_backward(grad_out.const_data_ptr(), opt_ptr(grad_sum), x.const_data_ptr(), weight.const_data_ptr(),
+                                       dx.data_ptr(), dw.data_ptr(), parts.data_ptr(), rows, (int)H, (float)eps,
+                                       at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "rmsnorm backward failed: ", pk_status_string(rc));
+    return {dx, dw};
+}
+
+std::tuple<torch::Tensor, torch::Tensor> swiglu_bwd(const torch::Tensor& grad, const torch::Tensor& gate, const torch::Tensor& up) {
+    check_bf16_cuda(grad, "grad"); check_bf16_cuda(gate, "gate"); check_bf16_cuda(up, "up");
+    TORCH_CHECK(gate.sizes() == up.sizes() && grad.sizes() == gate.sizes() && gate.stride(-1) == 1 && up.stride(-1) == 1,
+                "grad, gate and up must match, contiguous last dim");
+    at::cuda::OptionalCUDAGuard guard{device_of(gate)};
+    const int64_t cols = gate.size(-1);
+    torch::Tensor g2 = gate.dim() == 2 ? gate : gate.reshape({-1, cols});
+    torch::Tensor u2 = up.dim() == 2 ? up : up.reshape({-1, cols});
+    torch::Tensor gr = grad.contiguous();
+    torch::Tensor d_gate = torch::empty(gate.sizes(), gate.options()), d_up = torch::empty(gate.sizes(), gate.options());
+    const int rc = pk_swiglu_backward(gr.const_data_ptr(), g2.const_data_ptr(), u2.const_data_ptr(), d_gate.data_ptr(),
+                                      d_up.data_ptr(), g2.size(0), (int)cols, g2.stride(0), u2.stride(0),
+                                      at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "swiglu backward failed: ", pk_status_string(rc));
+    return {d_gate, d_up};
+}
+
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(prime_elementwise, m) {
@@ -209,6 +269,12 @@ TORCH_LIBRARY_FRAGMENT(prime_elementwise, m) {
     m.impl("residual_rmsnorm", torch::kCUDA, &residual_rmsnorm_fwd);
     m.def("swiglu(Tensor gate, Tensor up) -> Tensor");
     m.impl("swiglu", torch::kCUDA, &swiglu_fwd);
+    m.def("apply_rotary_backward(Tensor grad_q, Tensor grad_k, Tensor cos, Tensor sin, int unsqueeze_dim) -> (Tensor, Tensor)");
+    m.impl("apply_rotary_backward", torch::kCUDA, &apply_rotary_bwd);
+    m.def("rmsnorm_backward(Tensor grad_out, Tensor? grad_sum, Tensor x, Tensor weight, float eps) -> (Tensor, Tensor)");
+    m.impl("rmsnorm_backward", torch::kCUDA, &rmsnorm_bwd);
+    m.def("swiglu_backward(Tensor grad, Tensor gate, Tensor up) -> (Tensor, Tensor)");
+    m.impl("swiglu_backward", torch::kCUDA, &swiglu_bwd);
 }
 
 TORCH_LIBRARY_FRAGMENT(prime_rmsnorm, m) {
