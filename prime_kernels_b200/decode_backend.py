@@ -9,7 +9,8 @@ the stock forward.  With batch-invariant mode, decode rows of a mixed prefill/de
 the decode step so that a joining prefill does not change their arithmetic path ("repair").
 
 Differences from the reference: the kernel is geometry-generic, so any head-dim-64 Llama configuration is
-routed (not only two hard-coded ones) and the batch limit is ``decode.MAX_BATCH``; nothing here imports vLLM
+routed (not only two hard-coded ones) and the batch limit is ``decode.MAX_REQUESTS`` (one launch of the tensor-core
+kernel from 4 requests on); nothing here imports vLLM
 at module import -- the model, metadata and forward context are duck-typed, and :func:`install` takes the
 class to patch and the forward-context getter as arguments (``install_into_vllm`` fetches them from vLLM).
 Decode steps replayed from CUDA graphs do not re-enter Python, so the path a captured graph takes is fixed
@@ -71,11 +72,11 @@ def _kv_caches(model):
 
 def metadata_eligible(meta, model, geometry, batch: int) -> bool:
     """Step eligibility (the reference's ``_metadata_eligible``), for every geometry the kernel takes."""
-    from .decode import MAX_BATCH, MAX_SEQ
+    from .decode import MAX_REQUESTS, MAX_SEQ
 
     if meta is None or type(meta).__name__ != METADATA_CLASS:
         return False
-    if meta.max_query_len != 1 or meta.num_actual_tokens != batch or not 0 < batch <= MAX_BATCH:
+    if meta.max_query_len != 1 or meta.num_actual_tokens != batch or not 0 < batch <= MAX_REQUESTS:
         return False
     caches = _kv_caches(model)
     first = caches[0]
@@ -157,10 +158,10 @@ def route(model, input_ids, positions, meta, *, decode_step: Optional[Callable] 
     if meta is None or type(meta).__name__ != METADATA_CLASS or meta.max_query_len != 1:
         stats["stock_not_pure_decode"] += 1
         return None
-    from .decode import MAX_BATCH
+    from .decode import MAX_REQUESTS
 
     batch = input_ids.shape[0]
-    if batch > MAX_BATCH or meta.num_actual_tokens != batch:
+    if batch > MAX_REQUESTS or meta.num_actual_tokens != batch:
         stats["stock_decode_over_max_batch"] += 1
         return None
     if not metadata_eligible(meta, model, geometry, batch):

@@ -101,8 +101,8 @@ def test_other_metadata_class_batch_limit_and_cache_layout():
     model = make_model()
     z = torch.zeros(3, dtype=torch.long)
     assert db.route(model, z, z, decode_meta(3, OtherMetadata), decode_step=stub_decode_step) is None
-    big = torch.zeros(9, dtype=torch.long)
-    assert db.route(model, big, big, decode_meta(9), decode_step=stub_decode_step) is None
+    big = torch.zeros(65, dtype=torch.long)          # one launch takes up to 64 requests
+    assert db.route(model, big, big, decode_meta(65), decode_step=stub_decode_step) is None
     assert db.stats["stock_decode_over_max_batch"] == 1
     model.layers[1].self_attn.attn.kv_cache = torch.zeros(8, 5, 32, 128, dtype=torch.bfloat16)   # block size 32
     assert db.route(model, z, z, decode_meta(3), decode_step=stub_decode_step) is None
