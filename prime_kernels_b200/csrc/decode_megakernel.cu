@@ -1725,7 +1725,10 @@ static FastLayout fast_layout(const ModelGeom& g) {
 
 static int batched_np(int B) { return B <= 16 ? 16 : (B <= 32 ? 32 : 64); }
 
-static BatchedLayout batched_layout(const ModelGeom& g, int B) {
+// One layout for every batch size (sized for the maximum): the fp32 sums must be zero when a launch starts, and the
+// kernel leaves them zero, which only holds across launches of different batch sizes if a buffer never moves.
+static BatchedLayout batched_layout(const ModelGeom& g, int /*B*/) {
+    const int B = batched::kMaxReq;
     BatchedLayout l{};
     size_t off = 0;
     auto take = [&](size_t bytes) {
@@ -1800,6 +1803,7 @@ struct WsState {
     size_t bytes = 0;               // zeroed size
     unsigned long long sig = 0;     // geometry the workspace was last used with
     unsigned long long launches = 0;
+    int kb = 0;                     // kernel batch of the last CUDA-core launch (fixes the offsets of its buffers)
 };
 static std::unordered_map<const void*, WsState> g_ws_ready;     // workspace pointers already zeroed
 // largest dynamic shared memory opted in, per (device, kernel): the attribute belongs to the device's context
@@ -1835,19 +1839,23 @@ static int ensure_smem(const void* fn, size_t smem) {
 }
 
 // Zero the workspace in stream order when it is new, when it was last used with another geometry (the
-// fast kernel's 16-bit tags only tell consecutive launches of one geometry apart) and every 2^24 launches
-// (so that the launch epoch inside the tags never wraps).
-static int ensure_workspace(void* ws, size_t ws_bytes, size_t need, const ModelGeom& g, cudaStream_t stream) {
+// fast kernel's 16-bit tags only tell consecutive launches of one geometry apart), when the CUDA-core kernels'
+// buffers move because the kernel batch changed (`kb`: 1, 2, 3, 4 or 8; their offsets depend on it, and stale
+// words of another layout must never be mistaken for tagged words; 0 = the tensor-core kernel, whose region
+// is fixed) and every 2^24 launches (so that the launch epoch inside the tags never wraps).
+static int ensure_workspace(void* ws, size_t ws_bytes, size_t need, const ModelGeom& g, cudaStream_t stream, int kb = 0) {
     std::lock_guard<std::mutex> lk(g_mu);
     WsState& st = g_ws_ready[ws];
     const unsigned long long sig = geom_sig(g);
-    if (st.bytes < need || st.sig != sig || st.launches >= (1ull << 24)) {
+    const bool moved = kb != 0 && st.kb != 0 && st.kb != kb;
+    if (st.bytes < need || st.sig != sig || moved || st.launches >= (1ull << 24)) {
         cudaError_t e = cudaMemsetAsync(ws, 0, ws_bytes, stream);
         if (e != cudaSuccess) return (int)e;
         st.bytes = ws_bytes;
         st.sig = sig;
         st.launches = 0;
     }
+    if (kb != 0) st.kb = kb;
     ++st.launches;
     return 0;
 }
@@ -2002,7 +2010,7 @@ static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo
     auto fn = decode_fast_kernel<W, NW>;
     int rc = ensure_smem(reinterpret_cast<const void*>(fn), smem);
     if (rc) return rc;
-    rc = ensure_workspace(a.ws, a.ws_bytes, lay.total, g, a.stream);
+    rc = ensure_workspace(a.ws, a.ws_bytes, lay.total, g, a.stream, 1);      // the batch-1 layout
     if (rc) return rc;
 
     const FastLayout fl = fast_layout(g);
@@ -2260,7 +2268,7 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
 
     rc = ensure_smem(reinterpret_cast<const void*>(fn), smem);
     if (rc) return rc;
-    rc = ensure_workspace(a.ws, a.ws_bytes, lay.total, g, a.stream);
+    rc = ensure_workspace(a.ws, a.ws_bytes, lay.total, g, a.stream, KB);
     if (rc) return rc;
 
     unsigned char* ws = static_cast<unsigned char*>(a.ws);

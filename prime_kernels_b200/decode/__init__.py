@@ -156,11 +156,16 @@ def status_string(rc: int) -> str:
 
 def _check_kv(geometry: Geometry, kv_caches):
     first = kv_caches[0]
-    if first.dtype != torch.bfloat16 or first.dim() != 4:
-        raise ValueError("kv_caches must be 4-D BF16 tensors")
-    if first.shape[1] != geometry.kv_heads or first.shape[3] != 2 * HEAD_DIM or first.stride(3) != 1:
-        raise ValueError(
-            f"kv_caches must be [blocks, {geometry.kv_heads}, block_size, {2 * HEAD_DIM}] with unit last stride")
+    if first.dtype != torch.bfloat16 or first.dim() not in (4, 5):
+        raise ValueError("kv_caches must be 4-D or 5-D BF16 tensors")
+    if first.dim() == 4:
+        if first.shape[1] != geometry.kv_heads or first.shape[3] != 2 * HEAD_DIM or first.stride(3) != 1:
+            raise ValueError(
+                f"kv_caches must be [blocks, {geometry.kv_heads}, block_size, {2 * HEAD_DIM}] with unit last stride")
+    elif (first.shape[0] != 2 or first.shape[3] != geometry.kv_heads or first.shape[4] != HEAD_DIM or first.stride(4) != 1
+          or any(st % 8 for st in first.stride()[:4])):
+        raise ValueError(f"5-D kv_caches must be [2, blocks, block_size, {geometry.kv_heads}, {HEAD_DIM}] with unit last "
+                         "stride and the other strides multiples of 8 elements")
     for kv in kv_caches:
         if kv.shape != first.shape or kv.stride() != first.stride() or kv.dtype != first.dtype:
             raise ValueError("all layers must share one KV cache shape, dtype and strides")
@@ -227,7 +232,16 @@ def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_tab
         raise ValueError("cos_sin_cache must be BF16 or FP32")
     device = input_ids.device
     kv0 = kv_caches[0]
-    block_size = kv0.shape[2]
+    # cache layouts: [blocks, kv_heads, block_size, 128] (K in 0..63, V in 64..127: the reference's layout) or
+    # [2, blocks, block_size, kv_heads, 64] (K and V planes: vLLM's FlashAttention layout)
+    if kv0.ndim == 5:
+        if kv0.shape[0] != 2 or kv0.shape[4] != 64 or kv0.stride(4) != 1:
+            raise ValueError("5-D kv caches must be [2, blocks, block_size, kv_heads, 64] with a contiguous head dim")
+        block_size = kv0.shape[2]
+        kv_layout = (0, kv0.stride(0), kv0.stride(1), kv0.stride(2), kv0.stride(3))
+    else:
+        block_size = kv0.shape[2]
+        kv_layout = (0, kv0.shape[3] // 2, kv0.stride(0), kv0.stride(2), kv0.stride(1))
     max_seq = block_table.shape[1] * block_size
     if max_seq > MAX_SEQ:
         raise ValueError(f"context limit {max_seq} exceeds the kernel's {MAX_SEQ}")
@@ -243,7 +257,7 @@ def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_tab
         cut = (lambda t: t) if whole else (lambda t: t[g0:g1])
         return torch.ops.prime_decode.decode_step(
             cut(input_ids), cut(positions), cut(seq_lens), cut(block_table), cut(slot_mapping), embed, embed_lookup,
-            layers_t, final_norm, kv_t, 0, kv0.shape[3] // 2, kv0.stride(0), kv0.stride(2), kv0.stride(1), block_size,
+            layers_t, final_norm, kv_t, *kv_layout, block_size,
             cos_sin_cache, rt.out if whole else rt.out[g0:g1], (logits if whole else logits[g0:g1]) if lm_head else None,
             (next_ids if whole else next_ids[g0:g1]) if lm_head else None, lo, rt.scratch, geometry.hidden,
             geometry.intermediate, geometry.layers, geometry.q_heads, geometry.kv_heads, geometry.vocab,

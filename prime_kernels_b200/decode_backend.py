@@ -81,8 +81,18 @@ def metadata_eligible(meta, model, geometry, batch: int) -> bool:
     caches = _kv_caches(model)
     first = caches[0]
     bt = meta.block_table
-    if (first.dtype != torch.bfloat16 or first.ndim != 4 or first.shape[1] != geometry.kv_heads
-            or first.shape[2] != BLOCK_SIZE or first.shape[3] != 2 * HEAD_DIM or first.stride(3) != 1
+    # the reference's cache layout [blocks, kv_heads, 16, 128], or vLLM's FlashAttention layout
+    # [2, blocks, 16, kv_heads, 64] (the kernels read either through strides)
+    if first.ndim == 4:
+        layout_ok = (first.shape[1] == geometry.kv_heads and first.shape[2] == BLOCK_SIZE
+                     and first.shape[3] == 2 * HEAD_DIM and first.stride(3) == 1)
+    elif first.ndim == 5:
+        layout_ok = (first.shape[0] == 2 and first.shape[2] == BLOCK_SIZE and first.shape[3] == geometry.kv_heads
+                     and first.shape[4] == HEAD_DIM and first.stride(4) == 1
+                     and all(st % 8 == 0 for st in first.stride()[:4]))
+    else:
+        layout_ok = False
+    if (first.dtype != torch.bfloat16 or not layout_ok
             or bt.dtype != torch.int32 or bt.shape[0] < batch or bt.stride(1) != 1 or bt.shape[1] < 1
             or bt.shape[1] * BLOCK_SIZE > MAX_SEQ):
         return False

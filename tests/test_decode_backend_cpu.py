@@ -109,6 +109,24 @@ def test_other_metadata_class_batch_limit_and_cache_layout():
     assert db.stats["stock_unsupported_metadata"] == 1
 
 
+def test_vllm_native_cache_layout_is_routed():
+    """vLLM's FlashAttention backend keeps K and V as planes of one tensor, [2, blocks, 16, kv_heads, 64]: the router
+    takes it (the kernels read the cache through strides); other block sizes and head dims fall through."""
+    model = make_model()
+    kvh = model.config.num_key_value_heads
+    for layer in model.layers:
+        layer.self_attn.attn.kv_cache = torch.zeros(2, 8, 16, kvh, 64, dtype=torch.bfloat16)
+    z = torch.zeros(3, dtype=torch.long)
+    assert db.route(model, z, z, decode_meta(3), decode_step=stub_decode_step) is not None
+    assert db.stats["backend_decode"] == 1 and calls[-1][1]["kv_caches"][0].ndim == 5
+    for layer in model.layers:
+        layer.self_attn.attn.kv_cache = torch.zeros(2, 8, 32, kvh, 64, dtype=torch.bfloat16)      # block size 32
+    assert db.route(model, z, z, decode_meta(3), decode_step=stub_decode_step) is None
+    for layer in model.layers:
+        layer.self_attn.attn.kv_cache = torch.zeros(2, 8, 16, kvh, 128, dtype=torch.bfloat16)     # head dim 128
+    assert db.route(model, z, z, decode_meta(3), decode_step=stub_decode_step) is None
+
+
 def test_repair_recomputes_only_single_token_requests():
     model = make_model()
     # requests: 0 prefill (3 tokens), 1 decode, 2 prefill (2 tokens), 3 decode  -> token rows 3 and 6

@@ -152,3 +152,84 @@ def test_batched_device_driven_generation_matches_stepwise(cuda_device):
     same = (ids_a == ids_b).all(dim=1)
     first_diff = int((~same).float().argmax()) if not bool(same.all()) else steps
     assert first_diff >= steps // 2
+
+
+@pytest.mark.parametrize("B", [1, 3, 6, 20])
+def test_vllm_cache_layout_gives_the_same_step(cuda_device, B):
+    """The same step on a [blocks, kv_heads, 16, 128] cache and on vLLM's [2, blocks, 16, kv_heads, 64] planes with
+    the same contents: every kernel reads the cache through strides (the tensor-core kernel's bulk copies fall back
+    to one 128-byte copy per row), so hidden states, logits and the appended rows agree (bit-equal on the CUDA-core
+    kernels, within the bf16 tolerance on the tensor-core kernel whose split-K sums meet in a run-dependent order)."""
+    from prime_kernels_b200 import decode as D
+
+    geom = D.Geometry("layouts", 192, 512, 2, 3, 1, 1024)
+    wd = harness.weights_to(harness.make_weights(geom, 9, norm_weights="random"), cuda_device)
+    csd = harness.make_cos_sin_cache(geom, 256, cuda_device)
+    ctx = 77
+    kv = harness.PagedKV(geom, B, 256, cuda_device, shuffle=True, seed=2)
+    g2 = torch.Generator().manual_seed(4)
+    for cache in kv.kv_caches:
+        cache.copy_(torch.randn(cache.shape, generator=g2).to(torch.bfloat16))
+    # the same contents as K / V planes: [blocks, kvh, bs, 128] -> [2, blocks, bs, kvh, 64]
+    planes = [torch.stack([c[..., :64], c[..., 64:]]).permute(0, 1, 3, 2, 4).contiguous() for c in kv.kv_caches]
+    pos = torch.full((B,), ctx, dtype=torch.int64, device=cuda_device)
+    ids = (torch.arange(B) * 91 % geom.vocab).to(cuda_device)
+    outs = []
+    for caches in (kv.kv_caches, planes):
+        hid, logits, nxt = D.decode_step(geom, input_ids=ids, positions=pos, seq_lens=(pos + 1).to(torch.int32),
+                                         block_table=kv.block_table, slot_mapping=kv.slots(pos), embed=wd["embed"],
+                                         layers=wd["layers"], final_norm=wd["final_norm"], kv_caches=caches,
+                                         cos_sin_cache=csd, eps=geom.eps, lm_head=True)
+        D.check_status(geom, cuda_device)
+        outs.append((hid.clone(), logits.clone()))
+    if B < 4:
+        assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    else:
+        assert (outs[0][1].float() - outs[1][1].float()).abs().max() <= LOGIT_TOL
+        assert (outs[0][0].float() - outs[1][0].float()).abs().max() <= 2 ** -4
+    # the appended row went to the same slot of both layouts
+    blk = kv.block_table[:, ctx // 16].long()
+    for l in range(geom.layers):
+        a = kv.kv_caches[l][blk, :, ctx % 16, :]                                  # [B, kvh, 128]
+        b = torch.cat([planes[l][0][blk, ctx % 16], planes[l][1][blk, ctx % 16]], -1)   # [B, kvh, 128]
+        if B < 4:
+            assert torch.equal(a, b)
+        else:
+            assert (a.float() - b.float()).abs().max() <= 2 ** -5
+
+
+def test_alternating_batch_sizes_on_one_workspace(cuda_device):
+    """One geometry, one workspace, launches of changing batch size (tensor-core kernel with N = 16 / 32 / 64, CUDA-core
+    kernels of batch 1, 2, 3): the tensor-core kernel's fp32 sums must be zero when a launch starts, so its buffers
+    may not move with the batch, and the CUDA-core kernels' buffers (whose offsets depend on the kernel batch) are
+    re-zeroed when they move.  Every step is checked against the restatement."""
+    from prime_kernels_b200 import decode as D
+
+    geom = D.Geometry("alternate", 192, 512, 2, 3, 1, 1024)
+    w = harness.make_weights(geom, 13, norm_weights="random")
+    wd = harness.weights_to(w, cuda_device)
+    cs = harness.make_cos_sin_cache(geom, 128)
+    csd = cs.to(cuda_device)
+    gen = torch.Generator().manual_seed(3)
+    for B in (16, 17, 5, 33, 2, 1, 64, 3, 20, 1, 16):
+        ctxs = [11 + (7 * b) % 40 for b in range(B)]
+        keys = [[torch.randn(geom.kv_heads, c, 64, generator=gen).to(torch.bfloat16) for c in ctxs] for _ in range(geom.layers)]
+        vals = [[torch.randn(geom.kv_heads, c, 64, generator=gen).to(torch.bfloat16) for c in ctxs] for _ in range(geom.layers)]
+        kv = harness.PagedKV(geom, B, 128, cuda_device, shuffle=True, seed=B)
+        for layer in range(geom.layers):
+            for b, c in enumerate(ctxs):
+                kvb = torch.cat([keys[layer][b], vals[layer][b]], -1).to(cuda_device)
+                for t0 in range(0, c, 16):
+                    n = min(16, c - t0)
+                    kv.kv_caches[layer][int(kv.block_table[b, t0 // 16]), :, :n, :] = kvb[:, t0:t0 + n, :]
+        cur = torch.randint(0, geom.vocab, (B,), generator=gen)
+        pos = torch.tensor(ctxs, dtype=torch.int64)
+        hid, logits, nxt = D.decode_step(geom, input_ids=cur.to(cuda_device), positions=pos.to(cuda_device),
+                                         seq_lens=(pos + 1).to(torch.int32).to(cuda_device), block_table=kv.block_table,
+                                         slot_mapping=kv.slots(pos), embed=wd["embed"], layers=wd["layers"],
+                                         final_norm=wd["final_norm"], kv_caches=kv.kv_caches, cos_sin_cache=csd,
+                                         eps=geom.eps, lm_head=True)
+        D.check_status(geom, cuda_device)
+        rh, rl, _ = R.decode_step(geom, w, cur, pos, keys, vals, cs)
+        assert (logits.cpu().float() - rl).abs().max() <= LOGIT_TOL, f"batch {B}"
+        assert (hid.cpu().float() - rh.float()).abs().max() <= 2 ** -4, f"batch {B}"

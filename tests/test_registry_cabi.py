@@ -61,7 +61,7 @@ def test_status_strings_and_sizes_without_a_device():
     assert lib.pk_rmsnorm_scale_bytes(1, 960) == 8 * 512
     assert lib.pk_rmsnorm_scale_bytes(8192, 4096) == 64 * 32 * 512
     assert lib.mk_workspace_bytes(1, 2048) == lib.mk_workspace_bytes(8, 8192) > 0
-    assert lib.decode360_workspace_bytes() > lib.mk_workspace_bytes(1, 1)
+    assert lib.decode360_workspace_bytes() > 0
     m = _cabi.PkDecodeModel(960, 2560, 32, 15, 5, 49152, 0, 1e-5)
     # from 4 requests on the workspace also holds the tensor-core kernel's region, behind the CUDA-core kernels' one
     assert lib.pk_decode_workspace_bytes(ctypes.byref(m), 8) > lib.decode360_workspace_bytes()
