@@ -123,14 +123,15 @@ size_t pk_decode_workspace_bytes(const PkDecodeModel* model, int max_batch);
  * 16 / 32 / 64, accumulators in tensor memory, every weight streamed once per step. */
 int pk_decode_step(const PkDecodeModel* model, const PkDecodeArgs* args);
 /* Same step on the tensor-core kernel whatever the batch (1..64); pk_decode_step picks it by itself from
- * pk_decode_set_tc_min_batch requests on (default 4: measured faster than the CUDA-core kernels from there) when the
+ * pk_decode_set_tc_min_batch requests on (default: the measured cross-over, 4 requests, 2 for hidden >= 2048) when the
  * workspace has pk_decode_workspace_bytes(model, n >= 4) bytes, and always above 8.  No counterpart in the reference
  * (its decode kernels have no tensor-core path beyond wmma at batch 2,
  * prime_kernels/decode_megakernel_360m/csrc/block360.cu:312-364).  One workspace serves all kernels. */
 int pk_decode_step_tc(const PkDecodeModel* model, const PkDecodeArgs* args);
 /* Same step on the CUDA-core kernels only (1..8 requests). */
 int pk_decode_step_cc(const PkDecodeModel* model, const PkDecodeArgs* args);
-/* Smallest batch pk_decode_step and mk_decode hand to the tensor-core kernel (1..9; 9 = only above 8 requests). */
+/* Smallest batch pk_decode_step and mk_decode hand to the tensor-core kernel (1..9; 9 = only above 8 requests;
+ * 0 = the default, the measured cross-over: 2 requests for hidden >= 2048, else 4). */
 void pk_decode_set_tc_min_batch(int n);
 /* Zero a workspace in stream order (also done implicitly the first time a pointer is seen). */
 int pk_decode_workspace_init(void* workspace, size_t bytes, void* stream);

@@ -1809,7 +1809,7 @@ static std::unordered_map<const void*, WsState> g_ws_ready;     // workspace poi
 // largest dynamic shared memory opted in, per (device, kernel): the attribute belongs to the device's context
 static std::unordered_map<unsigned long long, int> g_kernel_smem;
 static unsigned g_spin_limit = kSpinLimit;
-static int g_tc_min_batch = 4;       // pk_decode_step hands launches of this many requests or more to the tensor-core kernel
+static int g_tc_min_batch = 0;       // smallest batch pk_decode_step hands to the tensor-core kernel; 0: by model size (below)
 static int g_fast_warps = -1;        // batch-1 fast path: -1 = not decided yet (environment), 0 = off, 7 / 8 = consumer warps per CTA
 
 static unsigned long long geom_sig(const ModelGeom& g) {
@@ -2185,8 +2185,11 @@ static int batched_launch(const ModelGeom& g, const StepArgs& a, const DeviceInf
 static int decode_launch(const ModelGeom& g, const StepArgs& a) {
     if (a.B < 1 || a.B > batched::kMaxReq) return kErrBatch;
     if (a.path == 2 && a.B > kMaxB) return kErrBatch;
+    // measured cross-over: 4 requests for the small models, 2 where a layer's weights are large enough to hide the
+    // grid barriers (hidden >= 2048: SmolLM2-1.7B)
+    const int tc_min = g_tc_min_batch > 0 ? g_tc_min_batch : (g.H >= 2048 ? 2 : 4);
     const bool tc = a.path == 1 || a.B > kMaxB ||
-                    (a.path == 0 && a.B >= g_tc_min_batch && batched_eligible(g) && a.ws_bytes >= batched_ws_bytes(g, a.B));
+                    (a.path == 0 && a.B >= tc_min && batched_eligible(g) && a.ws_bytes >= batched_ws_bytes(g, a.B));
     if (tc) {
         // the tensor-core kernel: always from 9 requests on, from g_tc_min_batch on when the geometry and the
         // workspace allow it (same argument checks as below)
@@ -2377,10 +2380,10 @@ static ModelGeom to_geom(const PkDecodeModel* m) {
 
 extern "C" size_t pk_decode_workspace_bytes(const PkDecodeModel* m, int max_batch) {
     if (!m || max_batch < 1 || max_batch > batched::kMaxReq || m->kv_heads <= 0) return 0;
-    // up to 3 requests only the CUDA-core kernels run; from 4 on the workspace also holds the tensor-core kernel's
-    // region (behind the CUDA-core kernels' batch-8 region, which batches 5..7 need anyway)
+    // below the tensor-core cross-over (4 requests; 2 for hidden >= 2048) only the CUDA-core kernels run; from there on
+    // the workspace also holds the tensor-core kernel's region (behind the CUDA-core kernels' batch-8 region, which batches 5..7 need anyway)
     const ModelGeom g = to_geom(m);
-    if (max_batch < 4) return ws_layout(g, max_batch).total;
+    if (max_batch < (g.H >= 2048 ? 2 : 4)) return ws_layout(g, max_batch).total;
     return batched_ws_bytes(g, max_batch);
 }
 
@@ -2420,8 +2423,9 @@ extern "C" int pk_decode_step_cc(const PkDecodeModel* m, const PkDecodeArgs* a) 
     return decode_launch(to_geom(m), s);
 }
 
-// Smallest batch pk_decode_step / mk_decode hand to the tensor-core kernel (default 4; 9 = only above 8 requests).
-extern "C" void pk_decode_set_tc_min_batch(int n) { g_tc_min_batch = n < 1 ? 1 : (n > kMaxB + 1 ? kMaxB + 1 : n); }
+// Smallest batch pk_decode_step / mk_decode hand to the tensor-core kernel (1..9; 9 = only above 8 requests;
+// 0 = the default: 2 for hidden >= 2048, else 4).
+extern "C" void pk_decode_set_tc_min_batch(int n) { g_tc_min_batch = n < 0 ? 0 : (n > kMaxB + 1 ? kMaxB + 1 : n); }
 
 // Zero a workspace in stream order and mark it ready (also done implicitly on first use).
 extern "C" int pk_decode_workspace_init(void* workspace, size_t bytes, void* stream) {

@@ -37,14 +37,22 @@ def _decode_step_fake(input_ids, positions, seq_lens, block_table, slot_mapping,
     return 0
 
 
-_tc_min_batch = 4      # batches from here on run on the tensor-core kernel (measured faster from 4 requests)
+_tc_min_batch = 0      # batches from here on run on the tensor-core kernel; 0: the measured cross-over (tc_min_batch)
+
+
+def tc_min_batch(geometry: Geometry) -> int:
+    """Smallest batch that runs on the tensor-core kernel: 4 requests, 2 where a layer's weights are large enough to
+    hide the kernel's grid barriers (hidden >= 2048: SmolLM2-1.7B), unless ``set_tensor_core_min_batch`` overrides."""
+    if _tc_min_batch > 0:
+        return _tc_min_batch
+    return 2 if geometry.hidden >= 2048 else 4
 
 
 def set_tensor_core_min_batch(n: int) -> None:
     """Smallest batch ``decode_step`` (and the C entries pk_decode_step / mk_decode) hand to the tensor-core kernel;
-    ``MAX_BATCH + 1`` keeps batches up to 8 on the CUDA-core kernels."""
+    ``MAX_BATCH + 1`` keeps batches up to 8 on the CUDA-core kernels, 0 restores the default (``tc_min_batch``)."""
     global _tc_min_batch
-    _tc_min_batch = max(1, min(int(n), MAX_BATCH + 1))
+    _tc_min_batch = max(0, min(int(n), MAX_BATCH + 1))
     library().pk_decode_set_tc_min_batch(_tc_min_batch)
 
 
@@ -274,7 +282,7 @@ def decode_step(geometry: Geometry, *, input_ids, positions, seq_lens, block_tab
             return rt.out[:batch], logits[:batch], next_ids[:batch]
         return rt.out[:batch]
 
-    if tensor_cores == "force" or (tensor_cores and (batch >= _tc_min_batch or batch > MAX_BATCH or batch > rt.group)):
+    if tensor_cores == "force" or (tensor_cores and (batch >= tc_min_batch(geometry) or batch > MAX_BATCH or batch > rt.group)):
         return tensor_core_launch()
     # A launch of the CUDA-core kernels takes up to rt.group requests (MAX_BATCH, fewer when the geometry's activation
     # staging does not fit shared memory at that batch: status 9111 / 9105 lowers the group once and for all).

@@ -38,7 +38,7 @@ def _cuda_core_kernels_up_to_8_requests(cuda_device):
 
     D.set_tensor_core_min_batch(D.MAX_BATCH + 1)
     yield
-    D.set_tensor_core_min_batch(4)
+    D.set_tensor_core_min_batch(0)
 
 
 def _step(D, geom, wd, kv, csd, cur, pos, lm_head=True, layer_outputs=None):
