@@ -424,18 +424,15 @@ def main():
         step = D.HostStep(geom, batch, embed=weights["embed"], layers=weights["layers"], final_norm=weights["final_norm"],
                           kv_caches=kv2.kv_caches, cos_sin_cache=cos_sin, block_table=kv2.block_table,
                           embed_lookup=weights.get("embed_lookup"))
-        bt_host = kv2.block_table.cpu()
-        cur = prompt[:, -1].clone()
+        # host side of a serving loop: block table and current ids as numpy arrays, slots computed on the CPU
+        bt_host = kv2.block_table.cpu().numpy().astype("int64")
+        cur = prompt[:, -1].clone().numpy()
         pos0 = prompt_len - 1
-        h_pos = torch.empty(batch, dtype=torch.int64)
-        h_seq = torch.empty(batch, dtype=torch.int32)
 
         def e2e_step(t):
             pos = pos0 + t
-            h_pos.fill_(pos)
-            h_seq.fill_(pos + 1)
-            nxt = step(cur, h_pos, h_seq, bt_host[:batch, pos // 16].to(torch.int64) * 16 + pos % 16)
-            cur.copy_(nxt)
+            nxt = step.step_numpy(cur, pos, pos + 1, bt_host[:batch, pos // 16] * 16 + pos % 16)
+            cur[:] = nxt
 
         for t in range(W):
             e2e_step(t)

@@ -406,6 +406,9 @@ class HostStep:
             torch.cuda.current_stream(dev).wait_stream(side)
             torch.cuda.synchronize(dev)
             self.graph = g
+        self._stream = torch.cuda.current_stream(dev)
+        # numpy views of the pinned buffers (ids, positions, slots, sequence lengths, next ids)
+        self._np = (self.h_ids.numpy(), self.h_pos.numpy(), self.h_slot.numpy(), self.h_seq.numpy(), self.h_next.numpy())
 
     def _views(self, buf):
         b = self.batch
@@ -418,14 +421,30 @@ class HostStep:
         self.h_next.copy_(nxt, non_blocking=True)
 
     def __call__(self, ids, positions, seq_lens, slot_mapping):
+        """Step inputs as host tensors ``[B]``; returns the greedy next ids (pinned host tensor, int64)."""
         self.h_ids.copy_(ids)
         self.h_pos.copy_(positions)
         self.h_seq.copy_(seq_lens)
         self.h_slot.copy_(slot_mapping)
+        return self._run()
+
+    def step_numpy(self, ids, positions, seq_lens, slot_mapping):
+        """Same step with the inputs as numpy arrays, sequences or scalars (broadcast over the batch), written straight
+        into the pinned staging buffer: no tensor dispatch on the host side of a serving loop.  Returns the greedy
+        next ids as a numpy view ``[B]`` (int64) of the pinned result buffer."""
+        n = self._np
+        n[0][:] = ids
+        n[1][:] = positions
+        n[2][:] = slot_mapping
+        n[3][:] = seq_lens
+        self._run()
+        return n[4]
+
+    def _run(self):
         if self.graph is not None:
             self.graph.replay()
         else:
             self._enqueue()
-        torch.cuda.current_stream(self.device).synchronize()
+        self._stream.synchronize()
         return self.h_next
 

@@ -703,6 +703,22 @@ def test_host_driven_step_matches_device_driven_generation(cuda_device, graph):
         cur = nxt.clone()
     assert torch.equal(torch.stack(got), want)
     D.check_status(geom, cuda_device)
+    # the numpy entry (inputs written straight into the pinned staging buffer) on a fresh copy of the cache
+    kv3 = harness.PagedKV(geom, B, 128, cuda_device, shuffle=True, seed=1)
+    g3 = torch.Generator().manual_seed(4)
+    for l in range(geom.layers):
+        kv3.kv_caches[l].copy_((torch.randn(kv3.kv_caches[l].shape, generator=g3) * 0.5).to(torch.bfloat16).to(cuda_device))
+    step3 = D.HostStep(geom, B, embed=wd["embed"], layers=wd["layers"], final_norm=wd["final_norm"],
+                       kv_caches=kv3.kv_caches, cos_sin_cache=csd, block_table=kv3.block_table, graph=graph)
+    bt3 = kv3.block_table.cpu().numpy().astype("int64")
+    cur3, got3 = first.numpy().copy(), []
+    for t in range(steps):
+        pos = ctx + t
+        nxt = step3.step_numpy(cur3, pos, pos + 1, bt3[:, pos // 16] * 16 + pos % 16)
+        got3.append(torch.from_numpy(nxt.copy()))
+        cur3[:] = nxt
+    assert torch.equal(torch.stack(got3), want)
+    D.check_status(geom, cuda_device)
 
 
 def test_wide_geometry_falls_back_to_smaller_launch_groups(cuda_device):
