@@ -37,7 +37,8 @@ struct Widths {
     static constexpr int H = H_, I = I_, QH = QH_, KVH = KVH_, G = QH_ / KVH_;
     static constexpr int NQKV = (QH_ + 2 * KVH_) * kD;
     static constexpr int AD = QH_ * kD;                           // attention output width (K of the O projection)
-    static constexpr int NC = ((kNominalCtas - QH_) / KVH_) < 8 ? ((kNominalCtas - QH_) / KVH_) : 8;   // max chunks per kv head
+    // max chunks per kv head: a chunk is one run of 16 positions per warp up to 16 x NW x NC positions, longer beyond
+    static constexpr int NC = ((kNominalCtas - QH_) / KVH_) < 16 ? ((kNominalCtas - QH_) / KVH_) : 16;
     static_assert(QH_ % KVH_ == 0 && H_ % 32 == 0 && I_ % 32 == 0, "unsupported widths");
 };
 
@@ -50,7 +51,8 @@ __host__ __device__ constexpr int attn_words() {
 struct FastParams {
     const unsigned long long* layers;   // device table [L][6]
     const unsigned long long* kv;       // device table [L]
-    const uint16_t* embed;              // [V, H] bf16 (tied lm_head)
+    const void* embed;                  // lm_head matrix: [V, H] bf16, or packed MXFP8 rows
+    const uint16_t* embed_bf16;         // [V, H] bf16 rows for the input look-up (= embed for bf16 weights)
     const uint16_t* final_norm;
     const void* input_ids;
     const long long* positions;
@@ -274,14 +276,18 @@ struct Ph<W, NW, kDown> { static constexpr int K = W::I, WIDX = 5, PAIR = 0, RPE
 template <class W, int NW>
 struct Ph<W, NW, kLM> { static constexpr int K = W::H, WIDX = -1, PAIR = 0, RPE = (NW >= 12 ? 2 : 4); };
 
-template <class W, int NW>
+// bytes of one stored weight row: bf16, or packed MXFP8 ([K e4m3][K/32 e8m0], padded to 16 bytes)
+template <int WF>
+__host__ __device__ constexpr int fast_row_bytes(int K) { return WF ? ((K + K / 32 + 15) & ~15) : K * 2; }
+
+template <class W, int NW, int WF>
 __device__ __forceinline__ void phase_consts(int t, int& rowbytes, int& rpe, int& widx) {
     switch (t) {
-        case kQKV: rowbytes = Ph<W, NW, kQKV>::K * 2; rpe = Ph<W, NW, kQKV>::RPE; widx = Ph<W, NW, kQKV>::WIDX; break;
-        case kO: rowbytes = Ph<W, NW, kO>::K * 2; rpe = Ph<W, NW, kO>::RPE; widx = Ph<W, NW, kO>::WIDX; break;
-        case kGU: rowbytes = Ph<W, NW, kGU>::K * 2; rpe = Ph<W, NW, kGU>::RPE; widx = Ph<W, NW, kGU>::WIDX; break;
-        case kDown: rowbytes = Ph<W, NW, kDown>::K * 2; rpe = Ph<W, NW, kDown>::RPE; widx = Ph<W, NW, kDown>::WIDX; break;
-        default: rowbytes = Ph<W, NW, kLM>::K * 2; rpe = Ph<W, NW, kLM>::RPE; widx = Ph<W, NW, kLM>::WIDX; break;
+        case kQKV: rowbytes = fast_row_bytes<WF>(Ph<W, NW, kQKV>::K); rpe = Ph<W, NW, kQKV>::RPE; widx = Ph<W, NW, kQKV>::WIDX; break;
+        case kO: rowbytes = fast_row_bytes<WF>(Ph<W, NW, kO>::K); rpe = Ph<W, NW, kO>::RPE; widx = Ph<W, NW, kO>::WIDX; break;
+        case kGU: rowbytes = fast_row_bytes<WF>(Ph<W, NW, kGU>::K); rpe = Ph<W, NW, kGU>::RPE; widx = Ph<W, NW, kGU>::WIDX; break;
+        case kDown: rowbytes = fast_row_bytes<WF>(Ph<W, NW, kDown>::K); rpe = Ph<W, NW, kDown>::RPE; widx = Ph<W, NW, kDown>::WIDX; break;
+        default: rowbytes = fast_row_bytes<WF>(Ph<W, NW, kLM>::K); rpe = Ph<W, NW, kLM>::RPE; widx = Ph<W, NW, kLM>::WIDX; break;
     }
 }
 
@@ -298,7 +304,7 @@ __device__ __forceinline__ void warp_share(int nrows, int cta, int ncta, int war
 // order (4 phases per layer, then the lm_head), in closed form from the row shares.  All lanes run the same
 // loop; every iteration a lane retires up to two consumed entries (non-blocking probes) and issues up to two
 // new ones if its ring has room.  Nothing here waits on a consumer, so one slow ring never stalls the others.
-template <class W, int NW>
+template <class W, int NW, int WF>
 __device__ void producer_loop(const FastParams& p, FShared<NW>& sh, unsigned char* ring_base, int lane) {
     const bool active = lane < NW;
     const int w = active ? lane : 0;
@@ -340,7 +346,7 @@ __device__ void producer_loop(const FastParams& p, FShared<NW>& sh, unsigned cha
         for (int r = 0; r < 2; ++r) {
             if (more) {
                 int rowbytes, rpe, widx;
-                phase_consts<W, NW>(t, rowbytes, rpe, widx);
+                phase_consts<W, NW, WF>(t, rowbytes, rpe, widx);
                 const int nre = min(rpe, sh.row_b[t][w] - row);
                 const uint32_t part = (uint32_t)(nre * rowbytes);
                 const bool pair = t == kGU || t == kQKV;
@@ -419,10 +425,43 @@ __device__ __forceinline__ void gemv_rows(const uint4* ep, const uint4* act, int
     for (int r = 0; r < NR; ++r) v[r] = acc[r] + acc2[r];
 }
 
+// The same for packed MXFP8 rows ([K e4m3][K/32 e8m0][pad]): a 16-byte chunk is 16 weights against two activation
+// chunks; the chunk's partial sum is scaled by its E8M0 (one per 32 along K, i.e. per two chunks) - exact
+// de-quantisation, fp32 accumulation.
+template <int K, int NR, int RB>
+__device__ __forceinline__ void gemv_rows_fp8(const uint4* ep, const uint4* act, int lane, int nlive, float (&v)[8]) {
+    constexpr int KC = K / 16;
+    constexpr int IT = (KC + 31) / 32;
+    float acc[NR], acc2[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) acc[r] = acc2[r] = 0.f;
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+        const int ch = it * 32 + lane;
+        const bool ok = (it + 1) * 32 <= KC || ch < KC;
+        const uint4 a0 = ok ? act[2 * ch] : make_uint4(0u, 0u, 0u, 0u);
+        const uint4 a1 = ok ? act[2 * ch + 1] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            if (ok && r < nlive) {
+                const unsigned char* row = reinterpret_cast<const unsigned char*>(ep) + r * RB;
+                const uint4 wq = *reinterpret_cast<const uint4*>(row + ch * 16);
+                const uint32_t sb = row[K + (ch >> 1)];
+                const float scale = __uint_as_float(sb ? (sb << 23) : 0x00400000u);
+                const float part = dot16_e4m3(wq, a0, a1, 0.f);
+                if (it & 1) acc2[r] = fmaf(scale, part, acc2[r]);
+                else acc[r] = fmaf(scale, part, acc[r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) v[r] = acc[r] + acc2[r];
+}
+
 // One GEMV phase of one warp: its ring entries of phase type t at `layer`.  One body for all phase types
 // (run-time t) so that the wait, the reduction and the ring refill exist once in the instruction stream;
 // only the dot products (compile-time K) and the epilogues are switched.
-template <class W, int NW>
+template <class W, int NW, int WF>
 __device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, const uint4* act, const float* res) {
     const FastParams& p = c.p;
     FShared<NW>& sh = c.sh;
@@ -430,7 +469,7 @@ __device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, co
     const int ra = sh.row_a[t][w], rb = sh.row_b[t][w];
     const int par = layer & 1;
     int rowbytes, rpe, widx;
-    phase_consts<W, NW>(t, rowbytes, rpe, widx);
+    phase_consts<W, NW, WF>(t, rowbytes, rpe, widx);
     uint32_t best = 0u;      // lm_head: bf16 order key << 16 | (0xffff - local row)
 #pragma unroll 1
     for (int row = ra; row < rb; row += rpe) {
@@ -444,12 +483,26 @@ __device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, co
         }
         const uint4* ep = reinterpret_cast<const uint4*>(c.ring + eoff);
         float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        switch (t) {
-            case kQKV: gemv_rows<Ph<W, NW, kQKV>::K / 8, 2 * Ph<W, NW, kQKV>::RPE>(ep, act, lane, 2 * nre, v); break;
-            case kO: gemv_rows<Ph<W, NW, kO>::K / 8, Ph<W, NW, kO>::RPE>(ep, act, lane, nre, v); break;
-            case kGU: gemv_rows<Ph<W, NW, kGU>::K / 8, 2 * Ph<W, NW, kGU>::RPE>(ep, act, lane, 2 * nre, v); break;
-            case kDown: gemv_rows<Ph<W, NW, kDown>::K / 8, Ph<W, NW, kDown>::RPE>(ep, act, lane, nre, v); break;
-            default: gemv_rows<Ph<W, NW, kLM>::K / 8, Ph<W, NW, kLM>::RPE>(ep, act, lane, nre, v); break;
+        if constexpr (WF == 0) {
+            switch (t) {
+                case kQKV: gemv_rows<Ph<W, NW, kQKV>::K / 8, 2 * Ph<W, NW, kQKV>::RPE>(ep, act, lane, 2 * nre, v); break;
+                case kO: gemv_rows<Ph<W, NW, kO>::K / 8, Ph<W, NW, kO>::RPE>(ep, act, lane, nre, v); break;
+                case kGU: gemv_rows<Ph<W, NW, kGU>::K / 8, 2 * Ph<W, NW, kGU>::RPE>(ep, act, lane, 2 * nre, v); break;
+                case kDown: gemv_rows<Ph<W, NW, kDown>::K / 8, Ph<W, NW, kDown>::RPE>(ep, act, lane, nre, v); break;
+                default: gemv_rows<Ph<W, NW, kLM>::K / 8, Ph<W, NW, kLM>::RPE>(ep, act, lane, nre, v); break;
+            }
+        } else {
+            constexpr int nq = 2 * Ph<W, NW, kQKV>::RPE, no = Ph<W, NW, kO>::RPE, ng = 2 * Ph<W, NW, kGU>::RPE,
+                          nd = Ph<W, NW, kDown>::RPE, nl = Ph<W, NW, kLM>::RPE;
+            constexpr int kq = Ph<W, NW, kQKV>::K, ko = Ph<W, NW, kO>::K, kg = Ph<W, NW, kGU>::K, kd = Ph<W, NW, kDown>::K,
+                          kl = Ph<W, NW, kLM>::K;
+            switch (t) {
+                case kQKV: gemv_rows_fp8<kq, nq, fast_row_bytes<1>(kq)>(ep, act, lane, 2 * nre, v); break;
+                case kO: gemv_rows_fp8<ko, no, fast_row_bytes<1>(ko)>(ep, act, lane, nre, v); break;
+                case kGU: gemv_rows_fp8<kg, ng, fast_row_bytes<1>(kg)>(ep, act, lane, 2 * nre, v); break;
+                case kDown: gemv_rows_fp8<kd, nd, fast_row_bytes<1>(kd)>(ep, act, lane, nre, v); break;
+                default: gemv_rows_fp8<kl, nl, fast_row_bytes<1>(kl)>(ep, act, lane, nre, v); break;
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh.empty[w][slot]);      // every lane's loads of this entry have been consumed
@@ -540,7 +593,7 @@ __device__ __forceinline__ void stage_norm(FC<NW>& c, const uint32_t* src_words,
 #pragma unroll
         for (int u = 0; u < PPT; ++u) {
             const int pk = tid + u * NT;
-            const uint2 e = pk < NP ? __ldg(reinterpret_cast<const uint2*>(c.p.embed + (size_t)sh.tok * W::H) + pk)
+            const uint2 e = pk < NP ? __ldg(reinterpret_cast<const uint2*>(c.p.embed_bf16 + (size_t)sh.tok * W::H) + pk)
                                     : make_uint2(0u, 0u);
             x[u][0] = bf16_lo(e.x); x[u][1] = bf16_hi(e.x);
             x[u][2] = bf16_lo(e.y); x[u][3] = bf16_hi(e.y);
@@ -903,7 +956,7 @@ __device__ __forceinline__ void attention_item(FC<NW>& c, int layer, const int w
 }
 
 // ------------------------------------------------------------------ the kernel
-template <class W, int NW>
+template <class W, int NW, int WF>
 __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const FastParams p) {
     constexpr int NT = (NW + 1) * 32;      // NW consumer warps + the producer warp
     constexpr int NTC = NW * 32;           // consumer threads
@@ -989,7 +1042,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const Fas
     c.T16 = ((sh.epoch % 511u) + 1u) << 23;
     c.T32 = (sh.epoch + 1u) << 7;
     if (warp == NW) {
-        producer_loop<W, NW>(p, sh, ring_base, lane);
+        producer_loop<W, NW, WF>(p, sh, ring_base, lane);
     } else {
 
     // block-table look-ups of this CTA's attention item do not depend on the layer: resolve them once
@@ -1093,7 +1146,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const Fas
                     reinterpret_cast<uint32_t*>(p.out_hidden)[i] = reinterpret_cast<const uint32_t*>(act0)[i];
             if (!p.lm_head) break;
         }
-        gemv_phase<W, NW>(c, t, layer, act, res);
+        gemv_phase<W, NW, WF>(c, t, layer, act, res);
         // Nobody in this CTA polls the next hand-off before the CTA's own results are on their way: reads of a
         // line that is still being written slow the writes down (measured: several microseconds per hand-off
         // when the warps without rows in a phase started polling at once).

@@ -1698,7 +1698,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 static int fast_nc(const ModelGeom& g) {
     const int nc = (fast::kNominalCtas - g.QH) / (g.KVH > 0 ? g.KVH : 1);      // Widths::NC
-    return nc < 8 ? nc : 8;
+    return nc < 16 ? nc : 16;
 }
 
 static FastLayout fast_layout(const ModelGeom& g) {
@@ -1989,7 +1989,7 @@ static int fast_warps() {
     return g_fast_warps;
 }
 
-template <class W, int NW>
+template <class W, int NW, int WF>
 static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo& di, const WsLayout& lay) {
     using namespace fast;
     // the attention items take the first NC * KVH CTAs, the head merges the last QH
@@ -2001,13 +2001,13 @@ static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo
     if ((size_t)di.smem_optin < fixed + (size_t)NW * 4096) return kFastNotEligible;
     const int rw = (int)(((size_t)di.smem_optin - fixed) / NW / 128 * 128);
     // every entry must fit the ring (an empty ring restarts at its base)
-#define PK_ENT(T) (Ph<W, NW, T>::K * 2 * Ph<W, NW, T>::RPE * (Ph<W, NW, T>::PAIR ? 2 : 1))
+#define PK_ENT(T) (fast_row_bytes<WF>(Ph<W, NW, T>::K) * Ph<W, NW, T>::RPE * (Ph<W, NW, T>::PAIR ? 2 : 1))
     const int ent[5] = {PK_ENT(kQKV), PK_ENT(kO), PK_ENT(kGU), PK_ENT(kDown), PK_ENT(kLM)};
 #undef PK_ENT
     for (int t = 0; t < 5; ++t)
         if (ent[t] > rw) return kFastNotEligible;
     const size_t smem = fixed + (size_t)NW * rw;
-    auto fn = decode_fast_kernel<W, NW>;
+    auto fn = decode_fast_kernel<W, NW, WF>;
     int rc = ensure_smem(reinterpret_cast<const void*>(fn), smem);
     if (rc) return rc;
     rc = ensure_workspace(a.ws, a.ws_bytes, lay.total, g, a.stream, 1);      // the batch-1 layout
@@ -2019,7 +2019,8 @@ static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo
     FastParams p{};
     p.layers = static_cast<const unsigned long long*>(a.layers);
     p.kv = static_cast<const unsigned long long*>(a.kv);
-    p.embed = static_cast<const uint16_t*>(a.embed);
+    p.embed = a.embed;
+    p.embed_bf16 = static_cast<const uint16_t*>(a.embed_lookup ? a.embed_lookup : a.embed);
     p.final_norm = static_cast<const uint16_t*>(a.final_norm);
     p.input_ids = a.input_ids;
     p.positions = static_cast<const long long*>(a.positions);
@@ -2077,8 +2078,13 @@ static int fast_launch(const ModelGeom& g, const StepArgs& a, const DeviceInfo& 
     using W360 = fast::Widths<960, 2560, 15, 5>;
     const bool is135 = g.H == 576 && g.I == 1536 && g.QH == 9 && g.KVH == 3;
     const bool is360 = g.H == 960 && g.I == 2560 && g.QH == 15 && g.KVH == 5;
-    if (is135) return nw == 8 ? fast_launch_t<W135, 8>(g, a, di, lay) : fast_launch_t<W135, 7>(g, a, di, lay);
-    if (is360) return nw == 8 ? fast_launch_t<W360, 8>(g, a, di, lay) : fast_launch_t<W360, 7>(g, a, di, lay);
+    if (g.wfmt) {       // MXFP8 weights: seven consumer warps only
+        if (is135) return fast_launch_t<W135, 7, 1>(g, a, di, lay);
+        if (is360) return fast_launch_t<W360, 7, 1>(g, a, di, lay);
+        return kFastNotEligible;
+    }
+    if (is135) return nw == 8 ? fast_launch_t<W135, 8, 0>(g, a, di, lay) : fast_launch_t<W135, 7, 0>(g, a, di, lay);
+    if (is360) return nw == 8 ? fast_launch_t<W360, 8, 0>(g, a, di, lay) : fast_launch_t<W360, 7, 0>(g, a, di, lay);
     return kFastNotEligible;
 }
 
@@ -2245,7 +2251,9 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
     if (di.major != 10) return kErrArch;
     if (!di.coop) return kErrCoop;
 
-    if (a.B == 1 && g.wfmt == 0 && (!a.embed_lookup || a.embed_lookup == a.embed)) {
+    // batch 1: the kernel specialised for the SmolLM2-135M / 360M widths (bf16 weights with the tied embedding as
+    // lm_head, or MXFP8 weights with the bf16 embedding rows given separately)
+    if (a.B == 1 && ((g.wfmt == 0 && (!a.embed_lookup || a.embed_lookup == a.embed)) || (g.wfmt == 1 && a.embed_lookup))) {
         rc = fast_launch(g, a, di, lay);
         if (rc != kFastNotEligible) return rc;
     }

@@ -213,3 +213,56 @@ def test_padded_row_and_sequence_overflow(cuda_device, warps):
     D.check_status(geom, cuda_device)
     assert torch.isfinite(hid.float()).all()
     assert not torch.equal(kv.kv_caches[0], before[0])
+
+
+@pytest.mark.parametrize("which,ctx", [("360m", 0), ("360m", 77), ("360m", 1200), ("135m", 300)])
+def test_fast_kernel_with_mxfp8_weights(cuda_device, which, ctx):
+    """MXFP8 weights (E4M3 + one E8M0 per 32 along K, de-quantised in registers inside the GEMV) on the batch-1
+    kernel: against the restatement on the exactly de-quantised weights, and against the generic kernel of this
+    library on the same packed weights, over three teacher-forced steps with alternating lm_head."""
+    from prime_kernels_b200 import decode as D
+
+    h, i, qh, kvh = WIDTHS[which]
+    geom = D.Geometry(f"{which}-mx", h, i, 2, qh, kvh, 2048, weight_format=1)
+    w = harness.make_weights(geom, 5, norm_weights="random")
+    wq = D.pack_weights_mxfp8(harness.weights_to(w, cuda_device))
+    wo = {"embed": D.unpack_matrix_mxfp8(wq["embed"], geom.hidden).cpu(), "embed_lookup": w["embed"],
+          "final_norm": w["final_norm"], "layers": []}
+    for (n1, _, _, n2, _, _), (_, qkv_p, o_p, _, gu_p, down_p) in zip(w["layers"], wq["layers"]):
+        wo["layers"].append((n1, D.unpack_matrix_mxfp8(qkv_p, geom.hidden).cpu(),
+                             D.unpack_matrix_mxfp8(o_p, geom.q_heads * 64).cpu(), n2,
+                             D.unpack_matrix_mxfp8(gu_p, geom.hidden).cpu(),
+                             D.unpack_matrix_mxfp8(down_p, geom.intermediate).cpu()))
+    cap = (ctx + 48 + 15) // 16 * 16
+    cs = harness.make_cos_sin_cache(geom, cap)
+    csd = cs.to(cuda_device)
+    gen = torch.Generator().manual_seed(31)
+    keys = [[torch.randn(geom.kv_heads, ctx, 64, generator=gen).to(torch.bfloat16)] for _ in range(geom.layers)]
+    vals = [[torch.randn(geom.kv_heads, ctx, 64, generator=gen).to(torch.bfloat16)] for _ in range(geom.layers)]
+    results = {}
+    for path in (7, 0):                       # the batch-1 kernel, then the generic kernel
+        _set_path(path)
+        kv = harness.PagedKV(geom, 1, cap, cuda_device, shuffle=True, seed=2)
+        if ctx:
+            kv.load_prefix([k[0][None] for k in keys], [v[0][None] for v in vals])
+        ks = [[k[0].clone()] for k in keys]
+        vs = [[v[0].clone()] for v in vals]
+        cur = torch.tensor([123])
+        outs = []
+        for s in range(3):
+            pos = torch.tensor([ctx + s], dtype=torch.int64)
+            hid, logits, nxt = D.decode_step(geom, input_ids=cur.to(cuda_device), positions=pos.to(cuda_device),
+                                             seq_lens=(pos + 1).to(torch.int32).to(cuda_device), block_table=kv.block_table,
+                                             slot_mapping=kv.slots(pos), embed=wq["embed"], embed_lookup=wq["embed_lookup"],
+                                             layers=wq["layers"], final_norm=wq["final_norm"], kv_caches=kv.kv_caches,
+                                             cos_sin_cache=csd, eps=geom.eps, lm_head=True)
+            D.check_status(geom, cuda_device)
+            rh, rl, _ = R.decode_step(geom, wo, cur, pos, ks, vs, cs)
+            assert (logits.cpu().float() - rl).abs().max() <= LOGIT_TOL, f"path {path} step {s}"
+            assert (hid.cpu().float() - rh.float()).abs().max() <= 2 ** -4
+            outs.append((hid.clone(), logits.clone()))
+            cur = rl.argmax(-1)
+        results[path] = outs
+    for (ha, la), (hb, lb) in zip(results[7], results[0]):
+        assert (la.float() - lb.float()).abs().max() <= LOGIT_TOL
+        assert (ha.float() - hb.float()).abs().max() <= 2 ** -4
