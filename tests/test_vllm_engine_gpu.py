@@ -26,6 +26,7 @@ def test_router_inside_a_vllm_engine(cuda_device):
     res = json.loads(lines[-1])
     if "skip" in res:
         pytest.skip(res["skip"])
+    assert "error" not in res, f"the router failed inside the engine: {res.get('error')}\n{res.get('trace')}"
     assert res["cache_shape"][0] == 2 and res["cache_shape"][2:] == [16, 3, 64]        # vLLM's [2, blocks, 16, kv_heads, 64]
     for case in res["cases"]:
         print(case)

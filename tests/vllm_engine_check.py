@@ -48,32 +48,41 @@ def main():
             cache = model.model.layers[0].self_attn.attn.kv_cache
             return list(cache.shape)
 
-        cache_shape = llm.apply_model(init)[0]
-        sp = SamplingParams(temperature=0.0, max_tokens=8, logprobs=5, detokenize=False)
-        from prime_kernels_b200 import decode_backend as db
+        try:
+            run_cases(llm, init, SamplingParams, LlamaModel)
+        except Exception as e:                   # a failure past this point is the router's, not the engine's
+            import traceback
 
-        cases = []
-        for n in (3, 6):                          # CUDA-core kernel (3 requests), tensor-core kernel (6)
-            prompts = [{"prompt_token_ids": [(7 * i + 3 * j + 11) % 49152 for j in range(5 + 3 * i)]} for i in range(n)]
-            stock = llm.generate(prompts, sp, use_tqdm=False)
-            original = db.install_into_vllm()
-            db.stats.clear()
-            routed = llm.generate(prompts, sp, use_tqdm=False)
-            stats = dict(db.stats)
-            if original is not None:
-                LlamaModel.forward = original
-            worst, equal_tokens, total_tokens = 0.0, 0, 0
-            for a, b in zip(stock, routed):
-                ta, tb = a.outputs[0].token_ids, b.outputs[0].token_ids
-                total_tokens += len(ta)
-                for step, (x, y) in enumerate(zip(a.outputs[0].logprobs, b.outputs[0].logprobs)):
-                    if ta[step] != tb[step]:
-                        break
-                    equal_tokens += 1
-                    worst = max(worst, abs(x[ta[step]].logprob - y[tb[step]].logprob))
-            cases.append({"requests": n, "stats": stats, "equal_tokens": equal_tokens, "total_tokens": total_tokens,
-                          "max_logprob_diff": worst})
-        print(json.dumps({"cache_shape": cache_shape, "cases": cases}))
+            print(json.dumps({"error": f"{type(e).__name__}: {e}"[:300], "trace": traceback.format_exc()[-1500:]}))
+
+
+def run_cases(llm, init, SamplingParams, LlamaModel):
+    cache_shape = llm.apply_model(init)[0]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, logprobs=5, detokenize=False)
+    from prime_kernels_b200 import decode_backend as db
+
+    cases = []
+    for n in (3, 6):                          # CUDA-core kernel (3 requests), tensor-core kernel (6)
+        prompts = [{"prompt_token_ids": [(7 * i + 3 * j + 11) % 49152 for j in range(5 + 3 * i)]} for i in range(n)]
+        stock = llm.generate(prompts, sp, use_tqdm=False)
+        original = db.install_into_vllm()
+        db.stats.clear()
+        routed = llm.generate(prompts, sp, use_tqdm=False)
+        stats = dict(db.stats)
+        if original is not None:
+            LlamaModel.forward = original
+        worst, equal_tokens, total_tokens = 0.0, 0, 0
+        for a, b in zip(stock, routed):
+            ta, tb = a.outputs[0].token_ids, b.outputs[0].token_ids
+            total_tokens += len(ta)
+            for step, (x, y) in enumerate(zip(a.outputs[0].logprobs, b.outputs[0].logprobs)):
+                if ta[step] != tb[step]:
+                    break
+                equal_tokens += 1
+                worst = max(worst, abs(x[ta[step]].logprob - y[tb[step]].logprob))
+        cases.append({"requests": n, "stats": stats, "equal_tokens": equal_tokens, "total_tokens": total_tokens,
+                      "max_logprob_diff": worst})
+    print(json.dumps({"cache_shape": cache_shape, "cases": cases}))
 
 
 if __name__ == "__main__":
