@@ -33,6 +33,8 @@ def _oracle_weights(D, w, wq, geom):
     ("gqa3-b16-mxfp8", (192, 512, 3, 3, 1, 1024), 16, [70] * 16, True, 16),
     ("mha-b24-mxfp8-block8", (128, 256, 2, 2, 2, 512), 24, [150 - i for i in range(24)], True, 8),
     ("wide-b16", (960, 2560, 2, 15, 5, 2048), 16, [130] * 16, False, 16),                             # SmolLM2-360M widths
+    ("wide17-b2", (2048, 8192, 2, 32, 32, 2048), 2, [30, 61], False, 16),         # SmolLM2-1.7B widths: tensor cores from 2 requests
+    ("wide17-b3-mxfp8", (2048, 8192, 2, 32, 32, 2048), 3, [9, 100, 47], True, 16),
 ])
 def test_batched_kernel_against_restatement(cuda_device, name, dims, B, ctxs, mxfp8, block_size):
     from prime_kernels_b200 import decode as D
