@@ -194,9 +194,55 @@ def config_block(wl, gname, batch, prompt_len, world):
             "replicas": world, "l2": "weights (>= 269 MB per step) exceed the 126 MB L2; no flush needed"}
 
 
+def reference_cuda_kernel_same_box(geom, prompt_len, steps=20):
+    """Supplementary to the CPU arm: the reference project's own decode kernel for this model (its 24-CTA sm_89
+    design, compiled for sm_100a from the reference checkout by oracle/build_ref.sh with the device check shimmed),
+    timed on this box's GPU at the workload's context with CUDA events.  Hidden-state step, no lm_head (the reference
+    kernels have none).  Returns None when the oracle build or a GPU is missing."""
+    import torch
+
+    try:
+        from oracle import ref_megakernel as REF
+        from prime_kernels_b200 import harness
+    except Exception:
+        return None
+    if not torch.cuda.is_available():
+        return None
+    if geom.name == "smollm2-360m" and REF.available_360m_fast():
+        step, label = REF.decode_step_360m_fast, "decode_megakernel_360m_lossless (fast line, plain bf16 weights)"
+    elif geom.name == "smollm2-135m" and REF.available():
+        step, label = REF.decode_step, "decode_megakernel"
+    else:
+        return None
+    dev = torch.device("cuda:0")
+    weights = harness.weights_to(harness.make_weights(geom, 0), dev)
+    cap = (prompt_len + 64 + 15) // 16 * 16
+    kv = harness.PagedKV(geom, 1, cap, dev)
+    for cache in kv.kv_caches:
+        cache.normal_()
+    pos = torch.tensor([prompt_len], dtype=torch.int64, device=dev)
+    kw = dict(input_ids=torch.tensor([17], device=dev), positions=pos, seq_lens=(pos + 1).to(torch.int32),
+              block_table=kv.block_table, slot_mapping=kv.slots(pos), embed=weights["embed"], layers=weights["layers"],
+              final_norm=weights["final_norm"], kv_caches=kv.kv_caches,
+              cos_sin_cache=harness.make_cos_sin_cache(geom, cap, dev), eps=1e-5)
+    for _ in range(3):
+        step(**kw)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step(**kw)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    us = e0.elapsed_time(e1) / steps * 1e3
+    return {"kernel": label, "us_per_step": round(us, 1), "tok_s": round(1e6 / us, 1), "context": prompt_len,
+            "note": "the reference's CUDA kernel on this GPU (hidden-state step, no lm_head), CUDA events"}
+
+
 def run_reference(args, wl):
     """The CPU arm: the reference's own oracle (HuggingFace eager bf16) on the host cores, a bounded sample of the
-    same workload.  Imports nothing that loads the CUDA libraries of this repository."""
+    same workload.  Imports nothing that loads the CUDA libraries of this repository; as a supplementary detail it
+    also times the reference project's own CUDA kernel on this box when oracle/_ref holds its sm_100a build."""
     from prime_kernels_b200.geometry import GEOMETRIES
 
     gname, batch, prompt_len, _ = WORKLOADS[wl]
@@ -208,11 +254,19 @@ def run_reference(args, wl):
         return
     steps = max(1, min(args.steps, 16))          # bounded sample: at most 16 timed decode steps
     toks, cores, desc = cpu_reference(geom, batch, prompt_len, steps)
+    detail = {"note": "CPU arm: prompt prefilled untimed, then `steps` timed decode steps"}
+    if batch == 1:
+        try:
+            same_box = reference_cuda_kernel_same_box(geom, prompt_len)
+        except Exception as e:          # supplementary: never let it break the arm
+            same_box = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+        if same_box:
+            detail["reference_cuda_kernel_same_box"] = same_box
     line = {"metric": METRIC, "value": toks, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps,
             "steps_requested": args.steps, "warmup": 0, "ms_per_step": 1e3 * batch / toks, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
             "config": config_block(wl, gname, batch, prompt_len, int(os.environ.get("WORLD_SIZE", "1"))),
-            "detail": {"note": "CPU arm: prompt prefilled untimed, then `steps` timed decode steps"},
+            "detail": detail,
             "cpu_baseline": {"value": toks, "unit": "tok/s", "cores": cores, "kind": "reference", "sample": desc},
             "e2e": {"value": toks, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
