@@ -114,11 +114,13 @@ typedef struct PkDecodeArgs {
     void* workspace; size_t workspace_bytes; int max_seq_len; int lm_head; int advance;
 } PkDecodeArgs;
 
-/* Generic form of mk_workspace_bytes / decode360_workspace_bytes; max_batch 1..64 (a workspace sized for more than 8
- * requests serves the tensor-core kernel and must not be shared with launches of up to 8 requests). */
+/* Generic form of mk_workspace_bytes / decode360_workspace_bytes; max_batch 1..64.  One workspace serves every kernel and
+ * every batch up to max_batch: from the tensor-core cross-over on (4 requests; 2 for hidden >= 2048) it also holds the
+ * tensor-core kernel's region (same size whatever the batch), behind the CUDA-core kernels' region. */
 size_t pk_decode_workspace_bytes(const PkDecodeModel* model, int max_batch);
-/* Generic form of mk_decode / decode360 (one cooperative launch on args->stream).  1..8 requests run on the CUDA-core
- * kernels (batch 1 of the SmolLM2-135M / 360M widths on a kernel specialised for them), 9..64 requests on the
+/* Generic form of mk_decode / decode360 (one cooperative launch on args->stream), 1..64 requests.  Small batches run on
+ * the CUDA-core kernels (batch 1 of the SmolLM2-135M / 360M widths, bf16 or MXFP8 weights, on a kernel specialised for
+ * them); from the cross-over on (pk_decode_set_tc_min_batch) and always above 8 requests the step runs on the
  * tensor-core kernel: projections as tcgen05 GEMMs with the weight tile as the 128-row operand, batch padded to
  * 16 / 32 / 64, accumulators in tensor memory, every weight streamed once per step. */
 int pk_decode_step(const PkDecodeModel* model, const PkDecodeArgs* args);

@@ -1,7 +1,8 @@
-// Batched decode step (9..64 requests) with the projections on the 5th-generation tensor cores
+// Batched decode step (up to 64 requests; the default from 4, or from 2 for wide models) with the projections on the
+// 5th-generation tensor cores
 // (included by decode_megakernel.cu).
 //
-// At these batch sizes every projection is a real GEMM, C[rows, B] = W[rows, K] . X[B, K]^T.  It is mapped
+// From a handful of requests on every projection is a real GEMM, C[rows, B] = W[rows, K] . X[B, K]^T.  It is mapped
 // "swap-AB": the A operand is a tile of 128 weight rows (so a weight byte is streamed exactly once per step,
 // like in the GEMV kernels), the B operand is the activation matrix with the batch padded to N = 16 / 32 / 64,
 // and the fp32 accumulator tile (128 lanes x N columns) lives in tensor memory:

@@ -1685,7 +1685,7 @@ struct ModelGeom {
 struct WsLayout {
     size_t ctrl, argkey, x, qkv, attn, h1, act, part, fast, total;
 };
-// Region of the tensor-core batched kernel (9..64 requests).
+// Region of the tensor-core batched kernel.
 struct BatchedLayout {
     size_t bctrl, argkey, c_qkv, c_o, c_gu, c_down, x, h1, xn, attn, act, part, total;
 };
@@ -2088,7 +2088,7 @@ static int fast_launch(const ModelGeom& g, const StepArgs& a, const DeviceInfo& 
     return kFastNotEligible;
 }
 
-// ---- tensor-core batched path (decode_batched.cuh): 9..64 requests in one launch -------------------
+// ---- tensor-core batched path (decode_batched.cuh): up to 64 requests in one launch -------------------
 template <int NP, int G, int WF>
 static int batched_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo& di) {
     using namespace batched;
