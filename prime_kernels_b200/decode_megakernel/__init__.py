@@ -28,7 +28,7 @@ SOURCE_SHA256 = hashlib.sha256(SOURCE.read_bytes()).hexdigest()
 CACHE_ROOT = SOURCE.parent.parent / "lib"
 
 GEOMETRY = _generic.SMOLLM2_135M
-MAX_BATCH = _generic.MAX_BATCH
+MAX_BATCH = _generic.MAX_REQUESTS      # one launch takes up to 64 requests (tensor-core kernel from 4 on)
 MAX_SEQ = _generic.MAX_SEQ
 HIDDEN = GEOMETRY.hidden
 KV_HEADS = GEOMETRY.kv_heads
@@ -40,7 +40,7 @@ EPS = GEOMETRY.eps
 def decode_step(*, input_ids, positions, seq_lens, block_table, slot_mapping, embed, layers, final_norm,
                 kv_caches, cos_sin_cache, eps, lm_head=False):
     batch = input_ids.shape[0]
-    if not 1 <= batch <= MAX_BATCH:      # one launch, like the reference entry (the generic op micro-batches beyond)
+    if not 1 <= batch <= MAX_BATCH:      # one launch, like the reference entry
         raise ValueError(f"batch must be 1..{MAX_BATCH}, got {batch}")
     return _generic.decode_step(GEOMETRY, input_ids=input_ids, positions=positions, seq_lens=seq_lens,
                                 block_table=block_table, slot_mapping=slot_mapping, embed=embed, layers=layers,

@@ -25,7 +25,7 @@ INCLUDE_SHA256 = hashlib.sha256((SOURCE.parent / "decode_fast.cuh").read_bytes()
 CACHE_ROOT = SOURCE.parent.parent / "lib"
 
 GEOMETRY = _generic.SMOLLM2_360M
-MAX_BATCH = _generic.MAX_BATCH
+MAX_BATCH = _generic.MAX_REQUESTS      # one launch takes up to 64 requests (tensor-core kernel from 4 on)
 MAX_SEQ = _generic.MAX_SEQ
 HIDDEN = GEOMETRY.hidden
 INTERMEDIATE = GEOMETRY.intermediate
