@@ -130,8 +130,8 @@ def test_decode_contract_errors_are_valueerrors():
 
     from prime_kernels_b200 import decode_megakernel as a
 
-    ids = torch.zeros(9, dtype=torch.int64)
-    with pytest.raises(ValueError, match="batch must be 1..8"):
+    ids = torch.zeros(65, dtype=torch.int64)
+    with pytest.raises(ValueError, match="batch must be 1..64"):
         a.decode_step(input_ids=ids, positions=ids, seq_lens=ids, block_table=ids, slot_mapping=ids, embed=None,
                       layers=[], final_norm=None, kv_caches=[], cos_sin_cache=None, eps=1e-5)
     ids = torch.zeros(1, dtype=torch.int64)
