@@ -37,7 +37,7 @@ constexpr int kThreadsB = 256;        // warps 0-3: operand staging + epilogue; 
 constexpr int kStages = 8;            // ring of staged 64-wide K blocks (A tile 16 KB + B tile NP x 128 bytes each)
 constexpr int kDepth = 4;             // cp.async groups (K blocks) a producer thread keeps in flight
 constexpr int kConv = 4;              // MXFP8 weights: de-quantised bf16 A slots (the raw bytes use a ring of kStages)
-constexpr int kNcB = 16;              // max split-KV chunks per (request, kv head)
+constexpr int kNcB = 32;              // max split-KV chunks per (request, kv head): one lane per chunk in the merge
 constexpr int kMaxReq = 64;
 constexpr int kAStage = 128 * 128;    // bytes of one A stage (128 rows x 64 bf16)
 constexpr int kKvStages = 4;          // attention: runs of 16 positions in flight per warp
