@@ -84,6 +84,10 @@ int pk_rmsnorm_backward(const void* grad_out, const void* grad_sum, const void* 
  * [K e4m3][K/32 e8m0][zero pad to 16 B]; pk_mxfp8_packed_row_bytes(K) is the row stride (-1: bad K). */
 long long pk_mxfp8_packed_row_bytes(int K);
 int pk_pack_weights_mxfp8(const void* weights_bf16, void* packed, long long rows, int K, void* stream);
+/* Same with the scale rule chosen: 0 = round-up (above), 1 = floor: e = clamp(biased_exponent(amax) - 8, 0, 254), values
+ * converted from fp32 with finite saturation - the block-scale rule of the reference's flash_moe kernels
+ * (prime_kernels/flash_moe/csrc/kernels/fused_moe_mxfp8_kernel.cu:4-20).  The packed format is the same. */
+int pk_pack_weights_mxfp8_ex(const void* weights_bf16, void* packed, long long rows, int K, int scale_mode, void* stream);
 
 /* ---------------------------------------------------------------- decode megakernel, generic geometry */
 

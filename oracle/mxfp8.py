@@ -58,6 +58,10 @@ def port() -> ctypes.CDLL:
         lib.pk_oracle_rmsnorm_mxfp8.restype = ctypes.c_int
         lib.pk_oracle_quantise_weight.argtypes = [u16p, ctypes.c_int64, ctypes.c_int, u8p, u8p]
         lib.pk_oracle_quantise_weight.restype = ctypes.c_int
+        lib.pk_oracle_quantise_weight_floor.argtypes = [u16p, ctypes.c_int64, ctypes.c_int, u8p, u8p]
+        lib.pk_oracle_quantise_weight_floor.restype = ctypes.c_int
+        lib.pk_float_to_e4m3.argtypes = [ctypes.c_float]
+        lib.pk_float_to_e4m3.restype = ctypes.c_uint8
         _PORT = lib
     return _PORT
 
@@ -145,13 +149,15 @@ def quantise_ref(branch, residual, weight, s, eps, math=1):
     return vals, scales, rrms
 
 
-def quantise_weight(w_bits):
-    """Per-32-along-K MXFP8 quantisation of a [rows, K] bf16 (uint16 view) matrix."""
+def quantise_weight(w_bits, scale_mode="roundup"):
+    """Per-32-along-K MXFP8 quantisation of a [rows, K] bf16 (uint16 view) matrix.  ``scale_mode``: "roundup" (the
+    rmsnorm quantiser's rule, never saturates) or "floor" (the flash_moe block-scale rule, may saturate at 448)."""
     rows, k = w_bits.shape
     vals = np.zeros((rows, k), np.uint8)
     scales = np.zeros((rows, k // 32), np.uint8)
     w = np.ascontiguousarray(w_bits, np.uint16)
-    rc = port().pk_oracle_quantise_weight(_ptr(w, u16p), rows, k, _ptr(vals, u8p), _ptr(scales, u8p))
+    fn = port().pk_oracle_quantise_weight if scale_mode == "roundup" else port().pk_oracle_quantise_weight_floor
+    rc = fn(_ptr(w, u16p), rows, k, _ptr(vals, u8p), _ptr(scales, u8p))
     if rc:
         raise ValueError("K must be a multiple of 32")
     return vals, scales

@@ -64,14 +64,31 @@ uint16_t pk_e8m0_to_bf16(uint8_t e) {
     return (uint16_t)((uint16_t)e << 7);
 }
 
+/* |value| (finite, fp32) -> FP8 E4M3 magnitude bits, round-nearest-even, finite saturation. */
+static uint8_t pk_mag_to_e4m3(float a, uint8_t sign);
+
+/* fp32 -> FP8 E4M3 (fn), round-nearest-even, finite saturation: what cvt.rn.satfinite.e4m3x2.f32 /
+ * __nv_cvt_float2_to_fp8x2(.., __NV_SATFINITE, __NV_E4M3) do to one value. */
+uint8_t pk_float_to_e4m3(float f) {
+    uint32_t u = f2u(f);
+    uint8_t sign = (uint8_t)((u >> 24) & 0x80);
+    uint32_t mag = u & 0x7fffffffu;
+    if (mag > 0x7f800000u) return 0x7f;                       /* NaN: canonical, sign dropped */
+    if (mag == 0x7f800000u) return (uint8_t)(sign | 0x7e);    /* inf -> largest finite */
+    return pk_mag_to_e4m3(u2f(mag), sign);
+}
+
 /* bf16 -> FP8 E4M3 (fn: no inf, max 448), round-nearest-even, finite saturation. */
 uint8_t pk_bf16_to_e4m3(uint16_t b) {
     uint8_t sign = (uint8_t)((b >> 8) & 0x80);
     uint32_t mag = b & 0x7fffu;
     if (mag > 0x7f80u) return 0x7f;                           /* NaN: canonical, sign dropped */
-    float a = pk_bf16_to_float((uint16_t)mag);
-    if (a >= 464.0f) return (uint8_t)(sign | 0x7e);           /* >= halfway past 448 -> sat 448 */
     if (mag >= 0x7f80u) return (uint8_t)(sign | 0x7e);
+    return pk_mag_to_e4m3(pk_bf16_to_float((uint16_t)mag), sign);
+}
+
+static uint8_t pk_mag_to_e4m3(float a, uint8_t sign) {
+    if (a >= 464.0f) return (uint8_t)(sign | 0x7e);           /* >= halfway past 448 -> sat 448 */
     if (a < 0.0009765625f) return sign;                       /* < 2^-10: below half the min subnormal */
     /* scale so that one e4m3 ulp at this magnitude becomes 1.0, then round to nearest even */
     int e;
@@ -186,6 +203,30 @@ int pk_oracle_quantise_weight(const uint16_t* w, int64_t rows, int K, uint8_t* v
             for (int k = 0; k < 32; ++k)
                 vals[r * K + g + k] = pk_bf16_to_e4m3(pk_float_to_bf16(pk_bf16_to_float(w[r * K + g + k]) * inv));
             scales[r * (K / 32) + g / 32] = sf;
+        }
+    }
+    return 0;
+}
+
+/*
+ * Second weight recipe ("floor"): the block-scale rule of the reference's flash_moe kernels
+ * (prime_kernels/flash_moe/csrc/kernels/fused_moe_mxfp8_kernel.cu:4-20, mx_block_scale + store_fp8x16):
+ * e = clamp(biased_exponent(amax) - 8, 0, 254), i.e. scale 2^(floor(log2 amax) - 8); values w * 2^(127 - e)
+ * converted from fp32 with round-to-nearest-even and finite saturation (a block's largest values may saturate
+ * at 448).  Same packed format as the round-up recipe.
+ */
+int pk_oracle_quantise_weight_floor(const uint16_t* w, int64_t rows, int K, uint8_t* vals, uint8_t* scales) {
+    if (K % 32) return 1;
+    for (int64_t r = 0; r < rows; ++r) {
+        for (int g = 0; g < K; g += 32) {
+            float amax = 0.f;
+            for (int k = 0; k < 32; ++k) amax = fmaxf(amax, fabsf(pk_bf16_to_float(w[r * K + g + k])));
+            int e = (int)((f2u(amax) >> 23) & 0xffu) - 8;
+            e = e < 0 ? 0 : (e > 254 ? 254 : e);
+            const float inv = u2f((uint32_t)(254 - e) << 23);
+            for (int k = 0; k < 32; ++k)
+                vals[r * K + g + k] = pk_float_to_e4m3(pk_bf16_to_float(w[r * K + g + k]) * inv);
+            scales[r * (K / 32) + g / 32] = (uint8_t)e;
         }
     }
     return 0;

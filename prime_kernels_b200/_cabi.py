@@ -51,6 +51,7 @@ SYMBOLS = {
     "pk_rmsnorm_backward": (ci, [vp, vp, vp, vp, vp, vp, vp, ll, ci, ctypes.c_float, vp]),
     "pk_mxfp8_packed_row_bytes": (ll, [ci]),
     "pk_pack_weights_mxfp8": (ci, [vp, vp, ll, ci, vp]),
+    "pk_pack_weights_mxfp8_ex": (ci, [vp, vp, ll, ci, ci, vp]),
     "pk_decode_workspace_bytes": (sz, [ctypes.POINTER(PkDecodeModel), ci]),
     "pk_decode_step": (ci, [ctypes.POINTER(PkDecodeModel), ctypes.POINTER(PkDecodeArgs)]),
     "pk_decode_step_tc": (ci, [ctypes.POINTER(PkDecodeModel), ctypes.POINTER(PkDecodeArgs)]),

@@ -752,8 +752,11 @@ extern "C" long long pk_rmsnorm_scale_bytes(int N, int C) {
 // One warp per row; lane owns whole 32-element groups (group g handled by lane g % 32).
 namespace pk {
 
+// floor_mode: the block-scale rule of the reference's flash_moe kernels instead
+// (prime_kernels/flash_moe/csrc/kernels/fused_moe_mxfp8_kernel.cu:4-20): e = clamp(biased_exponent(amax) - 8, 0, 254),
+// values w * 2^(127 - e) converted from fp32 with finite saturation (the largest values of a group may saturate).
 __global__ void __launch_bounds__(256) pack_weights_mxfp8_kernel(const uint16_t* __restrict__ w, uint8_t* __restrict__ out,
-                                                                 long long rows, int K, int rowbytes) {
+                                                                 long long rows, int K, int rowbytes, int floor_mode) {
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
@@ -771,9 +774,18 @@ __global__ void __launch_bounds__(256) pack_weights_mxfp8_kernel(const uint16_t*
         float amax = 0.f;
 #pragma unroll
         for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(v[i])), fabsf(bf16_hi(v[i]))));
-        const uint32_t sf = e8m0_roundup(__fmul_rn(amax, 1.f / 448.f));
-        const uint32_t e = 254u - sf;
-        const float inv = __uint_as_float(e ? (e << 23) : 0x00400000u);
+        uint32_t sf;
+        float inv;
+        if (floor_mode) {
+            int ef = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 8;
+            ef = ef < 0 ? 0 : (ef > 254 ? 254 : ef);
+            sf = (uint32_t)ef;
+            inv = __uint_as_float((uint32_t)(254 - ef) << 23);
+        } else {
+            sf = e8m0_roundup(__fmul_rn(amax, 1.f / 448.f));
+            const uint32_t e = 254u - sf;
+            inv = __uint_as_float(e ? (e << 23) : 0x00400000u);
+        }
         uint32_t q[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -792,9 +804,11 @@ __global__ void __launch_bounds__(256) pack_weights_mxfp8_kernel(const uint16_t*
 extern "C" long long pk_mxfp8_packed_row_bytes(int K) { return K % 32 ? -1 : ((long long)K + K / 32 + 15) / 16 * 16; }
 
 // No counterpart in the reference (it consumes pre-quantised weights, flash_moe/__init__.py:165-170).
-extern "C" int pk_pack_weights_mxfp8(const void* weights_bf16, void* packed, long long rows, int K, void* stream) {
+// scale_mode 0: round-up scales (the rmsnorm quantiser's rule, never saturates); 1: floor scales (flash_moe's rule).
+extern "C" int pk_pack_weights_mxfp8_ex(const void* weights_bf16, void* packed, long long rows, int K, int scale_mode,
+                                        void* stream) {
     using namespace pk;
-    if (rows < 0 || K <= 0 || (K % 32) != 0) return kErrShape;
+    if (rows < 0 || K <= 0 || (K % 32) != 0 || (scale_mode != 0 && scale_mode != 1)) return kErrShape;
     if (rows == 0) return kOk;
     if (!weights_bf16 || !packed) return kErrNull;
     if ((reinterpret_cast<uintptr_t>(weights_bf16) % 16) || (reinterpret_cast<uintptr_t>(packed) % 16)) return kErrAlign;
@@ -802,6 +816,10 @@ extern "C" int pk_pack_weights_mxfp8(const void* weights_bf16, void* packed, lon
     const long long blocks = (rows + 7) / 8;
     if (blocks > 0x7fffffffLL) return kErrShape;
     pack_weights_mxfp8_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint16_t*>(weights_bf16), static_cast<uint8_t*>(packed), rows, K, rowbytes);
+        static_cast<const uint16_t*>(weights_bf16), static_cast<uint8_t*>(packed), rows, K, rowbytes, scale_mode);
     return (int)cudaPeekAtLastError();
+}
+
+extern "C" int pk_pack_weights_mxfp8(const void* weights_bf16, void* packed, long long rows, int K, void* stream) {
+    return pk_pack_weights_mxfp8_ex(weights_bf16, packed, rows, K, 0, stream);
 }

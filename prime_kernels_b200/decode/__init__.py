@@ -124,9 +124,16 @@ def packed_row_bytes(k: int) -> int:
     return int(library().pk_mxfp8_packed_row_bytes(int(k)))
 
 
-def pack_matrix_mxfp8(w: torch.Tensor) -> torch.Tensor:
+SCALE_MODES = {"roundup": 0, "floor": 1}
+
+
+def pack_matrix_mxfp8(w: torch.Tensor, scale_mode: str = "roundup") -> torch.Tensor:
     """Quantise a bf16 CUDA matrix ``[rows, K]`` to the packed MXFP8 row format the decode GEMV streams:
-    ``[K e4m3][K/32 e8m0][zero pad to 16 B]`` per row (uint8 ``[rows, packed_row_bytes(K)]``)."""
+    ``[K e4m3][K/32 e8m0][zero pad to 16 B]`` per row (uint8 ``[rows, packed_row_bytes(K)]``).  ``scale_mode``:
+    ``"roundup"`` (scale 2^ceil(log2(amax / 448)): the fused norm-quant op's rule, never saturates) or ``"floor"``
+    (scale 2^(floor(log2 amax) - 8): the block-scale rule of the reference's flash_moe kernels, may saturate)."""
+    if scale_mode not in SCALE_MODES:
+        raise ValueError(f"scale_mode must be one of {sorted(SCALE_MODES)}")
     if w.dtype != torch.bfloat16 or w.dim() != 2 or not w.is_cuda or not w.is_contiguous():
         raise ValueError("expected a contiguous 2-D BF16 CUDA tensor")
     rows, k = w.shape
@@ -135,19 +142,19 @@ def pack_matrix_mxfp8(w: torch.Tensor) -> torch.Tensor:
         raise ValueError("K must be a multiple of 32")
     out = torch.empty((rows, rb), dtype=torch.uint8, device=w.device)
     with torch.cuda.device(w.device):
-        rc = library().pk_pack_weights_mxfp8(w.data_ptr(), out.data_ptr(), rows, k,
-                                             torch.cuda.current_stream(w.device).cuda_stream)
+        rc = library().pk_pack_weights_mxfp8_ex(w.data_ptr(), out.data_ptr(), rows, k, SCALE_MODES[scale_mode],
+                                                torch.cuda.current_stream(w.device).cuda_stream)
     if rc != 0:
         raise RuntimeError(f"pack_weights_mxfp8 failed: {status_string(rc)}")
     return out
 
 
-def pack_weights_mxfp8(weights: dict) -> dict:
+def pack_weights_mxfp8(weights: dict, scale_mode: str = "roundup") -> dict:
     """MXFP8 variant of a weight dict (``embed``, ``layers``, ``final_norm``): every projection matrix and
     the tied lm_head are packed; norm weights stay bf16; ``embed_lookup`` keeps the bf16 embedding rows."""
-    layers = [(n1, pack_matrix_mxfp8(qkv), pack_matrix_mxfp8(o), n2, pack_matrix_mxfp8(gu), pack_matrix_mxfp8(down))
-              for (n1, qkv, o, n2, gu, down) in weights["layers"]]
-    return {"embed": pack_matrix_mxfp8(weights["embed"]), "embed_lookup": weights["embed"], "layers": layers,
+    pk = lambda m: pack_matrix_mxfp8(m, scale_mode)      # noqa: E731
+    layers = [(n1, pk(qkv), pk(o), n2, pk(gu), pk(down)) for (n1, qkv, o, n2, gu, down) in weights["layers"]]
+    return {"embed": pk(weights["embed"]), "embed_lookup": weights["embed"], "layers": layers,
             "final_norm": weights["final_norm"]}
 
 

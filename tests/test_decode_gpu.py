@@ -201,6 +201,52 @@ def test_mxfp8_weight_packing_is_bit_exact(cuda_device):
                 .reshape(rows, k) * 2 ** -3 + 1e-30).all()
 
 
+def test_mxfp8_weight_packing_floor_mode_is_bit_exact(cuda_device):
+    """The second scale rule (floor: the block-scale rule of the reference's flash_moe kernels, values may saturate)
+    against the CPU oracle, and a decode step on weights packed that way against the restatement on their exact
+    de-quantisation: the kernels do not care which rule produced the bytes."""
+    from oracle import mxfp8
+    from prime_kernels_b200 import decode as D
+
+    g = torch.Generator().manual_seed(4)
+    saturated = 0
+    for rows, k in [(7, 960), (64, 2560), (33, 32)]:
+        w = (torch.randn(rows, k, generator=g) * 0.02).to(torch.bfloat16)
+        w[0, :32] = 0
+        packed = D.pack_matrix_mxfp8(w.to(cuda_device), scale_mode="floor").cpu().numpy()
+        vals, scales = mxfp8.quantise_weight(w.view(torch.int16).numpy().view(np.uint16), scale_mode="floor")
+        assert np.array_equal(packed[:, :k], vals)
+        assert np.array_equal(packed[:, k:k + k // 32], scales)
+        saturated += int(((vals & 0x7f) == 0x7e).sum())
+        other = D.pack_matrix_mxfp8(w.to(cuda_device)).cpu().numpy()
+        assert (packed[:, k:k + k // 32].astype(int) <= other[:, k:k + k // 32].astype(int)).all()     # floor never above round-up
+    assert saturated > 0            # groups whose largest value lies in (448, 512) x scale saturate, by design
+    geom = D.Geometry("mx-floor", 192, 512, 2, 3, 1, 1024, weight_format=1)
+    wts = harness.make_weights(geom, 2, norm_weights="random")
+    wq = D.pack_weights_mxfp8(harness.weights_to(wts, cuda_device), scale_mode="floor")
+    wo = {"embed": D.unpack_matrix_mxfp8(wq["embed"], geom.hidden).cpu(), "embed_lookup": wts["embed"],
+          "final_norm": wts["final_norm"], "layers": []}
+    for (n1, _, _, n2, _, _), (_, qkv_p, o_p, _, gu_p, down_p) in zip(wts["layers"], wq["layers"]):
+        wo["layers"].append((n1, D.unpack_matrix_mxfp8(qkv_p, geom.hidden).cpu(), D.unpack_matrix_mxfp8(o_p, geom.q_heads * 64).cpu(),
+                             n2, D.unpack_matrix_mxfp8(gu_p, geom.hidden).cpu(), D.unpack_matrix_mxfp8(down_p, geom.intermediate).cpu()))
+    cs = harness.make_cos_sin_cache(geom, 128)
+    ctx = 33
+    keys = [[torch.randn(1, ctx, 64, generator=g).to(torch.bfloat16)] for _ in range(geom.layers)]
+    vals_ = [[torch.randn(1, ctx, 64, generator=g).to(torch.bfloat16)] for _ in range(geom.layers)]
+    kv = harness.PagedKV(geom, 1, 64, cuda_device)
+    kv.load_prefix([torch.stack(k) for k in keys], [torch.stack(v) for v in vals_])
+    cur, pos = torch.tensor([77]), torch.tensor([ctx], dtype=torch.int64)
+    hid, logits, _ = D.decode_step(geom, input_ids=cur.to(cuda_device), positions=pos.to(cuda_device),
+                                   seq_lens=(pos + 1).to(torch.int32).to(cuda_device), block_table=kv.block_table,
+                                   slot_mapping=kv.slots(pos), embed=wq["embed"], embed_lookup=wq["embed_lookup"],
+                                   layers=wq["layers"], final_norm=wq["final_norm"], kv_caches=kv.kv_caches,
+                                   cos_sin_cache=cs.to(cuda_device), eps=geom.eps, lm_head=True)
+    D.check_status(geom, cuda_device)
+    rh, rl, _ = R.decode_step(geom, wo, cur, pos, keys, vals_, cs)
+    assert (logits.cpu().float() - rl).abs().max() <= LOGIT_TOL
+    assert (hid.cpu().float() - rh.float()).abs().max() <= 2 ** -4
+
+
 @pytest.mark.parametrize("B", [1, 4])
 def test_mxfp8_weights_decode_against_restatement(cuda_device, B):
     """MXFP8 weights (E4M3 + E8M0 per 32 along K), bf16 activations and KV: the oracle runs the same step on

@@ -110,3 +110,36 @@ def test_ragged_shapes_define_padding_as_zero():
     _, _, _, res1 = mxfp8.quantise_port(x, x, w, None, 1e-6, mode=1, want_res=True)
     a = torch.from_numpy(x.view(np.int16)).view(torch.bfloat16).float()
     assert (torch.from_numpy(res1.view(np.int16)).view(torch.bfloat16).float() == (a + a).to(torch.bfloat16).float()).all()
+
+
+def test_floor_scale_rule_known_answers_and_fp32_conversion():
+    """The floor rule (flash_moe's block scale): e = clamp(biased_exponent(amax) - 8, 0, 254), values from fp32 with
+    finite saturation.  Known answers, and the fp32 -> e4m3 conversion against PyTorch's own for in-range values."""
+    import torch
+
+    lib = mxfp8.port()
+    # fp32 -> e4m3 against torch (round to nearest even; torch does not saturate, so stay within +-448)
+    g = np.random.default_rng(7)
+    xs = np.concatenate([g.uniform(-448, 448, 4000), g.uniform(-1, 1, 4000), g.uniform(-2 ** -6, 2 ** -6, 2000),
+                         np.array([0.0, 2 ** -9, 2 ** -10, 3 * 2 ** -11, 448.0, -448.0, 256.0, 17.0, 18.0, 19.0, 1.0625])]).astype(np.float32)
+    want = torch.from_numpy(xs).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    got = np.array([lib.pk_float_to_e4m3(float(x)) for x in xs], dtype=np.uint8)
+    assert np.array_equal(got & 0x7f, want & 0x7f) and np.array_equal((got >> 7)[xs != 0], (want >> 7)[xs != 0])
+    assert lib.pk_float_to_e4m3(486.0) == 0x7e and lib.pk_float_to_e4m3(-1e9) == 0xfe       # saturation
+    # one group with amax 1.0: biased exponent 127 -> e = 119 (scale 2^-8); 1.0 -> 256 = 0x78; 1.9 -> 486.4 -> saturates
+    w = np.zeros((1, 32), np.float32)
+    w[0, 0], w[0, 1], w[0, 2] = 1.0, -0.5, 2.0 ** -9
+    bits = torch.from_numpy(w).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    vals, scales = mxfp8.quantise_weight(bits, scale_mode="floor")
+    assert scales[0, 0] == 119 and vals[0, 0] == 0x78 and vals[0, 1] == (0x80 | 0x70) and vals[0, 2] == 0x30   # 0.5 -> 128, 2^-9 -> 0.5
+    w[0, 0] = 1.9
+    bits = torch.from_numpy(w).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    vals, scales = mxfp8.quantise_weight(bits, scale_mode="floor")
+    assert scales[0, 0] == 119 and vals[0, 0] == 0x7e          # 1.9 * 256 = 486 > 464: saturated at 448
+    # the round-up rule on the same group never saturates: scale 2^-7 (sf 120), 1.9 * 128 = 243 -> 240
+    vals2, scales2 = mxfp8.quantise_weight(bits, scale_mode="roundup")
+    assert scales2[0, 0] == 120 and vals2[0, 0] == 0x77
+    # all-zero group: e = clamp(0 - 8) = 0, values 0
+    z = np.zeros((1, 32), np.uint16)
+    vals, scales = mxfp8.quantise_weight(z, scale_mode="floor")
+    assert scales[0, 0] == 0 and not vals.any()
