@@ -88,6 +88,7 @@ struct BParams {
     float* part;                        // [B][KVH][kNcB][G][66]
     long long k_off, v_off, block_stride, token_stride, head_stride;
     int block_size, bt_stride, ids_i64, cs_fp32;
+    int bs_shift;                       // log2(block_size) when it is a power of two, else -1 (the run loop then divides)
     int H, I, L, QH, KVH, V, G, nb, wfmt, lm_head, advance, max_seq_len;
     unsigned spin_limit;
     float eps;
@@ -640,27 +641,30 @@ __device__ void attention_item_b(BC& c, int layer, int b, int kvh, int chunk) {
 
     // a window of 32 block-table entries, one per lane, refreshed as the runs move along
     const int* bt = p.block_table + (size_t)b * p.bt_stride;
-    const int bs = p.block_size;
-    int bt_base = ws / bs;
+    const int bs = p.block_size, bsh = p.bs_shift;
+    // position -> (block-table index, position inside the block): shifts for the usual power-of-two block sizes
+    auto blk_of = [&](int pos) { return bsh >= 0 ? (pos >> bsh) : pos / bs; };
+    auto in_blk = [&](int pos) { return bsh >= 0 ? (pos & (bs - 1)) : pos % bs; };
+    int bt_base = blk_of(ws);
     int btc = __ldg(bt + min(bt_base + lane, p.bt_stride - 1));
     const bool packed = p.token_stride == 2 * kD && p.v_off == p.k_off + kD;
     auto issue = [&](int r0) {
         const int st = (int)(c.kvi % kKvStages);
         const int n = max(0, min(16, wcopy - r0));
-        if ((r0 + 15) / bs >= bt_base + 32) {
-            bt_base = r0 / bs;
+        if (blk_of(r0 + 15) >= bt_base + 32) {
+            bt_base = blk_of(r0);
             btc = __ldg(bt + min(bt_base + lane, p.bt_stride - 1));
         }
-        const int j = lane & 15, pj = r0 + j;
-        const int blk = __shfl_sync(kFullMask, btc, (pj / bs - bt_base) & 31);
+        const int j = lane & 15, pj = r0 + j, pin = in_blk(pj);
+        const int blk = __shfl_sync(kFullMask, btc, (blk_of(pj) - bt_base) & 31);
         if (lane == 0) mbar_expect_tx(&bars[st], (uint32_t)n * 256u);      // n == 0: the phase completes at once
         __syncwarp();
         unsigned char* dst = ring + st * kRunBytes + j * 256;
-        const long long e = (long long)blk * p.block_stride + (long long)(pj % bs) * p.token_stride + hs;
+        const long long e = (long long)blk * p.block_stride + (long long)pin * p.token_stride + hs;
         if (packed) {
             // one copy per piece of a block: lane j starts a piece when position j is the first of the run or of a block
-            if (lane < 16 && j < n && (j == 0 || pj % bs == 0))
-                bulk_g2s_plain(dst, kvr + p.k_off + e, (uint32_t)min(bs - pj % bs, n - j) * 256u, &bars[st]);
+            if (lane < 16 && j < n && (j == 0 || pin == 0))
+                bulk_g2s_plain(dst, kvr + p.k_off + e, (uint32_t)min(bs - pin, n - j) * 256u, &bars[st]);
         } else if (j < n) {
             const bool isv = lane >= 16;
             bulk_g2s_plain(dst + (isv ? 128 : 0), kvr + (isv ? p.v_off : p.k_off) + e, 128u, &bars[st]);
@@ -711,6 +715,13 @@ __device__ void attention_item_b(BC& c, int layer, int b, int kvh, int chunk) {
         l[hh] = 0.f;
         acc[hh][0] = acc[hh][1] = 0.f;
     }
+    // this lane's half of every query head, in the lane's (rotated) chunk order: loop-invariant, kept in registers
+    uint4 qreg[G][4];
+#pragma unroll
+    for (int hh = 0; hh < G; ++hh)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            qreg[hh][i] = *reinterpret_cast<const uint4*>(qkvb_s + hh * 32 + 16 * half + 4 * ((i + pl) & 3));
     bool alive = true;
 #pragma unroll 1
     for (int k = 0; k < nruns; ++k) {
@@ -738,7 +749,7 @@ __device__ void attention_item_b(BC& c, int layer, int b, int kvh, int chunk) {
             const uint4 k4 = *reinterpret_cast<const uint4*>(krow + ii * 16);
 #pragma unroll
             for (int hh = 0; hh < G; ++hh) {
-                const uint4 q4 = *reinterpret_cast<const uint4*>(qkvb_s + hh * 32 + 16 * half + 4 * ii);
+                const uint4 q4 = qreg[hh][i];
                 d0[hh] = fma2_bf16(k4.x, q4.x, d0[hh]);
                 d1[hh] = fma2_bf16(k4.y, q4.y, d1[hh]);
                 d0[hh] = fma2_bf16(k4.z, q4.z, d0[hh]);

@@ -2144,6 +2144,9 @@ static int batched_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceI
     p.token_stride = a.token_stride;
     p.head_stride = a.head_stride;
     p.block_size = a.block_size;
+    p.bs_shift = -1;
+    for (int sft = 0; sft < 16; ++sft)
+        if ((1 << sft) == a.block_size) p.bs_shift = sft;
     p.bt_stride = a.bt_stride;
     p.ids_i64 = a.ids_i64 ? 1 : 0;
     p.cs_fp32 = a.cs_fp32 ? 1 : 0;
