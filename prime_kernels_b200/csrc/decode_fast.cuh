@@ -139,7 +139,7 @@ struct FC {
     uint32_t T32;       // (epoch + 1) << 7: the epoch part of a 32-bit tag
     int warp, lane, cta, ncta;
     uint32_t consumed;          // ring entries this warp has used so far
-    uint2 nwv[2];               // this thread's norm weights of the *next* norm phase (fetched one phase ahead)
+    uint2 nwv[3];               // this thread's norm weights of the *next* norm phase (fetched one phase ahead)
     uint32_t pre_off;           // ring offset of the upcoming phase's first entry, valid when pre_ok
     bool pre_ok;                // that entry has landed (checked before the staging of the phase)
     unsigned long long* prof;
@@ -270,18 +270,24 @@ struct Ph<W, NW, kQKV> { static constexpr int K = W::H, WIDX = 1, PAIR = 1, RPE 
 template <class W, int NW>
 struct Ph<W, NW, kO> { static constexpr int K = W::AD, WIDX = 2, PAIR = 0, RPE = 2; };
 template <class W, int NW>
-struct Ph<W, NW, kGU> { static constexpr int K = W::H, WIDX = 4, PAIR = 1, RPE = (NW >= 12 ? 1 : 3); };
+struct Ph<W, NW, kGU> { static constexpr int K = W::H, WIDX = 4, PAIR = 1, RPE = ((NW >= 12 || W::H * 2 >= 4096) ? 1 : 3); };
 template <class W, int NW>
 struct Ph<W, NW, kDown> { static constexpr int K = W::I, WIDX = 5, PAIR = 0, RPE = (W::I * 2 > 4096 ? 1 : 2); };
 template <class W, int NW>
-struct Ph<W, NW, kLM> { static constexpr int K = W::H, WIDX = -1, PAIR = 0, RPE = (NW >= 12 ? 2 : 4); };
+struct Ph<W, NW, kLM> { static constexpr int K = W::H, WIDX = -1, PAIR = 0, RPE = ((NW >= 12 || W::H * 2 >= 4096) ? 2 : 4); };
+
+// A bf16 row of the down projection longer than 8 KB travels as KS ring entries of K / KS weights each (a ring
+// holds three 8 KB entries at the widest model); the consumer adds the parts' dot products before the epilogue.
+template <class W, int WF>
+__host__ __device__ constexpr int down_ks() { return (WF == 0 && W::I * 2 > 8192) ? 2 : 1; }
 
 // bytes of one stored weight row: bf16, or packed MXFP8 ([K e4m3][K/32 e8m0], padded to 16 bytes)
 template <int WF>
 __host__ __device__ constexpr int fast_row_bytes(int K) { return WF ? ((K + K / 32 + 15) & ~15) : K * 2; }
 
 template <class W, int NW, int WF>
-__device__ __forceinline__ void phase_consts(int t, int& rowbytes, int& rpe, int& widx) {
+__device__ __forceinline__ void phase_consts(int t, int& rowbytes, int& rpe, int& widx, int& ks) {
+    ks = t == kDown ? down_ks<W, WF>() : 1;
     switch (t) {
         case kQKV: rowbytes = fast_row_bytes<WF>(Ph<W, NW, kQKV>::K); rpe = Ph<W, NW, kQKV>::RPE; widx = Ph<W, NW, kQKV>::WIDX; break;
         case kO: rowbytes = fast_row_bytes<WF>(Ph<W, NW, kO>::K); rpe = Ph<W, NW, kO>::RPE; widx = Ph<W, NW, kO>::WIDX; break;
@@ -311,7 +317,7 @@ __device__ void producer_loop(const FastParams& p, FShared<NW>& sh, unsigned cha
     const uint32_t RW = (uint32_t)p.ring_bytes;
     unsigned char* ring = ring_base + (size_t)w * RW;
     const uint64_t pol = evict_first_policy();
-    int layer = 0, t = -1, row = 0;        // cursor: next entry starts at unit `row` of phase t in `layer`
+    int layer = 0, t = -1, row = 0, sub = 0;   // cursor: next entry is part `sub` of unit `row` of phase t in `layer`
     bool more = active;
     auto next_phase = [&]() {
         for (;;) {
@@ -345,10 +351,10 @@ __device__ void producer_loop(const FastParams& p, FShared<NW>& sh, unsigned cha
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             if (more) {
-                int rowbytes, rpe, widx;
-                phase_consts<W, NW, WF>(t, rowbytes, rpe, widx);
+                int rowbytes, rpe, widx, ks;
+                phase_consts<W, NW, WF>(t, rowbytes, rpe, widx, ks);
                 const int nre = min(rpe, sh.row_b[t][w] - row);
-                const uint32_t part = (uint32_t)(nre * rowbytes);
+                const uint32_t part = (uint32_t)(nre * rowbytes / ks);        // ks > 1 only with one row per entry
                 const bool pair = t == kGU || t == kQKV;
                 const uint32_t bytes = pair ? 2u * part : part;
                 if (issued == tail) head = 0;      // empty ring: restart at its base, so any entry <= RW fits
@@ -365,7 +371,7 @@ __device__ void producer_loop(const FastParams& p, FShared<NW>& sh, unsigned cha
                     // QKV units pair row d with row d + 32 of the same head; gate/up units pair row r with row I + r
                     const int row0 = t == kQKV ? ((row >> 5) << 6) + (row & 31) : row;
                     const size_t pair_off = (size_t)(t == kQKV ? 32 : W::I) * rowbytes;
-                    const unsigned char* src = base + (size_t)row0 * rowbytes;
+                    const unsigned char* src = base + (size_t)row0 * rowbytes + (size_t)sub * part;
                     mbar_expect_tx(&sh.full[w][slot], bytes);
                     bulk_g2s(ring + off, src, part, &sh.full[w][slot], pol);
                     if (pair) bulk_g2s(ring + off + part, src + pair_off, part, &sh.full[w][slot], pol);
@@ -373,8 +379,11 @@ __device__ void producer_loop(const FastParams& p, FShared<NW>& sh, unsigned cha
                     if (head >= RW) head = 0;
                     used += foot;
                     ++issued;
-                    row += rpe;
-                    if (row >= sh.row_b[t][w]) next_phase();
+                    if (++sub == ks) {
+                        sub = 0;
+                        row += rpe;
+                        if (row >= sh.row_b[t][w]) next_phase();
+                    }
                     progressed = true;
                 }
             }
@@ -422,7 +431,7 @@ __device__ __forceinline__ void gemv_rows(const uint4* ep, const uint4* act, int
         }
     }
 #pragma unroll
-    for (int r = 0; r < NR; ++r) v[r] = acc[r] + acc2[r];
+    for (int r = 0; r < NR; ++r) v[r] += acc[r] + acc2[r];     // v: zero, or the sum over the row's earlier parts
 }
 
 // The same for packed MXFP8 rows ([K e4m3][K/32 e8m0][pad]): a 16-byte chunk is 16 weights against two activation
@@ -468,45 +477,55 @@ __device__ __forceinline__ void gemv_phase(FC<NW>& c, const int t, int layer, co
     const int w = c.warp, lane = c.lane;
     const int ra = sh.row_a[t][w], rb = sh.row_b[t][w];
     const int par = layer & 1;
-    int rowbytes, rpe, widx;
-    phase_consts<W, NW, WF>(t, rowbytes, rpe, widx);
+    int rowbytes, rpe, widx, ks;
+    phase_consts<W, NW, WF>(t, rowbytes, rpe, widx, ks);
     uint32_t best = 0u;      // lm_head: bf16 order key << 16 | (0xffff - local row)
+    bool gone = false;
 #pragma unroll 1
     for (int row = ra; row < rb; row += rpe) {
         const int nre = min(rpe, rb - row);
-        const uint32_t slot = c.consumed % kFE;
-        uint32_t eoff = c.pre_off;
-        if (!(row == ra && c.pre_ok)) {
-            // after an abort the staged bytes are undefined: leave the phase (warp-uniform)
-            if (!__all_sync(kFullMask, f_wait_mbar(c, &sh.full[w][slot], (c.consumed / kFE) & 1))) break;
-            eoff = sh.ent_off[w][slot];
-        }
-        const uint4* ep = reinterpret_cast<const uint4*>(c.ring + eoff);
         float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if constexpr (WF == 0) {
-            switch (t) {
-                case kQKV: gemv_rows<Ph<W, NW, kQKV>::K / 8, 2 * Ph<W, NW, kQKV>::RPE>(ep, act, lane, 2 * nre, v); break;
-                case kO: gemv_rows<Ph<W, NW, kO>::K / 8, Ph<W, NW, kO>::RPE>(ep, act, lane, nre, v); break;
-                case kGU: gemv_rows<Ph<W, NW, kGU>::K / 8, 2 * Ph<W, NW, kGU>::RPE>(ep, act, lane, 2 * nre, v); break;
-                case kDown: gemv_rows<Ph<W, NW, kDown>::K / 8, Ph<W, NW, kDown>::RPE>(ep, act, lane, nre, v); break;
-                default: gemv_rows<Ph<W, NW, kLM>::K / 8, Ph<W, NW, kLM>::RPE>(ep, act, lane, nre, v); break;
+#pragma unroll 1
+        for (int part = 0; part < ks; ++part) {
+            const uint32_t slot = c.consumed % kFE;
+            uint32_t eoff = c.pre_off;
+            if (!(row == ra && part == 0 && c.pre_ok)) {
+                // after an abort the staged bytes are undefined: leave the phase (warp-uniform)
+                if (!__all_sync(kFullMask, f_wait_mbar(c, &sh.full[w][slot], (c.consumed / kFE) & 1))) {
+                    gone = true;
+                    break;
+                }
+                eoff = sh.ent_off[w][slot];
             }
-        } else {
-            constexpr int nq = 2 * Ph<W, NW, kQKV>::RPE, no = Ph<W, NW, kO>::RPE, ng = 2 * Ph<W, NW, kGU>::RPE,
-                          nd = Ph<W, NW, kDown>::RPE, nl = Ph<W, NW, kLM>::RPE;
-            constexpr int kq = Ph<W, NW, kQKV>::K, ko = Ph<W, NW, kO>::K, kg = Ph<W, NW, kGU>::K, kd = Ph<W, NW, kDown>::K,
-                          kl = Ph<W, NW, kLM>::K;
-            switch (t) {
-                case kQKV: gemv_rows_fp8<kq, nq, fast_row_bytes<1>(kq)>(ep, act, lane, 2 * nre, v); break;
-                case kO: gemv_rows_fp8<ko, no, fast_row_bytes<1>(ko)>(ep, act, lane, nre, v); break;
-                case kGU: gemv_rows_fp8<kg, ng, fast_row_bytes<1>(kg)>(ep, act, lane, 2 * nre, v); break;
-                case kDown: gemv_rows_fp8<kd, nd, fast_row_bytes<1>(kd)>(ep, act, lane, nre, v); break;
-                default: gemv_rows_fp8<kl, nl, fast_row_bytes<1>(kl)>(ep, act, lane, nre, v); break;
+            const uint4* ep = reinterpret_cast<const uint4*>(c.ring + eoff);
+            if constexpr (WF == 0) {
+                constexpr int KSD = down_ks<W, 0>();
+                constexpr int KCD = Ph<W, NW, kDown>::K / 8 / KSD;
+                switch (t) {
+                    case kQKV: gemv_rows<Ph<W, NW, kQKV>::K / 8, 2 * Ph<W, NW, kQKV>::RPE>(ep, act, lane, 2 * nre, v); break;
+                    case kO: gemv_rows<Ph<W, NW, kO>::K / 8, Ph<W, NW, kO>::RPE>(ep, act, lane, nre, v); break;
+                    case kGU: gemv_rows<Ph<W, NW, kGU>::K / 8, 2 * Ph<W, NW, kGU>::RPE>(ep, act, lane, 2 * nre, v); break;
+                    case kDown: gemv_rows<KCD, Ph<W, NW, kDown>::RPE>(ep, act + part * KCD, lane, nre, v); break;
+                    default: gemv_rows<Ph<W, NW, kLM>::K / 8, Ph<W, NW, kLM>::RPE>(ep, act, lane, nre, v); break;
+                }
+            } else {
+                constexpr int nq = 2 * Ph<W, NW, kQKV>::RPE, no = Ph<W, NW, kO>::RPE, ng = 2 * Ph<W, NW, kGU>::RPE,
+                              nd = Ph<W, NW, kDown>::RPE, nl = Ph<W, NW, kLM>::RPE;
+                constexpr int kq = Ph<W, NW, kQKV>::K, ko = Ph<W, NW, kO>::K, kg = Ph<W, NW, kGU>::K, kd = Ph<W, NW, kDown>::K,
+                              kl = Ph<W, NW, kLM>::K;
+                switch (t) {
+                    case kQKV: gemv_rows_fp8<kq, nq, fast_row_bytes<1>(kq)>(ep, act, lane, 2 * nre, v); break;
+                    case kO: gemv_rows_fp8<ko, no, fast_row_bytes<1>(ko)>(ep, act, lane, nre, v); break;
+                    case kGU: gemv_rows_fp8<kg, ng, fast_row_bytes<1>(kg)>(ep, act, lane, 2 * nre, v); break;
+                    case kDown: gemv_rows_fp8<kd, nd, fast_row_bytes<1>(kd)>(ep, act, lane, nre, v); break;
+                    default: gemv_rows_fp8<kl, nl, fast_row_bytes<1>(kl)>(ep, act, lane, nre, v); break;
+                }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.empty[w][slot]);      // every lane's loads of this entry have been consumed
+            ++c.consumed;
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh.empty[w][slot]);      // every lane's loads of this entry have been consumed
-        ++c.consumed;
+        if (gone) break;
         // lane 4 j ends up with the total of staged row j (j < 8)
         const float mine = transpose_reduce<8>(v, lane);
         const int vj = lane >> 2;
@@ -583,7 +602,7 @@ __device__ __forceinline__ void stage_norm(FC<NW>& c, const uint32_t* src_words,
     constexpr int PPT = (NP + NT - 1) / NT;
     const int tid = threadIdx.x;
     FShared<NW>& sh = c.sh;
-    static_assert(PPT <= 2, "norm weights are carried in two registers pairs per thread");
+    static_assert(PPT <= 3, "norm weights are carried in three register pairs per thread");
     // the norm weights were fetched during the previous phase (c.nwv): nothing here waits for DRAM
     uint2 wv[PPT];
 #pragma unroll
@@ -966,8 +985,8 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const Fas
     extern __shared__ __align__(128) unsigned char smem_raw[];
     FShared<NW>& sh = *reinterpret_cast<FShared<NW>*>(smem_raw);
     size_t off = (sizeof(FShared<NW>) + 127) & ~size_t(127);
-    uint4* act0 = reinterpret_cast<uint4*>(smem_raw + off);
-    off += ((size_t)ACT * 2 + 127) & ~size_t(127);
+    uint4* act0 = reinterpret_cast<uint4*>(smem_raw + off);      // norm outputs (H); act1: attention output / SwiGLU product
+    off += ((size_t)W::H * 2 + 127) & ~size_t(127);
     uint4* act1 = reinterpret_cast<uint4*>(smem_raw + off);
     off += ((size_t)ACT * 2 + 127) & ~size_t(127);
     float* res0 = reinterpret_cast<float*>(smem_raw + off);
@@ -1038,7 +1057,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const Fas
     __syncthreads();
 
     FC<NW> c{p, sh, {act0, act1}, {res0, res1}, attn, ring_base + (size_t)warp * p.ring_bytes, 0u, 0u, warp, lane, cta, ncta,
-             0u, {make_uint2(0u, 0u), make_uint2(0u, 0u)}, 0u, false, nullptr};
+             0u, {make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u)}, 0u, false, nullptr};
     c.T16 = ((sh.epoch % 511u) + 1u) << 23;
     c.T32 = (sh.epoch + 1u) << 7;
     if (warp == NW) {
@@ -1089,7 +1108,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_fast_kernel(const Fas
         constexpr int NP = W::H / 4;
         const uint2* nw0 = reinterpret_cast<const uint2*>(sh.norm_ptr[0]);
 #pragma unroll
-        for (int u = 0; u < 2; ++u)
+        for (int u = 0; u < 3; ++u)
             if (tid + u * NTC < NP) c.nwv[u] = __ldg(nw0 + tid + u * NTC);
     }
     csync<NW>();

@@ -1996,13 +1996,13 @@ static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo
     if (di.sm_count < kNominalCtas || di.sm_count < W::NC * W::KVH + W::QH) return kFastNotEligible;
     constexpr int ACT = W::H > W::I ? W::H : W::I;
     constexpr size_t kAttnWords = (size_t)attn_words<W, NW>();
-    const size_t fixed = align_up(sizeof(FShared<NW>), 128) + 2 * align_up((size_t)ACT * 2, 128) +
+    const size_t fixed = align_up(sizeof(FShared<NW>), 128) + align_up((size_t)W::H * 2, 128) + align_up((size_t)ACT * 2, 128) +
                          2 * align_up((size_t)W::H * 4, 128) + align_up(kAttnWords * 4, 128);
     if ((size_t)di.smem_optin < fixed + (size_t)NW * 4096) return kFastNotEligible;
     const int rw = (int)(((size_t)di.smem_optin - fixed) / NW / 128 * 128);
     // every entry must fit the ring (an empty ring restarts at its base)
 #define PK_ENT(T) (fast_row_bytes<WF>(Ph<W, NW, T>::K) * Ph<W, NW, T>::RPE * (Ph<W, NW, T>::PAIR ? 2 : 1))
-    const int ent[5] = {PK_ENT(kQKV), PK_ENT(kO), PK_ENT(kGU), PK_ENT(kDown), PK_ENT(kLM)};
+    const int ent[5] = {PK_ENT(kQKV), PK_ENT(kO), PK_ENT(kGU), PK_ENT(kDown) / down_ks<W, WF>(), PK_ENT(kLM)};
 #undef PK_ENT
     for (int t = 0; t < 5; ++t)
         if (ent[t] > rw) return kFastNotEligible;
@@ -2076,13 +2076,17 @@ static int fast_launch(const ModelGeom& g, const StepArgs& a, const DeviceInfo& 
     if (nw == 0 || g.L > kMaxLayers) return kFastNotEligible;
     using W135 = fast::Widths<576, 1536, 9, 3>;
     using W360 = fast::Widths<960, 2560, 15, 5>;
+    using W17 = fast::Widths<2048, 8192, 32, 32>;
     const bool is135 = g.H == 576 && g.I == 1536 && g.QH == 9 && g.KVH == 3;
     const bool is360 = g.H == 960 && g.I == 2560 && g.QH == 15 && g.KVH == 5;
+    const bool is17 = g.H == 2048 && g.I == 8192 && g.QH == 32 && g.KVH == 32;
     if (g.wfmt) {       // MXFP8 weights: seven consumer warps only
         if (is135) return fast_launch_t<W135, 7, 1>(g, a, di, lay);
         if (is360) return fast_launch_t<W360, 7, 1>(g, a, di, lay);
+        if (is17) return fast_launch_t<W17, 7, 1>(g, a, di, lay);
         return kFastNotEligible;
     }
+    if (is17) return fast_launch_t<W17, 7, 0>(g, a, di, lay);
     if (is135) return nw == 8 ? fast_launch_t<W135, 8, 0>(g, a, di, lay) : fast_launch_t<W135, 7, 0>(g, a, di, lay);
     if (is360) return nw == 8 ? fast_launch_t<W360, 8, 0>(g, a, di, lay) : fast_launch_t<W360, 7, 0>(g, a, di, lay);
     return kFastNotEligible;
