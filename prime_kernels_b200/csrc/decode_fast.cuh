@@ -28,7 +28,7 @@ namespace pk {
 namespace fast {
 
 constexpr int kFE = 8;             // ring entries in flight per warp
-constexpr int kPre = 2;            // 16-position runs per warp whose cache offsets are resolved at kernel start
+constexpr int kPre = 4;            // 16-position runs per warp whose cache offsets are resolved at kernel start
 constexpr int kKvPtrs = 64;        // per-layer KV base pointers cached in shared memory
 constexpr int kNominalCtas = 128;  // compile-time lower bound of the grid (the host checks it)
 
@@ -37,8 +37,11 @@ struct Widths {
     static constexpr int H = H_, I = I_, QH = QH_, KVH = KVH_, G = QH_ / KVH_;
     static constexpr int NQKV = (QH_ + 2 * KVH_) * kD;
     static constexpr int AD = QH_ * kD;                           // attention output width (K of the O projection)
-    // max chunks per kv head: a chunk is one run of 16 positions per warp up to 16 x NW x NC positions, longer beyond
-    static constexpr int NC = ((kNominalCtas - QH_) / KVH_) < 16 ? ((kNominalCtas - QH_) / KVH_) : 16;
+    // max chunks per kv head: a chunk is one run of 16 positions per warp up to 16 x NW x NC positions, longer beyond.
+    // Grouped-query widths keep the QH merging CTAs free of attention items; with one query head per kv head the
+    // items may use every CTA (a merging CTA then merges after its own item, which no other item waits for).
+    static constexpr int NCRAW = (QH_ == KVH_) ? kNominalCtas / KVH_ : (kNominalCtas - QH_) / KVH_;
+    static constexpr int NC = NCRAW < 16 ? NCRAW : 16;
     static_assert(QH_ % KVH_ == 0 && H_ % 32 == 0 && I_ % 32 == 0, "unsupported widths");
 };
 

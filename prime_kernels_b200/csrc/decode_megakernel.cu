@@ -1697,7 +1697,8 @@ struct FastLayout {
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 static int fast_nc(const ModelGeom& g) {
-    const int nc = (fast::kNominalCtas - g.QH) / (g.KVH > 0 ? g.KVH : 1);      // Widths::NC
+    const int kvh = g.KVH > 0 ? g.KVH : 1;
+    const int nc = g.QH == g.KVH ? fast::kNominalCtas / kvh : (fast::kNominalCtas - g.QH) / kvh;      // Widths::NC
     return nc < 16 ? nc : 16;
 }
 
@@ -1993,7 +1994,7 @@ template <class W, int NW, int WF>
 static int fast_launch_t(const ModelGeom& g, const StepArgs& a, const DeviceInfo& di, const WsLayout& lay) {
     using namespace fast;
     // the attention items take the first NC * KVH CTAs, the head merges the last QH
-    if (di.sm_count < kNominalCtas || di.sm_count < W::NC * W::KVH + W::QH) return kFastNotEligible;
+    if (di.sm_count < kNominalCtas || di.sm_count < W::NC * W::KVH + (W::G == 1 ? 0 : W::QH)) return kFastNotEligible;
     constexpr int ACT = W::H > W::I ? W::H : W::I;
     constexpr size_t kAttnWords = (size_t)attn_words<W, NW>();
     const size_t fixed = align_up(sizeof(FShared<NW>), 128) + align_up((size_t)W::H * 2, 128) + align_up((size_t)ACT * 2, 128) +
