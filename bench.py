@@ -41,13 +41,16 @@ WORKLOADS = {
     "smollm2-360m-mxfp8-b1": ("smollm2-360m", 1, 4096, 128),
     "smollm2-360m-mxfp8-b4": ("smollm2-360m", 4, 4096, 128),
     "smollm2-360m-mxfp8-b16": ("smollm2-360m", 16, 4096, 32),
+    "smollm2-1.7b-mxfp8-b1": ("smollm2-1.7b", 1, 1024, 128),
 }
 METRIC = "SmolLM2-360M bs1 decode tok/s & % HBM roofline; aggregate tok/s @1/2/4/8 GPUs"
 # DRAM bytes per launch measured with ncu (dram__bytes_read + write) divided by the algorithmic bytes of the
 # captured launch: decode_fast_kernel, SmolLM2-360M batch 1 at context 503-505: 747.7 MB / 744.3 MB;
+# decode_fast_kernel, SmolLM2-1.7B batch 1 at context 203: 3467 MB / 3463 MB;
 # decode_batched_kernel, SmolLM2-360M MXFP8 batch 16 at context 1027: 1051.7 MB / 1046.6 MB.  Traffic grows with
 # the same units as the algorithmic bytes (weights + KV positions), so other contexts are scaled by them.
 NCU_TRAFFIC_RATIO = {("smollm2-360m", 1, False): (1.005, "ncu capture of decode_fast_kernel at context 503-505"),
+                     ("smollm2-1.7b", 1, False): (1.001, "ncu capture of decode_fast_kernel at context 203"),
                      ("smollm2-360m", 16, True): (1.005, "ncu capture of decode_batched_kernel at context 1027")}
 
 

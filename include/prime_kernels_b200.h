@@ -123,7 +123,7 @@ typedef struct PkDecodeArgs {
  * tensor-core kernel's region (same size whatever the batch), behind the CUDA-core kernels' region. */
 size_t pk_decode_workspace_bytes(const PkDecodeModel* model, int max_batch);
 /* Generic form of mk_decode / decode360 (one cooperative launch on args->stream), 1..64 requests.  Small batches run on
- * the CUDA-core kernels (batch 1 of the SmolLM2-135M / 360M widths, bf16 or MXFP8 weights, on a kernel specialised for
+ * the CUDA-core kernels (batch 1 of the SmolLM2-135M / 360M / 1.7B widths, bf16 or MXFP8 weights, on a kernel specialised for
  * them); from the cross-over on (pk_decode_set_tc_min_batch) and always above 8 requests the step runs on the
  * tensor-core kernel: projections as tcgen05 GEMMs with the weight tile as the 128-row operand, batch padded to
  * 16 / 32 / 64, accumulators in tensor memory, every weight streamed once per step. */
@@ -170,7 +170,7 @@ void pk_decode_set_profile(void* buffer, size_t bytes);
 /* Replaces mk_status_string / decode360_status_string for every code above. */
 const char* pk_status_string(int status);
 /* Tuning and test knobs, process-wide; no counterpart in the reference.
- * pk_decode_set_fast_path: batch-1 bf16 steps of the SmolLM2-135M / 360M widths run on a kernel specialised
+ * pk_decode_set_fast_path: batch-1 steps of the SmolLM2-135M / 360M / 1.7B widths run on a kernel specialised
  * for those widths with `warps` (7 or 8) consumer warps per CTA; 0 sends every step to the generic kernel
  * (default: environment variable PK_DECODE_FAST, else 7).  Both kernels keep the same rounding points.
  * pk_decode_set_spin_limit: bound, in polling rounds, of every device-side wait of later launches (the

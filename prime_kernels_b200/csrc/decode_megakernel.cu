@@ -2259,7 +2259,7 @@ static int decode_launch(const ModelGeom& g, const StepArgs& a) {
     if (di.major != 10) return kErrArch;
     if (!di.coop) return kErrCoop;
 
-    // batch 1: the kernel specialised for the SmolLM2-135M / 360M widths (bf16 weights with the tied embedding as
+    // batch 1: the kernel specialised for the SmolLM2-135M / 360M / 1.7B widths (bf16 weights with the tied embedding as
     // lm_head, or MXFP8 weights with the bf16 embedding rows given separately)
     if (a.B == 1 && ((g.wfmt == 0 && (!a.embed_lookup || a.embed_lookup == a.embed)) || (g.wfmt == 1 && a.embed_lookup))) {
         rc = fast_launch(g, a, di, lay);
@@ -2484,7 +2484,7 @@ extern "C" int pk_decode_status(void* workspace, void* stream) {
 extern "C" const char* pk_status_string(int status) { return status_string(status); }
 
 // Tuning / test knobs (process-wide).
-// Batch-1 bf16 steps of SmolLM2-135M / 360M widths run on the specialised kernel with `warps` (7 or 8)
+// Batch-1 steps of the SmolLM2-135M / 360M / 1.7B widths run on the specialised kernel with `warps` (7 or 8)
 // consumer warps per CTA; 0 sends every step to the generic kernel.  Default: environment PK_DECODE_FAST, else 7
 // (7 consumer warps + the producer warp = 256 threads measured 8 % faster than 8 + 1).
 extern "C" int pk_decode_set_fast_path(int warps) {
