@@ -570,6 +570,13 @@ __device__ void norm_phase(BC& c, int which, int layer, const uint16_t* weight, 
         }
         __syncthreads();
     }
+    if (which == 2) {
+        // the q / k / v sums were consumed by the attention items two barriers ago: clear them for the next layer
+        // (the CTAs without a row to normalise do most of it)
+        const int total4 = p.nb * (p.QH + 2 * p.KVH) * (kD / 4);
+        for (int e = c.cta * kThreadsB + c.tid; e < total4; e += c.ncta * kThreadsB)
+            reinterpret_cast<float4*>(p.c_qkv)[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 }
 
 // act = bf16( bf16(silu(bf16 gate)) * bf16 up ) over [nb][I]; clears the gate/up sums.  Four elements per thread
@@ -821,6 +828,18 @@ __device__ void attention_item_b(BC& c, int layer, int b, int kvh, int chunk) {
     for (int off = 16; off >= 1; off >>= 1)
 #pragma unroll
         for (int hh = 0; hh < G; ++hh) l[hh] += __shfl_xor_sync(kFullMask, l[hh], off);
+    if (sh.ncmax == 1) {
+        // every request of the step is a single chunk: the item's result is final (what the merge would compute
+        // from one partial), and the step runs without the merge phase and its barrier
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) {
+            const float inv = 1.f / l[hh];
+            reinterpret_cast<uint32_t*>(p.attn + (size_t)b * p.QH * kD + (kvh * G + hh) * kD)[lane] =
+                pack_bf16x2(acc[hh][0] * inv, acc[hh][1] * inv);
+        }
+        __syncwarp();
+        return;
+    }
     float* part = p.part + ((size_t)(b * p.KVH + kvh) * kNcB + chunk) * G * 66;
 #pragma unroll
     for (int hh = 0; hh < G; ++hh) {
@@ -861,9 +880,6 @@ __device__ void merge_phase(BC& c) {
         const float inv = 1.f / den;
         reinterpret_cast<uint32_t*>(p.attn + (size_t)b * p.QH * kD + hq * kD)[lane] = pack_bf16x2(a0 * inv, a1 * inv);
     }
-    // the q / k / v sums have been consumed by every attention item: clear them for the next layer
-    const long long total = (long long)p.nb * (p.QH + 2 * p.KVH) * kD;
-    for (long long e = (long long)c.cta * kThreadsB + c.tid; e < total; e += (long long)c.ncta * kThreadsB) p.c_qkv[e] = 0.f;
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -900,7 +916,8 @@ __global__ void __launch_bounds__(kThreadsB, 1) decode_batched_kernel(const BPar
             smax = max(smax, min(max(p.seq_lens[b], 1), p.max_seq_len));
         }
         // chunks per (request, kv head): the split that minimises rounds x (runs per item + a prologue's worth),
-        // counted for the longest request; at most kNcB chunks, at least 64 positions each
+        // counted for the longest request; at most kNcB chunks, at least 64 positions each.  With one chunk the
+        // items write the final attention output and the merge phase is skipped.
         const int units = p.nb * p.KVH, nwarps = (int)gridDim.x * (kThreadsB / 32);
         int lc = 64;
         long long best = -1;
@@ -908,7 +925,8 @@ __global__ void __launch_bounds__(kThreadsB, 1) decode_batched_kernel(const BPar
             const int l = max(64, (((smax + nc - 1) / nc) + 15) & ~15);
             const int ncr = (smax + l - 1) / l;
             const long long rounds = ((long long)units * ncr + nwarps - 1) / nwarps;
-            const long long cost = rounds * (l / 16 + 3);
+            // more than one chunk adds the merge phase and its grid barrier (about eight runs' worth of time)
+            const long long cost = rounds * (l / 16 + 3) + (ncr > 1 ? 8 : 0);
             if (best < 0 || cost < best) {
                 best = cost;
                 lc = l;
@@ -974,8 +992,13 @@ __global__ void __launch_bounds__(kThreadsB, 1) decode_batched_kernel(const BPar
             }
         }
         sync_phase();
-        merge_phase(c);
-        sync_phase();
+        if (sh.ncmax > 1) {
+            merge_phase(c);
+            sync_phase();
+        } else {        // single-chunk step: the items wrote the attention output themselves
+            stamp();
+            stamp();
+        }
         gemm_phase<NP, WF>(c, p.gd[kO], wptr(layer, 2), p.attn, p.c_o, 0);
         sync_phase();
         norm_phase(c, 2, layer, reinterpret_cast<const uint16_t*>(wptr(layer, 3)), false);
