@@ -171,9 +171,9 @@ def aggregate_throughput(world, batch, steps, ms_max):
     return world * batch * steps / (ms_max * 1e-3)
 
 
-def cpu_reference(geom, batch, prompt_len, sample_steps, seed=1234):
-    """HuggingFace eager bf16 decode on the host cores: prefill the prompt, then time `sample_steps`
-    decode steps.  Returns (tok/s, threads, description)."""
+def cpu_reference(geom, batch, prompt_len, sample_steps, seed=1234, warmup_steps=3):
+    """HuggingFace eager bf16 decode on the host cores: prefill the prompt, `warmup_steps` untimed decode steps,
+    then time `sample_steps` decode steps.  Returns (tok/s, threads, description)."""
     import torch
 
     from oracle import decode_hf
@@ -183,10 +183,10 @@ def cpu_reference(geom, batch, prompt_len, sample_steps, seed=1234):
     torch.set_num_threads(max(1, len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)))
     weights = harness.make_weights(geom, 0)
     prompt = torch.randint(0, geom.vocab, (batch, prompt_len), generator=torch.Generator().manual_seed(seed))
-    res = decode_hf.run(geom, weights, prompt, sample_steps)
+    res = decode_hf.run(geom, weights, prompt, sample_steps, warmup_steps=warmup_steps)
     toks = batch / res["seconds_per_step"]
     desc = (f"HF LlamaForCausalLM eager bf16 on CPU (the reference's own oracle), {geom.name} B={batch}, "
-            f"{prompt_len}-token prompt prefilled untimed, {sample_steps} timed decode steps")
+            f"{prompt_len}-token prompt prefilled and {warmup_steps} decode steps untimed, {sample_steps} timed decode steps")
     return toks, torch.get_num_threads(), desc
 
 
@@ -256,8 +256,9 @@ def run_reference(args, wl):
     if rank != 0:
         return
     steps = max(1, min(args.steps, 16))          # bounded sample: at most 16 timed decode steps
-    toks, cores, desc = cpu_reference(geom, batch, prompt_len, steps)
-    detail = {"note": "CPU arm: prompt prefilled untimed, then `steps` timed decode steps"}
+    warm = max(3, min(args.warmup, 8))            # bounded like the sample
+    toks, cores, desc = cpu_reference(geom, batch, prompt_len, steps, warmup_steps=warm)
+    detail = {"note": "CPU arm: prompt prefilled and `warmup` decode steps untimed, then `steps` timed decode steps"}
     if batch == 1:
         try:
             same_box = reference_cuda_kernel_same_box(geom, prompt_len)
@@ -266,7 +267,7 @@ def run_reference(args, wl):
         if same_box:
             detail["reference_cuda_kernel_same_box"] = same_box
     line = {"metric": METRIC, "value": toks, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps,
-            "steps_requested": args.steps, "warmup": 0, "ms_per_step": 1e3 * batch / toks, "higher_is_better": True,
+            "steps_requested": args.steps, "warmup": warm, "ms_per_step": 1e3 * batch / toks, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
             "config": config_block(wl, gname, batch, prompt_len, int(os.environ.get("WORLD_SIZE", "1"))),
             "detail": detail,

@@ -67,14 +67,15 @@ def _cache_layers(cache):
 
 @torch.no_grad()
 def run(geometry, weights, prompt_ids: torch.Tensor, steps: int, forced_ids: torch.Tensor | None = None,
-        model=None):
+        model=None, warmup_steps: int = 0):
     """Prefill ``prompt_ids [B, T]`` then ``steps`` decode steps (greedy, or teacher-forced with
     ``forced_ids [steps, B]``).
 
     Returns a dict: ``prefill_k/prefill_v`` (lists ``[L][B, KVH, T, 64]`` bf16, the cache after the prompt
     *without* its last token -- the last prompt token is the first decode input), ``logits`` fp32
     ``[steps, B, V]``, ``hidden`` bf16 ``[steps, B, H]`` (final-normed), ``ids`` int64 ``[steps, B]``,
-    ``seconds_per_step``.
+    ``seconds_per_step``.  ``warmup_steps`` greedy decode steps run first, untimed and unrecorded (timing use only:
+    the recorded steps then continue from the context they leave).
     """
     model = model or build_model(geometry, weights)
     B, T = prompt_ids.shape
@@ -90,6 +91,10 @@ def run(geometry, weights, prompt_ids: torch.Tensor, steps: int, forced_ids: tor
         prefill_k = [torch.zeros(B, geometry.kv_heads, 0, HEAD_DIM, dtype=torch.bfloat16)] * geometry.layers
         prefill_v = prefill_k
     cur = prompt_ids[:, -1:]
+    for _ in range(warmup_steps):
+        res = model(input_ids=cur, past_key_values=cache, use_cache=True, output_hidden_states=True)
+        cache = res.past_key_values
+        cur = res.logits[:, -1, :].float().argmax(dim=-1).view(B, 1)
     t0 = time.perf_counter()
     for s in range(steps):
         res = model(input_ids=cur, past_key_values=cache, use_cache=True, output_hidden_states=True)
